@@ -1,0 +1,266 @@
+"""ctypes binding of ``libgdn2_b200.so`` (declared in ``include/gdn2_b200.h``).
+
+The library is the product: there is no other implementation behind these
+functions. If it is missing, cannot be built, or no CUDA device is present, the
+calls raise -- nothing falls back to the host.
+
+``NativeKernels`` is the one object the host-side API talks to; it turns torch
+tensors into raw pointers, sizes and the current CUDA stream.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import pathlib
+import threading
+
+import torch
+
+_PKG = pathlib.Path(__file__).resolve().parent
+_LIB_PATH = _PKG / "libgdn2_b200.so"
+
+GDN2_F32, GDN2_BF16, GDN2_F16 = 0, 1, 2
+PATH_AUTO, PATH_SIMT, PATH_TCGEN05 = 0, 1, 2
+_PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "tcgen05": PATH_TCGEN05}
+CHUNK = 64
+
+_DTYPES = {torch.float32: GDN2_F32, torch.bfloat16: GDN2_BF16, torch.float16: GDN2_F16}
+
+_vp, _i64, _f32, _int, _sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_float, ctypes.c_int, ctypes.c_size_t
+
+# name -> (restype, argtypes); every symbol include/gdn2_b200.h declares
+SIGNATURES = {
+    "gdn2_abi_version": (_int, []),
+    "gdn2_status_string": (ctypes.c_char_p, [_int]),
+    "gdn2_last_cuda_error": (_int, []),
+    "gdn2_decode": (_int, [_vp] * 8 + [_i64] * 7 + [_f32, _int, _vp]),
+    "gdn2_prefill_workspace_bytes": (_sz, [_i64] * 5 + [_int, _int]),
+    "gdn2_chunk_prep": (_int, [_vp] * 7 + [_sz] + [_i64] * 6 + [_f32, _int, _int, _vp]),
+    "gdn2_prefill_scan": (_int, [_vp, _sz, _vp, _vp, _vp, _vp] + [_i64] * 6 + [_int, _int, _vp]),
+    "gdn2_chunk_output": (_int, [_vp, _sz, _vp, _vp] + [_i64] * 6 + [_int, _int, _vp]),
+    "gdn2_check_device_status": (_int, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
+    "gdn2_selftest_mma": (_int, [_vp, _vp, _vp, _vp]),
+}
+
+_lock = threading.Lock()
+_lib = None
+
+
+class GDN2KernelError(RuntimeError):
+    """A C-ABI call returned a negative status."""
+
+
+def library_path() -> pathlib.Path:
+    return _LIB_PATH
+
+
+def load_library(build_if_missing: bool = True) -> ctypes.CDLL:
+    """Load (building in-tree first if needed) the shared library and bind every symbol."""
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not _LIB_PATH.exists():
+            if not build_if_missing:
+                raise GDN2KernelError(f"{_LIB_PATH} is missing; run `python -m gdn2_tilelang_b200.build`")
+            from . import build as _build
+
+            _build.build()
+        lib = ctypes.CDLL(str(_LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError here means header and library disagree
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+        return lib
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPES[dtype]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dtype}; use float16, bfloat16 or float32") from None
+
+
+def _check(lib, status: int, what: str):
+    if status != 0:
+        msg = lib.gdn2_status_string(status).decode()
+        extra = f" (cudaError {lib.gdn2_last_cuda_error()})" if status == -6 else ""
+        raise GDN2KernelError(f"{what}: {msg}{extra} [status {status}]")
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and t.device.type != "cuda":
+            raise ValueError(
+                "gdn2_tilelang_b200 runs on CUDA devices only (no host implementation is shipped); "
+                f"got a tensor on {t.device}"
+            )
+
+
+def _seq_view(t: torch.Tensor):
+    """(tensor, batch stride in tokens) for a ``[B,S,H,D]`` tensor whose ``[S,H,D]`` block is dense.
+
+    A slice ``x[:, a:b]`` of a contiguous tensor qualifies and is passed through without a copy.
+    """
+    B, S, H, D = t.shape
+    if t.stride(3) == 1 and t.stride(2) == D and t.stride(1) == H * D and (B == 1 or t.stride(0) % (H * D) == 0):
+        if t.data_ptr() % 16 == 0:
+            return t, (t.stride(0) // (H * D) if B > 1 else S)
+    t = t.contiguous()
+    return t, S
+
+
+class NativeKernels:
+    """Launches the CUDA kernels through the C ABI on the current stream of the tensors' device."""
+
+    def __init__(self):
+        self.lib = load_library()
+        self.prefill_path = _PATHS[os.environ.get("GDN2_B200_PREFILL_PATH", "auto")]
+        self.launches = 0   # kernels launched through this object (for the benchmark's accounting)
+
+    # -- helpers ---------------------------------------------------------------------------
+    @staticmethod
+    def _stream(t: torch.Tensor) -> int:
+        return torch.cuda.current_stream(t.device).cuda_stream
+
+    def resolved_path(self, DK: int, DV: int, dtype: torch.dtype, path=None) -> int:
+        p = self.prefill_path if path is None else _PATHS[path] if isinstance(path, str) else path
+        if p == PATH_AUTO:
+            p = PATH_TCGEN05 if (DK == 128 and DV == 128 and dtype == torch.bfloat16) else PATH_SIMT
+        return p
+
+    # -- decode ----------------------------------------------------------------------------
+    def decode(self, q, k, v, g, b, w, state, scale: float, out=None) -> torch.Tensor:
+        """``[B,n,H,D]`` tokens, ``state [B,H,DK,DV]`` fp32 contiguous, updated in place. Returns ``o``.
+
+        ``out`` may be a ``[B,n,H,DV]`` view into a longer preallocated sequence tensor.
+        """
+        _require_cuda(q, k, v, g, b, w, state)
+        B, n, H, DK = q.shape
+        DV = v.shape[-1]
+        code = dtype_code(q.dtype)
+        if state.dtype != torch.float32 or not state.is_contiguous():
+            raise ValueError("the recurrent state must be a contiguous float32 tensor")
+        views = [_seq_view(t) for t in (q, k, v, g, b, w)]
+        strides = {s for _, s in views}
+        if len(strides) != 1:
+            views = [(t.contiguous(), n) for t, _ in views]
+        in_bs = views[0][1]
+        q, k, v, g, b, w = (t for t, _ in views)
+        if out is None:
+            o, o_bs = torch.empty(B, n, H, DV, dtype=v.dtype, device=v.device), n
+        else:
+            o, o_bs = _seq_view(out)
+            if o is not out or out.dtype != v.dtype or tuple(out.shape) != (B, n, H, DV):
+                raise ValueError("`out` must be a [B,n,H,DV] view with dense [n,H,DV] blocks in v's dtype")
+        with torch.cuda.device(q.device):
+            rc = self.lib.gdn2_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
+                                      w.data_ptr(), state.data_ptr(), o.data_ptr(), B, n, H, DK, DV, in_bs, o_bs,
+                                      float(scale), code, self._stream(q))
+        _check(self.lib, rc, "gdn2_decode")
+        self.launches += 1
+        return o
+
+    # -- chunkwise forward -----------------------------------------------------------------
+    def chunk_forward(self, q, k, v, g, b, w, scale: float, initial_state=None, want_chunk_states=False,
+                      path=None, out=None, out_batch_stride=None):
+        """Whole chunks only (``S % 64 == 0``). Returns ``(o, final_state, chunk_states | None)``.
+
+        ``out`` may be a preallocated ``[B, S_total >= S, H, DV]`` tensor whose first ``S`` tokens
+        per batch entry receive the result (``out_batch_stride`` = its token stride).
+        """
+        _require_cuda(q, k, v, g, b, w, initial_state)
+        B, S, H, DK = q.shape
+        DV = v.shape[-1]
+        if S % CHUNK:
+            raise ValueError(f"sequence length {S} must be a multiple of {CHUNK}")
+        code = dtype_code(q.dtype)
+        p = self.resolved_path(DK, DV, q.dtype, path)
+        views = [_seq_view(t) for t in (q, k, v, g, b, w)]
+        if len({s for _, s in views}) != 1:
+            views = [(t.contiguous(), S) for t, _ in views]
+        in_bs = views[0][1]
+        q, k, v, g, b, w = (t for t, _ in views)
+        dev = q.device
+        nbytes = self.lib.gdn2_prefill_workspace_bytes(B, S, H, DK, DV, code, p)
+        if nbytes == 0:
+            raise GDN2KernelError(
+                f"no kernel for DK={DK}, DV={DV}, dtype={q.dtype} (SIMT family: DK<=128, DK%8==0, DV%4==0)")
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        if out is None:
+            out = torch.empty(B, S, H, DV, dtype=v.dtype, device=dev)
+            out_batch_stride = S
+        final_state = torch.empty(B, H, DK, DV, dtype=torch.float32, device=dev)
+        hs = torch.empty(B, S // CHUNK, H, DK, DV, dtype=torch.float32, device=dev) if want_chunk_states else None
+        if initial_state is not None:
+            if initial_state.dtype != torch.float32 or not initial_state.is_contiguous():
+                initial_state = initial_state.to(torch.float32).contiguous()
+        st = self._stream(q)
+        with torch.cuda.device(dev):
+            rc = self.lib.gdn2_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
+                                          w.data_ptr(), ws.data_ptr(), nbytes, B, S, H, DK, DV, in_bs,
+                                          float(scale), code, p, st)
+            _check(self.lib, rc, "gdn2_chunk_prep")
+            rc = self.lib.gdn2_prefill_scan(ws.data_ptr(), nbytes,
+                                            None if initial_state is None else initial_state.data_ptr(),
+                                            out.data_ptr(), final_state.data_ptr(),
+                                            None if hs is None else hs.data_ptr(), B, S, H, DK, DV,
+                                            out_batch_stride, code, p, st)
+            _check(self.lib, rc, "gdn2_prefill_scan")
+        self.launches += 3 if p == PATH_TCGEN05 else 2
+        return out, final_state, hs
+
+    def chunk_output(self, q, k, v, g, b, w, scale: float, chunk_states, path=None):
+        """Chunk-parallel output from stored chunk states (re-runs the chunk-local stage)."""
+        _require_cuda(q, chunk_states)
+        B, S, H, DK = q.shape
+        DV = v.shape[-1]
+        code = dtype_code(q.dtype)
+        p = self.resolved_path(DK, DV, q.dtype, path)
+        q, k, v, g, b, w = (t.contiguous() for t in (q, k, v, g, b, w))
+        nbytes = self.lib.gdn2_prefill_workspace_bytes(B, S, H, DK, DV, code, p)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        out = torch.empty(B, S, H, DV, dtype=v.dtype, device=q.device)
+        st = self._stream(q)
+        with torch.cuda.device(q.device):
+            rc = self.lib.gdn2_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
+                                          w.data_ptr(), ws.data_ptr(), nbytes, B, S, H, DK, DV, S, float(scale),
+                                          code, p, st)
+            _check(self.lib, rc, "gdn2_chunk_prep")
+            rc = self.lib.gdn2_chunk_output(ws.data_ptr(), nbytes, chunk_states.data_ptr(), out.data_ptr(),
+                                            B, S, H, DK, DV, S, code, p, st)
+            _check(self.lib, rc, "gdn2_chunk_output")
+        self.launches += 3 if p == PATH_TCGEN05 else 2
+        return out
+
+    # -- diagnostics -------------------------------------------------------------------------
+    def check_device_status(self, device=None):
+        """Raise if any kernel on ``device`` gave up on a bounded wait since the last check."""
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        detail = ctypes.c_uint32(0)
+        with torch.cuda.device(device):
+            rc = self.lib.gdn2_check_device_status(torch.cuda.current_stream(device).cuda_stream,
+                                                   ctypes.byref(detail))
+        if rc != 0:
+            raise GDN2KernelError(f"device status word = {detail.value:#x}: "
+                                  f"{self.lib.gdn2_status_string(rc).decode()}")
+
+    def selftest_mma(self, a: torch.Tensor, bt: torch.Tensor) -> torch.Tensor:
+        _require_cuda(a, bt)
+        out = torch.zeros(3, 128, 128, dtype=torch.float32, device=a.device)
+        with torch.cuda.device(a.device):
+            rc = self.lib.gdn2_selftest_mma(a.data_ptr(), bt.data_ptr(), out.data_ptr(), self._stream(a))
+        _check(self.lib, rc, "gdn2_selftest_mma")
+        return out
+
+
+_kernels = None
+
+
+def kernels() -> NativeKernels:
+    """The process-wide kernel launcher (created on first use)."""
+    global _kernels
+    if _kernels is None:
+        _kernels = NativeKernels()
+    return _kernels

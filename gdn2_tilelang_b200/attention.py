@@ -1,0 +1,252 @@
+"""``gdn2_attention`` and the ``GatedDeltaNet2`` token mixer, API-compatible with the reference
+(gdn2/attention.py of the reference project: ``resolve_backend`` 44-61, ``gdn2_attention``
+102-164, ``GDN2Cache`` 172-183, ``_ShortConv`` 186-215, ``_GatedRMSNorm`` 218-229,
+``GatedDeltaNet2`` 232-491).
+
+Differences a user of the reference should know about:
+
+* inference only -- the functional op runs under ``no_grad`` and has no backward;
+* the only backend is the CUDA kernel library. ``"auto"`` and ``"tilelang"`` (kept as an alias so
+  existing configs load) resolve to ``"cuda"``; ``"torch"`` and non-CUDA tensors raise, because no
+  host implementation is shipped;
+* ``init_cache`` allocates ``conv_state`` in the layer's parameter dtype (the reference allocates
+  it in float32 and then fails on a bf16 layer); ``recurrent_state`` stays float32;
+* the module's parameter names and shapes are unchanged, so ``state_dict``s are interchangeable.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .config import DEFAULT_KERNEL_CONFIG, GDN2Config, GatedDeltaNet2Config
+from .forward import chunk_gdn2_fwd
+from .inference import gdn2_decode, gdn2_prefill
+
+__all__ = ["gdn2_attention", "GatedDeltaNet2", "GDN2Cache", "resolve_backend"]
+
+_BACKENDS = ("auto", "cuda", "tilelang", "torch")
+
+
+def resolve_backend(backend: str, on_cuda: bool, needs_grad: bool = False) -> str:
+    """Validate ``backend`` and return the concrete one, which can only be ``"cuda"``.
+
+    Raises ``ValueError`` for an unknown name, for the host-only ``"torch"`` backend, when the
+    tensors are not on a CUDA device, and when gradients are requested.
+    """
+    if backend not in _BACKENDS:
+        raise ValueError(f"unknown backend {backend!r}; expected one of {_BACKENDS}")
+    if backend == "torch":
+        raise ValueError("backend 'torch' (the host reference path) is not part of this package; "
+                         "use the reference project's gdn2.reference for a host evaluation")
+    if not on_cuda:
+        raise ValueError(f"backend {backend!r} requires a CUDA device")
+    if needs_grad:
+        raise ValueError("the sm_100a kernels implement the forward / serving path only; "
+                         "call under torch.no_grad() or detach the inputs")
+    return "cuda"
+
+
+def gdn2_attention(q, k, v, g, b, w, scale=None, initial_state=None, output_final_state=False,
+                   config: GDN2Config = DEFAULT_KERNEL_CONFIG, cu_seqlens=None):
+    """Gated DeltaNet-2 attention over a full sequence.
+
+    ``q, k, b, g``: ``[B, S, H, DK]``; ``v, w``: ``[B, S, H, DV]``; ``g`` is the natural-log decay
+    (``<= 0``). Returns ``(o [B, S, H, DV] in the input dtype, final_state float32 | None)``.
+    ``cu_seqlens`` is not implemented and raises, as in the reference.
+    """
+    scale = q.shape[-1] ** -0.5 if scale is None else scale
+    needs_grad = torch.is_grad_enabled() and any(
+        t is not None and t.requires_grad for t in (q, k, v, g, b, w, initial_state))
+    resolve_backend(config.backend, q.device.type == "cuda", needs_grad)
+    if cu_seqlens is not None:
+        raise NotImplementedError("packed variable-length batches are not implemented yet; pad the batch instead")
+    return chunk_gdn2_fwd(q, k, v, g, b, w, scale, initial_state, output_final_state, config)
+
+
+@dataclass
+class GDN2Cache:
+    """Per-layer decoding cache: ``recurrent_state [B, H_v, DK, DV]`` float32 and ``conv_state
+    [B, 2*HK*DK + H*DV, conv_size-1]`` (the last pre-convolution q | k | v projections) or ``None``."""
+
+    recurrent_state: torch.Tensor
+    conv_state: torch.Tensor | None = None
+
+
+class _ShortConv(nn.Module):
+    """Causal depthwise conv1d + SiLU over ``[B, S, C]`` with a ``kernel_size-1`` column cache."""
+
+    def __init__(self, channels: int, kernel_size: int = 4, activation: bool = True):
+        super().__init__()
+        self.channels, self.kernel_size, self.activation = channels, kernel_size, activation
+        self.conv = nn.Conv1d(channels, channels, kernel_size, groups=channels, padding=kernel_size - 1)
+
+    def forward(self, x):
+        y = self.conv(x.transpose(1, 2))[..., : x.shape[1]].transpose(1, 2)
+        return F.silu(y) if self.activation else y
+
+    def decode(self, x, state):
+        """``x [B, n, C]`` continuing from ``state [B, C, kernel_size-1]``; returns ``(y, new_state)``."""
+        buf = torch.cat([state.to(x.dtype), x.transpose(1, 2)], dim=-1)
+        y = F.conv1d(buf, self.conv.weight, self.conv.bias, groups=self.channels).transpose(1, 2)
+        return (F.silu(y) if self.activation else y), buf[..., -(self.kernel_size - 1):]
+
+    def step(self, x, state):
+        y, state = self.decode(x.unsqueeze(1), state)
+        return y[:, 0], state
+
+
+class _GatedRMSNorm(nn.Module):
+    """Per-head RMSNorm multiplied by a SiLU gate, computed in float32."""
+
+    def __init__(self, dim: int, eps: float = 1e-5):
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(dim))
+
+    def forward(self, x, gate):
+        x = x.float()
+        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps)
+        return (x * self.weight.float() * F.silu(gate.float())).to(gate.dtype)
+
+
+class GatedDeltaNet2(nn.Module):
+    """Gated DeltaNet-2 token mixer: projections, short convolution, L2-normalised q/k, the decay /
+    erase / write gates, the recurrent attention kernels, gated RMSNorm and the output projection."""
+
+    def __init__(self, config: GatedDeltaNet2Config):
+        super().__init__()
+        self.cfg = config
+        H = config.num_heads
+        HK = config.num_kv_heads or H
+        if H % HK != 0:
+            raise ValueError(f"num_heads {H} must be a multiple of num_kv_heads {HK}")
+        DK = config.head_dim_k
+        DV = config.head_dim_v or config.head_dim_k
+        self.num_heads, self.num_kv_heads = H, HK
+        self.head_dim_k, self.head_dim_v = DK, DV
+        self.head_repeat = H // HK
+        d_qk, d_v = HK * DK, H * DV
+        hid = config.hidden_size
+        self.q_proj = nn.Linear(hid, d_qk, bias=False)
+        self.k_proj = nn.Linear(hid, d_qk, bias=False)
+        self.v_proj = nn.Linear(hid, d_v, bias=False)
+        self.b_proj = nn.Linear(hid, d_qk, bias=False)
+        self.w_proj = nn.Linear(hid, d_v, bias=False)
+        self.f_proj = nn.Linear(hid, d_qk, bias=False)
+        self.o_gate_proj = nn.Linear(hid, d_v, bias=False)
+        self.o_proj = nn.Linear(d_v, hid, bias=False)
+        if config.conv_size > 0:
+            self.q_conv = _ShortConv(d_qk, config.conv_size)
+            self.k_conv = _ShortConv(d_qk, config.conv_size)
+            self.v_conv = _ShortConv(d_v, config.conv_size)
+        else:
+            self.q_conv = self.k_conv = self.v_conv = None
+        lo, hi = config.a_init_range
+        self.A_log = nn.Parameter(torch.empty(HK).uniform_(lo, hi).log_())
+        dt_lo, dt_hi = config.dt_init_range
+        dt = torch.empty(HK, DK).uniform_(dt_lo, dt_hi)
+        self.dt_bias = nn.Parameter(dt + torch.log(-torch.expm1(-dt)))   # inverse softplus of dt
+        self.o_norm = _GatedRMSNorm(DV, config.norm_eps)
+        self.scale = DK**-0.5
+        self.erase_scale = config.erase_gate_scale
+
+    # ------------------------------------------------------------------ pieces
+    def _gates(self, x, lead):
+        f = self.f_proj(x).view(*lead, self.num_kv_heads, self.head_dim_k)
+        return -self.A_log.float().exp().unsqueeze(-1) * F.softplus(f.float() + self.dt_bias.float())
+
+    def _expand(self, x):
+        return x if self.head_repeat == 1 else x.repeat_interleave(self.head_repeat, dim=-2)
+
+    def _front(self, x, conv_state, cached: bool):
+        """Everything before the attention kernels. Returns ``(q, k, v, g, b, w, new_conv_state)``."""
+        B, S, _ = x.shape
+        H, HK, DK, DV = self.num_heads, self.num_kv_heads, self.head_dim_k, self.head_dim_v
+        q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
+        new_conv = None
+        if self.q_conv is not None:
+            d = HK * DK
+            if cached:
+                q, cq = self.q_conv.decode(q, conv_state[:, :d])
+                k, ck = self.k_conv.decode(k, conv_state[:, d:2 * d])
+                v, cv = self.v_conv.decode(v, conv_state[:, 2 * d:])
+                new_conv = torch.cat([cq, ck, cv], dim=1)
+            else:
+                width = self.cfg.conv_size - 1
+                tail = torch.cat([q, k, v], dim=-1).transpose(1, 2)
+                new_conv = F.pad(tail, (max(0, width - S), 0))[..., -width:]
+                q, k, v = self.q_conv(q), self.k_conv(k), self.v_conv(v)
+        q = F.normalize(q.view(B, S, HK, DK), p=2, dim=-1)
+        k = F.normalize(k.view(B, S, HK, DK), p=2, dim=-1)
+        v = v.view(B, S, H, DV)
+        g = self._gates(x, (B, S))
+        b = torch.sigmoid(self.b_proj(x).view(B, S, HK, DK)) * self.erase_scale
+        w = torch.sigmoid(self.w_proj(x).view(B, S, H, DV))
+        q, k, b, g = (self._expand(t) for t in (q, k, b, g))
+        return q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), b.contiguous(), w.contiguous(), new_conv
+
+    def _back(self, x, o):
+        B, S, _ = x.shape
+        gate = self.o_gate_proj(x).view(B, S, self.num_heads, self.head_dim_v)
+        o = self.o_norm(o, gate).reshape(B, S, self.num_heads * self.head_dim_v)
+        return self._reduce(self.o_proj(o))
+
+    def _reduce(self, y):
+        """Hook for the head-parallel variant (sum over ranks); identity on one device."""
+        return y
+
+    # ------------------------------------------------------------------ public API
+    @torch.no_grad()
+    def forward(self, hidden_states, cache: GDN2Cache | None = None, use_cache: bool = False, cu_seqlens=None):
+        """Full-sequence forward. Returns ``(output [B, S, hidden], GDN2Cache | None)``."""
+        q, k, v, g, b, w, conv = self._front(hidden_states, None, cached=False)
+        o, final_state = gdn2_attention(
+            q, k, v, g, b, w, scale=self.scale,
+            initial_state=cache.recurrent_state if cache is not None else None,
+            output_final_state=use_cache, config=self.cfg.kernel, cu_seqlens=cu_seqlens)
+        out = self._back(hidden_states, o)
+        return out, (GDN2Cache(final_state, conv if use_cache else None) if use_cache else None)
+
+    @torch.no_grad()
+    def prefill(self, hidden_states, cache: GDN2Cache | None = None):
+        """Prefill a prompt (or a segment of one) and return ``(output, cache)`` to decode from."""
+        if cache is None:
+            cache = self.init_cache(hidden_states.shape[0], device=hidden_states.device)
+        q, k, v, g, b, w, conv = self._front(hidden_states, cache.conv_state, cached=self.q_conv is not None)
+        if conv is not None:
+            cache.conv_state = conv
+        o, state = gdn2_prefill(q, k, v, g, b, w, cache.recurrent_state, scale=self.scale, config=self.cfg.kernel)
+        cache.recurrent_state = state
+        return self._back(hidden_states, o), cache
+
+    @torch.no_grad()
+    def decode(self, hidden_states, cache: GDN2Cache):
+        """Decode ``n`` tokens ``[B, n, hidden]``; ``cache.recurrent_state`` is updated in place."""
+        q, k, v, g, b, w, conv = self._front(hidden_states, cache.conv_state, cached=self.q_conv is not None)
+        if conv is not None:
+            cache.conv_state = conv
+        o = gdn2_decode(q, k, v, g, b, w, cache.recurrent_state, scale=self.scale)
+        return self._back(hidden_states, o), cache
+
+    @torch.no_grad()
+    def step(self, hidden_states, cache: GDN2Cache):
+        """Decode one token ``[B, hidden]``."""
+        out, cache = self.decode(hidden_states.unsqueeze(1), cache)
+        return out[:, 0], cache
+
+    def init_cache(self, batch_size: int, device=None, dtype=torch.float32) -> GDN2Cache:
+        """Empty cache: float32 recurrent state, conv tail in the layer's parameter dtype."""
+        if dtype != torch.float32:
+            raise ValueError("the recurrent state is kept in float32")
+        device = self.o_proj.weight.device if device is None else device
+        state = torch.zeros(batch_size, self.num_heads, self.head_dim_k, self.head_dim_v, device=device, dtype=dtype)
+        conv_state = None
+        if self.q_conv is not None:
+            channels = 2 * self.num_kv_heads * self.head_dim_k + self.num_heads * self.head_dim_v
+            conv_state = torch.zeros(batch_size, channels, self.cfg.conv_size - 1, device=device,
+                                     dtype=self.o_proj.weight.dtype)
+        return GDN2Cache(state, conv_state)

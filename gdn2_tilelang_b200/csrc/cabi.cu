@@ -1,0 +1,180 @@
+// extern "C" entry points declared in include/gdn2_b200.h: argument validation, kernel-family
+// dispatch and error reporting. Nothing here allocates device memory.
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace gdn2 {
+
+namespace {
+thread_local int g_last_cuda_error = 0;
+__device__ uint32_t g_device_status;   // one word per device image of this library
+}  // namespace
+
+int record_cuda_error(cudaError_t e) {
+  g_last_cuda_error = static_cast<int>(e);
+  return GDN2_ERR_CUDA;
+}
+
+uint32_t* device_status_word() {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+  return static_cast<uint32_t*>(p);
+}
+
+namespace {
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool valid_dtype(int dtype) { return dtype == GDN2_F32 || dtype == GDN2_BF16 || dtype == GDN2_F16; }
+
+// Resolve AUTO and check that the chosen family supports the shape. Returns a gdn2_status.
+int resolve_path(int64_t DK, int64_t DV, int dtype, int path, int* resolved) {
+  const bool tc_ok = (DK == 128 && DV == 128 && dtype == GDN2_BF16);
+  const bool simt_ok = (DK >= 8 && DK <= 128 && DK % 8 == 0 && DV >= 4 && DV % 4 == 0);
+  if (path == GDN2_PATH_AUTO) path = tc_ok ? GDN2_PATH_TCGEN05 : GDN2_PATH_SIMT;
+  if (path == GDN2_PATH_TCGEN05 && !tc_ok) return GDN2_ERR_UNSUPPORTED;
+  if (path == GDN2_PATH_SIMT && !simt_ok) return GDN2_ERR_UNSUPPORTED;
+  if (path != GDN2_PATH_SIMT && path != GDN2_PATH_TCGEN05) return GDN2_ERR_UNSUPPORTED;
+  *resolved = path;
+  return GDN2_OK;
+}
+
+int check_prefill_shape(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype) {
+  if (!valid_dtype(dtype)) return GDN2_ERR_BAD_DTYPE;
+  if (B <= 0 || S <= 0 || H <= 0 || DK <= 0 || DV <= 0 || S % kChunk != 0) return GDN2_ERR_BAD_SHAPE;
+  if (B * H > 2147483647LL / 4 || S > (1LL << 30)) return GDN2_ERR_BAD_SHAPE;
+  return GDN2_OK;
+}
+
+}  // namespace
+}  // namespace gdn2
+
+using namespace gdn2;
+
+extern "C" {
+
+int gdn2_abi_version(void) { return GDN2_B200_ABI_VERSION; }
+
+const char* gdn2_status_string(int status) {
+  switch (status) {
+    case GDN2_OK: return "ok";
+    case GDN2_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case GDN2_ERR_BAD_SHAPE: return "bad shape (sizes must be positive, S a multiple of 64)";
+    case GDN2_ERR_BAD_DTYPE: return "unknown element type";
+    case GDN2_ERR_MISALIGNED: return "a pointer is not 16-byte aligned";
+    case GDN2_ERR_WORKSPACE: return "workspace too small";
+    case GDN2_ERR_CUDA: return "a CUDA call failed (see gdn2_last_cuda_error)";
+    case GDN2_ERR_DEVICE_WAIT: return "a kernel gave up on a bounded wait";
+    case GDN2_ERR_UNSUPPORTED: return "no kernel is built for this shape / dtype / path";
+    default: return "unknown status";
+  }
+}
+
+int gdn2_last_cuda_error(void) { return g_last_cuda_error; }
+
+int gdn2_decode(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                float* state, void* o, int64_t B, int64_t n, int64_t H, int64_t DK, int64_t DV,
+                int64_t in_batch_stride, int64_t o_batch_stride, float scale, int dtype, void* stream) {
+  if (!q || !k || !v || !g || !b || !w || !state || !o) return GDN2_ERR_NULL_POINTER;
+  if (!valid_dtype(dtype)) return GDN2_ERR_BAD_DTYPE;
+  if (B <= 0 || n <= 0 || H <= 0 || DK <= 0 || DV <= 0 || DK > 256) return GDN2_ERR_BAD_SHAPE;
+  if (B * H > 2147483647LL / 4 || n > (1 << 24)) return GDN2_ERR_BAD_SHAPE;
+  if (in_batch_stride < n || o_batch_stride < n) return GDN2_ERR_BAD_SHAPE;
+  if (DK == 128 && DV == 128 && !aligned16(state)) return GDN2_ERR_MISALIGNED;
+  return launch_decode(q, k, v, g, b, w, state, o, (int)B, (int)n, (int)H, (int)DK, (int)DV, in_batch_stride,
+                       o_batch_stride, scale, dtype, static_cast<cudaStream_t>(stream));
+}
+
+size_t gdn2_prefill_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path) {
+  if (check_prefill_shape(B, S, H, DK, DV, dtype) != GDN2_OK) return 0;
+  int p;
+  if (resolve_path(DK, DV, dtype, path, &p) != GDN2_OK) return 0;
+  return make_ws_layout(B, S, H, (int)DK, (int)DV, p == GDN2_PATH_TCGEN05 ? 2 : 4).total;
+}
+
+int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                    void* workspace, size_t workspace_bytes, int64_t B, int64_t S, int64_t H, int64_t DK,
+                    int64_t DV, int64_t in_batch_stride, float scale, int dtype, int path, void* stream) {
+  if (!q || !k || !v || !g || !b || !w || !workspace) return GDN2_ERR_NULL_POINTER;
+  int rc = check_prefill_shape(B, S, H, DK, DV, dtype);
+  if (rc != GDN2_OK) return rc;
+  if (in_batch_stride < S) return GDN2_ERR_BAD_SHAPE;
+  int p;
+  rc = resolve_path(DK, DV, dtype, path, &p);
+  if (rc != GDN2_OK) return rc;
+  if (!aligned16(workspace) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(g) ||
+      !aligned16(b) || !aligned16(w))
+    return GDN2_ERR_MISALIGNED;
+  const WsLayout L = make_ws_layout(B, S, H, (int)DK, (int)DV, p == GDN2_PATH_TCGEN05 ? 2 : 4);
+  if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
+  const WsPtrs P = ws_pointers(workspace, L);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p == GDN2_PATH_TCGEN05) {
+    rc = launch_prep_tc(q, k, v, g, b, w, L, P, (int)B, (int)S, (int)H, in_batch_stride, scale, st);
+    if (rc != GDN2_OK) return rc;
+    // chunks whose decay is too fast for the factorised diagonal blocks are redone exactly
+    return launch_prep_simt(q, k, v, g, b, w, L, P, (int)B, (int)S, (int)H, in_batch_stride, scale, dtype, true, st);
+  }
+  return launch_prep_simt(q, k, v, g, b, w, L, P, (int)B, (int)S, (int)H, in_batch_stride, scale, dtype, false, st);
+}
+
+int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
+                      float* final_state, float* chunk_states, int64_t B, int64_t S, int64_t H, int64_t DK,
+                      int64_t DV, int64_t o_batch_stride, int dtype, int path, void* stream) {
+  if (!workspace || !o) return GDN2_ERR_NULL_POINTER;
+  int rc = check_prefill_shape(B, S, H, DK, DV, dtype);
+  if (rc != GDN2_OK) return rc;
+  if (o_batch_stride < S) return GDN2_ERR_BAD_SHAPE;
+  int p;
+  rc = resolve_path(DK, DV, dtype, path, &p);
+  if (rc != GDN2_OK) return rc;
+  if (!aligned16(workspace)) return GDN2_ERR_MISALIGNED;
+  const WsLayout L = make_ws_layout(B, S, H, (int)DK, (int)DV, p == GDN2_PATH_TCGEN05 ? 2 : 4);
+  if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
+  const WsPtrs P = ws_pointers(const_cast<void*>(workspace), L);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (p == GDN2_PATH_TCGEN05)
+    return launch_scan_tc(L, P, initial_state, o, final_state, chunk_states, (int)B, (int)S, (int)H,
+                          o_batch_stride, st);
+  return launch_scan_simt(L, P, initial_state, o, final_state, chunk_states, (int)B, (int)S, (int)H,
+                          o_batch_stride, dtype, st);
+}
+
+int gdn2_chunk_output(const void* workspace, size_t workspace_bytes, const float* chunk_states, void* o,
+                      int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int64_t o_batch_stride, int dtype,
+                      int path, void* stream) {
+  if (!workspace || !o || !chunk_states) return GDN2_ERR_NULL_POINTER;
+  int rc = check_prefill_shape(B, S, H, DK, DV, dtype);
+  if (rc != GDN2_OK) return rc;
+  if (o_batch_stride < S) return GDN2_ERR_BAD_SHAPE;
+  int p;
+  rc = resolve_path(DK, DV, dtype, path, &p);
+  if (rc != GDN2_OK) return rc;
+  if (!aligned16(workspace)) return GDN2_ERR_MISALIGNED;
+  const WsLayout L = make_ws_layout(B, S, H, (int)DK, (int)DV, p == GDN2_PATH_TCGEN05 ? 2 : 4);
+  if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
+  const WsPtrs P = ws_pointers(const_cast<void*>(workspace), L);
+  return launch_output_simt(L, P, chunk_states, o, (int)B, (int)S, (int)H, o_batch_stride, dtype,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int gdn2_check_device_status(void* stream, uint32_t* detail) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint32_t* dw = device_status_word();
+  if (!dw) return record_cuda_error(cudaGetLastError());
+  uint32_t host = 0;
+  GDN2_CUDA_TRY(cudaMemcpyAsync(&host, dw, sizeof(host), cudaMemcpyDeviceToHost, st));
+  GDN2_CUDA_TRY(cudaStreamSynchronize(st));
+  if (host != 0) GDN2_CUDA_TRY(cudaMemsetAsync(dw, 0, sizeof(host), st));
+  if (detail) *detail = host;
+  return host == 0 ? GDN2_OK : GDN2_ERR_DEVICE_WAIT;
+}
+
+int gdn2_selftest_mma(const float* a, const float* bt, float* out, void* stream) {
+  if (!a || !bt || !out) return GDN2_ERR_NULL_POINTER;
+  if (!aligned16(a) || !aligned16(bt) || !aligned16(out)) return GDN2_ERR_MISALIGNED;
+  return launch_selftest_mma(a, bt, out, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,124 @@
+// Shared definitions for the GDN-2 sm_100a kernels: element conversion, the workspace layout
+// that the chunk-local stage writes and the scan reads, and launch-error plumbing.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/gdn2_b200.h"
+
+namespace gdn2 {
+
+constexpr int kChunk = 64;                       // tokens per chunk (BS)
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ---------------------------------------------------------------- element conversion
+
+template <typename T> __device__ __forceinline__ float to_f32(T x);
+template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
+
+// ---------------------------------------------------------------- workspace layout
+//
+// One record set per chunk-head, index ch = (b*H + h)*NC + n. All matrices are stored as
+// "K-chunked" operand images: a matrix with R rows and a reduction axis of K elements is an
+// array [K/E][R][E] where E elements fill 16 bytes (E = 8 for bf16, 4 for fp32). This is the
+// no-swizzle, K-major shared-memory layout tcgen05.mma reads (8 rows x 16 bytes core matrices,
+// 128 bytes between 8-row groups, R*16 bytes between adjacent K chunks), so the scan can bring a
+// record on chip with one bulk copy and hand it to the tensor core unchanged.
+//
+//   WQ   rows 0..63 = W (per token), rows 64..127 = Qg = scale*q*gamma (per token); K = DK; type TW
+//   AQK  rows = query token r, K = key token s; lower triangular incl. diagonal;      type TW
+//   KGT  rows = key channel, K = token: k * gamma_C / gamma_t;                         fp32
+//   UT   rows = value channel, K = token: U;                                           fp32
+//   GL   gamma at the chunk's last token, [DK];                                        fp32
+//
+// TW is bf16 on the tcgen05 path and fp32 on the SIMT path.
+
+struct WsLayout {
+  int64_t nch;        // number of chunk-heads
+  int DK, DV;
+  int esz;            // bytes per TW element (2 or 4)
+  size_t wq_bytes, aqk_bytes, kgt_bytes, ut_bytes, gl_bytes;   // per chunk-head
+  size_t off_wq, off_aqk, off_kgt, off_ut, off_gl, off_flags, total;
+};
+
+__host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+__host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK, int DV, int esz) {
+  WsLayout L;
+  L.nch = B * H * (S / kChunk);
+  L.DK = DK; L.DV = DV; L.esz = esz;
+  L.wq_bytes = (size_t)2 * kChunk * DK * esz;
+  L.aqk_bytes = (size_t)kChunk * kChunk * esz;
+  L.kgt_bytes = (size_t)DK * kChunk * 4;
+  L.ut_bytes = (size_t)DV * kChunk * 4;
+  L.gl_bytes = (size_t)DK * 4;
+  size_t off = 0;
+  L.off_wq = off;   off = align_up(off + L.wq_bytes * L.nch, 1024);
+  L.off_aqk = off;  off = align_up(off + L.aqk_bytes * L.nch, 1024);
+  L.off_kgt = off;  off = align_up(off + L.kgt_bytes * L.nch, 1024);
+  L.off_ut = off;   off = align_up(off + L.ut_bytes * L.nch, 1024);
+  L.off_gl = off;   off = align_up(off + L.gl_bytes * L.nch, 1024);
+  L.off_flags = off; off = align_up(off + sizeof(int) * L.nch, 1024);
+  L.total = off;
+  return L;
+}
+
+// element offset of (row, kk) inside a K-chunked image with R rows and E elements per 16 bytes
+template <int E> __host__ __device__ __forceinline__ int kc_index(int row, int kk, int R) {
+  return ((kk / E) * R + row) * E + (kk % E);
+}
+
+struct WsPtrs {
+  char* wq; char* aqk; float* kgt; float* ut; float* gl; int* flags;
+};
+
+__host__ inline WsPtrs ws_pointers(void* base, const WsLayout& L) {
+  char* p = static_cast<char*>(base);
+  return WsPtrs{p + L.off_wq, p + L.off_aqk, reinterpret_cast<float*>(p + L.off_kgt),
+                reinterpret_cast<float*>(p + L.off_ut), reinterpret_cast<float*>(p + L.off_gl),
+                reinterpret_cast<int*>(p + L.off_flags)};
+}
+
+// ---------------------------------------------------------------- host-side error plumbing
+
+int record_cuda_error(cudaError_t e);   // stores e for gdn2_last_cuda_error(), returns GDN2_ERR_CUDA
+
+#define GDN2_CUDA_TRY(expr)                                     \
+  do {                                                          \
+    cudaError_t e__ = (expr);                                   \
+    if (e__ != cudaSuccess) return gdn2::record_cuda_error(e__); \
+  } while (0)
+
+// Device status word: kernels OR a code into it when a bounded wait runs out.
+uint32_t* device_status_word();   // device pointer for the current device (lazily initialised)
+
+// ---------------------------------------------------------------- launchers (one per .cu file)
+
+int launch_decode(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                  float* state, void* o, int B, int n, int H, int DK, int DV, int64_t in_bs, int64_t o_bs,
+                  float scale, int dtype, cudaStream_t st);
+int launch_prep_simt(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                     const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
+                     int dtype, bool only_flagged, cudaStream_t st);
+int launch_scan_simt(const WsLayout& L, const WsPtrs& P, const float* s0, void* o, float* sT, float* hs,
+                     int B, int S, int H, int64_t o_bs, int dtype, cudaStream_t st);
+int launch_output_simt(const WsLayout& L, const WsPtrs& P, const float* hs, void* o, int B, int S, int H,
+                       int64_t o_bs, int dtype, cudaStream_t st);
+int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                   const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
+                   cudaStream_t st);
+int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o, float* sT, float* hs,
+                   int B, int S, int H, int64_t o_bs, cudaStream_t st);
+int launch_selftest_mma(const float* a, const float* bt, float* out, cudaStream_t st);
+
+}  // namespace gdn2

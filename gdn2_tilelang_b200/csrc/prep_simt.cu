@@ -1,0 +1,182 @@
+// Chunk-local stage of the chunkwise forward, SIMT (CUDA-core) family: any DK <= 128 (multiple
+// of 8), any DV (multiple of 4), fp32 arithmetic throughout. One 256-thread block per
+// (chunk, batch*head).
+//
+// Every entry of the two intra-chunk matrices is evaluated with the exact pairwise decay
+//     sum_c x_r[c] * k_s[c] * exp2(G_r[c] - G_s[c]),   r >= s   (exponent <= 0 by construction)
+// which is the form the reference uses only for its diagonal sub-blocks (intra_diag_kernel,
+// gdn2/forward.py:220-235 of the reference project); using it everywhere makes this family safe
+// for arbitrarily fast decay without any reference-row factorisation. The inverse (I + Tm)^-1 is
+// built column by column with forward substitution (solve_kernel, gdn2/forward.py:424-434), then
+// W = Ai E, U = Ai (w*v), KG and Qg follow wy_kernel (gdn2/forward.py:512-533) and the query
+// scaling of prefill_scan_kernel (gdn2/inference.py:461).
+//
+// This family also serves as the exact path for chunks the tensor-core family flags as decaying
+// too fast for its factorised diagonal blocks (`only_flagged`).
+#include "common.cuh"
+
+namespace gdn2 {
+
+namespace {
+
+template <typename TW> struct Epc;                     // elements per 16-byte chunk
+template <> struct Epc<float> { static constexpr int v = 4; };
+template <> struct Epc<__nv_bfloat16> { static constexpr int v = 8; };
+
+template <typename TIn, typename TW>
+__global__ void __launch_bounds__(256)
+prep_simt_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn* __restrict__ v,
+                 const float* __restrict__ g, const TIn* __restrict__ b, const TIn* __restrict__ w,
+                 WsLayout L, WsPtrs P, int S, int H, int64_t in_bs, float scale, int only_flagged) {
+  constexpr int BS = kChunk;
+  constexpr int E = Epc<TW>::v;
+  const int DK = L.DK, DV = L.DV;
+  const int NC = S / BS;
+  const int n = blockIdx.x, bh = blockIdx.y;
+  const int ib = bh / H, ih = bh % H;
+  const int64_t ch = (int64_t)bh * NC + n;
+  if (only_flagged && P.flags[ch] == 0) return;
+  const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+
+  extern __shared__ float sm[];
+  float* Gs = sm;                    // [BS][DK] cumulative log2 decay
+  float* ks = Gs + BS * DK;          // [BS][DK] k
+  float* es = ks + BS * DK;          // [BS][DK] b*k, later E = b*k*gamma
+  float* qs = es + BS * DK;          // [BS][DK] q, later the w*v tiles
+  float* Tm = qs + BS * DK;          // [BS][BS] strictly lower
+  float* Aq = Tm + BS * BS;          // [BS][BS] lower incl. diagonal (scaled)
+  float* Ai = Aq + BS * BS;          // [BS][BS] (I + Tm)^-1
+
+  const size_t tok0 = ((size_t)ib * in_bs + (size_t)n * BS) * H + ih;   // token index of row 0 (stride H per row)
+  for (int idx = tid; idx < BS * DK; idx += 256) {
+    const int t = idx / DK, c = idx % DK;
+    const size_t gi = (tok0 + (size_t)t * H) * DK + c;
+    const float kk = to_f32(k[gi]);
+    ks[idx] = kk;
+    qs[idx] = to_f32(q[gi]);
+    es[idx] = to_f32(b[gi]) * kk;
+    Gs[idx] = g[gi];
+  }
+  for (int idx = tid; idx < BS * BS; idx += 256) { Tm[idx] = 0.f; Aq[idx] = 0.f; Ai[idx] = 0.f; }
+  __syncthreads();
+  if (tid < DK) {
+    float run = 0.f;
+    for (int t = 0; t < BS; ++t) { run += Gs[t * DK + tid]; Gs[t * DK + tid] = run * kLog2e; }
+  }
+  __syncthreads();
+
+  // pairwise matrices: warp `wid` takes rows {wid+8j, 63-(wid+8j)}, 65 pairs per row pair
+  for (int j = 0; j < 4; ++j) {
+    for (int half = 0; half < 2; ++half) {
+      const int r = half ? (BS - 1 - (wid + 8 * j)) : (wid + 8 * j);
+      for (int s = 0; s <= r; ++s) {
+        float aq = 0.f, ae = 0.f;
+        for (int c = lane; c < DK; c += 32) {
+          const float kd = ks[s * DK + c] * exp2f(Gs[r * DK + c] - Gs[s * DK + c]);
+          aq = fmaf(qs[r * DK + c], kd, aq);
+          ae = fmaf(es[r * DK + c], kd, ae);
+        }
+#pragma unroll
+        for (int off = 16; off; off >>= 1) {
+          aq += __shfl_xor_sync(0xffffffffu, aq, off);
+          ae += __shfl_xor_sync(0xffffffffu, ae, off);
+        }
+        if (lane == 0) {
+          Aq[r * BS + s] = aq * scale;
+          if (s < r) Tm[r * BS + s] = ae;
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  // inverse by columns: thread j solves (I + Tm) x = e_j
+  if (tid < BS) {
+    const int j = tid;
+    Ai[j * BS + j] = 1.f;
+    for (int r = j + 1; r < BS; ++r) {
+      float acc = 0.f;
+      for (int s = j; s < r; ++s) acc = fmaf(Tm[r * BS + s], Ai[s * BS + j], acc);
+      Ai[r * BS + j] = -acc;
+    }
+  }
+  // outputs that need only G, q, k: Aqk image, Qg rows, KG^T image, gamma_last; E in place
+  TW* wq = reinterpret_cast<TW*>(P.wq + (size_t)ch * L.wq_bytes);
+  TW* aqk = reinterpret_cast<TW*>(P.aqk + (size_t)ch * L.aqk_bytes);
+  float* kgt = P.kgt + (size_t)ch * (L.kgt_bytes / 4);
+  float* ut = P.ut + (size_t)ch * (L.ut_bytes / 4);
+  float* gl = P.gl + (size_t)ch * DK;
+  for (int idx = tid; idx < BS * BS; idx += 256) {
+    const int r = idx / BS, s = idx % BS;
+    aqk[kc_index<E>(r, s, BS)] = from_f32<TW>(Aq[idx]);
+  }
+  for (int idx = tid; idx < BS * DK; idx += 256) {
+    const int t = idx / DK, c = idx % DK;
+    const float G = Gs[idx];
+    const float gam = exp2f(G);
+    wq[kc_index<E>(BS + t, c, 2 * BS)] = from_f32<TW>(scale * qs[idx] * gam);
+    kgt[kc_index<4>(c, t, DK)] = ks[idx] * exp2f(Gs[(BS - 1) * DK + c] - G);
+    es[idx] *= gam;
+  }
+  if (tid < DK) gl[tid] = exp2f(Gs[(BS - 1) * DK + tid]);
+  __syncthreads();
+
+  // W = Ai E
+  for (int idx = tid; idx < BS * DK; idx += 256) {
+    const int r = idx / DK, c = idx % DK;
+    float acc = 0.f;
+    for (int s = 0; s <= r; ++s) acc = fmaf(Ai[r * BS + s], es[s * DK + c], acc);
+    wq[kc_index<E>(r, c, 2 * BS)] = from_f32<TW>(acc);
+  }
+  // U = Ai (w*v), value columns in tiles of DK
+  for (int c0 = 0; c0 < DV; c0 += DK) {
+    const int cw = min(DK, DV - c0);
+    __syncthreads();
+    for (int idx = tid; idx < BS * cw; idx += 256) {
+      const int t = idx / cw, c = idx % cw;
+      const size_t gi = (tok0 + (size_t)t * H) * DV + c0 + c;
+      qs[t * DK + c] = to_f32(w[gi]) * to_f32(v[gi]);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < BS * cw; idx += 256) {
+      const int r = idx / cw, c = idx % cw;
+      float acc = 0.f;
+      for (int s = 0; s <= r; ++s) acc = fmaf(Ai[r * BS + s], qs[s * DK + c], acc);
+      ut[kc_index<4>(c0 + c, r, DV)] = acc;
+    }
+  }
+}
+
+template <typename TIn, typename TW>
+int launch_typed(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                 const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
+                 bool only_flagged, cudaStream_t st) {
+  const size_t smem = ((size_t)4 * kChunk * L.DK + 3 * kChunk * kChunk) * sizeof(float);
+  auto kern = prep_simt_kernel<TIn, TW>;
+  GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(S / kChunk, B * H);
+  kern<<<grid, 256, smem, st>>>(static_cast<const TIn*>(q), static_cast<const TIn*>(k), static_cast<const TIn*>(v),
+                                g, static_cast<const TIn*>(b), static_cast<const TIn*>(w), L, P, S, H, in_bs, scale,
+                                only_flagged ? 1 : 0);
+  GDN2_CUDA_TRY(cudaGetLastError());
+  return GDN2_OK;
+}
+
+}  // namespace
+
+int launch_prep_simt(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                     const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
+                     int dtype, bool only_flagged, cudaStream_t st) {
+  if (L.esz == 4) {
+    switch (dtype) {
+      case GDN2_F32: return launch_typed<float, float>(q, k, v, g, b, w, L, P, B, S, H, in_bs, scale, only_flagged, st);
+      case GDN2_BF16: return launch_typed<__nv_bfloat16, float>(q, k, v, g, b, w, L, P, B, S, H, in_bs, scale, only_flagged, st);
+      case GDN2_F16: return launch_typed<__half, float>(q, k, v, g, b, w, L, P, B, S, H, in_bs, scale, only_flagged, st);
+      default: return GDN2_ERR_BAD_DTYPE;
+    }
+  }
+  if (dtype != GDN2_BF16) return GDN2_ERR_UNSUPPORTED;
+  return launch_typed<__nv_bfloat16, __nv_bfloat16>(q, k, v, g, b, w, L, P, B, S, H, in_bs, scale, only_flagged, st);
+}
+
+}  // namespace gdn2

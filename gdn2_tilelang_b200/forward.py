@@ -1,0 +1,59 @@
+"""Training-style chunkwise forward driver: ``chunk_gdn2_fwd``.
+
+Mirrors the reference driver (gdn2/forward.py:832-899 of the reference project): the chunk-local
+stage, then the state scan, then the output. Here the scan and the output are one fused kernel
+that can also store the state entering every chunk (``return_chunk_states=True``), which is what
+the reference's ``state_kernel`` materialises as ``h [B, NC, H, DK, DV]``; they are kept in
+float32. A sequence length that is not a multiple of 64 is not padded: the ragged tail runs
+through the recurrent decode kernel, which is arithmetically the same recurrence.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _cabi
+from .config import DEFAULT_KERNEL_CONFIG, GDN2Config
+from .inference import _check_inputs
+
+__all__ = ["chunk_gdn2_fwd", "chunk_gdn2_output"]
+
+
+@torch.no_grad()
+def chunk_gdn2_fwd(q, k, v, g, b, w, scale, initial_state=None, output_final_state=False,
+                   config: GDN2Config = DEFAULT_KERNEL_CONFIG, return_chunk_states=False):
+    """Returns ``(o, final_state | None)`` or, with ``return_chunk_states``, ``(o, final_state | None, h)``.
+
+    ``o`` is ``[B, S, H, DV]`` in the input dtype, ``final_state`` ``[B, H, DK, DV]`` float32,
+    ``h`` ``[B, S // 64, H, DK, DV]`` float32 (whole chunks only).
+    """
+    config.validate()
+    B, S, H, DK, DV = _check_inputs(q, k, v, g, b, w)
+    BS = config.chunk_size
+    n_full = (S // BS) * BS
+    K = _cabi.kernels()
+    g = g.float()
+    o = torch.empty(B, S, H, DV, dtype=v.dtype, device=q.device)
+    state, hs = initial_state, None
+    if state is not None and state.shape != (B, H, DK, DV):
+        raise ValueError(f"initial_state must have shape {(B, H, DK, DV)}, got {tuple(state.shape)}")
+    if n_full:
+        _, state, hs = K.chunk_forward(*(t[:, :n_full] for t in (q, k, v, g, b, w)), scale, state,
+                                       want_chunk_states=return_chunk_states, out=o, out_batch_stride=S)
+    if S > n_full:
+        if state is None:
+            state = torch.zeros(B, H, DK, DV, dtype=torch.float32, device=q.device)
+        elif n_full == 0:
+            state = state.to(torch.float32).clone()   # never write into the caller's initial state
+        K.decode(*(t[:, n_full:] for t in (q, k, v, g, b, w)), state, scale, out=o[:, n_full:])
+    final = state if output_final_state else None
+    return (o, final, hs) if return_chunk_states else (o, final)
+
+
+@torch.no_grad()
+def chunk_gdn2_output(q, k, v, g, b, w, scale, chunk_states, config: GDN2Config = DEFAULT_KERNEL_CONFIG):
+    """Chunk-parallel output from stored chunk states ``h`` (the reference's ``output_kernel`` stage,
+    gdn2/forward.py:644-727). ``S`` must be a multiple of 64. Returns ``o [B, S, H, DV]``."""
+    config.validate()
+    _check_inputs(q, k, v, g, b, w)
+    return _cabi.kernels().chunk_output(q, k, v, g.float(), b, w, scale, chunk_states)

@@ -1,0 +1,133 @@
+/*
+ * gdn2_b200 -- C ABI of the Gated DeltaNet-2 forward / serving kernels for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain device pointers and sizes, launches on the given CUDA stream
+ * (a cudaStream_t passed as void*, NULL = the legacy default stream), allocates nothing and
+ * returns 0 or a negative gdn2_status. No C++ or framework types cross this boundary.
+ *
+ * Tensor conventions (identical to the reference project's Python API):
+ *   q, k, b : [B, S, H, DK]   v, w : [B, S, H, DV]   element type `dtype`
+ *   g       : [B, S, H, DK]   fp32 natural-log decay, <= 0
+ *   state   : [B, H, DK, DV]  fp32, contiguous
+ *   o       : [B, S, H, DV]   element type `dtype`
+ * The [S, H, D] block of one batch entry is contiguous; consecutive batch entries are
+ * `in_batch_stride` (inputs) / `o_batch_stride` (o) TOKENS apart, counted in rows of H*D elements
+ * (pass S for a contiguous tensor). This lets a caller hand over a slice of a longer sequence --
+ * the whole chunks to the chunkwise path, the ragged tail to gdn2_decode -- without copying it.
+ *
+ * The reference project has no native layer: its kernels are TileLang JIT factories called from
+ * Python. Each function below names the reference Python interface whose device work it replaces
+ * (paths relative to the reference project's root).
+ */
+#ifndef GDN2_B200_H_
+#define GDN2_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GDN2_B200_ABI_VERSION 1
+
+/* element type of q, k, v, b, w and o */
+enum gdn2_dtype { GDN2_F32 = 0, GDN2_BF16 = 1, GDN2_F16 = 2 };
+
+enum gdn2_status {
+  GDN2_OK = 0,
+  GDN2_ERR_NULL_POINTER = -1,   /* a required pointer is NULL */
+  GDN2_ERR_BAD_SHAPE = -2,      /* a size is <= 0, S is not a multiple of 64, or a head dim is unsupported */
+  GDN2_ERR_BAD_DTYPE = -3,      /* dtype is not a gdn2_dtype */
+  GDN2_ERR_MISALIGNED = -4,     /* a pointer is not 16-byte aligned */
+  GDN2_ERR_WORKSPACE = -5,      /* the workspace is smaller than gdn2_prefill_workspace_bytes() */
+  GDN2_ERR_CUDA = -6,           /* a CUDA runtime call failed; see gdn2_last_cuda_error() */
+  GDN2_ERR_DEVICE_WAIT = -7,    /* a kernel gave up on a bounded wait (reported by gdn2_check_device_status) */
+  GDN2_ERR_UNSUPPORTED = -8     /* valid arguments, but no kernel is built for this combination */
+};
+
+/* Which kernel family runs the chunkwise prefill. AUTO picks the tcgen05 family when the shape
+ * allows it (DK = DV = 128, bf16) and the SIMT family otherwise. The explicit values exist so the
+ * two families can be cross-checked against each other; both are hand-written CUDA for sm_100a. */
+enum gdn2_prefill_path { GDN2_PATH_AUTO = 0, GDN2_PATH_SIMT = 1, GDN2_PATH_TCGEN05 = 2 };
+
+/* ABI version of the loaded library (== GDN2_B200_ABI_VERSION it was built with). */
+int gdn2_abi_version(void);
+
+/* Human-readable text for a gdn2_status. Never NULL. */
+const char* gdn2_status_string(int status);
+
+/* cudaError_t (as int) of the last failed CUDA call made by this library on the calling thread. */
+int gdn2_last_cuda_error(void);
+
+/*
+ * n-token recurrent decode; `state` is read once, updated in place and written once.
+ *   q,k,b [B,n,H,DK]  v,w [B,n,H,DV]  g [B,n,H,DK] fp32  state [B,H,DK,DV] fp32  o [B,n,H,DV]
+ * n = 1 is the single-token step. Supported: DK <= 256, any DV >= 1, n >= 1.
+ * Replaces decode_step_kernel / decode_multi_kernel and the device branch of gdn2_decode and
+ * gdn2_decode_step (gdn2/inference.py:61-153, 199-303, 306-353, 156-196).
+ */
+int gdn2_decode(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                float* state, void* o, int64_t B, int64_t n, int64_t H, int64_t DK, int64_t DV,
+                int64_t in_batch_stride, int64_t o_batch_stride, float scale, int dtype, void* stream);
+
+/*
+ * Bytes of scratch the chunkwise prefill needs for a [B,S,H,DK,DV] problem (S a multiple of 64).
+ * Returns 0 for an unsupported combination. `path` is a gdn2_prefill_path.
+ */
+size_t gdn2_prefill_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path);
+
+/*
+ * Chunk-local stage of the chunkwise forward (chunk = 64 tokens): cumulative log2 decay, the
+ * intra-chunk matrices Aqk / Akk, the (I + Akk)^-1 solve and the WY factors W, U, KG, plus the
+ * decayed queries, written into `workspace` in the operand layout the scan consumes.
+ * Replaces cumsum_kernel, intra_diag_kernel, inter_blocks_kernel, solve_kernel, wy_kernel and their
+ * driver wy_stages (gdn2/forward.py:65-535, 756-829).
+ */
+int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                    void* workspace, size_t workspace_bytes, int64_t B, int64_t S, int64_t H, int64_t DK,
+                    int64_t DV, int64_t in_batch_stride, float scale, int dtype, int path, void* stream);
+
+/*
+ * Sequential state scan over chunks fused with the output: per chunk Un = U - W S,
+ * o = Qg S + tril(Aqk) Un, S <- diag(gamma_C) S + KG^T Un, with the fp32 state resident on chip.
+ *   initial_state  [B,H,DK,DV] fp32 or NULL (zeros)
+ *   final_state    [B,H,DK,DV] fp32 or NULL (not written)
+ *   chunk_states   [B,S/64,H,DK,DV] fp32 or NULL; when given, the state entering every chunk is stored
+ * Replaces prefill_scan_kernel (gdn2/inference.py:356-479) and, with chunk_states, the
+ * state_kernel + output_kernel pair of the training-style forward (gdn2/forward.py:538-727).
+ */
+int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
+                      float* final_state, float* chunk_states, int64_t B, int64_t S, int64_t H, int64_t DK,
+                      int64_t DV, int64_t o_batch_stride, int dtype, int path, void* stream);
+
+/*
+ * Chunk-parallel output from stored chunk states: o = Qg h_n + tril(Aqk) Un_n with
+ * Un_n = U - W h_n, one thread block per (chunk, batch, head). Needs the workspace of
+ * gdn2_chunk_prep and the chunk_states of gdn2_prefill_scan.
+ * Replaces output_kernel (gdn2/forward.py:644-727).
+ */
+int gdn2_chunk_output(const void* workspace, size_t workspace_bytes, const float* chunk_states, void* o,
+                      int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int64_t o_batch_stride, int dtype,
+                      int path, void* stream);
+
+/*
+ * Kernels with bounded waits record a non-zero word when a wait runs out. This copies the word
+ * for the current device to the host (synchronising `stream` first), clears it and returns
+ * GDN2_OK or GDN2_ERR_DEVICE_WAIT. `detail` (may be NULL) receives the raw word.
+ */
+int gdn2_check_device_status(void* stream, uint32_t* detail);
+
+/*
+ * Self-test of the tcgen05 / TMEM / bulk-copy building blocks on tiny fixed operands
+ * (one 128x128x64 bf16 and one tf32 product through shared-memory descriptors, a TMEM round trip).
+ * `out` receives 3*128*128 fp32 results (the bf16 product, the tf32 product, then 2*tf32+1 after a
+ * TMEM store/load round trip); `a` and `bt` are [128,64] fp32 row-major inputs (A, and B transposed).
+ * No counterpart in the reference.
+ */
+int gdn2_selftest_mma(const float* a, const float* bt, float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GDN2_B200_H_ */

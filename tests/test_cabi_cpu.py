@@ -1,0 +1,88 @@
+"""The C-ABI library builds, loads and exports what ``include/gdn2_b200.h`` declares; argument
+validation is exercised with calls that return before any device work (no GPU needed)."""
+
+from __future__ import annotations
+
+import ctypes
+import pathlib
+import re
+
+import pytest
+
+from gdn2_tilelang_b200 import _cabi
+
+ROOT = pathlib.Path(__file__).resolve().parents[1]
+HEADER = (ROOT / "include" / "gdn2_b200.h").read_text()
+
+
+@pytest.fixture(scope="module")
+def lib():
+    return _cabi.load_library()
+
+
+def declared_symbols():
+    return sorted(set(re.findall(r"^(?:int|size_t|const char\*)\s+(gdn2_[a-z0-9_]+)\s*\(", HEADER, re.M)))
+
+
+def test_header_and_binding_table_agree():
+    assert declared_symbols() == sorted(_cabi.SIGNATURES)
+
+
+@pytest.mark.parametrize("name", declared_symbols())
+def test_symbol_is_exported(lib, name):
+    assert getattr(lib, name) is not None
+
+
+def test_abi_version_matches_header(lib):
+    want = int(re.search(r"#define GDN2_B200_ABI_VERSION (\d+)", HEADER).group(1))
+    assert lib.gdn2_abi_version() == want
+
+
+def test_status_strings(lib):
+    seen = {lib.gdn2_status_string(s) for s in range(0, -9, -1)}
+    assert len(seen) == 9 and all(seen)
+    assert lib.gdn2_status_string(-99) == b"unknown status"
+
+
+def test_workspace_query(lib):
+    f = lib.gdn2_prefill_workspace_bytes
+    big = f(4, 16000, 16, 128, 128, _cabi.GDN2_BF16, _cabi.PATH_AUTO)
+    # per chunk-head: WQ 32 KiB + AQK 8 KiB + KG^T 32 KiB + U^T 32 KiB + gamma_last 512 B (+ flag)
+    per = 32768 + 8192 + 32768 + 32768 + 512 + 4
+    nch = 4 * 16 * 250
+    assert per * nch <= big <= per * nch + 8 * 1024
+    assert f(1, 100, 1, 128, 128, _cabi.GDN2_BF16, 0) == 0          # S not a multiple of 64
+    assert f(1, 64, 1, 36, 32, _cabi.GDN2_F32, 0) == 0              # DK not a multiple of 8
+    assert f(1, 64, 1, 256, 32, _cabi.GDN2_F32, 0) == 0             # DK too large for the chunkwise kernels
+    assert f(1, 64, 1, 64, 64, _cabi.GDN2_BF16, _cabi.PATH_TCGEN05) == 0   # tcgen05 family is D=128 only
+    assert f(1, 64, 1, 64, 64, _cabi.GDN2_BF16, _cabi.PATH_SIMT) > 0
+    assert f(1, 64, 1, 32, 24, 7, 0) == 0                           # bad dtype
+
+
+def test_argument_validation_returns_status_without_device_work(lib):
+    null = None
+    one = ctypes.c_void_p(16)   # never dereferenced: validation fails first
+    assert lib.gdn2_decode(null, one, one, one, one, one, one, one, 1, 1, 1, 32, 32, 1, 1, 1.0, 0, None) == -1
+    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 1, 1, 1, 32, 32, 1, 1, 1.0, 9, None) == -3
+    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 0, 1, 1, 32, 32, 1, 1, 1.0, 0, None) == -2
+    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 1, 1, 1, 512, 32, 1, 1, 1.0, 0, None) == -2
+    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 1, 4, 1, 32, 32, 2, 4, 1.0, 0, None) == -2
+    misaligned = ctypes.c_void_p(24)
+    assert lib.gdn2_decode(one, one, one, one, one, one, misaligned, one, 1, 1, 1, 128, 128, 1, 1, 1.0, 0, None) == -4
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, null, 0, 1, 64, 1, 32, 32, 64, 1.0, 0, 0, None) == -1
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 0, 1, 65, 1, 32, 32, 65, 1.0, 0, 0, None) == -2
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 0, 1, 64, 1, 32, 32, 64, 1.0, 0, 2, None) == -8
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, misaligned, 1 << 30, 1, 64, 1, 32, 32, 64, 1.0, 0, 0, None) == -4
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 16, 1, 64, 1, 32, 32, 64, 1.0, 0, 0, None) == -5
+    assert lib.gdn2_prefill_scan(one, 16, null, one, null, null, 1, 64, 1, 32, 32, 64, 0, 0, None) == -5
+    assert lib.gdn2_prefill_scan(one, 1 << 30, null, null, null, null, 1, 64, 1, 32, 32, 64, 0, 0, None) == -1
+    assert lib.gdn2_chunk_output(one, 1 << 30, null, one, 1, 64, 1, 32, 32, 64, 0, 0, None) == -1
+    assert lib.gdn2_selftest_mma(null, one, one, None) == -1
+
+
+def test_dtype_codes():
+    import torch
+
+    assert _cabi.dtype_code(torch.float32) == 0 and _cabi.dtype_code(torch.bfloat16) == 1
+    with pytest.raises(TypeError):
+        _cabi.dtype_code(torch.float64)

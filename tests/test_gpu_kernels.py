@@ -1,0 +1,252 @@
+"""Parity of the CUDA kernels (through the C ABI) with the oracle and the golden fixtures.
+
+Tolerances: float32 inputs -> the reference tests' own bounds (rel-max 2e-5 chunkwise, 1e-5 decode);
+bf16 inputs -> output max-abs <= 2e-2 and final-state relative Frobenius error <= 1e-3 against the
+oracle fed the same bf16-rounded inputs (the acceptance bounds of the benchmark definition)."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import gdn2_tilelang_b200 as gdn2
+from gdn2_tilelang_b200 import _cabi
+from oracle import gdn2_oracle as orc
+from tests.conftest import golden_state, load_golden
+from tests.golden.make_golden import CORE_CASES, DECODE_CASES, PREFILL_CASES
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+O_ABS_BF16, STATE_FRO = 2e-2, 1e-3
+
+
+def cuda(*ts):
+    return tuple(t.to(DEV) for t in ts)
+
+
+def bf16_inputs(B, S, H, DK, DV, **kw):
+    """bf16-rounded inputs: returns (device bf16 tensors + fp32 g, host fp32 copies of the rounded values)."""
+    q, k, v, g, b, w = orc.make_inputs(B, S, H, DK, DV, **kw)
+    qh, kh, vh, bh, wh = (t.bfloat16() for t in (q, k, v, b, w))
+    dev = (qh.to(DEV), kh.to(DEV), vh.to(DEV), g.to(DEV), bh.to(DEV), wh.to(DEV))
+    host = (qh.float(), kh.float(), vh.float(), g, bh.float(), wh.float())
+    return dev, host
+
+
+@pytest.fixture(scope="module")
+def K():
+    k = _cabi.kernels()
+    yield k
+    k.check_device_status()
+
+
+# ---- tensor-core building blocks -------------------------------------------------------------------
+
+
+def test_tcgen05_selftest(K):
+    gen = torch.Generator().manual_seed(0)
+    a = torch.randn(128, 64, generator=gen)
+    bt = torch.randn(128, 64, generator=gen)
+    out = K.selftest_mma(a.to(DEV), bt.to(DEV)).cpu()
+    K.check_device_status()
+    ref16 = a.bfloat16().float() @ bt.bfloat16().float().T
+    ref32 = a.double() @ bt.double().T
+    assert orc.rel_max_err(out[0], ref16) < 1e-5          # exact products, fp32 accumulation
+    assert orc.rel_max_err(out[1], ref32) < 3e-3          # tf32 operands: 10-bit mantissa
+    assert torch.equal(out[2], 2 * out[1] + 1)            # TMEM store/load round trip
+
+
+# ---- decode ------------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("name", sorted(DECODE_CASES))
+def test_decode_fp32_matches_golden(K, name):
+    B, n, H, DK, DV = DECODE_CASES[name]
+    gold = load_golden(name)
+    ins = orc.make_inputs(B, n, H, DK, DV, seed=1, gate="softplus")
+    state = golden_state(B, H, DK, DV, 1, 0.3).to(DEV)
+    o = gdn2.gdn2_decode(*cuda(*ins), state)
+    assert orc.rel_max_err(o.cpu(), gold["o"]) < 1e-5
+    assert orc.rel_max_err(state.cpu(), gold["state"]) < 1e-5
+
+
+@pytest.mark.parametrize("DK,DV", [(128, 128), (64, 64), (32, 24), (256, 40), (72, 100)])
+@pytest.mark.parametrize("n", [1, 8, 37])
+def test_decode_bf16_vs_oracle(K, DK, DV, n):
+    B, H = 3, 5
+    dev, host = bf16_inputs(B, n, H, DK, DV, seed=n, gate="softplus", decay_scale=1.0)
+    s0 = golden_state(B, H, DK, DV, n, 0.3)
+    state = s0.to(DEV)
+    o = gdn2.gdn2_decode(*dev, state)
+    s_ref = s0.clone()
+    o_ref = orc.decode(*host, s_ref)
+    assert o.dtype == torch.bfloat16
+    assert orc.max_abs_err(o.float().cpu(), o_ref) < O_ABS_BF16
+    assert orc.rel_fro_err(state.cpu(), s_ref) < 1e-5
+
+
+def test_decode_multi_equals_repeated_single(K):
+    dev, _ = bf16_inputs(4, 12, 16, 128, 128, seed=3)
+    s0 = (torch.randn(4, 16, 128, 128, generator=torch.Generator().manual_seed(1)) * 0.02).to(DEV)
+    sm = s0.clone()
+    om = gdn2.gdn2_decode(*dev, sm)
+    s1 = s0.clone()
+    o1 = torch.cat([gdn2.gdn2_decode(*(t[:, i:i + 1] for t in dev), s1) for i in range(12)], 1)
+    assert torch.equal(om, o1) and torch.equal(sm, s1)      # same kernel arithmetic per token: bit-exact
+    st = s0.clone()
+    os_ = gdn2.gdn2_decode_step(*(t[:, 0] for t in dev), st)
+    assert torch.equal(os_, o1[:, 0])
+
+
+def test_decode_zero_gates_only_decay(K):
+    dev, host = bf16_inputs(2, 9, 4, 128, 128, seed=5)
+    q, k, v, g, b, w = dev
+    s0 = golden_state(2, 4, 128, 128, 9, 1.0)
+    st = s0.to(DEV)
+    gdn2.gdn2_decode(q, k, v, g, torch.zeros_like(b), torch.zeros_like(w), st)
+    want = s0 * host[3].sum(dim=1).exp().unsqueeze(-1)
+    assert orc.rel_max_err(st.cpu(), want) < 1e-5
+
+
+# ---- chunkwise forward, SIMT family (float32 inputs) ---------------------------------------------------
+
+
+@pytest.mark.parametrize("name", sorted(CORE_CASES))
+def test_chunk_forward_fp32_matches_golden(K, name):
+    B, S, H, DK, DV, gate, ds, with_s0 = CORE_CASES[name]
+    gold = load_golden(name)
+    ins = orc.make_inputs(B, S, H, DK, DV, seed=0, gate=gate, decay_scale=ds)
+    s0 = golden_state(B, H, DK, DV, 0, 0.5).to(DEV) if with_s0 else None
+    o, s, h = gdn2.chunk_gdn2_fwd(*cuda(*ins), DK**-0.5, s0, True, return_chunk_states=True)
+    tol = 1e-4 if ds >= 8 else 2e-5
+    assert o.dtype == torch.float32
+    assert orc.rel_max_err(o.cpu(), gold["o_recurrent"]) < tol
+    assert orc.rel_max_err(s.cpu(), gold["s_recurrent"]) < tol
+    assert torch.isfinite(o).all()
+    if "f_h" in gold:
+        assert orc.rel_max_err(h.cpu().permute(0, 2, 1, 3, 4), gold["f_h"]) < tol
+    o2 = gdn2.chunk_gdn2_output(*cuda(*ins), DK**-0.5, h)
+    assert orc.rel_max_err(o2.cpu(), o.cpu()) < 1e-5
+
+
+@pytest.mark.parametrize("name", sorted(PREFILL_CASES))
+def test_prefill_fp32_matches_golden(K, name):
+    B, S, H, DK, DV = PREFILL_CASES[name]
+    gold = load_golden(name)
+    ins = orc.make_inputs(B, S, H, DK, DV, seed=2, gate="softplus")
+    s0 = golden_state(B, H, DK, DV, 2, 0.3).to(DEV)
+    o, state = gdn2.gdn2_prefill(*cuda(*ins), s0.clone())
+    assert o.shape == (B, S, H, DV)
+    assert orc.rel_max_err(o.cpu(), gold["o"]) < 2e-5
+    assert orc.rel_max_err(state.cpu(), gold["state"]) < 2e-5
+
+
+@pytest.mark.parametrize("decay_scale", [0.0, 1.0, 8.0, 30.0])
+def test_fast_decay_stays_finite(K, decay_scale):
+    ins = orc.make_inputs(1, 128, 2, 32, 32, gate="softplus", decay_scale=decay_scale)
+    o_ref, _ = orc.recurrence(*ins)
+    o, _ = gdn2.gdn2_attention(*cuda(*ins))
+    assert torch.isfinite(o).all()
+    assert orc.rel_max_err(o.cpu(), o_ref) < 1e-4
+
+
+def test_attention_cfg0_matches_reference_torch_backend(K):
+    gold = load_golden("cfg0_b1_s256_h4_d64")
+    ins = orc.make_inputs(1, 256, 4, 64, 64, seed=0)
+    o, s = gdn2.gdn2_attention(*cuda(*ins), output_final_state=True)
+    assert orc.rel_max_err(o.cpu(), gold["o_attention"]) < 2e-5
+    assert orc.rel_max_err(s.cpu(), gold["s_attention"]) < 2e-5
+
+
+# ---- chunkwise forward, D = 128 bf16: both kernel families --------------------------------------------
+
+
+def _run_paths(K, dev, s0, paths=("simt", "tcgen05")):
+    out = {}
+    for p in paths:
+        o, s, h = K.chunk_forward(*dev, 128**-0.5, s0, want_chunk_states=True, path=p)
+        K.check_device_status()
+        out[p] = (o.float().cpu(), s.cpu(), h.cpu())
+    return out
+
+
+@pytest.mark.parametrize("variant", ["gdn2", "kda", "gdn"])
+def test_d128_bf16_both_families_vs_oracle(K, variant):
+    B, S, H, D = 2, 512, 4, 128
+    q, k, v, g, b, w = orc.make_inputs(B, S, H, D, D, seed=11)
+    if variant in ("kda", "gdn"):
+        w = b.clone()                                    # tied erase / write gates
+    if variant == "gdn":
+        g = g[..., :1].expand(-1, -1, -1, D).contiguous()  # one decay per head
+    host = tuple(t.bfloat16().float() for t in (q, k, v)) + (g, b.bfloat16().float(), w.bfloat16().float())
+    dev = tuple(t.bfloat16().to(DEV) for t in (q, k, v)) + (g.to(DEV), b.bfloat16().to(DEV), w.bfloat16().to(DEV))
+    s0 = golden_state(B, H, D, D, 11, 0.1)
+    o_ref, s_ref, h_ref = orc.chunkwise(*host, None, s0, return_chunk_states=True)
+    res = _run_paths(K, dev, s0.to(DEV))
+    for p, (o, s, h) in res.items():
+        assert orc.max_abs_err(o, o_ref) < O_ABS_BF16, p
+        assert orc.rel_fro_err(s, s_ref) < STATE_FRO, p
+        assert orc.rel_fro_err(h, h_ref) < STATE_FRO, p
+    assert orc.max_abs_err(res["simt"][0], res["tcgen05"][0]) < O_ABS_BF16
+
+
+def test_d128_golden_case_tcgen05(K):
+    gold = load_golden("d128_s128_h2")
+    q, k, v, g, b, w = orc.make_inputs(1, 128, 2, 128, 128, seed=0)
+    dev = tuple(t.bfloat16().to(DEV) for t in (q, k, v)) + (g.to(DEV), b.bfloat16().to(DEV), w.bfloat16().to(DEV))
+    s0 = golden_state(1, 2, 128, 128, 0, 0.5).to(DEV)
+    o, s, _ = K.chunk_forward(*dev, 128**-0.5, s0, path="tcgen05")
+    K.check_device_status()
+    # golden outputs come from unrounded fp32 inputs, so allow the bf16 input rounding on top
+    assert orc.max_abs_err(o.float().cpu(), gold["o_recurrent"]) < 3e-2
+    assert orc.rel_fro_err(s.cpu(), gold["s_recurrent"]) < 1e-2
+
+
+def test_prefill_ragged_d128_bf16(K):
+    B, S, H, D = 2, 64 * 5 + 37, 3, 128
+    dev, host = bf16_inputs(B, S, H, D, D, seed=13)
+    o, state = gdn2.gdn2_prefill(*dev)
+    o_ref, s_ref = orc.prefill(*host)
+    assert o.shape == (B, S, H, D) and o.dtype == torch.bfloat16
+    assert orc.max_abs_err(o.float().cpu(), o_ref) < O_ABS_BF16
+    assert orc.rel_fro_err(state.cpu(), s_ref) < STATE_FRO
+
+
+def test_fast_decay_d128_bf16_takes_exact_path(K):
+    dev, host = bf16_inputs(1, 128, 2, 128, 128, seed=17, gate="softplus", decay_scale=30.0)
+    o_ref, s_ref = orc.recurrence(*host)
+    o, s = gdn2.gdn2_attention(*dev, output_final_state=True)
+    assert torch.isfinite(o).all()
+    assert orc.max_abs_err(o.float().cpu(), o_ref) < O_ABS_BF16
+
+
+# ---- size-independent properties at benchmark-like sizes ---------------------------------------------
+
+
+def test_large_segmented_prefill_and_linearity(K):
+    B, S, H, D = 2, 64 * 40 + 37, 16, 128
+    dev, _ = bf16_inputs(B, S, H, D, D, seed=21)
+    q, k, v, g, b, w = dev
+    o_all, s_all = gdn2.gdn2_prefill(*dev)
+    outs, state = [], None
+    for lo, hi in ((0, 64 * 10), (64 * 10, 64 * 25 + 5), (64 * 25 + 5, S)):
+        o, state = gdn2.gdn2_prefill(*(t[:, lo:hi] for t in dev), state)
+        outs.append(o)
+    assert orc.max_abs_err(torch.cat(outs, 1).float(), o_all.float()) < O_ABS_BF16
+    assert orc.rel_fro_err(state, s_all) < STATE_FRO
+    # with a zero initial state the output is linear in v
+    o2, s2 = gdn2.gdn2_prefill(q, k, (2 * v.float()).bfloat16(), g, b, w)
+    assert orc.max_abs_err(o2.float(), 2 * o_all.float()) < 2 * O_ABS_BF16
+    assert orc.rel_fro_err(s2, 2 * s_all) < STATE_FRO
+    K.check_device_status()
+
+
+def test_zero_gates_only_decay_large(K):
+    B, S, H, D = 1, 64 * 8, 16, 128
+    dev, host = bf16_inputs(B, S, H, D, D, seed=23)
+    q, k, v, g, b, w = dev
+    s0 = golden_state(B, H, D, D, 23, 1.0)
+    _, s = gdn2.gdn2_attention(q, k, v, g, torch.zeros_like(b), torch.zeros_like(w),
+                               initial_state=s0.to(DEV), output_final_state=True)
+    want = s0 * host[3].sum(dim=1).exp().unsqueeze(-1)
+    assert orc.rel_fro_err(s.cpu(), want) < STATE_FRO

@@ -1,0 +1,53 @@
+"""The GatedDeltaNet2 layer on the GPU: golden parity (float32, small heads), a bf16 D=128 layer
+against the layer oracle, and serving-path self-consistency."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import gdn2_tilelang_b200 as gdn2
+from oracle import gdn2_oracle as orc
+from oracle import layer_oracle as lorc
+from tests.conftest import load_golden
+from tests.golden.make_golden import LAYER
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def test_layer_fp32_matches_reference_module_outputs():
+    gold = load_golden("layer_h64")
+    sd = lorc.random_state_dict(lorc.LayerDims(**LAYER), seed=3, std=0.2)
+    layer = gdn2.GatedDeltaNet2(gdn2.GatedDeltaNet2Config(**LAYER)).eval()
+    layer.load_state_dict(sd)
+    layer.to(DEV)
+    x = torch.randn(2, 90, LAYER["hidden_size"], generator=torch.Generator().manual_seed(4)).to(DEV)
+    full, cache_f = layer(x, use_cache=True)
+    pre, cache = layer.prefill(x[:, :70])
+    dec, cache = layer.decode(x[:, 70:75], cache)
+    steps = torch.stack([layer.step(x[:, t], cache)[0] for t in range(75, 90)], 1)
+    for mine, key in ((full, "full"), (cache_f.recurrent_state, "full_state"), (pre, "prefill"), (dec, "decode"),
+                      (steps, "steps"), (cache.recurrent_state, "final_state"), (cache.conv_state, "final_conv")):
+        assert orc.rel_max_err(mine.float().cpu(), gold[key]) < 1e-4, key
+
+
+def test_layer_bf16_d128_vs_oracle():
+    dims = lorc.LayerDims(hidden_size=256, num_heads=4, num_kv_heads=2, head_dim_k=128, head_dim_v=128)
+    sd = lorc.random_state_dict(dims, seed=5, std=0.05, dtype=torch.bfloat16)
+    cfg = gdn2.GatedDeltaNet2Config(hidden_size=256, num_heads=4, num_kv_heads=2)
+    layer = gdn2.GatedDeltaNet2(cfg).to(torch.bfloat16).eval()
+    layer.load_state_dict(sd)
+    layer.to(DEV)
+    x = torch.randn(2, 200, 256, generator=torch.Generator().manual_seed(6)).bfloat16()
+    pre, cache = layer.prefill(x[:, :150].to(DEV))
+    dec, cache = layer.decode(x[:, 150:158].to(DEV), cache)
+    steps = torch.stack([layer.step(x[:, t].to(DEV), cache)[0] for t in range(158, 200)], 1)
+    got = torch.cat([pre, dec, steps], 1).float().cpu()
+    # oracle in float32 on the same bf16 weights and inputs
+    sd32 = {k: v.float() for k, v in sd.items()}
+    state, conv = lorc.init_cache(dims, 2)
+    ref, state, conv = lorc.prefill(sd32, dims, x.float(), state, conv)
+    assert orc.rel_max_err(got, ref) < 5e-2
+    assert orc.rel_fro_err(cache.recurrent_state.cpu(), state) < 2e-2
+    assert cache.conv_state.dtype == torch.bfloat16 and cache.recurrent_state.dtype == torch.float32
