@@ -41,6 +41,7 @@ SIGNATURES = {
     "gdn2_chunk_output": (_int, [_vp, _sz, _vp, _vp] + [_i64] * 6 + [_int, _int, _vp]),
     "gdn2_check_device_status": (_int, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
     "gdn2_selftest_mma": (_int, [_vp, _vp, _vp, _vp]),
+    "gdn2_prefill_static": (_int, [_vp] * 9 + [_i64] * 7 + [_f32, _int, _vp]),
 }
 
 _lock = threading.Lock()

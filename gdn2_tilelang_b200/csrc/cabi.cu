@@ -67,6 +67,8 @@ const char* gdn2_status_string(int status) {
     case GDN2_ERR_CUDA: return "a CUDA call failed (see gdn2_last_cuda_error)";
     case GDN2_ERR_DEVICE_WAIT: return "a kernel gave up on a bounded wait";
     case GDN2_ERR_UNSUPPORTED: return "no kernel is built for this shape / dtype / path";
+    case GDN2_ERR_STATIC_LIMIT:
+      return "the problem needs more scratch than the built-in static buffer (GDN2_STATIC_SCRATCH_BYTES) holds";
     default: return "unknown status";
   }
 }

@@ -43,7 +43,8 @@ enum gdn2_status {
   GDN2_ERR_WORKSPACE = -5,      /* the workspace is smaller than gdn2_prefill_workspace_bytes() */
   GDN2_ERR_CUDA = -6,           /* a CUDA runtime call failed; see gdn2_last_cuda_error() */
   GDN2_ERR_DEVICE_WAIT = -7,    /* a kernel gave up on a bounded wait (reported by gdn2_check_device_status) */
-  GDN2_ERR_UNSUPPORTED = -8     /* valid arguments, but no kernel is built for this combination */
+  GDN2_ERR_UNSUPPORTED = -8,    /* valid arguments, but no kernel is built for this combination */
+  GDN2_ERR_STATIC_LIMIT = -9    /* gdn2_prefill_static: the problem needs more than GDN2_STATIC_SCRATCH_BYTES */
 };
 
 /* Which kernel family runs the chunkwise prefill. AUTO picks the tcgen05 family when the shape
@@ -126,6 +127,37 @@ int gdn2_check_device_status(void* stream, uint32_t* detail);
  * No counterpart in the reference.
  */
 int gdn2_selftest_mma(const float* a, const float* bt, float* out, void* stream);
+
+/*
+ * Whole-chunk prefill that allocates nothing and asks the caller for no workspace: the chunk-local
+ * stage and the fused scan of gdn2_chunk_prep + gdn2_prefill_scan, exchanging their intermediates
+ * through a fixed scratch array built into the library. It has no counterpart in the reference.
+ *
+ * It exists for callers that cannot obtain device memory at call time: a plugin inside a serving
+ * engine that has already given all free HBM to its own pool, a latency-critical loop that cannot
+ * afford the device-wide synchronisation cudaMalloc / cudaFree imply, or a host that only lends
+ * pre-registered input and output buffers. Such callers still pass q, k, v, g, b, w,
+ * initial_state (may be NULL), o and final_state (may be NULL) exactly as for the two-call form;
+ * S must be a multiple of 64 (send a ragged tail through gdn2_decode).
+ *
+ * Limit: the problem's scratch, gdn2_prefill_workspace_bytes(B, S, H, DK, DV, dtype, AUTO), must
+ * not exceed GDN2_STATIC_SCRATCH_BYTES -- about 320 chunk-heads (B * H * S/64) at DK = DV = 128 in
+ * bf16. Larger problems return GDN2_ERR_STATIC_LIMIT and launch nothing; split them over batch,
+ * heads or sequence segments, or use the two-call form. Every GPU that loads the library holds the
+ * array until the process exits.
+ *
+ * The first call on each device resolves the array's device address (cudaGetSymbolAddress) with
+ * that device current; make that first call outside any stream capture. All calls on a device
+ * share the one array, which keeps whatever the previous call left in it: each call rewrites every
+ * record it later reads, so nothing needs clearing, but two calls that overlap on the GPU (different
+ * streams, or concurrent host threads) race on it -- serialise them.
+ */
+#define GDN2_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+int gdn2_prefill_static(const void* q, const void* k, const void* v, const float* g, const void* b,
+                        const void* w, const float* initial_state, void* o, float* final_state,
+                        int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV,
+                        int64_t in_batch_stride, int64_t o_batch_stride, float scale, int dtype,
+                        void* stream);
 
 #ifdef __cplusplus
 }

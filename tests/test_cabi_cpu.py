@@ -39,8 +39,8 @@ def test_abi_version_matches_header(lib):
 
 
 def test_status_strings(lib):
-    seen = {lib.gdn2_status_string(s) for s in range(0, -9, -1)}
-    assert len(seen) == 9 and all(seen)
+    seen = {lib.gdn2_status_string(s) for s in range(0, -10, -1)}
+    assert len(seen) == 10 and all(seen)
     assert lib.gdn2_status_string(-99) == b"unknown status"
 
 
