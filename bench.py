@@ -177,6 +177,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg")
     ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg")
+    ap.add_argument("--skip-e2e", action="store_true", help="omit the end-to-end leg (launch-list captures)")
+    ap.add_argument("--profile-case", choices=["prefill", "decode"],
+                    help="run a small case a profiler can capture (3 iterations, no JSON line) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -198,6 +201,23 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     B, S, H, DK, DV = (CFG[x] for x in ("B", "S", "H", "DK", "DV"))
+    if args.profile_case:
+        # small enough for a multi-pass capture, larger than L2: prefill B=1 S=4096+37 (workspace 107 MB),
+        # decode B=32 (state 134 MB)
+        if args.profile_case == "prefill":
+            ins = device_inputs(1, 4096 + 37, H, DK, DV, dev, seed=0)
+            for _ in range(3):
+                gdn2.gdn2_prefill(*ins)
+        else:
+            state = torch.randn(32, H, DK, DV, device=dev) * 0.02
+            for n in (1, 8):
+                dq = device_inputs(32, n, H, DK, DV, dev, seed=n)
+                for _ in range(3):
+                    gdn2.gdn2_decode(*dq, state)
+        torch.cuda.synchronize()
+        _cabi.kernels().check_device_status(dev)
+        print(f"profile case {args.profile_case} done")
+        return
     if H % world:
         raise SystemExit(f"{H} heads do not split over {world} ranks")
     Hl = H // world
@@ -241,7 +261,7 @@ def main():
 
     barrier()
     e2e_steps = max(2, min(args.steps, 5))
-    ms_e2e = time_events(e2e_step, e2e_steps, 1, barrier)
+    ms_e2e = float("nan") if args.skip_e2e else time_events(e2e_step, e2e_steps, 1, barrier)
     t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

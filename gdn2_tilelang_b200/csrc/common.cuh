@@ -26,6 +26,15 @@ template <> __device__ __forceinline__ float from_f32<float>(float x) { return x
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
 template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
 
+// Round to the nearest tf32 (10-bit mantissa). tcgen05.mma kind::tf32 reads fp32 words and ignores
+// the low 13 mantissa bits, i.e. truncates; rounding operands first removes that bias, which
+// otherwise shows up as a systematic ~1e-3 shrink of products of two tf32 operands.
+__device__ __forceinline__ float tf32_rn(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+
 // ---------------------------------------------------------------- workspace layout
 //
 // One record set per chunk-head, index ch = (b*H + h)*NC + n. All matrices are stored as

@@ -115,7 +115,8 @@ prep_simt_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn
     const float G = Gs[idx];
     const float gam = exp2f(G);
     wq[kc_index<E>(BS + t, c, 2 * BS)] = from_f32<TW>(scale * qs[idx] * gam);
-    kgt[kc_index<4>(c, t, DK)] = ks[idx] * exp2f(Gs[(BS - 1) * DK + c] - G);
+    const float kg = ks[idx] * exp2f(Gs[(BS - 1) * DK + c] - G);
+    kgt[kc_index<4>(c, t, DK)] = (sizeof(TW) == 2) ? tf32_rn(kg) : kg;   // bf16 workspace = tensor-core consumer
     es[idx] *= gam;
   }
   if (tid < DK) gl[tid] = exp2f(Gs[(BS - 1) * DK + tid]);

@@ -1,12 +1,315 @@
-// Chunk-local stage, tensor-core family (placeholder stage): marks every chunk for the exact
-// SIMT evaluation, which then fills the bf16 workspace the tensor-core scan consumes.
+// Chunk-local stage of the chunkwise forward, tensor-core (tcgen05 / TMEM) family, for
+// DK = DV = 128 and bf16 inputs. One 128-thread block per (chunk, batch*head); thread c owns key
+// channel c and value channel c, so the cumulative decay is a private running sum.
+//
+// What the reference spreads over five kernels (cumsum, intra_diag, inter_blocks, solve, wy:
+// gdn2/forward.py:65-535 of the reference project) is one kernel here, and the intermediates it
+// round-trips through HBM (G, Akk, Ai) never leave the SM:
+//
+//  1. G = log2(e) * cumsum(g) in registers. The overflow-safe factorisation of the reference
+//     (gdn2/forward.py:266-270): rows of sub-block i (16 tokens) are scaled by 2^(G_r - ref_i),
+//     ref_i = G at the sub-block's first row, and paired with key rows scaled by 2^(ref_i - G_s).
+//     Left of the diagonal both exponents are <= 0. ON the diagonal sub-block the key factor is
+//     >= 1 but bounded by the decay span of 16 tokens; the reference evaluates those blocks
+//     pairwise on CUDA cores (intra_diag_kernel) -- here they ride the same tensor-core product
+//     as long as every sub-block's span stays below 2^64. A chunk that decays faster is flagged in
+//     the workspace and redone exactly by the SIMT family's kernel.
+//  2. MMA1 (bf16, M = 128: rows 0..63 = b*k rows, 64..127 = q rows, all scaled by their own ref):
+//     four products A * B_i^T, B_i = key rows s < 16(i+1) scaled to ref_i, N = 16(i+1).
+//     Row block i of product i gives Tm (strictly lower) and Aqk (lower incl. diagonal, * scale).
+//  3. (I + Tm)^-1 by forward substitution in registers: two threads per column (even / odd source
+//     rows), one shuffle per row, Tm read as broadcast 128-bit shared loads.
+//  4. MMA2 (tf32, transposed so channels are M): W^T = E^T * Ai^T, U^T = (w*v)^T * Ai^T.
+//  5. Outputs in the scan's operand layout (common.cuh): WQ via shared staging + bulk stores, AQK,
+//     KG^T, U^T, gamma_last with 128-bit coalesced global stores.
 #include "common.cuh"
+#include "tc_utils.cuh"
 
 namespace gdn2 {
 
-int launch_prep_tc(const void*, const void*, const void*, const float*, const void*, const void*,
-                   const WsLayout& L, const WsPtrs& P, int, int, int, int64_t, float, cudaStream_t st) {
-  GDN2_CUDA_TRY(cudaMemsetAsync(P.flags, 1, sizeof(int) * (size_t)L.nch, st));
+namespace {
+
+constexpr int D = 128;
+constexpr int BS = kChunk;
+constexpr int A_PAD = 129;        // rows per K chunk of a 128-row bf16 image, +1 pad row: kills bank conflicts
+constexpr int B_PAD = 161;        // 160 key rows (16 + 32 + 48 + 64) + 1 pad row
+constexpr int TM_STRIDE = 72;     // floats per Tm row: [0,32) even source rows, [36,68) odd source rows
+constexpr float kMaxSpanLog2 = 64.f;
+
+struct PrepTcSmem {
+  union {
+    struct {
+      __nv_bfloat16 a_own[16 * A_PAD * 8];   // A of MMA1: [dk/8][129][8]
+      __nv_bfloat16 bfam[16 * B_PAD * 8];    // B of MMA1: [dk/8][161][8], rows: B_0 0..15, B_1 16..47, B_2 48..95, B_3 96..159
+    } ops;
+    struct {
+      float tm[BS * TM_STRIDE];              // strictly lower Tm, de-interleaved by source-row parity
+      float ai[16 * BS * 4];                 // B of MMA2: (I+Tm)^-1 as [s/4][64 r][4]
+    } sol;
+  } x;
+  float et[16 * D * 4];                      // A of MMA2: E^T  [tok/4][128 dk][4]
+  float zt[16 * D * 4];                      // A of MMA2: (w*v)^T [tok/4][128 dv][4]
+  __nv_bfloat16 wq[16 * A_PAD * 8];          // staging of the WQ record: [dk/8][129][8]
+  uint64_t bar_m1, bar_m2;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ float bf(const __nv_bfloat16* p) { return __bfloat162float(__ldg(p)); }
+
+__global__ void __launch_bounds__(128, 1)
+prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+               const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
+               const __nv_bfloat16* __restrict__ b, const __nv_bfloat16* __restrict__ w, WsPtrs P, int S, int H,
+               int64_t in_bs, float scale, uint32_t* status) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  PrepTcSmem& s = *reinterpret_cast<PrepTcSmem*>(smem_raw);
+  const int NC = S / BS;
+  const int n = blockIdx.x, bh = blockIdx.y;
+  const int ib = bh / H, ih = bh % H;
+  const int64_t ch = (int64_t)bh * NC + n;
+  const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+  const int c = tid;
+  const size_t row0 = ((size_t)ib * in_bs + (size_t)n * BS) * H + ih;   // token row of t = 0
+  const size_t rstride = (size_t)H * D;                                 // elements between tokens
+
+  // ---- 1. cumulative log2 decay of channel c
+  float G[BS];
+  {
+    const float* gp = g + row0 * D + c;
+#pragma unroll
+    for (int t = 0; t < BS; ++t) G[t] = __ldg(gp + t * rstride) * kLog2e;
+#pragma unroll
+    for (int t = 1; t < BS; ++t) G[t] += G[t - 1];
+  }
+  bool bad = false;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) bad |= !((G[16 * j] - G[16 * j + 15]) <= kMaxSpanLog2);
+  if (tid == 0) {
+    tc::mbar_init(&s.bar_m1, 1);
+    tc::mbar_init(&s.bar_m2, 1);
+    s.abort_flag = 0;
+    tc::mbar_init_fence();
+  }
+  const int any_bad = __syncthreads_or(bad ? 1 : 0);
+  if (tid == 0) P.flags[ch] = any_bad ? 1 : 0;
+  if (any_bad) return;              // the exact kernel redoes this chunk; nothing allocated yet
+  if (wid == 0) tc::tmem_alloc(&s.tmem_base, 256);
+
+  // ---- 1b. gated operands of channel c
+  {
+    const __nv_bfloat16* qp = q + row0 * D + c;
+    const __nv_bfloat16* kp = k + row0 * D + c;
+    const __nv_bfloat16* bp = b + row0 * D + c;
+    const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
+    const int cb = (c >> 3) * B_PAD * 8 + (c & 7);
+    float* kgt_g = P.kgt + (size_t)ch * (D * BS) + c * 4;
+    const float g_last = G[BS - 1];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int off_j = 8 * j * (j + 1);                       // first row of B_j: 0, 16, 48, 96
+      const float ref = G[16 * j];
+      const float refn = (j < 3) ? G[16 * j + 16] : 0.f;
+      const float gam_ref = exp2f(ref);
+      const float kg_c = (j < 3) ? exp2f(g_last - refn) : 1.f;
+      float cc[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) cc[i] = (i > j + 1) ? exp2f(G[16 * i] - refn) : 1.f;
+#pragma unroll
+      for (int t4 = 0; t4 < 4; ++t4) {
+        float e4[4], kg4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int t = 16 * j + 4 * t4 + u;
+          const float kf = bf(kp + t * rstride), qf = bf(qp + t * rstride), bv = bf(bp + t * rstride);
+          const float a = exp2f(G[t] - ref);                    // <= 1
+          const float co = exp2f(ref - G[t]);                   // >= 1, bounded by the span check
+          const float nx = (j < 3) ? exp2f(refn - G[t]) : exp2f(g_last - G[t]);   // <= 1
+          const float e = bv * kf;
+          s.x.ops.a_own[ca + t * 8] = __float2bfloat16_rn(e * a);
+          s.x.ops.a_own[ca + (BS + t) * 8] = __float2bfloat16_rn(qf * a);
+          s.x.ops.bfam[cb + (off_j + t) * 8] = __float2bfloat16_rn(kf * co);
+#pragma unroll
+          for (int i = j + 1; i < 4; ++i)
+            s.x.ops.bfam[cb + (8 * i * (i + 1) + t) * 8] = __float2bfloat16_rn(kf * nx * cc[i]);
+          const float gam = a * gam_ref;
+          e4[u] = tf32_rn(e * gam);
+          s.wq[ca + (BS + t) * 8] = __float2bfloat16_rn(scale * qf * gam);
+          kg4[u] = tf32_rn(kf * nx * kg_c);
+        }
+        const int tq = 4 * j + t4;                              // token quad index
+        *reinterpret_cast<float4*>(&s.et[(tq * D + c) * 4]) = make_float4(e4[0], e4[1], e4[2], e4[3]);
+        *reinterpret_cast<float4*>(kgt_g + (size_t)tq * D * 4) = make_float4(kg4[0], kg4[1], kg4[2], kg4[3]);
+      }
+    }
+    P.gl[(size_t)ch * D + c] = exp2f(g_last);
+  }
+  tc::fence_async_smem();
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tm = s.tmem_base;
+
+  // ---- 2. MMA1: D_i[128 x 16(i+1)] at TMEM columns 0, 16, 48, 96
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int off = 8 * i * (i + 1);
+      tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, off), tc::smem_u32(s.x.ops.a_own), A_PAD,
+                         tc::smem_u32(s.x.ops.bfam) + off * 16, B_PAD, D, tc::instr_desc(1, 128, 16 * (i + 1)),
+                         false);
+    }
+    tc::mma_commit(&s.bar_m1);
+  }
+  // value side while the tensor core works: (w*v)^T image
+  {
+    const __nv_bfloat16* vp = v + row0 * D + c;
+    const __nv_bfloat16* wp = w + row0 * D + c;
+#pragma unroll
+    for (int tq = 0; tq < 16; ++tq) {
+      float z[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) z[u] = tf32_rn(bf(vp + (4 * tq + u) * rstride) * bf(wp + (4 * tq + u) * rstride));
+      *reinterpret_cast<float4*>(&s.zt[(tq * D + c) * 4]) = make_float4(z[0], z[1], z[2], z[3]);
+    }
+  }
+  tc::mbar_wait(&s.bar_m1, 0, &s.abort_flag, status, 0x1000u);
+  tc::tc_fence_after_sync();
+
+  // ---- 2b. read back: lane = row (0..63 Tm, 64..127 Aqk); a warp spans sub-blocks i0 and i0+1
+  {
+    const int r = tid & 63;
+    const bool is_q = tid >= 64;
+    const int i0 = 2 * (wid & 1);
+    const bool hi = lane >= 16;
+    const uint32_t t_lo = tc::tmem_addr(tm, wid * 32, 8 * i0 * (i0 + 1));
+    const uint32_t t_hi = tc::tmem_addr(tm, wid * 32, 8 * (i0 + 1) * (i0 + 2));
+    float row[BS];
+#pragma unroll
+    for (int cg = 0; cg < 4; ++cg) {
+      float lo16[16], hi16[16];
+#pragma unroll
+      for (int x = 0; x < 16; ++x) { lo16[x] = 0.f; hi16[x] = 0.f; }
+      if (cg <= i0) tc::tmem_ld16(t_lo + 16 * cg, lo16);          // warp-uniform conditions
+      if (cg <= i0 + 1) tc::tmem_ld16(t_hi + 16 * cg, hi16);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int x = 0; x < 16; ++x) {
+        const int sc = 16 * cg + x;
+        const float val = hi ? hi16[x] : lo16[x];
+        const bool keep = is_q ? (sc <= r) : (sc < r);
+        row[sc] = keep ? (is_q ? val * scale : val) : 0.f;
+      }
+    }
+    if (!is_q) {
+      float* tr = s.x.sol.tm + r * TM_STRIDE;
+#pragma unroll
+      for (int m4 = 0; m4 < 8; ++m4) {
+        *reinterpret_cast<float4*>(tr + 4 * m4) =
+            make_float4(row[8 * m4], row[8 * m4 + 2], row[8 * m4 + 4], row[8 * m4 + 6]);
+        *reinterpret_cast<float4*>(tr + 36 + 4 * m4) =
+            make_float4(row[8 * m4 + 1], row[8 * m4 + 3], row[8 * m4 + 5], row[8 * m4 + 7]);
+      }
+    } else {
+      __nv_bfloat16* ag = reinterpret_cast<__nv_bfloat16*>(P.aqk + (size_t)ch * (BS * BS * 2));
+#pragma unroll
+      for (int kc = 0; kc < 8; ++kc)
+        *reinterpret_cast<uint4*>(ag + (kc * BS + r) * 8) = tc::pack8_bf16(&row[kc * 8]);
+    }
+  }
+  tc::tc_fence_before_sync();
+  __syncthreads();
+
+  // ---- 3. (I + Tm)^-1: thread (j, p) accumulates the source rows of parity p for column j
+  {
+    const int j = tid >> 1, p = tid & 1;
+    const float* tp = s.x.sol.tm + p * 36;
+    float x[32];
+#pragma unroll
+    for (int m = 0; m < 32; ++m) x[m] = 0.f;
+#pragma unroll
+    for (int r = 0; r < BS; ++r) {
+      float acc = 0.f;
+#pragma unroll
+      for (int mg = 0; mg < ((r + 1) / 2 + 3) / 4; ++mg) {      // entries at or right of the diagonal are 0
+        const float4 t4 = *reinterpret_cast<const float4*>(tp + r * TM_STRIDE + 4 * mg);
+        acc = fmaf(t4.x, x[4 * mg], acc);
+        acc = fmaf(t4.y, x[4 * mg + 1], acc);
+        acc = fmaf(t4.z, x[4 * mg + 2], acc);
+        acc = fmaf(t4.w, x[4 * mg + 3], acc);
+      }
+      const float tot = acc + __shfl_xor_sync(0xffffffffu, acc, 1);
+      const float xr = ((r == j) ? 1.f : 0.f) - tot;
+      if ((r & 1) == p) x[r >> 1] = xr;
+    }
+    float* ai = s.x.sol.ai + (j >> 2) * BS * 4 + (j & 3);
+#pragma unroll
+    for (int m = 0; m < 32; ++m) ai[(2 * m + p) * 4] = tf32_rn(x[m]);
+  }
+  tc::fence_async_smem();
+  tc::tc_fence_before_sync();
+  __syncthreads();
+
+  // ---- 4. MMA2 (tf32): W^T at TMEM columns 0..63, U^T at 64..127
+  if (tid == 0 && !s.abort_flag) {
+    tc::tc_fence_after_sync();
+    constexpr uint32_t idesc = tc::instr_desc(2, 128, BS);
+    tc::mma_tf32_ktile(tc::tmem_addr(tm, 0, 0), tc::smem_u32(s.et), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc, false);
+    tc::mma_tf32_ktile(tc::tmem_addr(tm, 0, 64), tc::smem_u32(s.zt), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc, false);
+    tc::mma_commit(&s.bar_m2);
+  }
+  tc::mbar_wait(&s.bar_m2, 0, &s.abort_flag, status, 0x2000u);
+  tc::tc_fence_after_sync();
+
+  // ---- 5. W rows into the WQ staging image, U^T straight to global
+  {
+    const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
+    float* ut_g = P.ut + (size_t)ch * (D * BS) + c * 4;
+    float val[32];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      tc::tmem_ld32(tc::tmem_addr(tm, wid * 32, half * 32), val);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s.wq[ca + (half * 32 + i) * 8] = __float2bfloat16_rn(val[i]);
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      tc::tmem_ld32(tc::tmem_addr(tm, wid * 32, 64 + half * 32), val);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int i4 = 0; i4 < 8; ++i4)
+        *reinterpret_cast<float4*>(ut_g + (size_t)(half * 8 + i4) * D * 4) =
+            make_float4(val[4 * i4], val[4 * i4 + 1], val[4 * i4 + 2], val[4 * i4 + 3]);
+    }
+  }
+  tc::fence_async_smem();
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  if (tid < 16 && !s.abort_flag) {
+    char* g_wq = P.wq + (size_t)ch * (2 * BS * D * 2) + (size_t)tid * (2 * BS * 16);
+    tc::bulk_s2g(g_wq, reinterpret_cast<const char*>(s.wq) + tid * A_PAD * 16, 2 * BS * 16);
+    tc::bulk_commit();
+    tc::bulk_wait_read_all();
+  }
+  __syncthreads();
+  if (wid == 0) tc::tmem_dealloc(tm, 256);
+}
+
+}  // namespace
+
+int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                   const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
+                   cudaStream_t st) {
+  if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
+  const size_t smem = sizeof(PrepTcSmem) + 128;
+  GDN2_CUDA_TRY(cudaFuncSetAttribute(prep_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(S / BS, B * H);
+  using bf16 = __nv_bfloat16;
+  prep_tc_kernel<<<grid, 128, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
+                                          static_cast<const bf16*>(v), g, static_cast<const bf16*>(b),
+                                          static_cast<const bf16*>(w), P, S, H, in_bs, scale, device_status_word());
+  GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }
 

@@ -155,7 +155,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         float4* pu = reinterpret_cast<float4*>(&s.un32[(tc4 * D + dv) * 4]);
         float4 u = *pu;
         u.x -= ws[j * 4 + 0]; u.y -= ws[j * 4 + 1]; u.z -= ws[j * 4 + 2]; u.w -= ws[j * 4 + 3];
-        *pu = u;
+        *pu = make_float4(tf32_rn(u.x), tf32_rn(u.y), tf32_rn(u.z), tf32_rn(u.w));
         ws[j * 4 + 0] = u.x; ws[j * 4 + 1] = u.y; ws[j * 4 + 2] = u.z; ws[j * 4 + 3] = u.w;
       }
 #pragma unroll
