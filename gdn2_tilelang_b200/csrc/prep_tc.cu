@@ -1,12 +1,12 @@
 // Chunk-local stage of the chunkwise forward, tensor-core (tcgen05 / TMEM) family, for
-// DK = DV = 128 and bf16 inputs. One 128-thread block per (chunk, batch*head); thread c owns key
-// channel c and value channel c, so the cumulative decay is a private running sum.
+// DK = DV = 128 and bf16 inputs. One 128-thread block per (chunk, batch*head), two blocks per SM;
+// thread c owns key channel c and value channel c, so the cumulative decay is a private running sum.
 //
 // What the reference spreads over five kernels (cumsum, intra_diag, inter_blocks, solve, wy:
 // gdn2/forward.py:65-535 of the reference project) is one kernel here, and the intermediates it
 // round-trips through HBM (G, Akk, Ai) never leave the SM:
 //
-//  1. G = log2(e) * cumsum(g) in registers. The overflow-safe factorisation of the reference
+//  1. G = log2(e) * cumsum(g) as a running sum. The overflow-safe factorisation of the reference
 //     (gdn2/forward.py:266-270): rows of sub-block i (16 tokens) are scaled by 2^(G_r - ref_i),
 //     ref_i = G at the sub-block's first row, and paired with key rows scaled by 2^(ref_i - G_s).
 //     Left of the diagonal both exponents are <= 0. ON the diagonal sub-block the key factor is
@@ -22,6 +22,11 @@
 //  4. MMA2 (tf32, transposed so channels are M): W^T = E^T * Ai^T, U^T = (w*v)^T * Ai^T.
 //  5. Outputs in the scan's operand layout (common.cuh): WQ via shared staging + bulk stores, AQK,
 //     KG^T, U^T, gamma_last with 128-bit coalesced global stores.
+//
+// Shared memory is two regions reused over the block's life so that two blocks fit on an SM:
+//   X (72.5 KiB): MMA1 operands, then Tm + Ai + (w*v)^T;   Y (32.25 KiB): E^T, then the WQ staging.
+// Qg = scale*q*gamma is produced in step 1 but only needed in step 5; it waits in 32 spare TMEM
+// columns of the thread's own lane (packed bf16 pairs).
 #include "common.cuh"
 #include "tc_utils.cuh"
 
@@ -35,6 +40,8 @@ constexpr int A_PAD = 129;        // rows per K chunk of a 128-row bf16 image, +
 constexpr int B_PAD = 161;        // 160 key rows (16 + 32 + 48 + 64) + 1 pad row
 constexpr int TM_STRIDE = 72;     // floats per Tm row: [0,32) even source rows, [36,68) odd source rows
 constexpr float kMaxSpanLog2 = 64.f;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kQgCol = 160;  // TMEM columns [160,192): packed Qg of the thread's channel
 
 struct PrepTcSmem {
   union {
@@ -45,19 +52,24 @@ struct PrepTcSmem {
     struct {
       float tm[BS * TM_STRIDE];              // strictly lower Tm, de-interleaved by source-row parity
       float ai[16 * BS * 4];                 // B of MMA2: (I+Tm)^-1 as [s/4][64 r][4]
+      float zt[16 * D * 4];                  // A of MMA2: (w*v)^T [tok/4][128 dv][4]
     } sol;
   } x;
-  float et[16 * D * 4];                      // A of MMA2: E^T  [tok/4][128 dk][4]
-  float zt[16 * D * 4];                      // A of MMA2: (w*v)^T [tok/4][128 dv][4]
-  __nv_bfloat16 wq[16 * A_PAD * 8];          // staging of the WQ record: [dk/8][129][8]
+  union {
+    float et[16 * D * 4];                    // A of MMA2: E^T  [tok/4][128 dk][4]
+    __nv_bfloat16 wq[16 * A_PAD * 8];        // staging of the WQ record: [dk/8][129][8]
+  } y;
   uint64_t bar_m1, bar_m2;
   uint32_t tmem_base;
   int abort_flag;
 };
 
 __device__ __forceinline__ float bf(const __nv_bfloat16* p) { return __bfloat162float(__ldg(p)); }
+__device__ __forceinline__ float pick4(int j, float a0, float a1, float a2, float a3) {
+  return j == 0 ? a0 : j == 1 ? a1 : j == 2 ? a2 : a3;
+}
 
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(128, 2)
 prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
                const __nv_bfloat16* __restrict__ b, const __nv_bfloat16* __restrict__ w, WsPtrs P, int S, int H,
@@ -72,19 +84,26 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const int c = tid;
   const size_t row0 = ((size_t)ib * in_bs + (size_t)n * BS) * H + ih;   // token row of t = 0
   const size_t rstride = (size_t)H * D;                                 // elements between tokens
+  const float* gp = g + row0 * D + c;
 
-  // ---- 1. cumulative log2 decay of channel c
-  float G[BS];
-  {
-    const float* gp = g + row0 * D + c;
-#pragma unroll
-    for (int t = 0; t < BS; ++t) G[t] = __ldg(gp + t * rstride) * kLog2e;
-#pragma unroll
-    for (int t = 1; t < BS; ++t) G[t] += G[t - 1];
-  }
+  // ---- 1a. G at the first row of every sub-block and at the last token; decay-span check
+  float ref0 = 0.f, ref1 = 0.f, ref2 = 0.f, ref3 = 0.f, g_last;
   bool bad = false;
+  {
+    float run = 0.f;
+#pragma unroll 1
+    for (int j = 0; j < 4; ++j) {
+      float gv[16];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) bad |= !((G[16 * j] - G[16 * j + 15]) <= kMaxSpanLog2);
+      for (int u = 0; u < 16; ++u) gv[u] = __ldg(gp + (16 * j + u) * rstride) * kLog2e;
+      const float first = run + gv[0];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) run += gv[u];
+      bad |= !((first - run) <= kMaxSpanLog2);
+      if (j == 0) ref0 = first; else if (j == 1) ref1 = first; else if (j == 2) ref2 = first; else ref3 = first;
+    }
+    g_last = run;
+  }
   if (tid == 0) {
     tc::mbar_init(&s.bar_m1, 1);
     tc::mbar_init(&s.bar_m2, 1);
@@ -94,9 +113,13 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (tid == 0) P.flags[ch] = any_bad ? 1 : 0;
   if (any_bad) return;              // the exact kernel redoes this chunk; nothing allocated yet
-  if (wid == 0) tc::tmem_alloc(&s.tmem_base, 256);
+  if (wid == 0) tc::tmem_alloc(&s.tmem_base, kTmemCols);
+  tc::tc_fence_before_sync();
+  __syncthreads();
+  tc::tc_fence_after_sync();
+  const uint32_t tm = s.tmem_base;
 
-  // ---- 1b. gated operands of channel c
+  // ---- 1b. gated operands of channel c, one 16-token sub-block per iteration
   {
     const __nv_bfloat16* qp = q + row0 * D + c;
     const __nv_bfloat16* kp = k + row0 * D + c;
@@ -104,54 +127,68 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
     const int cb = (c >> 3) * B_PAD * 8 + (c & 7);
     float* kgt_g = P.kgt + (size_t)ch * (D * BS) + c * 4;
-    const float g_last = G[BS - 1];
-#pragma unroll
+    float run = 0.f;
+#pragma unroll 1
     for (int j = 0; j < 4; ++j) {
+      float gv[16], kv[16], qv[16], bv[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const size_t off = (16 * j + u) * rstride;
+        gv[u] = __ldg(gp + off) * kLog2e;
+        kv[u] = bf(kp + off); qv[u] = bf(qp + off); bv[u] = bf(bp + off);
+      }
       const int off_j = 8 * j * (j + 1);                       // first row of B_j: 0, 16, 48, 96
-      const float ref = G[16 * j];
-      const float refn = (j < 3) ? G[16 * j + 16] : 0.f;
+      const float ref = pick4(j, ref0, ref1, ref2, ref3);
+      const float refn = pick4(j, ref1, ref2, ref3, 0.f);      // ref of the next sub-block (unused for j = 3)
       const float gam_ref = exp2f(ref);
       const float kg_c = (j < 3) ? exp2f(g_last - refn) : 1.f;
-      float cc[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) cc[i] = (i > j + 1) ? exp2f(G[16 * i] - refn) : 1.f;
+      const float cc_a = exp2f(pick4(j, ref2, ref3, 0.f, 0.f) - refn);   // B_{j+2} / B_{j+1}
+      const float cc_b = exp2f(ref3 - refn);                               // B_{j+3} / B_{j+1} (j = 0 only)
+      uint32_t qgp[8];
 #pragma unroll
       for (int t4 = 0; t4 < 4; ++t4) {
-        float e4[4], kg4[4];
+        float e4[4], kg4[4], qg4[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
-          const int t = 16 * j + 4 * t4 + u;
-          const float kf = bf(kp + t * rstride), qf = bf(qp + t * rstride), bv = bf(bp + t * rstride);
-          const float a = exp2f(G[t] - ref);                    // <= 1
-          const float co = exp2f(ref - G[t]);                   // >= 1, bounded by the span check
-          const float nx = (j < 3) ? exp2f(refn - G[t]) : exp2f(g_last - G[t]);   // <= 1
-          const float e = bv * kf;
+          const int uu = 4 * t4 + u;
+          const int t = 16 * j + uu;
+          run += gv[uu];
+          const float kf = kv[uu], qf = qv[uu];
+          const float a = exp2f(run - ref);                     // <= 1
+          const float co = exp2f(ref - run);                    // >= 1, bounded by the span check
+          const float nx = (j < 3) ? exp2f(refn - run) : exp2f(g_last - run);   // <= 1
+          const float e = bv[uu] * kf;
           s.x.ops.a_own[ca + t * 8] = __float2bfloat16_rn(e * a);
           s.x.ops.a_own[ca + (BS + t) * 8] = __float2bfloat16_rn(qf * a);
           s.x.ops.bfam[cb + (off_j + t) * 8] = __float2bfloat16_rn(kf * co);
-#pragma unroll
-          for (int i = j + 1; i < 4; ++i)
-            s.x.ops.bfam[cb + (8 * i * (i + 1) + t) * 8] = __float2bfloat16_rn(kf * nx * cc[i]);
+          const float kn = kf * nx;
+          if (j < 3) s.x.ops.bfam[cb + (8 * (j + 1) * (j + 2) + t) * 8] = __float2bfloat16_rn(kn);
+          if (j < 2) s.x.ops.bfam[cb + (8 * (j + 2) * (j + 3) + t) * 8] = __float2bfloat16_rn(kn * cc_a);
+          if (j < 1) s.x.ops.bfam[cb + (96 + t) * 8] = __float2bfloat16_rn(kn * cc_b);
           const float gam = a * gam_ref;
           e4[u] = tf32_rn(e * gam);
-          s.wq[ca + (BS + t) * 8] = __float2bfloat16_rn(scale * qf * gam);
-          kg4[u] = tf32_rn(kf * nx * kg_c);
+          qg4[u] = scale * qf * gam;
+          kg4[u] = tf32_rn(kn * kg_c);
         }
         const int tq = 4 * j + t4;                              // token quad index
-        *reinterpret_cast<float4*>(&s.et[(tq * D + c) * 4]) = make_float4(e4[0], e4[1], e4[2], e4[3]);
+        *reinterpret_cast<float4*>(&s.y.et[(tq * D + c) * 4]) = make_float4(e4[0], e4[1], e4[2], e4[3]);
         *reinterpret_cast<float4*>(kgt_g + (size_t)tq * D * 4) = make_float4(kg4[0], kg4[1], kg4[2], kg4[3]);
+        __nv_bfloat162 p01 = __floats2bfloat162_rn(qg4[0], qg4[1]), p23 = __floats2bfloat162_rn(qg4[2], qg4[3]);
+        qgp[2 * t4] = *reinterpret_cast<uint32_t*>(&p01);
+        qgp[2 * t4 + 1] = *reinterpret_cast<uint32_t*>(&p23);
       }
+      tc::tmem_st8(tc::tmem_addr(tm, wid * 32, kQgCol + 8 * j), qgp);
     }
+    tc::tmem_st_wait();
     P.gl[(size_t)ch * D + c] = exp2f(g_last);
   }
   tc::fence_async_smem();
   tc::tc_fence_before_sync();
   __syncthreads();
-  tc::tc_fence_after_sync();
-  const uint32_t tm = s.tmem_base;
 
   // ---- 2. MMA1: D_i[128 x 16(i+1)] at TMEM columns 0, 16, 48, 96
   if (tid == 0) {
+    tc::tc_fence_after_sync();
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int off = 8 * i * (i + 1);
@@ -161,22 +198,24 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     }
     tc::mma_commit(&s.bar_m1);
   }
-  // value side while the tensor core works: (w*v)^T image
+  // value side: raw loads issued while the tensor core works
+  float zv[4][16];
   {
     const __nv_bfloat16* vp = v + row0 * D + c;
     const __nv_bfloat16* wp = w + row0 * D + c;
 #pragma unroll
-    for (int tq = 0; tq < 16; ++tq) {
-      float z[4];
+    for (int jj = 0; jj < 4; ++jj)
 #pragma unroll
-      for (int u = 0; u < 4; ++u) z[u] = tf32_rn(bf(vp + (4 * tq + u) * rstride) * bf(wp + (4 * tq + u) * rstride));
-      *reinterpret_cast<float4*>(&s.zt[(tq * D + c) * 4]) = make_float4(z[0], z[1], z[2], z[3]);
-    }
+      for (int u = 0; u < 16; ++u) {
+        const size_t off = (16 * jj + u) * rstride;
+        zv[jj][u] = tf32_rn(bf(vp + off) * bf(wp + off));
+      }
   }
   tc::mbar_wait(&s.bar_m1, 0, &s.abort_flag, status, 0x1000u);
   tc::tc_fence_after_sync();
 
-  // ---- 2b. read back: lane = row (0..63 Tm, 64..127 Aqk); a warp spans sub-blocks i0 and i0+1
+  // ---- 2b. read back: lane = row (0..63 Tm, 64..127 Aqk); a warp spans sub-blocks i0 and i0+1.
+  //          The MMA1 operands are dead now: Tm, Ai and (w*v)^T take their place.
   {
     const int r = tid & 63;
     const bool is_q = tid >= 64;
@@ -216,6 +255,12 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       for (int kc = 0; kc < 8; ++kc)
         *reinterpret_cast<uint4*>(ag + (kc * BS + r) * 8) = tc::pack8_bf16(&row[kc * 8]);
     }
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+      for (int t4 = 0; t4 < 4; ++t4)
+        *reinterpret_cast<float4*>(&s.x.sol.zt[((4 * jj + t4) * D + c) * 4]) =
+            make_float4(zv[jj][4 * t4], zv[jj][4 * t4 + 1], zv[jj][4 * t4 + 2], zv[jj][4 * t4 + 3]);
   }
   tc::tc_fence_before_sync();
   __syncthreads();
@@ -254,14 +299,15 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   if (tid == 0 && !s.abort_flag) {
     tc::tc_fence_after_sync();
     constexpr uint32_t idesc = tc::instr_desc(2, 128, BS);
-    tc::mma_tf32_ktile(tc::tmem_addr(tm, 0, 0), tc::smem_u32(s.et), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc, false);
-    tc::mma_tf32_ktile(tc::tmem_addr(tm, 0, 64), tc::smem_u32(s.zt), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc, false);
+    tc::mma_tf32_ktile(tc::tmem_addr(tm, 0, 0), tc::smem_u32(s.y.et), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc, false);
+    tc::mma_tf32_ktile(tc::tmem_addr(tm, 0, 64), tc::smem_u32(s.x.sol.zt), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc,
+                       false);
     tc::mma_commit(&s.bar_m2);
   }
   tc::mbar_wait(&s.bar_m2, 0, &s.abort_flag, status, 0x2000u);
   tc::tc_fence_after_sync();
 
-  // ---- 5. W rows into the WQ staging image, U^T straight to global
+  // ---- 5. W and Qg rows into the WQ staging image (E^T is dead now), U^T straight to global
   {
     const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
     float* ut_g = P.ut + (size_t)ch * (D * BS) + c * 4;
@@ -271,7 +317,15 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       tc::tmem_ld32(tc::tmem_addr(tm, wid * 32, half * 32), val);
       tc::tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) s.wq[ca + (half * 32 + i) * 8] = __float2bfloat16_rn(val[i]);
+      for (int i = 0; i < 32; ++i) s.y.wq[ca + (half * 32 + i) * 8] = __float2bfloat16_rn(val[i]);
+    }
+    tc::tmem_ld32(tc::tmem_addr(tm, wid * 32, kQgCol), val);
+    tc::tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t pk = __float_as_uint(val[i]);
+      reinterpret_cast<uint16_t*>(s.y.wq)[ca + (BS + 2 * i) * 8] = static_cast<uint16_t>(pk & 0xFFFFu);
+      reinterpret_cast<uint16_t*>(s.y.wq)[ca + (BS + 2 * i + 1) * 8] = static_cast<uint16_t>(pk >> 16);
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -288,12 +342,12 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   __syncthreads();
   if (tid < 16 && !s.abort_flag) {
     char* g_wq = P.wq + (size_t)ch * (2 * BS * D * 2) + (size_t)tid * (2 * BS * 16);
-    tc::bulk_s2g(g_wq, reinterpret_cast<const char*>(s.wq) + tid * A_PAD * 16, 2 * BS * 16);
+    tc::bulk_s2g(g_wq, reinterpret_cast<const char*>(s.y.wq) + tid * A_PAD * 16, 2 * BS * 16);
     tc::bulk_commit();
     tc::bulk_wait_read_all();
   }
   __syncthreads();
-  if (wid == 0) tc::tmem_dealloc(tm, 256);
+  if (wid == 0) tc::tmem_dealloc(tm, kTmemCols);
 }
 
 }  // namespace

@@ -20,6 +20,8 @@
 // Operands arrive as whole records of the workspace (see common.cuh) with one bulk copy each into
 // a single shared-memory buffer per operand; a buffer is refilled for the next chunk as soon as
 // the MMA that reads it has completed, so the copies overlap the rest of the chunk's chain.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "tc_utils.cuh"
 
@@ -29,6 +31,9 @@ namespace {
 
 constexpr int D = 128;
 constexpr int BS = kChunk;
+#ifndef GDN2_SCAN_NSPLIT
+#define GDN2_SCAN_NSPLIT 2      // warps per TMEM lane quarter: 128 * NSPLIT threads per block
+#endif
 
 constexpr uint32_t kWqBytes = 2 * BS * D * 2;    // 32 KiB
 constexpr uint32_t kAqkBytes = BS * BS * 2;      //  8 KiB
@@ -53,15 +58,21 @@ enum : uint32_t {
   kWaitM3 = 0x400
 };
 
-__global__ void __launch_bounds__(128, 1)
+// NSPLIT warps share each 32-lane quarter of TMEM and split its columns (tokens / key channels)
+// between them, so the per-chunk register work is spread over 128 * NSPLIT threads.
+template <int NSPLIT>
+__global__ void __launch_bounds__(128 * NSPLIT, 1)
 scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16* __restrict__ o,
                float* __restrict__ sT, float* __restrict__ hs, int S, int H, int64_t o_bs, uint32_t* status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   ScanTcSmem& s = *reinterpret_cast<ScanTcSmem*>(smem_raw);
+  constexpr int TOK = BS / NSPLIT;                      // tokens per thread in the Un / output passes
+  constexpr int KCH = D / NSPLIT;                       // key channels per thread in the state pass
   const int NC = S / BS;
   const int bh = blockIdx.x, ib = bh / H, ih = bh % H;
   const int tid = threadIdx.x, wid = tid >> 5;
-  const int dv = tid;                                   // this thread's value channel = TMEM lane
+  const int lq = wid & 3, part = wid >> 2;              // TMEM lane quarter, column share
+  const int dv = lq * 32 + (tid & 31);                  // this thread's value channel = TMEM lane
   const int64_t ch0 = (int64_t)bh * NC;
 
   const char* g_wq = P.wq + (size_t)ch0 * kWqBytes;
@@ -78,13 +89,14 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     tc::mbar_init_fence();
   }
   if (wid == 0) tc::tmem_alloc(&s.tmem_base, 256);
-  s.gl[0][tid] = g_gl[tid];
+  if (tid < D) s.gl[0][tid] = g_gl[tid];
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tm = s.tmem_base;
-  const uint32_t t_state = tc::tmem_addr(tm, wid * 32, 0);      // this warp's lanes, state columns
-  const uint32_t t_d1 = tc::tmem_addr(tm, wid * 32, 128);
+  const uint32_t t_state = tc::tmem_addr(tm, lq * 32, part * KCH);          // this thread's share of the state row
+  const uint32_t t_ws = tc::tmem_addr(tm, lq * 32, 128 + part * TOK);       // (W S)^T columns of its tokens
+  const uint32_t t_o = tc::tmem_addr(tm, lq * 32, 192 + part * TOK);        // O^T columns of its tokens
 
   if (tid == 0) {   // operands of chunk 0
     tc::mbar_expect_tx(&s.bar_wq, kWqBytes);   tc::bulk_g2s(s.wq, g_wq, kWqBytes, &s.bar_wq);
@@ -93,23 +105,24 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     tc::mbar_expect_tx(&s.bar_kgt, kKgtBytes); tc::bulk_g2s(s.kgt, g_kgt, kKgtBytes, &s.bar_kgt);
   }
 
-  // initial state: S^T row of this thread -> bf16 image, chunk_states[0], and gamma_0-scaled TMEM copy
+  // initial state: this thread's share of its S^T row -> bf16 image, chunk_states[0], gamma_0-scaled TMEM copy
   {
     float* h0 = hs ? hs + (((size_t)ib * NC + 0) * H + ih) * D * D : nullptr;
-    float x[32];
-    for (int c0 = 0; c0 < D; c0 += 32) {
+    float x[16];
+#pragma unroll 1
+    for (int c0 = part * KCH; c0 < (part + 1) * KCH; c0 += 16) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) x[i] = s0 ? s0[((size_t)bh * D + c0 + i) * D + dv] : 0.f;
+      for (int i = 0; i < 16; ++i) x[i] = s0 ? s0[((size_t)bh * D + c0 + i) * D + dv] : 0.f;
       if (h0) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) h0[(size_t)(c0 + i) * D + dv] = x[i];
+        for (int i = 0; i < 16; ++i) h0[(size_t)(c0 + i) * D + dv] = x[i];
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
+      for (int j = 0; j < 2; ++j)
         *reinterpret_cast<uint4*>(&s.sb[((c0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&x[j * 8]);
 #pragma unroll
-      for (int i = 0; i < 32; ++i) x[i] *= s.gl[0][c0 + i];
-      tc::tmem_st32(t_state + c0, x);
+      for (int i = 0; i < 16; ++i) x[i] *= s.gl[0][c0 + i];
+      tc::tmem_st16(tc::tmem_addr(tm, lq * 32, c0), x);
     }
     tc::tmem_st_wait();
   }
@@ -125,7 +138,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     if (s.abort_flag) break;
     const uint32_t ph = n & 1;
     const bool more = n + 1 < NC;
-    float gl_next = more ? g_gl[(size_t)(n + 1) * D + tid] : 1.f;   // early, independent global load
+    float gl_next = (more && tid < D) ? g_gl[(size_t)(n + 1) * D + tid] : 1.f;   // early, independent global load
 
     // ---- MMA1: D1 = S^T * [W ; Qg]^T
     if (tid == 0) {
@@ -145,24 +158,25 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
 
     // ---- Un^T = U^T - (W S)^T, written as tf32 (in place) and bf16 operand images
     tc::mbar_wait(&s.bar_ut, ph, &s.abort_flag, status, kWaitUt);
-    for (int half = 0; half < 2; ++half) {
-      float ws[32];
-      tc::tmem_ld32(t_d1 + half * 32, ws);
-      tc::tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int tc4 = half * 8 + j;                     // token quad index
-        float4* pu = reinterpret_cast<float4*>(&s.un32[(tc4 * D + dv) * 4]);
+    for (int t0 = 0; t0 < TOK; t0 += 16) {
+      float ws[16];
+      tc::tmem_ld16(t_ws + t0, ws);
+      tc::tmem_ld_wait();
+      const int tok0 = part * TOK + t0;                   // first of 16 tokens
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float4* pu = reinterpret_cast<float4*>(&s.un32[((tok0 / 4 + j) * D + dv) * 4]);
         float4 u = *pu;
         u.x -= ws[j * 4 + 0]; u.y -= ws[j * 4 + 1]; u.z -= ws[j * 4 + 2]; u.w -= ws[j * 4 + 3];
         *pu = make_float4(tf32_rn(u.x), tf32_rn(u.y), tf32_rn(u.z), tf32_rn(u.w));
         ws[j * 4 + 0] = u.x; ws[j * 4 + 1] = u.y; ws[j * 4 + 2] = u.z; ws[j * 4 + 3] = u.w;
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        *reinterpret_cast<uint4*>(&s.unb[((half * 4 + j) * D + dv) * 8]) = tc::pack8_bf16(&ws[j * 8]);
+      for (int j = 0; j < 2; ++j)
+        *reinterpret_cast<uint4*>(&s.unb[((tok0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&ws[j * 8]);
     }
-    s.gl[(n + 1) & 1][tid] = gl_next;
+    if (tid < D) s.gl[(n + 1) & 1][tid] = gl_next;
     tc::fence_async_smem();
     tc::tc_fence_before_sync();
     __syncthreads();
@@ -190,14 +204,15 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       tc::bulk_g2s(s.aqk, g_aqk + (size_t)(n + 1) * kAqkBytes, kAqkBytes, &s.bar_aqk);
     }
     {
-      __nv_bfloat16* orow = o + (((size_t)ib * o_bs + (size_t)n * BS) * H + ih) * D + dv;
-      for (int half = 0; half < 2; ++half) {
-        float ov[32];
-        tc::tmem_ld32(t_d1 + 64 + half * 32, ov);
+      __nv_bfloat16* orow = o + (((size_t)ib * o_bs + (size_t)n * BS + part * TOK) * H + ih) * D + dv;
+#pragma unroll
+      for (int t0 = 0; t0 < TOK; t0 += 16) {
+        float ov[16];
+        tc::tmem_ld16(t_o + t0, ov);
         tc::tmem_ld_wait();
         if (!s.abort_flag) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) orow[(size_t)(half * 32 + i) * H * D] = __float2bfloat16_rn(ov[i]);
+          for (int i = 0; i < 16; ++i) orow[(size_t)(t0 + i) * H * D] = __float2bfloat16_rn(ov[i]);
         }
       }
     }
@@ -215,26 +230,27 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
       float* fin = (!more && sT) ? sT + (size_t)bh * D * D : nullptr;
       const float* gln = s.gl[(n + 1) & 1];
-      float x[32];
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        tc::tmem_ld32(t_state + c0, x);
+#pragma unroll
+      for (int k0 = 0; k0 < KCH; k0 += 16) {
+        const int c0 = part * KCH + k0;
+        float x[16];
+        tc::tmem_ld16(t_state + k0, x);
         tc::tmem_ld_wait();
-        if (s.abort_flag) break;
         if (hn) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) hn[(size_t)(c0 + i) * D + dv] = x[i];
+          for (int i = 0; i < 16; ++i) hn[(size_t)(c0 + i) * D + dv] = x[i];
         }
         if (fin) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) fin[(size_t)(c0 + i) * D + dv] = x[i];
+          for (int i = 0; i < 16; ++i) fin[(size_t)(c0 + i) * D + dv] = x[i];
         }
         if (more) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
+          for (int j = 0; j < 2; ++j)
             *reinterpret_cast<uint4*>(&s.sb[((c0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&x[j * 8]);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) x[i] *= gln[c0 + i];
-          tc::tmem_st32(t_state + c0, x);
+          for (int i = 0; i < 16; ++i) x[i] *= gln[c0 + i];
+          tc::tmem_st16(t_state + k0, x);
         }
       }
       tc::tmem_st_wait();
@@ -255,9 +271,21 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
                    int B, int S, int H, int64_t o_bs, cudaStream_t st) {
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
   const size_t smem = sizeof(ScanTcSmem) + 128;
-  GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  scan_tc_kernel<<<B * H, 128, smem, st>>>(L, P, s0, static_cast<__nv_bfloat16*>(o), sT, hs, S, H, o_bs,
-                                           device_status_word());
+  // Tuning knob: warps per TMEM lane quarter (1, 2 or 4 -> 128, 256 or 512 threads per block).
+  static const int nsplit = [] {
+    const char* e = getenv("GDN2_B200_SCAN_NSPLIT");
+    const int v = e ? atoi(e) : GDN2_SCAN_NSPLIT;
+    return (v == 1 || v == 2 || v == 4) ? v : GDN2_SCAN_NSPLIT;
+  }();
+  auto launch = [&](auto kern, int threads) -> int {
+    GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<B * H, threads, smem, st>>>(L, P, s0, static_cast<__nv_bfloat16*>(o), sT, hs, S, H, o_bs,
+                                       device_status_word());
+    return GDN2_OK;
+  };
+  int rc = nsplit == 1 ? launch(scan_tc_kernel<1>, 128) : nsplit == 2 ? launch(scan_tc_kernel<2>, 256)
+                                                                       : launch(scan_tc_kernel<4>, 512);
+  if (rc != GDN2_OK) return rc;
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }
