@@ -53,6 +53,13 @@ struct ScanTcSmem {
   int abort_flag;
 };
 
+#ifdef GDN2_SCAN_TIMING
+__device__ unsigned long long g_scan_timing[16];
+#define TICK(i) do { if (tid == 0 && blockIdx.x == 0) { long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; } } while (0)
+#else
+#define TICK(i) do {} while (0)
+#endif
+
 enum : uint32_t {
   kWaitWq = 0x10, kWaitUt = 0x20, kWaitAqk = 0x40, kWaitKgt = 0x80, kWaitM1 = 0x100, kWaitM2 = 0x200,
   kWaitM3 = 0x400
@@ -134,9 +141,13 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
   constexpr uint32_t idesc_m2 = tc::instr_desc(1, 128, 64);
   constexpr uint32_t idesc_m3 = tc::instr_desc(2, 128, 128);
 
+#ifdef GDN2_SCAN_TIMING
+  long long tacc[16] = {0}; long long tprev = clock64();
+#endif
   for (int n = 0; n < NC; ++n) {
     if (s.abort_flag) break;
     const uint32_t ph = n & 1;
+    TICK(0);
     const bool more = n + 1 < NC;
     float gl_next = (more && tid < D) ? g_gl[(size_t)(n + 1) * D + tid] : 1.f;   // early, independent global load
 
@@ -149,8 +160,10 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         tc::mma_commit(&s.bar_m1);
       }
     }
+    TICK(1);
     tc::mbar_wait(&s.bar_m1, ph, &s.abort_flag, status, kWaitM1);
     tc::tc_fence_after_sync();
+    TICK(2);
     if (tid == 0 && more && !s.abort_flag) {
       tc::mbar_expect_tx(&s.bar_wq, kWqBytes);
       tc::bulk_g2s(s.wq, g_wq + (size_t)(n + 1) * kWqBytes, kWqBytes, &s.bar_wq);
@@ -158,6 +171,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
 
     // ---- Un^T = U^T - (W S)^T, written as tf32 (in place) and bf16 operand images
     tc::mbar_wait(&s.bar_ut, ph, &s.abort_flag, status, kWaitUt);
+    TICK(3);
 #pragma unroll
     for (int t0 = 0; t0 < TOK; t0 += 16) {
       float ws[16];
@@ -177,9 +191,11 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         *reinterpret_cast<uint4*>(&s.unb[((tok0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&ws[j * 8]);
     }
     if (tid < D) s.gl[(n + 1) & 1][tid] = gl_next;
+    TICK(4);
     tc::fence_async_smem();
     tc::tc_fence_before_sync();
     __syncthreads();
+    TICK(5);
 
     // ---- MMA2: D1[:, 64:128] += Un^T * Aqk^T ; MMA3: ST += Un^T * KG
     if (tid == 0 && !s.abort_flag) {
@@ -197,8 +213,10 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     }
 
     // ---- output rows of this chunk
+    TICK(6);
     tc::mbar_wait(&s.bar_m2, ph, &s.abort_flag, status, kWaitM2);
     tc::tc_fence_after_sync();
+    TICK(7);
     if (tid == 0 && more && !s.abort_flag) {
       tc::mbar_expect_tx(&s.bar_aqk, kAqkBytes);
       tc::bulk_g2s(s.aqk, g_aqk + (size_t)(n + 1) * kAqkBytes, kAqkBytes, &s.bar_aqk);
@@ -218,8 +236,10 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     }
 
     // ---- new state: bf16 operand copy, optional snapshot, pre-scale for the next chunk
+    TICK(8);
     tc::mbar_wait(&s.bar_m3, ph, &s.abort_flag, status, kWaitM3);
     tc::tc_fence_after_sync();
+    TICK(9);
     if (tid == 0 && more && !s.abort_flag) {
       tc::mbar_expect_tx(&s.bar_kgt, kKgtBytes);
       tc::bulk_g2s(s.kgt, g_kgt + (size_t)(n + 1) * kKgtBytes, kKgtBytes, &s.bar_kgt);
@@ -255,10 +275,15 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       }
       tc::tmem_st_wait();
     }
+    TICK(10);
     tc::fence_async_smem();
     tc::tc_fence_before_sync();
     __syncthreads();
+    TICK(11);
   }
+#ifdef GDN2_SCAN_TIMING
+  if (tid == 0 && blockIdx.x == 0) for (int i = 0; i < 16; ++i) g_scan_timing[i] = tacc[i];
+#endif
 
   tc::tc_fence_before_sync();
   __syncthreads();
@@ -289,5 +314,11 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }
+
+#ifdef GDN2_SCAN_TIMING
+extern "C" int gdn2_debug_scan_timing(unsigned long long* out16) {
+  return cudaMemcpyFromSymbol(out16, g_scan_timing, sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : -6;
+}
+#endif
 
 }  // namespace gdn2
