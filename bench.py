@@ -294,7 +294,7 @@ def main():
     ms_prep = time_events(prep, args.steps, 3, barrier)
     ms_scan = time_events(scan, args.steps, 3, barrier)
     th = B * n_full * Hl                                   # token-heads per launch on this rank
-    ws_per_th = (2 * DK * 2 + 64 * 2 + DK * 4 + DV * 4) + DK * 4 / 64.0   # WQ + AQK + KG^T + U^T + gamma_last
+    ws_per_th = (2 * DK * 2 + 64 * 2 + DK * 2 + DV * 2) + DK * 4 / 64.0   # WQ + AQK + KG^T + U^T (fp16) + gamma_last
     in_per_th = 3 * DK * 2 + 2 * DV * 2 + DK * 4                          # q,k,b + v,w (bf16) + g (fp32)
     stages = {
         "chunk_prep": (ms_prep, th * (in_per_th + ws_per_th)),

@@ -13,6 +13,7 @@ namespace gdn2 {
 
 constexpr int kChunk = 64;                       // tokens per chunk (BS)
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kValScale = 256.f;               // tensor-core family: KGT = 256*KG, UT = U/256 (fp16)
 
 // ---------------------------------------------------------------- element conversion
 
@@ -46,16 +47,19 @@ __device__ __forceinline__ float tf32_rn(float x) {
 //
 //   WQ   rows 0..63 = W (per token), rows 64..127 = Qg = scale*q*gamma (per token); K = DK; type TW
 //   AQK  rows = query token r, K = key token s; lower triangular incl. diagonal;      type TW
-//   KGT  rows = key channel, K = token: k * gamma_C / gamma_t;                         fp32
-//   UT   rows = value channel, K = token: U;                                           fp32
+//   KGT  rows = key channel, K = token: k * gamma_C / gamma_t;                         type TV
+//   UT   rows = value channel, K = token: U;                                           type TV
 //   GL   gamma at the chunk's last token, [DK];                                        fp32
 //
-// TW is bf16 on the tcgen05 path and fp32 on the SIMT path.
+// SIMT family: TW = TV = fp32. Tensor-core family: TW = bf16 and TV = fp16 with a fixed power-of-two
+// scale (KGT holds 256 * KG, UT holds U / 256): fp16 carries the same 11 significant bits as the tf32
+// the value path needs (bf16's 8 are not enough), the scale keeps |U| up to 1.6e7 finite while
+// everything above 0.016 stays a normal number, and the product (Un/256) * (256 KG) is exact.
 
 struct WsLayout {
   int64_t nch;        // number of chunk-heads
   int DK, DV;
-  int esz;            // bytes per TW element (2 or 4)
+  int esz;            // bytes per TW element (2 or 4); TV has the same size
   size_t wq_bytes, aqk_bytes, kgt_bytes, ut_bytes, gl_bytes;   // per chunk-head
   size_t off_wq, off_aqk, off_kgt, off_ut, off_gl, off_flags, total;
 };
@@ -68,8 +72,8 @@ __host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK,
   L.DK = DK; L.DV = DV; L.esz = esz;
   L.wq_bytes = (size_t)2 * kChunk * DK * esz;
   L.aqk_bytes = (size_t)kChunk * kChunk * esz;
-  L.kgt_bytes = (size_t)DK * kChunk * 4;
-  L.ut_bytes = (size_t)DV * kChunk * 4;
+  L.kgt_bytes = (size_t)DK * kChunk * esz;
+  L.ut_bytes = (size_t)DV * kChunk * esz;
   L.gl_bytes = (size_t)DK * 4;
   size_t off = 0;
   L.off_wq = off;   off = align_up(off + L.wq_bytes * L.nch, 1024);
@@ -88,15 +92,33 @@ template <int E> __host__ __device__ __forceinline__ int kc_index(int row, int k
 }
 
 struct WsPtrs {
-  char* wq; char* aqk; float* kgt; float* ut; float* gl; int* flags;
+  char* wq; char* aqk; char* kgt; char* ut; float* gl; int* flags;
 };
 
 __host__ inline WsPtrs ws_pointers(void* base, const WsLayout& L) {
   char* p = static_cast<char*>(base);
-  return WsPtrs{p + L.off_wq, p + L.off_aqk, reinterpret_cast<float*>(p + L.off_kgt),
-                reinterpret_cast<float*>(p + L.off_ut), reinterpret_cast<float*>(p + L.off_gl),
+  return WsPtrs{p + L.off_wq, p + L.off_aqk, p + L.off_kgt, p + L.off_ut, reinterpret_cast<float*>(p + L.off_gl),
                 reinterpret_cast<int*>(p + L.off_flags)};
 }
+
+// Per-family element types of the workspace: TW for WQ/AQK, TV (+ scales) for KGT/UT.
+template <typename TW> struct WsTraits;
+template <> struct WsTraits<float> {
+  using TV = float;
+  static constexpr int E = 4;                       // elements per 16 bytes (both TW and TV)
+  static __device__ __forceinline__ float kg_store(float x) { return x; }
+  static __device__ __forceinline__ float u_store(float x) { return x; }
+  static __device__ __forceinline__ float kg_load(float x) { return x; }
+  static __device__ __forceinline__ float u_load(float x) { return x; }
+};
+template <> struct WsTraits<__nv_bfloat16> {
+  using TV = __half;
+  static constexpr int E = 8;
+  static __device__ __forceinline__ __half kg_store(float x) { return __float2half_rn(x * kValScale); }
+  static __device__ __forceinline__ __half u_store(float x) { return __float2half_rn(x * (1.f / kValScale)); }
+  static __device__ __forceinline__ float kg_load(__half x) { return __half2float(x) * (1.f / kValScale); }
+  static __device__ __forceinline__ float u_load(__half x) { return __half2float(x) * kValScale; }
+};
 
 // ---------------------------------------------------------------- host-side error plumbing
 

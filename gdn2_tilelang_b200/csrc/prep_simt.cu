@@ -19,9 +19,6 @@ namespace gdn2 {
 
 namespace {
 
-template <typename TW> struct Epc;                     // elements per 16-byte chunk
-template <> struct Epc<float> { static constexpr int v = 4; };
-template <> struct Epc<__nv_bfloat16> { static constexpr int v = 8; };
 
 template <typename TIn, typename TW>
 __global__ void __launch_bounds__(256)
@@ -29,7 +26,9 @@ prep_simt_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn
                  const float* __restrict__ g, const TIn* __restrict__ b, const TIn* __restrict__ w,
                  WsLayout L, WsPtrs P, int S, int H, int64_t in_bs, float scale, int only_flagged) {
   constexpr int BS = kChunk;
-  constexpr int E = Epc<TW>::v;
+  using WT = WsTraits<TW>;
+  using TV = typename WT::TV;
+  constexpr int E = WT::E;
   const int DK = L.DK, DV = L.DV;
   const int NC = S / BS;
   const int n = blockIdx.x, bh = blockIdx.y;
@@ -103,8 +102,8 @@ prep_simt_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn
   // outputs that need only G, q, k: Aqk image, Qg rows, KG^T image, gamma_last; E in place
   TW* wq = reinterpret_cast<TW*>(P.wq + (size_t)ch * L.wq_bytes);
   TW* aqk = reinterpret_cast<TW*>(P.aqk + (size_t)ch * L.aqk_bytes);
-  float* kgt = P.kgt + (size_t)ch * (L.kgt_bytes / 4);
-  float* ut = P.ut + (size_t)ch * (L.ut_bytes / 4);
+  TV* kgt = reinterpret_cast<TV*>(P.kgt + (size_t)ch * L.kgt_bytes);
+  TV* ut = reinterpret_cast<TV*>(P.ut + (size_t)ch * L.ut_bytes);
   float* gl = P.gl + (size_t)ch * DK;
   for (int idx = tid; idx < BS * BS; idx += 256) {
     const int r = idx / BS, s = idx % BS;
@@ -115,8 +114,7 @@ prep_simt_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn
     const float G = Gs[idx];
     const float gam = exp2f(G);
     wq[kc_index<E>(BS + t, c, 2 * BS)] = from_f32<TW>(scale * qs[idx] * gam);
-    const float kg = ks[idx] * exp2f(Gs[(BS - 1) * DK + c] - G);
-    kgt[kc_index<4>(c, t, DK)] = (sizeof(TW) == 2) ? tf32_rn(kg) : kg;   // bf16 workspace = tensor-core consumer
+    kgt[kc_index<E>(c, t, DK)] = WT::kg_store(ks[idx] * exp2f(Gs[(BS - 1) * DK + c] - G));
     es[idx] *= gam;
   }
   if (tid < DK) gl[tid] = exp2f(Gs[(BS - 1) * DK + tid]);
@@ -143,7 +141,7 @@ prep_simt_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn
       const int r = idx / cw, c = idx % cw;
       float acc = 0.f;
       for (int s = 0; s <= r; ++s) acc = fmaf(Ai[r * BS + s], qs[s * DK + c], acc);
-      ut[kc_index<4>(c0 + c, r, DV)] = acc;
+      ut[kc_index<E>(c0 + c, r, DV)] = WT::u_store(acc);
     }
   }
 }

@@ -21,7 +21,7 @@
 //     rows), one shuffle per row, Tm read as broadcast 128-bit shared loads.
 //  4. MMA2 (tf32, transposed so channels are M): W^T = E^T * Ai^T, U^T = (w*v)^T * Ai^T.
 //  5. Outputs in the scan's operand layout (common.cuh): WQ via shared staging + bulk stores, AQK,
-//     KG^T, U^T, gamma_last with 128-bit coalesced global stores.
+//     KG^T and U^T (scaled fp16), gamma_last with 128-bit coalesced global stores.
 //
 // Shared memory is two regions reused over the block's life so that two blocks fit on an SM:
 //   X (72.5 KiB): MMA1 operands, then Tm + Ai + (w*v)^T;   Y (32.25 KiB): E^T, then the WQ staging.
@@ -126,7 +126,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     const __nv_bfloat16* bp = b + row0 * D + c;
     const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
     const int cb = (c >> 3) * B_PAD * 8 + (c & 7);
-    float* kgt_g = P.kgt + (size_t)ch * (D * BS) + c * 4;
+    char* kgt_g = P.kgt + (size_t)ch * (D * BS * 2) + c * 16;   // fp16 image [tok/8][128 dk][8]
     float run = 0.f;
 #pragma unroll 1
     for (int j = 0; j < 4; ++j) {
@@ -144,7 +144,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       const float kg_c = (j < 3) ? exp2f(g_last - refn) : 1.f;
       const float cc_a = exp2f(pick4(j, ref2, ref3, 0.f, 0.f) - refn);   // B_{j+2} / B_{j+1}
       const float cc_b = exp2f(ref3 - refn);                               // B_{j+3} / B_{j+1} (j = 0 only)
-      uint32_t qgp[8];
+      uint32_t qgp[8], kgp[8];
 #pragma unroll
       for (int t4 = 0; t4 < 4; ++t4) {
         float e4[4], kg4[4], qg4[4];
@@ -168,16 +168,20 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
           const float gam = a * gam_ref;
           e4[u] = tf32_rn(e * gam);
           qg4[u] = scale * qf * gam;
-          kg4[u] = tf32_rn(kn * kg_c);
+          kg4[u] = kn * kg_c * kValScale;
         }
         const int tq = 4 * j + t4;                              // token quad index
         *reinterpret_cast<float4*>(&s.y.et[(tq * D + c) * 4]) = make_float4(e4[0], e4[1], e4[2], e4[3]);
-        *reinterpret_cast<float4*>(kgt_g + (size_t)tq * D * 4) = make_float4(kg4[0], kg4[1], kg4[2], kg4[3]);
+        __half2 h01 = __floats2half2_rn(kg4[0], kg4[1]), h23 = __floats2half2_rn(kg4[2], kg4[3]);
+        kgp[2 * t4] = *reinterpret_cast<uint32_t*>(&h01);
+        kgp[2 * t4 + 1] = *reinterpret_cast<uint32_t*>(&h23);
         __nv_bfloat162 p01 = __floats2bfloat162_rn(qg4[0], qg4[1]), p23 = __floats2bfloat162_rn(qg4[2], qg4[3]);
         qgp[2 * t4] = *reinterpret_cast<uint32_t*>(&p01);
         qgp[2 * t4 + 1] = *reinterpret_cast<uint32_t*>(&p23);
       }
       tc::tmem_st8(tc::tmem_addr(tm, wid * 32, kQgCol + 8 * j), qgp);
+      *reinterpret_cast<uint4*>(kgt_g + (size_t)(2 * j) * D * 16) = make_uint4(kgp[0], kgp[1], kgp[2], kgp[3]);
+      *reinterpret_cast<uint4*>(kgt_g + (size_t)(2 * j + 1) * D * 16) = make_uint4(kgp[4], kgp[5], kgp[6], kgp[7]);
     }
     tc::tmem_st_wait();
     P.gl[(size_t)ch * D + c] = exp2f(g_last);
@@ -310,7 +314,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   // ---- 5. W and Qg rows into the WQ staging image (E^T is dead now), U^T straight to global
   {
     const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
-    float* ut_g = P.ut + (size_t)ch * (D * BS) + c * 4;
+    char* ut_g = P.ut + (size_t)ch * (D * BS * 2) + c * 16;       // fp16 image [tok/8][128 dv][8]
     float val[32];
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -332,9 +336,16 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       tc::tmem_ld32(tc::tmem_addr(tm, wid * 32, 64 + half * 32), val);
       tc::tmem_ld_wait();
 #pragma unroll
-      for (int i4 = 0; i4 < 8; ++i4)
-        *reinterpret_cast<float4*>(ut_g + (size_t)(half * 8 + i4) * D * 4) =
-            make_float4(val[4 * i4], val[4 * i4 + 1], val[4 * i4 + 2], val[4 * i4 + 3]);
+      for (int i8 = 0; i8 < 4; ++i8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          __half2 h = __floats2half2_rn(val[8 * i8 + 2 * x] * (1.f / kValScale),
+                                        val[8 * i8 + 2 * x + 1] * (1.f / kValScale));
+          pk[x] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(ut_g + (size_t)(half * 4 + i8) * D * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
     }
   }
   tc::fence_async_smem();

@@ -17,9 +17,6 @@ namespace {
 
 constexpr int NV = 32;   // value columns per block
 
-template <typename TW> struct Epc;
-template <> struct Epc<float> { static constexpr int v = 4; };
-template <> struct Epc<__nv_bfloat16> { static constexpr int v = 8; };
 
 struct ScanSmem {
   float *Ws, *Qs, *As, *Ks, *Us, *Un, *St, *gl;
@@ -41,23 +38,25 @@ struct ScanSmem {
 template <typename TW>
 __device__ __forceinline__ void load_chunk_operands(const WsLayout& L, const WsPtrs& P, int64_t ch, int lo,
                                                     ScanSmem& s, bool want_kg) {
-  constexpr int E = Epc<TW>::v;
+  using WT = WsTraits<TW>;
+  using TV = typename WT::TV;
+  constexpr int E = WT::E;
   const int DK = L.DK, DV = L.DV, tid = threadIdx.x;
   const TW* wq = reinterpret_cast<const TW*>(P.wq + (size_t)ch * L.wq_bytes);
   const TW* aqk = reinterpret_cast<const TW*>(P.aqk + (size_t)ch * L.aqk_bytes);
-  const float* kgt = P.kgt + (size_t)ch * (L.kgt_bytes / 4);
-  const float* ut = P.ut + (size_t)ch * (L.ut_bytes / 4);
+  const TV* kgt = reinterpret_cast<const TV*>(P.kgt + (size_t)ch * L.kgt_bytes);
+  const TV* ut = reinterpret_cast<const TV*>(P.ut + (size_t)ch * L.ut_bytes);
   for (int idx = tid; idx < kChunk * DK; idx += 256) {
     const int t = idx / DK, c = idx % DK;
     s.Ws[idx] = to_f32(wq[kc_index<E>(t, c, 2 * kChunk)]);
     s.Qs[idx] = to_f32(wq[kc_index<E>(kChunk + t, c, 2 * kChunk)]);
-    if (want_kg) s.Ks[idx] = kgt[kc_index<4>(c, t, DK)];
+    if (want_kg) s.Ks[idx] = WT::kg_load(kgt[kc_index<E>(c, t, DK)]);
   }
   for (int idx = tid; idx < kChunk * kChunk; idx += 256)
     s.As[idx] = to_f32(aqk[kc_index<E>(idx / kChunk, idx % kChunk, kChunk)]);
   for (int idx = tid; idx < kChunk * NV; idx += 256) {
     const int t = idx / NV, c = lo + idx % NV;
-    s.Us[idx] = c < DV ? ut[kc_index<4>(c, t, DV)] : 0.f;
+    s.Us[idx] = c < DV ? WT::u_load(ut[kc_index<E>(c, t, DV)]) : 0.f;
   }
   if (want_kg && tid < DK) s.gl[tid] = P.gl[(size_t)ch * DK + tid];
 }

@@ -1,26 +1,32 @@
 // Sequential state scan fused with the output, tensor-core (tcgen05 / TMEM / TMA) family, for
-// DK = DV = 128, bf16 outputs, fp32 state. One 128-thread block per (batch, head), sequential
-// over chunks; the state never leaves the SM between chunks.
+// DK = DV = 128, bf16 outputs, fp32 state. One block per (batch, head), sequential over chunks; the
+// state never leaves the SM between chunks.
 //
 // The algebra of the reference's prefill_scan_kernel (gdn2/inference.py:446-475 of the reference
 // project) is evaluated TRANSPOSED so that every product has the 128 value channels as the MMA M
 // dimension (= TMEM lane = thread), tokens or key channels as N:
 //
-//   MMA1  D1[dv, 0:64]   = S^T[dv,dk] * W[tok,dk]^T          (W S)^T        bf16 operands
-//         D1[dv, 64:128] = S^T[dv,dk] * Qg[tok,dk]^T         (Qg S)^T       (one N = 128 product)
-//   regs  Un^T[dv,tok]   = U^T - D1[:, 0:64]
-//   MMA2  D1[dv, 64:128] += Un^T[dv,s] * Aqk[r,s]^T          (tril(Aqk) Un)^T   bf16 operands
-//   MMA3  ST[dv,dk]      += Un^T[dv,tok] * KG^T[dk,tok]^T    (KG^T Un)^T    tf32 operands
-//   regs  ST             <- gamma_C(next chunk)[dk] * ST after the bf16 copy of S^T is taken
+//   MMA1w  WS[dv, tok]  = S^T[dv,dk] * W[tok,dk]^T            (W S)^T          bf16
+//   MMA1q  O [dv, tok]  = S^T[dv,dk] * Qg[tok,dk]^T           (Qg S)^T         bf16
+//   regs   Un^T[dv,tok] = U^T - WS
+//   MMA3   ST[dv,dk]   += Un^T[dv,tok] * KG^T[dk,tok]^T       (KG^T Un)^T      fp16 (scaled, see common.cuh)
+//   MMA2   O [dv, r]   += Un^T[dv,s] * Aqk[r,s]^T             (tril(Aqk) Un)^T bf16
+//   regs   ST          <- gamma_C(next chunk)[dk] * ST after the bf16 copy of S^T is taken
 //
-// The value path (U, Un, KG) stays in fp32 storage / tf32 operands because rounding any of them to
-// bf16 alone costs about 1.7e-3 relative error in the final state; the erase path (W, S as an
-// operand, Aqk, Qg) is bf16. TMEM: columns [0,128) hold the fp32 state S^T, [128,256) hold D1.
+// Only MMA1w, the Un pass, MMA3 and the state pass are on the recurrence's critical path; the
+// kernel is organised around that:
+//   * warp 8 (one thread) issues every MMA and every bulk copy. It orders MMA1w before MMA1q and
+//     MMA3 before MMA2, so the critical products never queue behind the output products.
+//   * warps 0-7 (256 threads; two warps share each 32-lane quarter of TMEM and split its columns)
+//     do the register passes. The output pass of chunk n-1 (TMEM -> bf16 -> shared staging ->
+//     one 256-byte bulk store per token row) runs while MMA3 / MMA2 of chunk n execute; the O
+//     accumulator is double buffered in TMEM for that.
+//   * operands arrive as whole workspace records with one bulk copy each; WQ, KG^T and U^T are
+//     double buffered so that a copy is always issued a full chunk ahead of its use.
+//   * hand-offs are mbarriers (arrive / wait), every wait is bounded (tc_utils.cuh).
 //
-// Operands arrive as whole records of the workspace (see common.cuh) with one bulk copy each into
-// a single shared-memory buffer per operand; a buffer is refilled for the next chunk as soon as
-// the MMA that reads it has completed, so the copies overlap the rest of the chunk's chain.
-#include <cstdlib>
+// TMEM columns: [0,128) fp32 state S^T; [128,192) WS; [192,256) and [256,320) the two O accumulators.
+#include <cuda_fp16.h>
 
 #include "common.cuh"
 #include "tc_utils.cuh"
@@ -31,263 +37,291 @@ namespace {
 
 constexpr int D = 128;
 constexpr int BS = kChunk;
-#ifndef GDN2_SCAN_NSPLIT
-#define GDN2_SCAN_NSPLIT 2      // warps per TMEM lane quarter: 128 * NSPLIT threads per block
-#endif
+constexpr int kComputeThreads = 256;
+constexpr int kThreads = kComputeThreads + 32;
 
 constexpr uint32_t kWqBytes = 2 * BS * D * 2;    // 32 KiB
 constexpr uint32_t kAqkBytes = BS * BS * 2;      //  8 KiB
-constexpr uint32_t kKgtBytes = D * BS * 4;       // 32 KiB
-constexpr uint32_t kUtBytes = D * BS * 4;        // 32 KiB
+constexpr uint32_t kKgtBytes = D * BS * 2;       // 16 KiB (fp16)
+constexpr uint32_t kUtBytes = D * BS * 2;        // 16 KiB (fp16)
+constexpr uint32_t kColWs = 128, kColO = 192;
 
 struct ScanTcSmem {
-  __nv_bfloat16 wq[2 * BS * D];      // B of MMA1: [dk/8][128 rows: W tok 0..63, Qg tok 0..63][8]
+  __nv_bfloat16 wq[2][2 * BS * D];   // B of MMA1w/q: [dk/8][128 rows: W tok 0..63, Qg tok 0..63][8]
   __nv_bfloat16 aqk[BS * BS];        // B of MMA2: [s/8][64 r][8]
-  float kgt[D * BS];                 // B of MMA3: [tok/4][128 dk][4]
-  float un32[D * BS];                // U^T on arrival, Un^T in place: A of MMA3: [tok/4][128 dv][4]
+  __half kgt[2][D * BS];             // B of MMA3: [tok/8][128 dk][8], 256 * KG
+  __half ut[2][D * BS];              // U^T / 256: [tok/8][128 dv][8]
   __nv_bfloat16 sb[D * D];           // A of MMA1: S^T in bf16: [dk/8][128 dv][8]
+  __half un16[D * BS];               // A of MMA3: Un^T / 256: [tok/8][128 dv][8]
   __nv_bfloat16 unb[D * BS];         // A of MMA2: Un^T in bf16: [tok/8][128 dv][8]
+  __nv_bfloat16 ostage[BS * D];      // output rows [tok][dv] on their way to global memory
   float gl[2][D];                    // gamma at the last token of chunk n (slot n & 1)
-  uint64_t bar_wq, bar_aqk, bar_kgt, bar_ut, bar_m1, bar_m2, bar_m3;
+  uint64_t bar_wq[2], bar_kgt[2], bar_ut[2], bar_aqk;   // bulk-copy arrival
+  uint64_t bar_m1, bar_m3, bar_m2[2];                   // MMA completion
+  uint64_t bar_sb, bar_un;                              // compute threads -> issuer (256 arrivals)
   uint32_t tmem_base;
   int abort_flag;
 };
 
-#ifdef GDN2_SCAN_TIMING
-__device__ unsigned long long g_scan_timing[16];
-#define TICK(i) do { if (tid == 0 && blockIdx.x == 0) { long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; } } while (0)
-#else
-#define TICK(i) do {} while (0)
-#endif
-
 enum : uint32_t {
   kWaitWq = 0x10, kWaitUt = 0x20, kWaitAqk = 0x40, kWaitKgt = 0x80, kWaitM1 = 0x100, kWaitM2 = 0x200,
-  kWaitM3 = 0x400
+  kWaitM3 = 0x400, kWaitSb = 0x800, kWaitUn = 0x4000
 };
 
-// NSPLIT warps share each 32-lane quarter of TMEM and split its columns (tokens / key channels)
-// between them, so the per-chunk register work is spread over 128 * NSPLIT threads.
-template <int NSPLIT>
-__global__ void __launch_bounds__(128 * NSPLIT, 1)
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc::smem_u32(bar)) : "memory");
+}
+// barrier among the 256 compute threads only (hardware barrier 1)
+__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+__device__ __forceinline__ uint4 pack8_f16(const float* x) {
+  uint4 r;
+  __half2 t;
+  t = __floats2half2_rn(x[0], x[1]); r.x = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(x[2], x[3]); r.y = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(x[4], x[5]); r.z = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(x[6], x[7]); r.w = *reinterpret_cast<uint32_t*>(&t);
+  return r;
+}
+__device__ __forceinline__ void unpack8_f16(const uint4& p, float* x) {
+  float2 f;
+  f = __half22float2(*reinterpret_cast<const __half2*>(&p.x)); x[0] = f.x; x[1] = f.y;
+  f = __half22float2(*reinterpret_cast<const __half2*>(&p.y)); x[2] = f.x; x[3] = f.y;
+  f = __half22float2(*reinterpret_cast<const __half2*>(&p.z)); x[4] = f.x; x[5] = f.y;
+  f = __half22float2(*reinterpret_cast<const __half2*>(&p.w)); x[6] = f.x; x[7] = f.y;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
 scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16* __restrict__ o,
                float* __restrict__ sT, float* __restrict__ hs, int S, int H, int64_t o_bs, uint32_t* status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   ScanTcSmem& s = *reinterpret_cast<ScanTcSmem*>(smem_raw);
-  constexpr int TOK = BS / NSPLIT;                      // tokens per thread in the Un / output passes
-  constexpr int KCH = D / NSPLIT;                       // key channels per thread in the state pass
   const int NC = S / BS;
   const int bh = blockIdx.x, ib = bh / H, ih = bh % H;
-  const int tid = threadIdx.x, wid = tid >> 5;
-  const int lq = wid & 3, part = wid >> 2;              // TMEM lane quarter, column share
-  const int dv = lq * 32 + (tid & 31);                  // this thread's value channel = TMEM lane
+  const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
   const int64_t ch0 = (int64_t)bh * NC;
 
   const char* g_wq = P.wq + (size_t)ch0 * kWqBytes;
   const char* g_aqk = P.aqk + (size_t)ch0 * kAqkBytes;
-  const char* g_kgt = reinterpret_cast<const char*>(P.kgt) + (size_t)ch0 * kKgtBytes;
-  const char* g_ut = reinterpret_cast<const char*>(P.ut) + (size_t)ch0 * kUtBytes;
+  const char* g_kgt = P.kgt + (size_t)ch0 * kKgtBytes;
+  const char* g_ut = P.ut + (size_t)ch0 * kUtBytes;
   const float* g_gl = P.gl + (size_t)ch0 * D;
 
   if (tid == 0) {
-    tc::mbar_init(&s.bar_wq, 1); tc::mbar_init(&s.bar_aqk, 1); tc::mbar_init(&s.bar_kgt, 1);
-    tc::mbar_init(&s.bar_ut, 1); tc::mbar_init(&s.bar_m1, 1); tc::mbar_init(&s.bar_m2, 1);
-    tc::mbar_init(&s.bar_m3, 1);
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&s.bar_wq[i], 1); tc::mbar_init(&s.bar_kgt[i], 1); tc::mbar_init(&s.bar_ut[i], 1);
+      tc::mbar_init(&s.bar_m2[i], 1);
+    }
+    tc::mbar_init(&s.bar_aqk, 1); tc::mbar_init(&s.bar_m1, 1); tc::mbar_init(&s.bar_m3, 1);
+    tc::mbar_init(&s.bar_sb, kComputeThreads); tc::mbar_init(&s.bar_un, kComputeThreads);
     s.abort_flag = 0;
     tc::mbar_init_fence();
   }
-  if (wid == 0) tc::tmem_alloc(&s.tmem_base, 256);
+  if (wid == 0) tc::tmem_alloc(&s.tmem_base, 512);
   if (tid < D) s.gl[0][tid] = g_gl[tid];
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
   const uint32_t tm = s.tmem_base;
-  const uint32_t t_state = tc::tmem_addr(tm, lq * 32, part * KCH);          // this thread's share of the state row
-  const uint32_t t_ws = tc::tmem_addr(tm, lq * 32, 128 + part * TOK);       // (W S)^T columns of its tokens
-  const uint32_t t_o = tc::tmem_addr(tm, lq * 32, 192 + part * TOK);        // O^T columns of its tokens
 
-  if (tid == 0) {   // operands of chunk 0
-    tc::mbar_expect_tx(&s.bar_wq, kWqBytes);   tc::bulk_g2s(s.wq, g_wq, kWqBytes, &s.bar_wq);
-    tc::mbar_expect_tx(&s.bar_ut, kUtBytes);   tc::bulk_g2s(s.un32, g_ut, kUtBytes, &s.bar_ut);
-    tc::mbar_expect_tx(&s.bar_aqk, kAqkBytes); tc::bulk_g2s(s.aqk, g_aqk, kAqkBytes, &s.bar_aqk);
-    tc::mbar_expect_tx(&s.bar_kgt, kKgtBytes); tc::bulk_g2s(s.kgt, g_kgt, kKgtBytes, &s.bar_kgt);
-  }
+  if (wid == 8) {
+    // =============================== issuer: MMAs and bulk copies ===============================
+    if (lane == 0) {
+      constexpr uint32_t idesc_n64 = tc::instr_desc(1, 128, 64);     // bf16 operands, N = 64
+      constexpr uint32_t idesc_f16 = tc::instr_desc(0, 128, 128);    // fp16 operands, N = 128
+      auto load_wq = [&](int n) {
+        tc::mbar_expect_tx(&s.bar_wq[n & 1], kWqBytes);
+        tc::bulk_g2s(s.wq[n & 1], g_wq + (size_t)n * kWqBytes, kWqBytes, &s.bar_wq[n & 1]);
+      };
+      auto load_kgt = [&](int n) {
+        tc::mbar_expect_tx(&s.bar_kgt[n & 1], kKgtBytes);
+        tc::bulk_g2s(s.kgt[n & 1], g_kgt + (size_t)n * kKgtBytes, kKgtBytes, &s.bar_kgt[n & 1]);
+      };
+      auto load_ut = [&](int n) {
+        tc::mbar_expect_tx(&s.bar_ut[n & 1], kUtBytes);
+        tc::bulk_g2s(s.ut[n & 1], g_ut + (size_t)n * kUtBytes, kUtBytes, &s.bar_ut[n & 1]);
+      };
+      auto load_aqk = [&](int n) {
+        tc::mbar_expect_tx(&s.bar_aqk, kAqkBytes);
+        tc::bulk_g2s(s.aqk, g_aqk + (size_t)n * kAqkBytes, kAqkBytes, &s.bar_aqk);
+      };
+      load_wq(0); load_ut(0); load_kgt(0); load_aqk(0);
+      if (NC > 1) { load_wq(1); load_ut(1); load_kgt(1); }
+      const uint32_t a_sb = tc::smem_u32(s.sb), a_un16 = tc::smem_u32(s.un16), a_unb = tc::smem_u32(s.unb);
+      const uint32_t a_aqk = tc::smem_u32(s.aqk);
+      for (int n = 0; n < NC; ++n) {
+        const int b = n & 1;
+        const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
+        const uint32_t a_wq = tc::smem_u32(s.wq[b]);
+        // S^T (bf16) of chunk n is in place and O accumulator b has been read out
+        bool ok = tc::mbar_wait(&s.bar_sb, ph, &s.abort_flag, status, kWaitSb);
+        ok = ok && tc::mbar_wait(&s.bar_wq[b], ph2, &s.abort_flag, status, kWaitWq);
+        if (ok) {
+          tc::tc_fence_after_sync();
+          tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, kColWs), a_sb, D, a_wq, 2 * BS, D, idesc_n64, false);
+          tc::mma_commit(&s.bar_m1);
+          tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, kColO + 64 * b), a_sb, D, a_wq + BS * 16, 2 * BS, D, idesc_n64,
+                             false);
+        }
+        // Un^T of chunk n is in shared memory; the U^T buffer it came from is free again
+        ok = tc::mbar_wait(&s.bar_un, ph, &s.abort_flag, status, kWaitUn);
+        if (ok && n + 2 < NC) load_ut(n + 2);
+        ok = ok && tc::mbar_wait(&s.bar_kgt[b], ph2, &s.abort_flag, status, kWaitKgt);
+        if (ok) {
+          tc::tc_fence_after_sync();
+          tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, 0), a_un16, D, tc::smem_u32(s.kgt[b]), D, BS, idesc_f16, true);
+          tc::mma_commit(&s.bar_m3);
+        }
+        ok = ok && tc::mbar_wait(&s.bar_aqk, ph, &s.abort_flag, status, kWaitAqk);
+        if (ok) {
+          tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, kColO + 64 * b), a_unb, D, a_aqk, BS, BS, idesc_n64, true);
+          tc::mma_commit(&s.bar_m2[b]);
+        }
+        // every product of chunk n has completed: refill the buffers it read
+        ok = ok && tc::mbar_wait(&s.bar_m2[b], ph2, &s.abort_flag, status, kWaitM2);
+        if (ok) {
+          if (n + 2 < NC) { load_wq(n + 2); load_kgt(n + 2); }
+          if (n + 1 < NC) load_aqk(n + 1);
+        }
+      }
+    }
+  } else {
+    // =============================== compute threads ============================================
+    const int lq = wid & 3, part = wid >> 2;              // TMEM lane quarter, column share
+    const int dv = lq * 32 + lane;                        // this thread's value channel = TMEM lane
+    const uint32_t t_lane = tc::tmem_addr(tm, lq * 32, 0);
+    const int tokp = part * 32;                           // first of this thread's 32 tokens
+    const int dkp = part * 64;                            // first of this thread's 64 key channels
 
-  // initial state: this thread's share of its S^T row -> bf16 image, chunk_states[0], gamma_0-scaled TMEM copy
-  {
-    float* h0 = hs ? hs + (((size_t)ib * NC + 0) * H + ih) * D * D : nullptr;
-    float x[16];
+    // initial state: this thread's share of its S^T row -> bf16 image, chunk_states[0], gamma_0-scaled TMEM copy
+    {
+      float* h0 = hs ? hs + (((size_t)ib * NC + 0) * H + ih) * D * D : nullptr;
+      float x[16];
 #pragma unroll 1
-    for (int c0 = part * KCH; c0 < (part + 1) * KCH; c0 += 16) {
+      for (int c0 = dkp; c0 < dkp + 64; c0 += 16) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) x[i] = s0 ? s0[((size_t)bh * D + c0 + i) * D + dv] : 0.f;
-      if (h0) {
+        for (int i = 0; i < 16; ++i) x[i] = s0 ? s0[((size_t)bh * D + c0 + i) * D + dv] : 0.f;
+        if (h0) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) h0[(size_t)(c0 + i) * D + dv] = x[i];
-      }
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-        *reinterpret_cast<uint4*>(&s.sb[((c0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&x[j * 8]);
-#pragma unroll
-      for (int i = 0; i < 16; ++i) x[i] *= s.gl[0][c0 + i];
-      tc::tmem_st16(tc::tmem_addr(tm, lq * 32, c0), x);
-    }
-    tc::tmem_st_wait();
-  }
-  tc::fence_async_smem();
-  tc::tc_fence_before_sync();
-  __syncthreads();
-
-  constexpr uint32_t idesc_m1 = tc::instr_desc(1, 128, 128);
-  constexpr uint32_t idesc_m2 = tc::instr_desc(1, 128, 64);
-  constexpr uint32_t idesc_m3 = tc::instr_desc(2, 128, 128);
-
-#ifdef GDN2_SCAN_TIMING
-  long long tacc[16] = {0}; long long tprev = clock64();
-#endif
-  for (int n = 0; n < NC; ++n) {
-    if (s.abort_flag) break;
-    const uint32_t ph = n & 1;
-    TICK(0);
-    const bool more = n + 1 < NC;
-    float gl_next = (more && tid < D) ? g_gl[(size_t)(n + 1) * D + tid] : 1.f;   // early, independent global load
-
-    // ---- MMA1: D1 = S^T * [W ; Qg]^T
-    if (tid == 0) {
-      if (tc::mbar_wait(&s.bar_wq, ph, &s.abort_flag, status, kWaitWq)) {
-        tc::tc_fence_after_sync();
-        tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, 128), tc::smem_u32(s.sb), D, tc::smem_u32(s.wq), 2 * BS, D,
-                           idesc_m1, false);
-        tc::mma_commit(&s.bar_m1);
-      }
-    }
-    TICK(1);
-    tc::mbar_wait(&s.bar_m1, ph, &s.abort_flag, status, kWaitM1);
-    tc::tc_fence_after_sync();
-    TICK(2);
-    if (tid == 0 && more && !s.abort_flag) {
-      tc::mbar_expect_tx(&s.bar_wq, kWqBytes);
-      tc::bulk_g2s(s.wq, g_wq + (size_t)(n + 1) * kWqBytes, kWqBytes, &s.bar_wq);
-    }
-
-    // ---- Un^T = U^T - (W S)^T, written as tf32 (in place) and bf16 operand images
-    tc::mbar_wait(&s.bar_ut, ph, &s.abort_flag, status, kWaitUt);
-    TICK(3);
-#pragma unroll
-    for (int t0 = 0; t0 < TOK; t0 += 16) {
-      float ws[16];
-      tc::tmem_ld16(t_ws + t0, ws);
-      tc::tmem_ld_wait();
-      const int tok0 = part * TOK + t0;                   // first of 16 tokens
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float4* pu = reinterpret_cast<float4*>(&s.un32[((tok0 / 4 + j) * D + dv) * 4]);
-        float4 u = *pu;
-        u.x -= ws[j * 4 + 0]; u.y -= ws[j * 4 + 1]; u.z -= ws[j * 4 + 2]; u.w -= ws[j * 4 + 3];
-        *pu = make_float4(tf32_rn(u.x), tf32_rn(u.y), tf32_rn(u.z), tf32_rn(u.w));
-        ws[j * 4 + 0] = u.x; ws[j * 4 + 1] = u.y; ws[j * 4 + 2] = u.z; ws[j * 4 + 3] = u.w;
-      }
-#pragma unroll
-      for (int j = 0; j < 2; ++j)
-        *reinterpret_cast<uint4*>(&s.unb[((tok0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&ws[j * 8]);
-    }
-    if (tid < D) s.gl[(n + 1) & 1][tid] = gl_next;
-    TICK(4);
-    tc::fence_async_smem();
-    tc::tc_fence_before_sync();
-    __syncthreads();
-    TICK(5);
-
-    // ---- MMA2: D1[:, 64:128] += Un^T * Aqk^T ; MMA3: ST += Un^T * KG
-    if (tid == 0 && !s.abort_flag) {
-      tc::tc_fence_after_sync();
-      if (tc::mbar_wait(&s.bar_aqk, ph, &s.abort_flag, status, kWaitAqk)) {
-        tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, 192), tc::smem_u32(s.unb), D, tc::smem_u32(s.aqk), BS, BS,
-                           idesc_m2, true);
-        tc::mma_commit(&s.bar_m2);
-      }
-      if (tc::mbar_wait(&s.bar_kgt, ph, &s.abort_flag, status, kWaitKgt)) {
-        tc::mma_tf32_ktile(tc::tmem_addr(tm, 0, 0), tc::smem_u32(s.un32), D, tc::smem_u32(s.kgt), D, BS,
-                           idesc_m3, true);
-        tc::mma_commit(&s.bar_m3);
-      }
-    }
-
-    // ---- output rows of this chunk
-    TICK(6);
-    tc::mbar_wait(&s.bar_m2, ph, &s.abort_flag, status, kWaitM2);
-    tc::tc_fence_after_sync();
-    TICK(7);
-    if (tid == 0 && more && !s.abort_flag) {
-      tc::mbar_expect_tx(&s.bar_aqk, kAqkBytes);
-      tc::bulk_g2s(s.aqk, g_aqk + (size_t)(n + 1) * kAqkBytes, kAqkBytes, &s.bar_aqk);
-    }
-    {
-      __nv_bfloat16* orow = o + (((size_t)ib * o_bs + (size_t)n * BS + part * TOK) * H + ih) * D + dv;
-#pragma unroll
-      for (int t0 = 0; t0 < TOK; t0 += 16) {
-        float ov[16];
-        tc::tmem_ld16(t_o + t0, ov);
-        tc::tmem_ld_wait();
-        if (!s.abort_flag) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) orow[(size_t)(t0 + i) * H * D] = __float2bfloat16_rn(ov[i]);
+          for (int i = 0; i < 16; ++i) h0[(size_t)(c0 + i) * D + dv] = x[i];
         }
-      }
-    }
-
-    // ---- new state: bf16 operand copy, optional snapshot, pre-scale for the next chunk
-    TICK(8);
-    tc::mbar_wait(&s.bar_m3, ph, &s.abort_flag, status, kWaitM3);
-    tc::tc_fence_after_sync();
-    TICK(9);
-    if (tid == 0 && more && !s.abort_flag) {
-      tc::mbar_expect_tx(&s.bar_kgt, kKgtBytes);
-      tc::bulk_g2s(s.kgt, g_kgt + (size_t)(n + 1) * kKgtBytes, kKgtBytes, &s.bar_kgt);
-      tc::mbar_expect_tx(&s.bar_ut, kUtBytes);
-      tc::bulk_g2s(s.un32, g_ut + (size_t)(n + 1) * kUtBytes, kUtBytes, &s.bar_ut);
-    }
-    {
-      float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
-      float* fin = (!more && sT) ? sT + (size_t)bh * D * D : nullptr;
-      const float* gln = s.gl[(n + 1) & 1];
 #pragma unroll
-      for (int k0 = 0; k0 < KCH; k0 += 16) {
-        const int c0 = part * KCH + k0;
-        float x[16];
-        tc::tmem_ld16(t_state + k0, x);
-        tc::tmem_ld_wait();
-        if (hn) {
+        for (int j = 0; j < 2; ++j)
+          *reinterpret_cast<uint4*>(&s.sb[((c0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&x[j * 8]);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) hn[(size_t)(c0 + i) * D + dv] = x[i];
-        }
-        if (fin) {
-#pragma unroll
-          for (int i = 0; i < 16; ++i) fin[(size_t)(c0 + i) * D + dv] = x[i];
-        }
-        if (more) {
-#pragma unroll
-          for (int j = 0; j < 2; ++j)
-            *reinterpret_cast<uint4*>(&s.sb[((c0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&x[j * 8]);
-#pragma unroll
-          for (int i = 0; i < 16; ++i) x[i] *= gln[c0 + i];
-          tc::tmem_st16(t_state + k0, x);
-        }
+        for (int i = 0; i < 16; ++i) x[i] *= s.gl[0][c0 + i];
+        tc::tmem_st16(t_lane + c0, x);
       }
       tc::tmem_st_wait();
     }
-    TICK(10);
     tc::fence_async_smem();
     tc::tc_fence_before_sync();
-    __syncthreads();
-    TICK(11);
+    mbar_arrive(&s.bar_sb);
+
+    // output pass of chunk m: O accumulator (m & 1) -> bf16 -> staging -> one 256-byte bulk store per token row
+    auto output_pass = [&](int m) {
+      const int b = m & 1;
+      tc::mbar_wait(&s.bar_m2[b], (m >> 1) & 1, &s.abort_flag, status, kWaitM2);
+      tc::tc_fence_after_sync();
+      float ov[32];
+      tc::tmem_ld32(t_lane + kColO + 64 * b + tokp, ov);
+      tc::tmem_ld_wait();
+      if (tid < BS) tc::bulk_wait_read_all();              // the previous pass's stores have left the staging buffer
+      compute_sync();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s.ostage[(tokp + i) * D + dv] = __float2bfloat16_rn(ov[i]);
+      tc::fence_async_smem();
+      tc::tc_fence_before_sync();
+      compute_sync();
+      if (tid < BS && !s.abort_flag) {
+        __nv_bfloat16* orow = o + (((size_t)ib * o_bs + (size_t)m * BS + tid) * H + ih) * D;
+        tc::bulk_s2g(orow, &s.ostage[tid * D], D * 2);
+        tc::bulk_commit();
+      }
+    };
+
+    for (int n = 0; n < NC; ++n) {
+      compute_sync();                                      // publishes gl[]; makes the abort test uniform
+      if (s.abort_flag) break;
+      const int b = n & 1;
+      const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
+      const bool more = n + 1 < NC;
+      const float gl_next = (more && tid < D) ? g_gl[(size_t)(n + 1) * D + tid] : 1.f;
+
+      // ---- Un^T = U^T - (W S)^T for this thread's 32 tokens, as fp16 (scaled) and bf16 operand images
+      tc::mbar_wait(&s.bar_ut[b], ph2, &s.abort_flag, status, kWaitUt);
+      tc::mbar_wait(&s.bar_m1, ph, &s.abort_flag, status, kWaitM1);
+      tc::tc_fence_after_sync();
+      {
+        float ws[32];
+        tc::tmem_ld32(t_lane + kColWs + tokp, ws);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int t8 = tokp / 8 + j;
+          float u[8];
+          unpack8_f16(*reinterpret_cast<const uint4*>(&s.ut[b][(t8 * D + dv) * 8]), u);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) u[i] = fmaf(ws[j * 8 + i], -1.f / kValScale, u[i]);     // Un / 256
+          *reinterpret_cast<uint4*>(&s.un16[(t8 * D + dv) * 8]) = pack8_f16(u);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) u[i] *= kValScale;
+          *reinterpret_cast<uint4*>(&s.unb[(t8 * D + dv) * 8]) = tc::pack8_bf16(u);
+        }
+      }
+      if (tid < D) s.gl[(n + 1) & 1][tid] = gl_next;
+      tc::fence_async_smem();
+      tc::tc_fence_before_sync();
+      mbar_arrive(&s.bar_un);
+
+      // ---- while MMA3 / MMA2 of this chunk run: write out the previous chunk's rows
+      if (n > 0) output_pass(n - 1);
+
+      // ---- new state: bf16 operand copy, optional snapshot, pre-scale for the next chunk
+      tc::mbar_wait(&s.bar_m3, ph, &s.abort_flag, status, kWaitM3);
+      tc::tc_fence_after_sync();
+      if (n == 0) compute_sync();                          // gl[1] written above is read below (later chunks: output_pass syncs)
+      {
+        float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
+        float* fin = (!more && sT) ? sT + (size_t)bh * D * D : nullptr;
+        const float* gln = s.gl[(n + 1) & 1];
+#pragma unroll
+        for (int k0 = 0; k0 < 64; k0 += 32) {
+          const int c0 = dkp + k0;
+          float x[32];
+          tc::tmem_ld32(t_lane + c0, x);
+          tc::tmem_ld_wait();
+          if (hn) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) hn[(size_t)(c0 + i) * D + dv] = x[i];
+          }
+          if (fin) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) fin[(size_t)(c0 + i) * D + dv] = x[i];
+          }
+          if (more) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(&s.sb[((c0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&x[j * 8]);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) x[i] *= gln[c0 + i];
+            tc::tmem_st32(t_lane + c0, x);
+          }
+        }
+        tc::tmem_st_wait();
+      }
+      tc::fence_async_smem();
+      tc::tc_fence_before_sync();
+      if (more) mbar_arrive(&s.bar_sb);
+    }
+    compute_sync();
+    if (!s.abort_flag && NC > 0) output_pass(NC - 1);
+    if (tid < BS) tc::bulk_wait_read_all();
   }
-#ifdef GDN2_SCAN_TIMING
-  if (tid == 0 && blockIdx.x == 0) for (int i = 0; i < 16; ++i) g_scan_timing[i] = tacc[i];
-#endif
 
   tc::tc_fence_before_sync();
   __syncthreads();
-  if (wid == 0) tc::tmem_dealloc(tm, 256);
+  if (wid == 0) tc::tmem_dealloc(tm, 512);
 }
 
 }  // namespace
@@ -296,29 +330,11 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
                    int B, int S, int H, int64_t o_bs, cudaStream_t st) {
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
   const size_t smem = sizeof(ScanTcSmem) + 128;
-  // Tuning knob: warps per TMEM lane quarter (1, 2 or 4 -> 128, 256 or 512 threads per block).
-  static const int nsplit = [] {
-    const char* e = getenv("GDN2_B200_SCAN_NSPLIT");
-    const int v = e ? atoi(e) : GDN2_SCAN_NSPLIT;
-    return (v == 1 || v == 2 || v == 4) ? v : GDN2_SCAN_NSPLIT;
-  }();
-  auto launch = [&](auto kern, int threads) -> int {
-    GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<B * H, threads, smem, st>>>(L, P, s0, static_cast<__nv_bfloat16*>(o), sT, hs, S, H, o_bs,
-                                       device_status_word());
-    return GDN2_OK;
-  };
-  int rc = nsplit == 1 ? launch(scan_tc_kernel<1>, 128) : nsplit == 2 ? launch(scan_tc_kernel<2>, 256)
-                                                                       : launch(scan_tc_kernel<4>, 512);
-  if (rc != GDN2_OK) return rc;
+  GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  scan_tc_kernel<<<B * H, kThreads, smem, st>>>(L, P, s0, static_cast<__nv_bfloat16*>(o), sT, hs, S, H, o_bs,
+                                                device_status_word());
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }
-
-#ifdef GDN2_SCAN_TIMING
-extern "C" int gdn2_debug_scan_timing(unsigned long long* out16) {
-  return cudaMemcpyFromSymbol(out16, g_scan_timing, sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : -6;
-}
-#endif
 
 }  // namespace gdn2
