@@ -249,7 +249,7 @@ class NativeKernels:
 
     def selftest_mma(self, a: torch.Tensor, bt: torch.Tensor) -> torch.Tensor:
         _require_cuda(a, bt)
-        out = torch.zeros(3, 128, 128, dtype=torch.float32, device=a.device)
+        out = torch.zeros(4, 128, 128, dtype=torch.float32, device=a.device)
         with torch.cuda.device(a.device):
             rc = self.lib.gdn2_selftest_mma(a.data_ptr(), bt.data_ptr(), out.data_ptr(), self._stream(a))
         _check(self.lib, rc, "gdn2_selftest_mma")

@@ -19,7 +19,7 @@
 //     MMA3 before MMA2, so the critical products never queue behind the output products.
 //   * warps 0-7 (256 threads; two warps share each 32-lane quarter of TMEM and split its columns)
 //     do the register passes. The output pass of chunk n-1 (TMEM -> bf16 -> shared staging ->
-//     one 256-byte bulk store per token row) runs while MMA3 / MMA2 of chunk n execute; the O
+//     128-bit coalesced global stores) runs while MMA3 / MMA2 of chunk n execute; the O
 //     accumulator is double buffered in TMEM for that.
 //   * operands arrive as whole workspace records with one bulk copy each; WQ, KG^T and U^T are
 //     double buffered so that a copy is always issued a full chunk ahead of its use.
@@ -62,6 +62,17 @@ struct ScanTcSmem {
   uint32_t tmem_base;
   int abort_flag;
 };
+
+#ifdef GDN2_SCAN_TIMING
+__device__ unsigned long long g_scan_timing[32];
+#define TICK(i) do { if (blockIdx.x == 0) { long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; } } while (0)
+#define TDECL long long tacc[16] = {0}; long long tprev = clock64()
+#define TFLUSH(off) do { if (blockIdx.x == 0) for (int i_ = 0; i_ < 16; ++i_) g_scan_timing[off + i_] = tacc[i_]; } while (0)
+#else
+#define TICK(i) do {} while (0)
+#define TDECL do {} while (0)
+#define TFLUSH(off) do {} while (0)
+#endif
 
 enum : uint32_t {
   kWaitWq = 0x10, kWaitUt = 0x20, kWaitAqk = 0x40, kWaitKgt = 0x80, kWaitM1 = 0x100, kWaitM2 = 0x200,
@@ -149,13 +160,17 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       if (NC > 1) { load_wq(1); load_ut(1); load_kgt(1); }
       const uint32_t a_sb = tc::smem_u32(s.sb), a_un16 = tc::smem_u32(s.un16), a_unb = tc::smem_u32(s.unb);
       const uint32_t a_aqk = tc::smem_u32(s.aqk);
+      TDECL;
       for (int n = 0; n < NC; ++n) {
         const int b = n & 1;
         const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
         const uint32_t a_wq = tc::smem_u32(s.wq[b]);
+        TICK(0);
         // S^T (bf16) of chunk n is in place and O accumulator b has been read out
         bool ok = tc::mbar_wait(&s.bar_sb, ph, &s.abort_flag, status, kWaitSb);
+        TICK(1);
         ok = ok && tc::mbar_wait(&s.bar_wq[b], ph2, &s.abort_flag, status, kWaitWq);
+        TICK(2);
         if (ok) {
           tc::tc_fence_after_sync();
           tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, kColWs), a_sb, D, a_wq, 2 * BS, D, idesc_n64, false);
@@ -163,27 +178,35 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
           tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, kColO + 64 * b), a_sb, D, a_wq + BS * 16, 2 * BS, D, idesc_n64,
                              false);
         }
+        TICK(3);
         // Un^T of chunk n is in shared memory; the U^T buffer it came from is free again
         ok = tc::mbar_wait(&s.bar_un, ph, &s.abort_flag, status, kWaitUn);
+        TICK(4);
         if (ok && n + 2 < NC) load_ut(n + 2);
         ok = ok && tc::mbar_wait(&s.bar_kgt[b], ph2, &s.abort_flag, status, kWaitKgt);
+        TICK(5);
         if (ok) {
           tc::tc_fence_after_sync();
           tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, 0), a_un16, D, tc::smem_u32(s.kgt[b]), D, BS, idesc_f16, true);
           tc::mma_commit(&s.bar_m3);
         }
+        TICK(6);
         ok = ok && tc::mbar_wait(&s.bar_aqk, ph, &s.abort_flag, status, kWaitAqk);
+        TICK(7);
         if (ok) {
           tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, kColO + 64 * b), a_unb, D, a_aqk, BS, BS, idesc_n64, true);
           tc::mma_commit(&s.bar_m2[b]);
         }
+        TICK(8);
         // every product of chunk n has completed: refill the buffers it read
         ok = ok && tc::mbar_wait(&s.bar_m2[b], ph2, &s.abort_flag, status, kWaitM2);
+        TICK(9);
         if (ok) {
           if (n + 2 < NC) { load_wq(n + 2); load_kgt(n + 2); }
           if (n + 1 < NC) load_aqk(n + 1);
         }
       }
+      TFLUSH(0);
     }
   } else {
     // =============================== compute threads ============================================
@@ -218,7 +241,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     tc::tc_fence_before_sync();
     mbar_arrive(&s.bar_sb);
 
-    // output pass of chunk m: O accumulator (m & 1) -> bf16 -> staging -> one 256-byte bulk store per token row
+    // output pass of chunk m: O accumulator (m & 1) -> bf16 -> staging [tok][dv] -> 128-bit coalesced global stores
     auto output_pass = [&](int m) {
       const int b = m & 1;
       tc::mbar_wait(&s.bar_m2[b], (m >> 1) & 1, &s.abort_flag, status, kWaitM2);
@@ -226,23 +249,30 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       float ov[32];
       tc::tmem_ld32(t_lane + kColO + 64 * b + tokp, ov);
       tc::tmem_ld_wait();
-      if (tid < BS) tc::bulk_wait_read_all();              // the previous pass's stores have left the staging buffer
-      compute_sync();
+      compute_sync();                                      // the previous pass has drained the staging buffer
 #pragma unroll
       for (int i = 0; i < 32; ++i) s.ostage[(tokp + i) * D + dv] = __float2bfloat16_rn(ov[i]);
-      tc::fence_async_smem();
       tc::tc_fence_before_sync();
       compute_sync();
-      if (tid < BS && !s.abort_flag) {
-        __nv_bfloat16* orow = o + (((size_t)ib * o_bs + (size_t)m * BS + tid) * H + ih) * D;
-        tc::bulk_s2g(orow, &s.ostage[tid * D], D * 2);
-        tc::bulk_commit();
+      if (!s.abort_flag) {
+        // 64 rows x 256 bytes = 1024 16-byte pieces; thread t moves pieces t, t+256, t+512, t+768
+        __nv_bfloat16* obase = o + (((size_t)ib * o_bs + (size_t)m * BS) * H + ih) * D;
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int piece = tid + x * kComputeThreads;
+          const int row = piece >> 4, col = (piece & 15) * 8;
+          *reinterpret_cast<uint4*>(obase + (size_t)row * H * D + col) =
+              *reinterpret_cast<const uint4*>(&s.ostage[row * D + col]);
+        }
       }
     };
 
+    TDECL;
     for (int n = 0; n < NC; ++n) {
+      TICK(0);
       compute_sync();                                      // publishes gl[]; makes the abort test uniform
       if (s.abort_flag) break;
+      TICK(1);
       const int b = n & 1;
       const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
       const bool more = n + 1 < NC;
@@ -250,8 +280,10 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
 
       // ---- Un^T = U^T - (W S)^T for this thread's 32 tokens, as fp16 (scaled) and bf16 operand images
       tc::mbar_wait(&s.bar_ut[b], ph2, &s.abort_flag, status, kWaitUt);
+      TICK(2);
       tc::mbar_wait(&s.bar_m1, ph, &s.abort_flag, status, kWaitM1);
       tc::tc_fence_after_sync();
+      TICK(3);
       {
         float ws[32];
         tc::tmem_ld32(t_lane + kColWs + tokp, ws);
@@ -270,16 +302,20 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         }
       }
       if (tid < D) s.gl[(n + 1) & 1][tid] = gl_next;
+      TICK(4);
       tc::fence_async_smem();
       tc::tc_fence_before_sync();
       mbar_arrive(&s.bar_un);
+      TICK(5);
 
       // ---- while MMA3 / MMA2 of this chunk run: write out the previous chunk's rows
       if (n > 0) output_pass(n - 1);
 
       // ---- new state: bf16 operand copy, optional snapshot, pre-scale for the next chunk
+      TICK(6);
       tc::mbar_wait(&s.bar_m3, ph, &s.abort_flag, status, kWaitM3);
       tc::tc_fence_after_sync();
+      TICK(7);
       if (n == 0) compute_sync();                          // gl[1] written above is read below (later chunks: output_pass syncs)
       {
         float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
@@ -310,13 +346,15 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         }
         tc::tmem_st_wait();
       }
+      TICK(8);
       tc::fence_async_smem();
       tc::tc_fence_before_sync();
       if (more) mbar_arrive(&s.bar_sb);
+      TICK(9);
     }
+    if (tid == 0) TFLUSH(16);
     compute_sync();
     if (!s.abort_flag && NC > 0) output_pass(NC - 1);
-    if (tid < BS) tc::bulk_wait_read_all();
   }
 
   tc::tc_fence_before_sync();
@@ -336,5 +374,11 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }
+
+#ifdef GDN2_SCAN_TIMING
+extern "C" int gdn2_debug_scan_timing(unsigned long long* out32) {
+  return cudaMemcpyFromSymbol(out32, g_scan_timing, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -6;
+}
+#endif
 
 }  // namespace gdn2

@@ -4,6 +4,7 @@
 //   out[0] = A * B^T with bf16 operands        [128 x 128]
 //   out[1] = A * B^T with tf32 operands        [128 x 128]
 //   out[2] = 2 * out[1] + 1 after a TMEM store/load round trip
+//   out[3] = A * B^T with bf16 operands, A read from tensor memory (packed pairs), B from shared memory
 #include "common.cuh"
 #include "tc_utils.cuh"
 
@@ -65,12 +66,23 @@ selftest_kernel(const float* __restrict__ a, const float* __restrict__ bt, float
       *reinterpret_cast<uint4*>(&s.b16[(c * N + r) * 8]) = tc::pack8_bf16(xb);
     }
   }
+  {   // A row of this thread as packed bf16 pairs in TMEM columns [320, 352)
+    float pk[32];
+    for (int c = 0; c < 32; ++c) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(s.raw_a[tid * K + 2 * c], s.raw_a[tid * K + 2 * c + 1]);
+      pk[c] = __uint_as_float(*reinterpret_cast<uint32_t*>(&h));
+    }
+    tc::tmem_st32(tc::tmem_addr(tm, (wid & 3) * 32, 320), pk);
+    tc::tmem_st_wait();
+  }
   tc::fence_async_smem();
   tc::tc_fence_before_sync();
   __syncthreads();
 
   if (tid == 0 && !s.abort_flag) {
     tc::tc_fence_after_sync();
+    tc::mma_f16_ts_ktile(tc::tmem_addr(tm, 0, 384), tc::tmem_addr(tm, 0, 320), tc::smem_u32(s.b16), N, K,
+                         tc::instr_desc(1, M, N), false);
     tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, 0), tc::smem_u32(s.a16), M, tc::smem_u32(s.b16), N, K,
                        tc::instr_desc(1, M, N), false);
     // tf32: columns [128,192) from B rows 0..63, columns [192,256) from B rows 64..127
@@ -101,6 +113,11 @@ selftest_kernel(const float* __restrict__ a, const float* __restrict__ bt, float
     tc::tmem_ld32(tc::tmem_addr(tm, lane_base, 256 + c0), vals);
     tc::tmem_ld_wait();
     for (int i = 0; i < 32; ++i) out[(size_t)2 * M * N + tid * N + c0 + i] = vals[i];
+  }
+  for (int c0 = 0; c0 < N; c0 += 32) {
+    tc::tmem_ld32(tc::tmem_addr(tm, lane_base, 384 + c0), vals);
+    tc::tmem_ld_wait();
+    for (int i = 0; i < 32; ++i) out[(size_t)3 * M * N + tid * N + c0 + i] = vals[i];
   }
   tc::tc_fence_before_sync();
   __syncthreads();

@@ -215,6 +215,28 @@ __device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint6
       : "memory");
 }
 
+// A operand from tensor memory (16-bit elements packed two per 32-bit column, K along columns, row m in
+// lane m), B from shared memory. `a_tmem` addresses the first of the K/2 columns this MMA consumes.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[128 x N] (+)= A[128 x K] * B[N x K]^T, A in TMEM (8 columns per 16-element K step), B a K-chunked image.
+__device__ __forceinline__ void mma_f16_ts_ktile(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t b_rows,
+                                                 int K, uint32_t idesc, bool accumulate_first) {
+  for (int ks = 0; ks < K / 16; ++ks) {
+    const uint64_t bd = kchunk_desc(b_addr + ks * 2 * b_rows * 16, b_rows);
+    mma_f16_ts(d_tmem, a_tmem + ks * 8, bd, idesc, (ks > 0 || accumulate_first) ? 1u : 0u);
+  }
+}
+
 // mbarrier arrives once every tcgen05 operation issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))

@@ -122,8 +122,8 @@ int gdn2_check_device_status(void* stream, uint32_t* detail);
 /*
  * Self-test of the tcgen05 / TMEM / bulk-copy building blocks on tiny fixed operands
  * (one 128x128x64 bf16 and one tf32 product through shared-memory descriptors, a TMEM round trip).
- * `out` receives 3*128*128 fp32 results (the bf16 product, the tf32 product, then 2*tf32+1 after a
- * TMEM store/load round trip); `a` and `bt` are [128,64] fp32 row-major inputs (A, and B transposed).
+ * `out` receives 4*128*128 fp32 results (the bf16 product, the tf32 product, 2*tf32+1 after a TMEM
+ * store/load round trip, and the bf16 product again with A read from tensor memory); `a` and `bt` are [128,64] fp32 row-major inputs (A, and B transposed).
  * No counterpart in the reference.
  */
 int gdn2_selftest_mma(const float* a, const float* bt, float* out, void* stream);

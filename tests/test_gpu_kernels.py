@@ -54,6 +54,7 @@ def test_tcgen05_selftest(K):
     assert orc.rel_max_err(out[0], ref16) < 1e-5          # exact products, fp32 accumulation
     assert orc.rel_max_err(out[1], ref32) < 3e-3          # tf32 operands: 10-bit mantissa
     assert torch.equal(out[2], 2 * out[1] + 1)            # TMEM store/load round trip
+    assert torch.equal(out[3], out[0])                    # A operand from tensor memory == from shared memory
 
 
 # ---- decode ------------------------------------------------------------------------------------------
