@@ -15,17 +15,24 @@
 //
 // Only MMA1w, the Un pass, MMA3 and the state pass are on the recurrence's critical path; the
 // kernel is organised around that:
-//   * warp 8 (one thread) issues every MMA and every bulk copy. It orders MMA1w before MMA1q and
-//     MMA3 before MMA2, so the critical products never queue behind the output products.
+//   * warp 8 (one thread) issues every MMA, MMA3 before MMA2 so the state update never queues behind
+//     the output product; warp 9 (one thread) issues every bulk copy.
+//   * warps 10-13 read each finished O accumulator into registers, release it, and write the rows
+//     out through a shared staging tile with 128-bit coalesced stores, off the critical path.
 //   * warps 0-7 (256 threads; two warps share each 32-lane quarter of TMEM and split its columns)
-//     do the register passes. The output pass of chunk n-1 (TMEM -> bf16 -> shared staging ->
-//     128-bit coalesced global stores) runs while MMA3 / MMA2 of chunk n execute; the O
-//     accumulator is double buffered in TMEM for that.
+//     do the register passes. The output pass of chunk n (TMEM -> bf16 -> shared staging ->
+//     128-bit coalesced global stores) runs after the state hand-off, while MMA1w of chunk n+1
+//     executes; the O accumulator is double buffered in TMEM for that.
 //   * operands arrive as whole workspace records with one bulk copy each; WQ, KG^T and U^T are
 //     double buffered so that a copy is always issued a full chunk ahead of its use.
 //   * hand-offs are mbarriers (arrive / wait), every wait is bounded (tc_utils.cuh).
 //
-// TMEM columns: [0,128) fp32 state S^T; [128,192) WS; [192,256) and [256,320) the two O accumulators.
+//   * the A operands (S^T in bf16, Un^T in fp16 and bf16) never touch shared memory: the register
+//     passes store them as packed 16-bit pairs into tensor memory and the MMAs read them from there,
+//     which halves the shared-memory traffic the tensor core competes for.
+//
+// TMEM columns: [0,128) fp32 state S^T; [128,192) WS; [192,256) and [256,320) the two O accumulators;
+// [320,384) S^T bf16 pairs; [384,416) Un^T/256 fp16 pairs; [416,448) Un^T bf16 pairs.
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -38,26 +45,25 @@ namespace {
 constexpr int D = 128;
 constexpr int BS = kChunk;
 constexpr int kComputeThreads = 256;
-constexpr int kThreads = kComputeThreads + 32;
+constexpr int kOutputThreads = 128;
+constexpr int kThreads = kComputeThreads + 64 + kOutputThreads;   // + issuer warp + producer warp + output warps
 
 constexpr uint32_t kWqBytes = 2 * BS * D * 2;    // 32 KiB
 constexpr uint32_t kAqkBytes = BS * BS * 2;      //  8 KiB
 constexpr uint32_t kKgtBytes = D * BS * 2;       // 16 KiB (fp16)
 constexpr uint32_t kUtBytes = D * BS * 2;        // 16 KiB (fp16)
 constexpr uint32_t kColWs = 128, kColO = 192;
+constexpr uint32_t kColSb = 320, kColUn16 = 384, kColUnb = 416;   // packed 16-bit A operands in TMEM
 
 struct ScanTcSmem {
   __nv_bfloat16 wq[2][2 * BS * D];   // B of MMA1w/q: [dk/8][128 rows: W tok 0..63, Qg tok 0..63][8]
   __nv_bfloat16 aqk[BS * BS];        // B of MMA2: [s/8][64 r][8]
   __half kgt[2][D * BS];             // B of MMA3: [tok/8][128 dk][8], 256 * KG
   __half ut[2][D * BS];              // U^T / 256: [tok/8][128 dv][8]
-  __nv_bfloat16 sb[D * D];           // A of MMA1: S^T in bf16: [dk/8][128 dv][8]
-  __half un16[D * BS];               // A of MMA3: Un^T / 256: [tok/8][128 dv][8]
-  __nv_bfloat16 unb[D * BS];         // A of MMA2: Un^T in bf16: [tok/8][128 dv][8]
   __nv_bfloat16 ostage[BS * D];      // output rows [tok][dv] on their way to global memory
   float gl[2][D];                    // gamma at the last token of chunk n (slot n & 1)
   uint64_t bar_wq[2], bar_kgt[2], bar_ut[2], bar_aqk;   // bulk-copy arrival
-  uint64_t bar_m1, bar_m3, bar_m2[2];                   // MMA completion
+  uint64_t bar_m1, bar_m3, bar_m2;                      // MMA completion
   uint64_t bar_sb, bar_un;                              // compute threads -> issuer (256 arrivals)
   uint32_t tmem_base;
   int abort_flag;
@@ -84,6 +90,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 }
 // barrier among the 256 compute threads only (hardware barrier 1)
 __device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// barrier among the 128 output threads only (hardware barrier 2)
+__device__ __forceinline__ void output_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
 __device__ __forceinline__ uint4 pack8_f16(const float* x) {
   uint4 r;
@@ -93,6 +101,14 @@ __device__ __forceinline__ uint4 pack8_f16(const float* x) {
   t = __floats2half2_rn(x[4], x[5]); r.z = *reinterpret_cast<uint32_t*>(&t);
   t = __floats2half2_rn(x[6], x[7]); r.w = *reinterpret_cast<uint32_t*>(&t);
   return r;
+}
+__device__ __forceinline__ float pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return __uint_as_float(*reinterpret_cast<uint32_t*>(&t));
+}
+__device__ __forceinline__ float pack_f16x2(float lo, float hi) {
+  __half2 t = __floats2half2_rn(lo, hi);
+  return __uint_as_float(*reinterpret_cast<uint32_t*>(&t));
 }
 __device__ __forceinline__ void unpack8_f16(const uint4& p, float* x) {
   float2 f;
@@ -121,10 +137,9 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&s.bar_wq[i], 1); tc::mbar_init(&s.bar_kgt[i], 1); tc::mbar_init(&s.bar_ut[i], 1);
-      tc::mbar_init(&s.bar_m2[i], 1);
     }
-    tc::mbar_init(&s.bar_aqk, 1); tc::mbar_init(&s.bar_m1, 1); tc::mbar_init(&s.bar_m3, 1);
-    tc::mbar_init(&s.bar_sb, kComputeThreads); tc::mbar_init(&s.bar_un, kComputeThreads);
+    tc::mbar_init(&s.bar_aqk, 1); tc::mbar_init(&s.bar_m1, 1); tc::mbar_init(&s.bar_m3, 1); tc::mbar_init(&s.bar_m2, 1);
+    tc::mbar_init(&s.bar_sb, kComputeThreads + kOutputThreads); tc::mbar_init(&s.bar_un, kComputeThreads);
     s.abort_flag = 0;
     tc::mbar_init_fence();
   }
@@ -135,11 +150,9 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
   tc::tc_fence_after_sync();
   const uint32_t tm = s.tmem_base;
 
-  if (wid == 8) {
-    // =============================== issuer: MMAs and bulk copies ===============================
+  if (wid == 9) {
+    // =============================== producer: bulk copies of the workspace records ==============
     if (lane == 0) {
-      constexpr uint32_t idesc_n64 = tc::instr_desc(1, 128, 64);     // bf16 operands, N = 64
-      constexpr uint32_t idesc_f16 = tc::instr_desc(0, 128, 128);    // fp16 operands, N = 128
       auto load_wq = [&](int n) {
         tc::mbar_expect_tx(&s.bar_wq[n & 1], kWqBytes);
         tc::bulk_g2s(s.wq[n & 1], g_wq + (size_t)n * kWqBytes, kWqBytes, &s.bar_wq[n & 1]);
@@ -158,55 +171,96 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       };
       load_wq(0); load_ut(0); load_kgt(0); load_aqk(0);
       if (NC > 1) { load_wq(1); load_ut(1); load_kgt(1); }
-      const uint32_t a_sb = tc::smem_u32(s.sb), a_un16 = tc::smem_u32(s.un16), a_unb = tc::smem_u32(s.unb);
+      for (int n = 0; n < NC; ++n) {
+        const uint32_t ph = n & 1;
+        // the Un pass of chunk n has consumed its U^T buffer
+        bool ok = tc::mbar_wait(&s.bar_un, ph, &s.abort_flag, status, kWaitUn);
+        if (ok && n + 2 < NC) load_ut(n + 2);
+        // every product of chunk n has completed: refill the operand buffers it read
+        ok = ok && tc::mbar_wait(&s.bar_m2, ph, &s.abort_flag, status, kWaitM2);
+        if (ok) {
+          if (n + 1 < NC) load_aqk(n + 1);
+          if (n + 2 < NC) { load_wq(n + 2); load_kgt(n + 2); }
+        }
+      }
+    }
+  } else if (wid == 8) {
+    // =============================== issuer: every MMA, in critical-path order ==================
+    if (lane == 0) {
+      constexpr uint32_t idesc_n128 = tc::instr_desc(1, 128, 128);   // bf16 operands, N = 128
+      constexpr uint32_t idesc_n64 = tc::instr_desc(1, 128, 64);     // bf16 operands, N = 64
+      constexpr uint32_t idesc_f16 = tc::instr_desc(0, 128, 128);    // fp16 operands, N = 128
+      const uint32_t a_sb = tc::tmem_addr(tm, 0, kColSb), a_un16 = tc::tmem_addr(tm, 0, kColUn16);
+      const uint32_t a_unb = tc::tmem_addr(tm, 0, kColUnb);
       const uint32_t a_aqk = tc::smem_u32(s.aqk);
       TDECL;
       for (int n = 0; n < NC; ++n) {
         const int b = n & 1;
         const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
-        const uint32_t a_wq = tc::smem_u32(s.wq[b]);
         TICK(0);
-        // S^T (bf16) of chunk n is in place and O accumulator b has been read out
+        // S^T (bf16) of chunk n is in place and the O accumulator has been read out
         bool ok = tc::mbar_wait(&s.bar_sb, ph, &s.abort_flag, status, kWaitSb);
         TICK(1);
         ok = ok && tc::mbar_wait(&s.bar_wq[b], ph2, &s.abort_flag, status, kWaitWq);
         TICK(2);
         if (ok) {
           tc::tc_fence_after_sync();
-          tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, kColWs), a_sb, D, a_wq, 2 * BS, D, idesc_n64, false);
+          // one N = 128 product: columns [128,192) = (W S)^T, [192,256) = (Qg S)^T
+          tc::mma_f16_ts_ktile(tc::tmem_addr(tm, 0, kColWs), a_sb, tc::smem_u32(s.wq[b]), 2 * BS, D, idesc_n128, false);
           tc::mma_commit(&s.bar_m1);
-          tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, kColO + 64 * b), a_sb, D, a_wq + BS * 16, 2 * BS, D, idesc_n64,
-                             false);
         }
         TICK(3);
-        // Un^T of chunk n is in shared memory; the U^T buffer it came from is free again
         ok = tc::mbar_wait(&s.bar_un, ph, &s.abort_flag, status, kWaitUn);
         TICK(4);
-        if (ok && n + 2 < NC) load_ut(n + 2);
         ok = ok && tc::mbar_wait(&s.bar_kgt[b], ph2, &s.abort_flag, status, kWaitKgt);
         TICK(5);
         if (ok) {
           tc::tc_fence_after_sync();
-          tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, 0), a_un16, D, tc::smem_u32(s.kgt[b]), D, BS, idesc_f16, true);
+          tc::mma_f16_ts_ktile(tc::tmem_addr(tm, 0, 0), a_un16, tc::smem_u32(s.kgt[b]), D, BS, idesc_f16, true);
           tc::mma_commit(&s.bar_m3);
         }
         TICK(6);
         ok = ok && tc::mbar_wait(&s.bar_aqk, ph, &s.abort_flag, status, kWaitAqk);
         TICK(7);
         if (ok) {
-          tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, kColO + 64 * b), a_unb, D, a_aqk, BS, BS, idesc_n64, true);
-          tc::mma_commit(&s.bar_m2[b]);
+          tc::mma_f16_ts_ktile(tc::tmem_addr(tm, 0, kColO), a_unb, a_aqk, BS, BS, idesc_n64, true);
+          tc::mma_commit(&s.bar_m2);
         }
         TICK(8);
-        // every product of chunk n has completed: refill the buffers it read
-        ok = ok && tc::mbar_wait(&s.bar_m2[b], ph2, &s.abort_flag, status, kWaitM2);
-        TICK(9);
-        if (ok) {
-          if (n + 2 < NC) { load_wq(n + 2); load_kgt(n + 2); }
-          if (n + 1 < NC) load_aqk(n + 1);
-        }
       }
       TFLUSH(0);
+    }
+  } else if (wid >= 10) {
+    // =============================== output warps: O^T -> bf16 rows in global memory =============
+    const int lq = wid & 3;
+    const int dv = lq * 32 + lane;
+    const int otid = tid - (kComputeThreads + 64);
+    const uint32_t t_o = tc::tmem_addr(tm, lq * 32, kColO);
+    mbar_arrive(&s.bar_sb);                                // nothing to read out before chunk 0
+    for (int n = 0; n < NC; ++n) {
+      float ov[64];
+      tc::mbar_wait(&s.bar_m2, n & 1, &s.abort_flag, status, kWaitM2);
+      tc::tc_fence_after_sync();
+      tc::tmem_ld32(t_o, *reinterpret_cast<float(*)[32]>(&ov[0]));
+      tc::tmem_ld32(t_o + 32, *reinterpret_cast<float(*)[32]>(&ov[32]));
+      tc::tmem_ld_wait();
+      tc::tc_fence_before_sync();
+      if (n + 1 < NC) mbar_arrive(&s.bar_sb);              // the accumulator may be overwritten by the next MMA1
+      output_sync();                                       // the previous chunk's rows have left the staging buffer
+#pragma unroll
+      for (int i = 0; i < 64; ++i) s.ostage[i * D + dv] = __float2bfloat16_rn(ov[i]);
+      output_sync();
+      if (!s.abort_flag) {
+        // 64 rows x 256 bytes = 1024 16-byte pieces, 8 per thread, 128-bit coalesced stores
+        __nv_bfloat16* obase = o + (((size_t)ib * o_bs + (size_t)n * BS) * H + ih) * D;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          const int piece = otid + x * kOutputThreads;
+          const int row = piece >> 4, col = (piece & 15) * 8;
+          *reinterpret_cast<uint4*>(obase + (size_t)row * H * D + col) =
+              *reinterpret_cast<const uint4*>(&s.ostage[row * D + col]);
+        }
+      }
     }
   } else {
     // =============================== compute threads ============================================
@@ -228,44 +282,18 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
 #pragma unroll
           for (int i = 0; i < 16; ++i) h0[(size_t)(c0 + i) * D + dv] = x[i];
         }
+        uint32_t pk[8];
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-          *reinterpret_cast<uint4*>(&s.sb[((c0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&x[j * 8]);
+        for (int i = 0; i < 8; ++i) pk[i] = __float_as_uint(pack_bf16x2(x[2 * i], x[2 * i + 1]));
+        tc::tmem_st8(t_lane + kColSb + c0 / 2, pk);
 #pragma unroll
         for (int i = 0; i < 16; ++i) x[i] *= s.gl[0][c0 + i];
         tc::tmem_st16(t_lane + c0, x);
       }
       tc::tmem_st_wait();
     }
-    tc::fence_async_smem();
     tc::tc_fence_before_sync();
     mbar_arrive(&s.bar_sb);
-
-    // output pass of chunk m: O accumulator (m & 1) -> bf16 -> staging [tok][dv] -> 128-bit coalesced global stores
-    auto output_pass = [&](int m) {
-      const int b = m & 1;
-      tc::mbar_wait(&s.bar_m2[b], (m >> 1) & 1, &s.abort_flag, status, kWaitM2);
-      tc::tc_fence_after_sync();
-      float ov[32];
-      tc::tmem_ld32(t_lane + kColO + 64 * b + tokp, ov);
-      tc::tmem_ld_wait();
-      compute_sync();                                      // the previous pass has drained the staging buffer
-#pragma unroll
-      for (int i = 0; i < 32; ++i) s.ostage[(tokp + i) * D + dv] = __float2bfloat16_rn(ov[i]);
-      tc::tc_fence_before_sync();
-      compute_sync();
-      if (!s.abort_flag) {
-        // 64 rows x 256 bytes = 1024 16-byte pieces; thread t moves pieces t, t+256, t+512, t+768
-        __nv_bfloat16* obase = o + (((size_t)ib * o_bs + (size_t)m * BS) * H + ih) * D;
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          const int piece = tid + x * kComputeThreads;
-          const int row = piece >> 4, col = (piece & 15) * 8;
-          *reinterpret_cast<uint4*>(obase + (size_t)row * H * D + col) =
-              *reinterpret_cast<const uint4*>(&s.ostage[row * D + col]);
-        }
-      }
-    };
 
     TDECL;
     for (int n = 0; n < NC; ++n) {
@@ -288,6 +316,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         float ws[32];
         tc::tmem_ld32(t_lane + kColWs + tokp, ws);
         tc::tmem_ld_wait();
+        float p16[16], pb[16];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int t8 = tokp / 8 + j;
@@ -295,38 +324,39 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
           unpack8_f16(*reinterpret_cast<const uint4*>(&s.ut[b][(t8 * D + dv) * 8]), u);
 #pragma unroll
           for (int i = 0; i < 8; ++i) u[i] = fmaf(ws[j * 8 + i], -1.f / kValScale, u[i]);     // Un / 256
-          *reinterpret_cast<uint4*>(&s.un16[(t8 * D + dv) * 8]) = pack8_f16(u);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) u[i] *= kValScale;
-          *reinterpret_cast<uint4*>(&s.unb[(t8 * D + dv) * 8]) = tc::pack8_bf16(u);
+          for (int i = 0; i < 4; ++i) {
+            p16[j * 4 + i] = pack_f16x2(u[2 * i], u[2 * i + 1]);
+            pb[j * 4 + i] = pack_bf16x2(u[2 * i] * kValScale, u[2 * i + 1] * kValScale);
+          }
         }
+        tc::tmem_st16(t_lane + kColUn16 + tokp / 2, p16);
+        tc::tmem_st16(t_lane + kColUnb + tokp / 2, pb);
+        tc::tmem_st_wait();
       }
       if (tid < D) s.gl[(n + 1) & 1][tid] = gl_next;
       TICK(4);
-      tc::fence_async_smem();
       tc::tc_fence_before_sync();
       mbar_arrive(&s.bar_un);
       TICK(5);
 
-      // ---- while MMA3 / MMA2 of this chunk run: write out the previous chunk's rows
-      if (n > 0) output_pass(n - 1);
-
       // ---- new state: bf16 operand copy, optional snapshot, pre-scale for the next chunk
-      TICK(6);
       tc::mbar_wait(&s.bar_m3, ph, &s.abort_flag, status, kWaitM3);
       tc::tc_fence_after_sync();
       TICK(7);
-      if (n == 0) compute_sync();                          // gl[1] written above is read below (later chunks: output_pass syncs)
+      compute_sync();                                      // gl[(n+1)&1] written above is read below
       {
         float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
         float* fin = (!more && sT) ? sT + (size_t)bh * D * D : nullptr;
         const float* gln = s.gl[(n + 1) & 1];
+        float xs[2][32];
+        tc::tmem_ld32(t_lane + dkp, xs[0]);
+        tc::tmem_ld32(t_lane + dkp + 32, xs[1]);
+        tc::tmem_ld_wait();
 #pragma unroll
-        for (int k0 = 0; k0 < 64; k0 += 32) {
-          const int c0 = dkp + k0;
-          float x[32];
-          tc::tmem_ld32(t_lane + c0, x);
-          tc::tmem_ld_wait();
+        for (int hf = 0; hf < 2; ++hf) {
+          const int c0 = dkp + 32 * hf;
+          float (&x)[32] = xs[hf];
           if (hn) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) hn[(size_t)(c0 + i) * D + dv] = x[i];
@@ -336,25 +366,26 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
             for (int i = 0; i < 32; ++i) fin[(size_t)(c0 + i) * D + dv] = x[i];
           }
           if (more) {
+            float pk[16];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              *reinterpret_cast<uint4*>(&s.sb[((c0 / 8 + j) * D + dv) * 8]) = tc::pack8_bf16(&x[j * 8]);
+            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(x[2 * i], x[2 * i + 1]);
+            tc::tmem_st16(t_lane + kColSb + c0 / 2, pk);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) x[i] *= gln[c0 + i];
+            for (int i = 0; i < 8; ++i) {
+              const float4 g4 = *reinterpret_cast<const float4*>(&gln[c0 + 4 * i]);
+              x[4 * i] *= g4.x; x[4 * i + 1] *= g4.y; x[4 * i + 2] *= g4.z; x[4 * i + 3] *= g4.w;
+            }
             tc::tmem_st32(t_lane + c0, x);
           }
         }
         tc::tmem_st_wait();
       }
       TICK(8);
-      tc::fence_async_smem();
       tc::tc_fence_before_sync();
       if (more) mbar_arrive(&s.bar_sb);
       TICK(9);
     }
     if (tid == 0) TFLUSH(16);
-    compute_sync();
-    if (!s.abort_flag && NC > 0) output_pass(NC - 1);
   }
 
   tc::tc_fence_before_sync();
