@@ -17,8 +17,8 @@
 //  2. MMA1 (bf16, M = 128: rows 0..63 = b*k rows, 64..127 = q rows, all scaled by their own ref):
 //     four products A * B_i^T, B_i = key rows s < 16(i+1) scaled to ref_i, N = 16(i+1).
 //     Row block i of product i gives Tm (strictly lower) and Aqk (lower incl. diagonal, * scale).
-//  3. (I + Tm)^-1 by forward substitution in registers: two threads per column (even / odd source
-//     rows), one shuffle per row, Tm read as broadcast 128-bit shared loads.
+//  3. (I + Tm)^-1 by 16x16 blocks: the four diagonal blocks by forward substitution in registers,
+//     the off-diagonal blocks from 16 small products on warp-level register fragments.
 //  4. MMA2 (tf32, transposed so channels are M): W^T = E^T * Ai^T, U^T = (w*v)^T * Ai^T.
 //  5. Outputs in the scan's operand layout (common.cuh): WQ via shared staging + bulk stores, AQK,
 //     KG^T and U^T (scaled fp16), gamma_last with 128-bit coalesced global stores.
@@ -38,10 +38,17 @@ constexpr int D = 128;
 constexpr int BS = kChunk;
 constexpr int A_PAD = 129;        // rows per K chunk of a 128-row bf16 image, +1 pad row: kills bank conflicts
 constexpr int B_PAD = 161;        // 160 key rows (16 + 32 + 48 + 64) + 1 pad row
-constexpr int TM_STRIDE = 72;     // floats per Tm row: [0,32) even source rows, [36,68) odd source rows
+constexpr int TM_STRIDE = 68;     // floats per Tm row (row-major, padded against bank conflicts)
 constexpr float kMaxSpanLog2 = 64.f;
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kQgCol = 160;  // TMEM columns [160,192): packed Qg of the thread's channel
+
+#ifdef GDN2_SCAN_TIMING
+__device__ unsigned long long g_prep_timing[16];
+#define PTICK(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) { long long now_ = clock64(); g_prep_timing[i] = now_ - tprev; tprev = now_; } } while (0)
+#else
+#define PTICK(i) do {} while (0)
+#endif
 
 struct PrepTcSmem {
   union {
@@ -50,7 +57,7 @@ struct PrepTcSmem {
       __nv_bfloat16 bfam[16 * B_PAD * 8];    // B of MMA1: [dk/8][161][8], rows: B_0 0..15, B_1 16..47, B_2 48..95, B_3 96..159
     } ops;
     struct {
-      float tm[BS * TM_STRIDE];              // strictly lower Tm, de-interleaved by source-row parity
+      float tm[BS * TM_STRIDE];              // strictly lower Tm, row-major; N_ik = D_i T_ik overwrites its blocks
       float ai[16 * BS * 4];                 // B of MMA2: (I+Tm)^-1 as [s/4][64 r][4]
       float zt[16 * D * 4];                  // A of MMA2: (w*v)^T [tok/4][128 dv][4]
     } sol;
@@ -85,6 +92,9 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const size_t row0 = ((size_t)ib * in_bs + (size_t)n * BS) * H + ih;   // token row of t = 0
   const size_t rstride = (size_t)H * D;                                 // elements between tokens
   const float* gp = g + row0 * D + c;
+#ifdef GDN2_SCAN_TIMING
+  long long tprev = clock64();
+#endif
 
   // ---- 1a. G at the first row of every sub-block and at the last token; decay-span check
   float ref0 = 0.f, ref1 = 0.f, ref2 = 0.f, ref3 = 0.f, g_last;
@@ -110,6 +120,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     s.abort_flag = 0;
     tc::mbar_init_fence();
   }
+  PTICK(0);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (tid == 0) P.flags[ch] = any_bad ? 1 : 0;
   if (any_bad) return;              // the exact kernel redoes this chunk; nothing allocated yet
@@ -119,6 +130,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::tc_fence_after_sync();
   const uint32_t tm = s.tmem_base;
 
+  PTICK(1);
   // ---- 1b. gated operands of channel c, one 16-token sub-block per iteration
   {
     const __nv_bfloat16* qp = q + row0 * D + c;
@@ -190,6 +202,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::tc_fence_before_sync();
   __syncthreads();
 
+  PTICK(2);
   // ---- 2. MMA1: D_i[128 x 16(i+1)] at TMEM columns 0, 16, 48, 96
   if (tid == 0) {
     tc::tc_fence_after_sync();
@@ -202,6 +215,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     }
     tc::mma_commit(&s.bar_m1);
   }
+  PTICK(3);
   // value side: raw loads issued while the tensor core works
   float zv[4][16];
   {
@@ -215,8 +229,10 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         zv[jj][u] = tf32_rn(bf(vp + off) * bf(wp + off));
       }
   }
+  PTICK(4);
   tc::mbar_wait(&s.bar_m1, 0, &s.abort_flag, status, 0x1000u);
   tc::tc_fence_after_sync();
+  PTICK(5);
 
   // ---- 2b. read back: lane = row (0..63 Tm, 64..127 Aqk); a warp spans sub-blocks i0 and i0+1.
   //          The MMA1 operands are dead now: Tm, Ai and (w*v)^T take their place.
@@ -247,12 +263,8 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     if (!is_q) {
       float* tr = s.x.sol.tm + r * TM_STRIDE;
 #pragma unroll
-      for (int m4 = 0; m4 < 8; ++m4) {
-        *reinterpret_cast<float4*>(tr + 4 * m4) =
-            make_float4(row[8 * m4], row[8 * m4 + 2], row[8 * m4 + 4], row[8 * m4 + 6]);
-        *reinterpret_cast<float4*>(tr + 36 + 4 * m4) =
-            make_float4(row[8 * m4 + 1], row[8 * m4 + 3], row[8 * m4 + 5], row[8 * m4 + 7]);
-      }
+      for (int m4 = 0; m4 < 16; ++m4)
+        *reinterpret_cast<float4*>(tr + 4 * m4) = make_float4(row[4 * m4], row[4 * m4 + 1], row[4 * m4 + 2], row[4 * m4 + 3]);
     } else {
       __nv_bfloat16* ag = reinterpret_cast<__nv_bfloat16*>(P.aqk + (size_t)ch * (BS * BS * 2));
 #pragma unroll
@@ -269,36 +281,105 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::tc_fence_before_sync();
   __syncthreads();
 
-  // ---- 3. (I + Tm)^-1: thread (j, p) accumulates the source rows of parity p for column j
+  PTICK(6);
+  // ---- 3. (I + Tm)^-1 by 16x16 blocks. With D_i = (I + T_ii)^-1 and N_ik = D_i T_ik (i > k):
+  //          X_ii = D_i,   X_ij = - sum_{k=j}^{i-1} N_ik X_kj   (i > j),   zero above the diagonal.
+  //      The diagonal blocks are substituted column by column in registers (one thread per column);
+  //      the 16 block products run as warp-level m16n8k8 tf32 MMAs on register fragments.
   {
-    const int j = tid >> 1, p = tid & 1;
-    const float* tp = s.x.sol.tm + p * 36;
-    float x[32];
+    float* tmm = s.x.sol.tm;
+    float* aim = s.x.sol.ai;
+    auto AI = [](int r, int c) { return ((c >> 2) * BS + r) * 4 + (c & 3); };   // (row r, source token c) in the B image
+    if (tid < BS) {
+      const int i = tid >> 4, j = tid & 15;
+      const float* tb = tmm + (16 * i) * TM_STRIDE + 16 * i;
+      float x[16];
 #pragma unroll
-    for (int m = 0; m < 32; ++m) x[m] = 0.f;
+      for (int r = 0; r < 16; ++r) {
+        float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-    for (int r = 0; r < BS; ++r) {
-      float acc = 0.f;
-#pragma unroll
-      for (int mg = 0; mg < ((r + 1) / 2 + 3) / 4; ++mg) {      // entries at or right of the diagonal are 0
-        const float4 t4 = *reinterpret_cast<const float4*>(tp + r * TM_STRIDE + 4 * mg);
-        acc = fmaf(t4.x, x[4 * mg], acc);
-        acc = fmaf(t4.y, x[4 * mg + 1], acc);
-        acc = fmaf(t4.z, x[4 * mg + 2], acc);
-        acc = fmaf(t4.w, x[4 * mg + 3], acc);
+        for (int sc = 0; sc < r; ++sc) {
+          if (sc & 1) a1 = fmaf(tb[r * TM_STRIDE + sc], x[sc], a1);
+          else a0 = fmaf(tb[r * TM_STRIDE + sc], x[sc], a0);
+        }
+        x[r] = (r == j ? 1.f : 0.f) - (a0 + a1);            // rows above j stay 0, row j is 1
+        aim[AI(16 * i + r, 16 * i + j)] = tf32_rn(x[r]);
       }
-      const float tot = acc + __shfl_xor_sync(0xffffffffu, acc, 1);
-      const float xr = ((r == j) ? 1.f : 0.f) - tot;
-      if ((r & 1) == p) x[r >> 1] = xr;
-    }
-    float* ai = s.x.sol.ai + (j >> 2) * BS * 4 + (j & 3);
+    } else {
+      // zero the blocks above the diagonal: 6 blocks x 256 entries over 64 threads
+      const int z = tid - BS;
 #pragma unroll
-    for (int m = 0; m < 32; ++m) ai[(2 * m + p) * 4] = tf32_rn(x[m]);
+      for (int e = 0; e < 24; ++e) {
+        const int idx = z + 64 * e;                         // 0..1535
+        const int blk = idx >> 8, rr = (idx >> 4) & 15, cc = idx & 15;
+        const int bi = blk < 3 ? 0 : blk < 5 ? 1 : 2;       // (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
+        const int bj = blk < 3 ? blk + 1 : blk < 5 ? blk - 1 : 3;
+        aim[AI(16 * bi + rr, 16 * bj + cc)] = 0.f;
+      }
+    }
+    __syncthreads();
+    const int g8 = lane >> 2, t4 = lane & 3;
+    auto T_at = [&](int bi, int bk, int r, int cidx) { return tmm[(16 * bi + r) * TM_STRIDE + 16 * bk + cidx]; };
+    auto X_at = [&](int bi, int bk, int r, int cidx) { return aim[AI(16 * bi + r, 16 * bk + cidx)]; };
+    // acc[nt][..] += A(16x16) * B(16x16); A and B are read through (row, col) accessors
+    auto block_mma = [&](float (&acc)[2][4], auto a_at, auto b_at) {
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+        const uint32_t a[4] = {__float_as_uint(tf32_rn(a_at(g8, 8 * kt + t4))), __float_as_uint(tf32_rn(a_at(g8 + 8, 8 * kt + t4))),
+                               __float_as_uint(tf32_rn(a_at(g8, 8 * kt + t4 + 4))),
+                               __float_as_uint(tf32_rn(a_at(g8 + 8, 8 * kt + t4 + 4)))};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          const uint32_t b0 = __float_as_uint(tf32_rn(b_at(8 * kt + t4, 8 * nt + g8)));
+          const uint32_t b1 = __float_as_uint(tf32_rn(b_at(8 * kt + t4 + 4, 8 * nt + g8)));
+          asm volatile(
+              "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+              : "+f"(acc[nt][0]), "+f"(acc[nt][1]), "+f"(acc[nt][2]), "+f"(acc[nt][3])
+              : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+        }
+      }
+    };
+    // N_ik = D_i T_ik, in place over T_ik: warp w takes pairs w and w + 4 of (1,0) (2,0) (2,1) (3,0) (3,1) (3,2)
+#pragma unroll 1
+    for (int pidx = wid; pidx < 6; pidx += 4) {
+      const int bi = pidx < 1 ? 1 : pidx < 3 ? 2 : 3;
+      const int bk = pidx < 1 ? 0 : pidx < 3 ? pidx - 1 : pidx - 3;
+      float acc[2][4] = {};
+      block_mma(acc, [&](int r, int cidx) { return X_at(bi, bi, r, cidx); }, [&](int r, int cidx) { return T_at(bi, bk, r, cidx); });
+      __syncwarp();
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        float* d0 = tmm + (16 * bi + g8) * TM_STRIDE + 16 * bk + 8 * nt + 2 * t4;
+        d0[0] = acc[nt][0]; d0[1] = acc[nt][1];
+        d0[8 * TM_STRIDE] = acc[nt][2]; d0[8 * TM_STRIDE + 1] = acc[nt][3];
+      }
+    }
+    __syncthreads();
+    // X_ij, distance d = i - j = 1, 2, 3; warp w takes block (w + d, w)
+#pragma unroll 1
+    for (int d = 1; d < 4; ++d) {
+      if (wid + d < 4) {
+        const int bj = wid, bi = wid + d;
+        float acc[2][4] = {};
+#pragma unroll 1
+        for (int bk = bj; bk < bi; ++bk)
+          block_mma(acc, [&](int r, int cidx) { return T_at(bi, bk, r, cidx); }, [&](int r, int cidx) { return X_at(bk, bj, r, cidx); });
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          aim[AI(16 * bi + g8, 16 * bj + 8 * nt + 2 * t4)] = tf32_rn(-acc[nt][0]);
+          aim[AI(16 * bi + g8, 16 * bj + 8 * nt + 2 * t4 + 1)] = tf32_rn(-acc[nt][1]);
+          aim[AI(16 * bi + g8 + 8, 16 * bj + 8 * nt + 2 * t4)] = tf32_rn(-acc[nt][2]);
+          aim[AI(16 * bi + g8 + 8, 16 * bj + 8 * nt + 2 * t4 + 1)] = tf32_rn(-acc[nt][3]);
+        }
+      }
+      __syncthreads();
+    }
   }
   tc::fence_async_smem();
   tc::tc_fence_before_sync();
   __syncthreads();
 
+  PTICK(7);
   // ---- 4. MMA2 (tf32): W^T at TMEM columns 0..63, U^T at 64..127
   if (tid == 0 && !s.abort_flag) {
     tc::tc_fence_after_sync();
@@ -310,6 +391,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   }
   tc::mbar_wait(&s.bar_m2, 0, &s.abort_flag, status, 0x2000u);
   tc::tc_fence_after_sync();
+  PTICK(8);
 
   // ---- 5. W and Qg rows into the WQ staging image (E^T is dead now), U^T straight to global
   {
@@ -351,6 +433,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::fence_async_smem();
   tc::tc_fence_before_sync();
   __syncthreads();
+  PTICK(9);
   if (tid < 16 && !s.abort_flag) {
     char* g_wq = P.wq + (size_t)ch * (2 * BS * D * 2) + (size_t)tid * (2 * BS * 16);
     tc::bulk_s2g(g_wq, reinterpret_cast<const char*>(s.y.wq) + tid * A_PAD * 16, 2 * BS * 16);
@@ -358,6 +441,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     tc::bulk_wait_read_all();
   }
   __syncthreads();
+  PTICK(10);
   if (wid == 0) tc::tmem_dealloc(tm, kTmemCols);
 }
 
@@ -377,5 +461,11 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }
+
+#ifdef GDN2_SCAN_TIMING
+extern "C" int gdn2_debug_prep_timing(unsigned long long* out16) {
+  return cudaMemcpyFromSymbol(out16, g_prep_timing, sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : -6;
+}
+#endif
 
 }  // namespace gdn2
