@@ -7,11 +7,14 @@
 //     S     = a * S + k * u
 //     out  += S * (scale * q)
 //
-// Fast kernel (DK = DV = 128): one 128-thread block per (batch, head). Warp w owns key rows
-// [32w, 32w+32); lane l owns value columns [4l, 4l+4), so every state access is a 128-bit load
-// or store and a warp covers a full 512-byte row. The state tile lives in registers (128 per
-// thread) for all n tokens; the reductions over key rows are in-thread sums followed by one
-// 4-way cross-warp sum through shared memory.
+// Fast kernel (DK = DV = 128): one 128-thread block per (batch, head). Warp w owns value columns
+// [32w, 32w+32); inside the warp, 8 lanes x 4 columns cover those and the 4 lane groups split the key
+// rows into 32-row slabs, so every state access is a 128-bit load/store on full 128-byte lines and
+// the tile (128 registers per thread) stays in registers for all n tokens. Reductions over key rows
+// are in-thread sums plus two shuffle steps: no shared-memory reduction, no block barrier per token.
+// The output is formed from the OLD state in the same sweep as the read,
+//     o = scale*q^T (a*S + k u^T) = sum_r (scale*q_r*a_r) S_r + (scale*q.k) u,
+// and all sweeps use packed f32x2 arithmetic with per-row coefficients fetched as 128-bit broadcasts.
 //
 // Generic kernel: any DK <= 256 and any DV, one block per (32-column value tile, batch, head).
 #include "common.cuh"
@@ -22,6 +25,26 @@ namespace {
 
 constexpr int kTokBatch = 8;   // token vectors staged in shared memory per barrier round
 
+// packed fp32 pairs (Blackwell): two FMAs / multiplies per instruction on 64-bit register pairs
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return d;
+}
+
+constexpr int kRowPad = 132;   // 128 rows + one 16-byte slot per 32-row group: the 4 row groups hit distinct banks
+__device__ __forceinline__ int prow(int r) { return r + (r >> 5); }
+
 template <typename T>
 __global__ void __launch_bounds__(128, 3)
 decode_d128_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
@@ -31,72 +54,76 @@ decode_d128_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
   const int bh = blockIdx.x;
   const int ib = bh / H, ih = bh % H;
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+  const int rg = lane >> 3, cq = lane & 7;               // 32-row group, 4-column group inside the warp's 32 columns
+  const int col0 = 32 * wid + 4 * cq;
 
-  __shared__ float s_abk[kTokBatch][D];   // exp(g) * b * k
-  __shared__ float s_a[kTokBatch][D];     // exp(g)
-  __shared__ float s_k[kTokBatch][D];
-  __shared__ float s_q[kTokBatch][D];     // scale * q
-  __shared__ float s_wv[kTokBatch][D];    // w * v
-  __shared__ float4 s_red[2][4][32];      // cross-warp partial sums, double buffered
+  // per token and key row: (a*b*k, a*b*k, scale*q*a, scale*q*a) and (k, k, a, a), duplicated for the packed math
+  __shared__ float4 s_p1[kTokBatch][kRowPad];
+  __shared__ float4 s_p2[kTokBatch][kRowPad];
+  __shared__ float s_wv[kTokBatch][D];                   // w * v
+  __shared__ float s_qk[kTokBatch][4];                   // per-warp partial sums of scale * q . k
 
   float4 S[32];
-  float4* gS = reinterpret_cast<float4*>(state + ((size_t)bh * D + wid * 32) * D) + lane;
+  float4* gS = reinterpret_cast<float4*>(state + ((size_t)bh * D + 32 * rg) * D + col0);
 #pragma unroll
   for (int i = 0; i < 32; ++i) S[i] = __ldcs(gS + i * (D / 4));
 
   for (int t0 = 0; t0 < n; t0 += kTokBatch) {
     const int nt = min(kTokBatch, n - t0);
-    __syncthreads();   // previous round's vectors are no longer read
+    __syncthreads();                                     // the previous batch's vectors are no longer read
     for (int j = 0; j < nt; ++j) {
       const size_t tok = ((size_t)ib * in_bs + (t0 + j)) * H + ih;
       const float a = exp2f(g[tok * D + tid] * kLog2e);
       const float kk = to_f32(k[tok * D + tid]);
-      s_a[j][tid] = a;
-      s_abk[j][tid] = a * to_f32(b[tok * D + tid]) * kk;
-      s_k[j][tid] = kk;
-      s_q[j][tid] = to_f32(q[tok * D + tid]) * scale;
+      const float abk = a * to_f32(b[tok * D + tid]) * kk;
+      const float qs = to_f32(q[tok * D + tid]) * scale;
+      s_p1[j][prow(tid)] = make_float4(abk, abk, qs * a, qs * a);
+      s_p2[j][prow(tid)] = make_float4(kk, kk, a, a);
       s_wv[j][tid] = to_f32(w[tok * D + tid]) * to_f32(v[tok * D + tid]);
+      float qk = qs * kk;
+#pragma unroll
+      for (int off = 16; off; off >>= 1) qk += __shfl_xor_sync(0xffffffffu, qk, off);
+      if (lane == 0) s_qk[j][wid] = qk;
     }
     __syncthreads();
 
     for (int j = 0; j < nt; ++j) {
-      // read of the decayed state with the erase row
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      // pass 1 over the old state: read with the erase row, and the part of the output that does not depend on u
+      float2 rd0 = make_float2(0.f, 0.f), rd1 = rd0, oa0 = rd0, oa1 = rd0;
+      const float4* p1 = &s_p1[j][33 * rg];
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float c = s_abk[j][wid * 32 + i];
-        acc.x = fmaf(S[i].x, c, acc.x); acc.y = fmaf(S[i].y, c, acc.y);
-        acc.z = fmaf(S[i].z, c, acc.z); acc.w = fmaf(S[i].w, c, acc.w);
+        const float4 P = p1[i];
+        const float2 c_rd = make_float2(P.x, P.y), c_oa = make_float2(P.z, P.w);
+        rd0 = ffma2(make_float2(S[i].x, S[i].y), c_rd, rd0);
+        rd1 = ffma2(make_float2(S[i].z, S[i].w), c_rd, rd1);
+        oa0 = ffma2(make_float2(S[i].x, S[i].y), c_oa, oa0);
+        oa1 = ffma2(make_float2(S[i].z, S[i].w), c_oa, oa1);
       }
-      s_red[0][wid][lane] = acc;
-      __syncthreads();
-      float4 u = reinterpret_cast<const float4*>(s_wv[j])[lane];
+      float r8[8] = {rd0.x, rd0.y, rd1.x, rd1.y, oa0.x, oa0.y, oa1.x, oa1.y};
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const float4 p = s_red[0][x][lane];
-        u.x -= p.x; u.y -= p.y; u.z -= p.z; u.w -= p.w;
+      for (int x = 0; x < 8; ++x) {
+        r8[x] += __shfl_xor_sync(0xffffffffu, r8[x], 8);
+        r8[x] += __shfl_xor_sync(0xffffffffu, r8[x], 16);
       }
-      // decay + rank-1 write, then the output read
-      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 wv = *reinterpret_cast<const float4*>(&s_wv[j][col0]);
+      const float u0 = wv.x - r8[0], u1 = wv.y - r8[1], u2 = wv.z - r8[2], u3 = wv.w - r8[3];
+      if (rg == 0) {
+        const float qk = s_qk[j][0] + s_qk[j][1] + s_qk[j][2] + s_qk[j][3];
+        T* po = o + (((size_t)ib * o_bs + (t0 + j)) * H + ih) * D + col0;
+        po[0] = from_f32<T>(fmaf(qk, u0, r8[4])); po[1] = from_f32<T>(fmaf(qk, u1, r8[5]));
+        po[2] = from_f32<T>(fmaf(qk, u2, r8[6])); po[3] = from_f32<T>(fmaf(qk, u3, r8[7]));
+      }
+      // pass 2: decay and rank-1 write
+      const float2 uu0 = make_float2(u0, u1), uu1 = make_float2(u2, u3);
+      const float4* p2 = &s_p2[j][33 * rg];
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float a = s_a[j][wid * 32 + i], kk = s_k[j][wid * 32 + i], qq = s_q[j][wid * 32 + i];
-        S[i].x = fmaf(a, S[i].x, kk * u.x); S[i].y = fmaf(a, S[i].y, kk * u.y);
-        S[i].z = fmaf(a, S[i].z, kk * u.z); S[i].w = fmaf(a, S[i].w, kk * u.w);
-        acc.x = fmaf(S[i].x, qq, acc.x); acc.y = fmaf(S[i].y, qq, acc.y);
-        acc.z = fmaf(S[i].z, qq, acc.z); acc.w = fmaf(S[i].w, qq, acc.w);
-      }
-      s_red[1][wid][lane] = acc;
-      __syncthreads();
-      if (wid == 0) {
-        float4 r = s_red[1][0][lane];
-#pragma unroll
-        for (int x = 1; x < 4; ++x) {
-          const float4 p = s_red[1][x][lane];
-          r.x += p.x; r.y += p.y; r.z += p.z; r.w += p.w;
-        }
-        T* po = o + (((size_t)ib * o_bs + (t0 + j)) * H + ih) * D + lane * 4;
-        po[0] = from_f32<T>(r.x); po[1] = from_f32<T>(r.y); po[2] = from_f32<T>(r.z); po[3] = from_f32<T>(r.w);
+        const float4 Q = p2[i];
+        const float2 kk2 = make_float2(Q.x, Q.y), a2 = make_float2(Q.z, Q.w);
+        const float2 n0 = ffma2(a2, make_float2(S[i].x, S[i].y), fmul2(kk2, uu0));
+        const float2 n1 = ffma2(a2, make_float2(S[i].z, S[i].w), fmul2(kk2, uu1));
+        S[i] = make_float4(n0.x, n0.y, n1.x, n1.y);
       }
     }
   }
