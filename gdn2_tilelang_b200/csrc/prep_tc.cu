@@ -71,7 +71,6 @@ struct PrepTcSmem {
   int abort_flag;
 };
 
-__device__ __forceinline__ float bf(const __nv_bfloat16* p) { return __bfloat162float(__ldg(p)); }
 __device__ __forceinline__ float pick4(int j, float a0, float a1, float a2, float a3) {
   return j == 0 ? a0 : j == 1 ? a1 : j == 2 ? a2 : a3;
 }
@@ -131,7 +130,8 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const uint32_t tm = s.tmem_base;
 
   PTICK(1);
-  // ---- 1b. gated operands of channel c: a rolled loop over 16 token quads, the next quad's loads in flight
+  // ---- 1b. gated operands of channel c, one 16-token sub-block per iteration; the next sub-block's
+  //          64 loads are issued (raw, unconverted) before the current one is processed
   {
     const __nv_bfloat16* qp = q + row0 * D + c;
     const __nv_bfloat16* kp = k + row0 * D + c;
@@ -139,64 +139,70 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
     const int cb = (c >> 3) * B_PAD * 8 + (c & 7);
     char* kgt_g = P.kgt + (size_t)ch * (D * BS * 2) + c * 16;   // fp16 image [tok/8][128 dk][8]
-    float gq[4], kq[4], qq[4], bq[4], gn[4], kn4[4], qn[4], bn[4];
+    float gc[16], gn[16];
+    __nv_bfloat16 kc[16], qc[16], bc[16], kn_[16], qn_[16], bn_[16];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 16; ++u) {
       const size_t off = u * rstride;
-      gq[u] = __ldg(gp + off) * kLog2e; kq[u] = bf(kp + off); qq[u] = bf(qp + off); bq[u] = bf(bp + off);
+      gc[u] = __ldg(gp + off); kc[u] = __ldg(kp + off); qc[u] = __ldg(qp + off); bc[u] = __ldg(bp + off);
     }
-    float run = 0.f, ref = 0.f, refn = 0.f, gam_ref = 0.f, kg_c = 1.f, cc_a = 1.f, cc_b = 1.f;
-    int j = 0, off_j = 0;
+    float run = 0.f;
 #pragma unroll 1
-    for (int tq = 0; tq < 16; ++tq) {
-      if (tq + 1 < 16) {
+    for (int j = 0; j < 4; ++j) {
+      if (j < 3) {
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const size_t off = (4 * (tq + 1) + u) * rstride;
-          gn[u] = __ldg(gp + off) * kLog2e; kn4[u] = bf(kp + off); qn[u] = bf(qp + off); bn[u] = bf(bp + off);
+        for (int u = 0; u < 16; ++u) {
+          const size_t off = (16 * (j + 1) + u) * rstride;
+          gn[u] = __ldg(gp + off); kn_[u] = __ldg(kp + off); qn_[u] = __ldg(qp + off); bn_[u] = __ldg(bp + off);
         }
       }
-      if ((tq & 3) == 0) {                                      // entering sub-block j = tq / 4
-        j = tq >> 2;
-        off_j = 8 * j * (j + 1);                                // first row of B_j: 0, 16, 48, 96
-        ref = pick4(j, ref0, ref1, ref2, ref3);
-        refn = pick4(j, ref1, ref2, ref3, 0.f);                 // ref of the next sub-block (unused for j = 3)
-        gam_ref = exp2f(ref);
-        kg_c = (j < 3) ? exp2f(g_last - refn) : 1.f;
-        cc_a = exp2f(pick4(j, ref2, ref3, 0.f, 0.f) - refn);    // B_{j+2} relative to B_{j+1}
-        cc_b = exp2f(ref3 - refn);                              // B_{j+3} relative to B_{j+1} (j = 0 only)
-      }
-      float e4[4], kg4[4], qg4[4];
+      const int off_j = 8 * j * (j + 1);                       // first row of B_j: 0, 16, 48, 96
+      const float ref = pick4(j, ref0, ref1, ref2, ref3);
+      const float refn = pick4(j, ref1, ref2, ref3, 0.f);      // ref of the next sub-block (unused for j = 3)
+      const float gam_ref = exp2f(ref);
+      const float kg_c = (j < 3) ? exp2f(g_last - refn) : 1.f;
+      const float cc_a = exp2f(pick4(j, ref2, ref3, 0.f, 0.f) - refn);   // B_{j+2} relative to B_{j+1}
+      const float cc_b = exp2f(ref3 - refn);                               // B_{j+3} relative to B_{j+1} (j = 0 only)
+      uint32_t qgp[8], kgp[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int t = 4 * tq + u;
-        run += gq[u];
-        const float kf = kq[u], qf = qq[u];
-        const float a = exp2f(run - ref);                       // <= 1
-        const float co = exp2f(ref - run);                      // >= 1, bounded by the span check
-        const float nx = (j < 3) ? exp2f(refn - run) : exp2f(g_last - run);   // <= 1
-        const float e = bq[u] * kf;
-        s.x.ops.a_own[ca + t * 8] = __float2bfloat16_rn(e * a);
-        s.x.ops.a_own[ca + (BS + t) * 8] = __float2bfloat16_rn(qf * a);
-        s.x.ops.bfam[cb + (off_j + t) * 8] = __float2bfloat16_rn(kf * co);
-        const float kn = kf * nx;
-        if (j < 3) s.x.ops.bfam[cb + (8 * (j + 1) * (j + 2) + t) * 8] = __float2bfloat16_rn(kn);
-        if (j < 2) s.x.ops.bfam[cb + (8 * (j + 2) * (j + 3) + t) * 8] = __float2bfloat16_rn(kn * cc_a);
-        if (j < 1) s.x.ops.bfam[cb + (96 + t) * 8] = __float2bfloat16_rn(kn * cc_b);
-        const float gam = a * gam_ref;
-        e4[u] = tf32_rn(e * gam);
-        qg4[u] = scale * qf * gam;
-        kg4[u] = kn * kg_c * kValScale;
-      }
-      *reinterpret_cast<float4*>(&s.y.et[(tq * D + c) * 4]) = make_float4(e4[0], e4[1], e4[2], e4[3]);
-      __half2 h01 = __floats2half2_rn(kg4[0], kg4[1]), h23 = __floats2half2_rn(kg4[2], kg4[3]);
-      *reinterpret_cast<uint2*>(kgt_g + (size_t)(tq >> 1) * D * 16 + (tq & 1) * 8) =
-          make_uint2(*reinterpret_cast<uint32_t*>(&h01), *reinterpret_cast<uint32_t*>(&h23));
-      __nv_bfloat162 p01 = __floats2bfloat162_rn(qg4[0], qg4[1]), p23 = __floats2bfloat162_rn(qg4[2], qg4[3]);
-      const uint32_t qgp[2] = {*reinterpret_cast<uint32_t*>(&p01), *reinterpret_cast<uint32_t*>(&p23)};
-      tc::tmem_st2(tc::tmem_addr(tm, wid * 32, kQgCol + 2 * tq), qgp);
+      for (int t4 = 0; t4 < 4; ++t4) {
+        float e4[4], kg4[4], qg4[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) { gq[u] = gn[u]; kq[u] = kn4[u]; qq[u] = qn[u]; bq[u] = bn[u]; }
+        for (int u = 0; u < 4; ++u) {
+          const int uu = 4 * t4 + u;
+          const int t = 16 * j + uu;
+          run += gc[uu] * kLog2e;
+          const float kf = __bfloat162float(kc[uu]), qf = __bfloat162float(qc[uu]);
+          const float a = exp2f(run - ref);                     // <= 1
+          const float co = exp2f(ref - run);                    // >= 1, bounded by the span check
+          const float nx = (j < 3) ? exp2f(refn - run) : exp2f(g_last - run);   // <= 1
+          const float e = __bfloat162float(bc[uu]) * kf;
+          s.x.ops.a_own[ca + t * 8] = __float2bfloat16_rn(e * a);
+          s.x.ops.a_own[ca + (BS + t) * 8] = __float2bfloat16_rn(qf * a);
+          s.x.ops.bfam[cb + (off_j + t) * 8] = __float2bfloat16_rn(kf * co);
+          const float kn = kf * nx;
+          if (j < 3) s.x.ops.bfam[cb + (8 * (j + 1) * (j + 2) + t) * 8] = __float2bfloat16_rn(kn);
+          if (j < 2) s.x.ops.bfam[cb + (8 * (j + 2) * (j + 3) + t) * 8] = __float2bfloat16_rn(kn * cc_a);
+          if (j < 1) s.x.ops.bfam[cb + (96 + t) * 8] = __float2bfloat16_rn(kn * cc_b);
+          const float gam = a * gam_ref;
+          e4[u] = tf32_rn(e * gam);
+          qg4[u] = scale * qf * gam;
+          kg4[u] = kn * kg_c * kValScale;
+        }
+        const int tq = 4 * j + t4;                              // token quad index
+        *reinterpret_cast<float4*>(&s.y.et[(tq * D + c) * 4]) = make_float4(e4[0], e4[1], e4[2], e4[3]);
+        __half2 h01 = __floats2half2_rn(kg4[0], kg4[1]), h23 = __floats2half2_rn(kg4[2], kg4[3]);
+        kgp[2 * t4] = *reinterpret_cast<uint32_t*>(&h01);
+        kgp[2 * t4 + 1] = *reinterpret_cast<uint32_t*>(&h23);
+        __nv_bfloat162 p01 = __floats2bfloat162_rn(qg4[0], qg4[1]), p23 = __floats2bfloat162_rn(qg4[2], qg4[3]);
+        qgp[2 * t4] = *reinterpret_cast<uint32_t*>(&p01);
+        qgp[2 * t4 + 1] = *reinterpret_cast<uint32_t*>(&p23);
+      }
+      tc::tmem_st8(tc::tmem_addr(tm, wid * 32, kQgCol + 8 * j), qgp);
+      *reinterpret_cast<uint4*>(kgt_g + (size_t)(2 * j) * D * 16) = make_uint4(kgp[0], kgp[1], kgp[2], kgp[3]);
+      *reinterpret_cast<uint4*>(kgt_g + (size_t)(2 * j + 1) * D * 16) = make_uint4(kgp[4], kgp[5], kgp[6], kgp[7]);
+#pragma unroll
+      for (int u = 0; u < 16; ++u) { gc[u] = gn[u]; kc[u] = kn_[u]; qc[u] = qn_[u]; bc[u] = bn_[u]; }
     }
     tc::tmem_st_wait();
     P.gl[(size_t)ch * D + c] = exp2f(g_last);
@@ -224,13 +230,22 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   {
     const __nv_bfloat16* vp = v + row0 * D + c;
     const __nv_bfloat16* wp = w + row0 * D + c;
+    __nv_bfloat16 vr[2][16], wr[2][16];                   // raw values: converted one group behind the loads
 #pragma unroll
-    for (int jj = 0; jj < 4; ++jj)
+    for (int u = 0; u < 16; ++u) { vr[0][u] = __ldg(vp + u * rstride); wr[0][u] = __ldg(wp + u * rstride); }
 #pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        const size_t off = (16 * jj + u) * rstride;
-        zv[jj][u] = tf32_rn(bf(vp + off) * bf(wp + off));
+    for (int jj = 0; jj < 4; ++jj) {
+      if (jj < 3) {
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const size_t off = (16 * (jj + 1) + u) * rstride;
+          vr[(jj + 1) & 1][u] = __ldg(vp + off); wr[(jj + 1) & 1][u] = __ldg(wp + off);
+        }
       }
+#pragma unroll
+      for (int u = 0; u < 16; ++u)
+        zv[jj][u] = tf32_rn(__bfloat162float(vr[jj & 1][u]) * __bfloat162float(wr[jj & 1][u]));
+    }
   }
   PTICK(4);
   tc::mbar_wait(&s.bar_m1, 0, &s.abort_flag, status, 0x1000u);

@@ -93,15 +93,6 @@ __device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 256;"
 // barrier among the 128 output threads only (hardware barrier 2)
 __device__ __forceinline__ void output_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
-__device__ __forceinline__ uint4 pack8_f16(const float* x) {
-  uint4 r;
-  __half2 t;
-  t = __floats2half2_rn(x[0], x[1]); r.x = *reinterpret_cast<uint32_t*>(&t);
-  t = __floats2half2_rn(x[2], x[3]); r.y = *reinterpret_cast<uint32_t*>(&t);
-  t = __floats2half2_rn(x[4], x[5]); r.z = *reinterpret_cast<uint32_t*>(&t);
-  t = __floats2half2_rn(x[6], x[7]); r.w = *reinterpret_cast<uint32_t*>(&t);
-  return r;
-}
 __device__ __forceinline__ float pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
   return __uint_as_float(*reinterpret_cast<uint32_t*>(&t));
