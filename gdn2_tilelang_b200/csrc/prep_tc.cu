@@ -41,6 +41,7 @@ constexpr int B_PAD = 161;        // 160 key rows (16 + 32 + 48 + 64) + 1 pad ro
 constexpr int TM_STRIDE = 68;     // floats per Tm row (row-major, padded against bank conflicts)
 constexpr float kMaxSpanLog2 = 64.f;
 constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kZCol = 192;   // TMEM columns [192,256): w*v of the thread's value channel (fp32)
 constexpr uint32_t kQgCol = 160;  // TMEM columns [160,192): packed Qg of the thread's channel
 
 #ifdef GDN2_SCAN_TIMING
@@ -71,6 +72,13 @@ struct PrepTcSmem {
   int abort_flag;
 };
 
+// 2^x by the hardware approximation alone (about 2 ulp; arguments here are differences of log2 decays,
+// results that underflow flush to zero, which is the right answer for a vanished decay)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float pick4(int j, float a0, float a1, float a2, float a3) {
   return j == 0 ? a0 : j == 1 ? a1 : j == 2 ? a2 : a3;
 }
@@ -94,6 +102,24 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
 #ifdef GDN2_SCAN_TIMING
   long long tprev = clock64();
 #endif
+
+  // Pull the whole input tile of this chunk-head towards L2 before anything depends on it: 64 rows x
+  // (5 x 256 B + 512 B) = 896 128-byte lines, 7 per thread.
+  {
+    const char* base[6] = {reinterpret_cast<const char*>(g + row0 * D), reinterpret_cast<const char*>(k + row0 * D),
+                           reinterpret_cast<const char*>(q + row0 * D), reinterpret_cast<const char*>(b + row0 * D),
+                           reinterpret_cast<const char*>(v + row0 * D), reinterpret_cast<const char*>(w + row0 * D)};
+#pragma unroll
+    for (int i = 0; i < 7; ++i) {
+      const int line = tid + 128 * i;                     // 0..895: g takes lines [0,256), then 128 per bf16 tensor
+      const int ten = line < 256 ? 0 : 1 + ((line - 256) >> 7);
+      const int rem = line < 256 ? line : (line - 256) & 127;
+      const int per_row = ten == 0 ? 4 : 2;
+      const int rowi = rem / per_row, seg = rem % per_row;
+      const char* ptr = base[ten] + (size_t)rowi * rstride * (ten == 0 ? 4 : 2) + seg * 128;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+    }
+  }
 
   // ---- 1a. G at the first row of every sub-block and at the last token; decay-span check
   float ref0 = 0.f, ref1 = 0.f, ref2 = 0.f, ref3 = 0.f, g_last;
@@ -159,10 +185,10 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       const int off_j = 8 * j * (j + 1);                       // first row of B_j: 0, 16, 48, 96
       const float ref = pick4(j, ref0, ref1, ref2, ref3);
       const float refn = pick4(j, ref1, ref2, ref3, 0.f);      // ref of the next sub-block (unused for j = 3)
-      const float gam_ref = exp2f(ref);
-      const float kg_c = (j < 3) ? exp2f(g_last - refn) : 1.f;
-      const float cc_a = exp2f(pick4(j, ref2, ref3, 0.f, 0.f) - refn);   // B_{j+2} relative to B_{j+1}
-      const float cc_b = exp2f(ref3 - refn);                               // B_{j+3} relative to B_{j+1} (j = 0 only)
+      const float gam_ref = ex2(ref);
+      const float kg_c = (j < 3) ? ex2(g_last - refn) : 1.f;
+      const float cc_a = ex2(pick4(j, ref2, ref3, 0.f, 0.f) - refn);   // B_{j+2} relative to B_{j+1}
+      const float cc_b = ex2(ref3 - refn);                               // B_{j+3} relative to B_{j+1} (j = 0 only)
       uint32_t qgp[8], kgp[8];
 #pragma unroll
       for (int t4 = 0; t4 < 4; ++t4) {
@@ -173,9 +199,9 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
           const int t = 16 * j + uu;
           run += gc[uu] * kLog2e;
           const float kf = __bfloat162float(kc[uu]), qf = __bfloat162float(qc[uu]);
-          const float a = exp2f(run - ref);                     // <= 1
-          const float co = exp2f(ref - run);                    // >= 1, bounded by the span check
-          const float nx = (j < 3) ? exp2f(refn - run) : exp2f(g_last - run);   // <= 1
+          const float a = ex2(run - ref);                     // <= 1
+          const float co = ex2(ref - run);                    // >= 1, bounded by the span check
+          const float nx = (j < 3) ? ex2(refn - run) : ex2(g_last - run);   // <= 1
           const float e = __bfloat162float(bc[uu]) * kf;
           s.x.ops.a_own[ca + t * 8] = __float2bfloat16_rn(e * a);
           s.x.ops.a_own[ca + (BS + t) * 8] = __float2bfloat16_rn(qf * a);
@@ -205,7 +231,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       for (int u = 0; u < 16; ++u) { gc[u] = gn[u]; kc[u] = kn_[u]; qc[u] = qn_[u]; bc[u] = bn_[u]; }
     }
     tc::tmem_st_wait();
-    P.gl[(size_t)ch * D + c] = exp2f(g_last);
+    P.gl[(size_t)ch * D + c] = ex2(g_last);
   }
   tc::fence_async_smem();
   tc::tc_fence_before_sync();
@@ -215,7 +241,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   // ---- 2. MMA1: D_i[128 x 16(i+1)] at TMEM columns 0, 16, 48, 96
   if (tid == 0) {
     tc::tc_fence_after_sync();
-#pragma unroll
+#pragma unroll 1
     for (int i = 0; i < 4; ++i) {
       const int off = 8 * i * (i + 1);
       tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, off), tc::smem_u32(s.x.ops.a_own), A_PAD,
@@ -226,26 +252,31 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   }
   PTICK(3);
   // value side: raw loads issued while the tensor core works
-  float zv[4][16];
+  // z = w*v of this thread's value channel waits in TMEM columns [192,256) of its own lane until the
+  // MMA1 operands are dead and (w*v)^T can take their place in shared memory
   {
     const __nv_bfloat16* vp = v + row0 * D + c;
     const __nv_bfloat16* wp = w + row0 * D + c;
-    __nv_bfloat16 vr[2][16], wr[2][16];                   // raw values: converted one group behind the loads
+    __nv_bfloat16 vr[16], wr[16], vn[16], wn[16];         // raw values: converted one group behind the loads
 #pragma unroll
-    for (int u = 0; u < 16; ++u) { vr[0][u] = __ldg(vp + u * rstride); wr[0][u] = __ldg(wp + u * rstride); }
-#pragma unroll
+    for (int u = 0; u < 16; ++u) { vr[u] = __ldg(vp + u * rstride); wr[u] = __ldg(wp + u * rstride); }
+#pragma unroll 1
     for (int jj = 0; jj < 4; ++jj) {
       if (jj < 3) {
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
           const size_t off = (16 * (jj + 1) + u) * rstride;
-          vr[(jj + 1) & 1][u] = __ldg(vp + off); wr[(jj + 1) & 1][u] = __ldg(wp + off);
+          vn[u] = __ldg(vp + off); wn[u] = __ldg(wp + off);
         }
       }
+      float z[16];
 #pragma unroll
-      for (int u = 0; u < 16; ++u)
-        zv[jj][u] = tf32_rn(__bfloat162float(vr[jj & 1][u]) * __bfloat162float(wr[jj & 1][u]));
+      for (int u = 0; u < 16; ++u) z[u] = tf32_rn(__bfloat162float(vr[u]) * __bfloat162float(wr[u]));
+      tc::tmem_st16(tc::tmem_addr(tm, wid * 32, kZCol + 16 * jj), z);
+#pragma unroll
+      for (int u = 0; u < 16; ++u) { vr[u] = vn[u]; wr[u] = wn[u]; }
     }
+    tc::tmem_st_wait();
   }
   PTICK(4);
   tc::mbar_wait(&s.bar_m1, 0, &s.abort_flag, status, 0x1000u);
@@ -261,10 +292,11 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     const bool hi = lane >= 16;
     const uint32_t t_lo = tc::tmem_addr(tm, wid * 32, 8 * i0 * (i0 + 1));
     const uint32_t t_hi = tc::tmem_addr(tm, wid * 32, 8 * (i0 + 1) * (i0 + 2));
-    float row[BS];
-#pragma unroll
+    float* tr = s.x.sol.tm + r * TM_STRIDE;
+    __nv_bfloat16* ag = reinterpret_cast<__nv_bfloat16*>(P.aqk + (size_t)ch * (BS * BS * 2));
+#pragma unroll 1
     for (int cg = 0; cg < 4; ++cg) {
-      float lo16[16], hi16[16];
+      float lo16[16], hi16[16], row[16];
 #pragma unroll
       for (int x = 0; x < 16; ++x) { lo16[x] = 0.f; hi16[x] = 0.f; }
       if (cg <= i0) tc::tmem_ld16(t_lo + 16 * cg, lo16);          // warp-uniform conditions
@@ -275,26 +307,29 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         const int sc = 16 * cg + x;
         const float val = hi ? hi16[x] : lo16[x];
         const bool keep = is_q ? (sc <= r) : (sc < r);
-        row[sc] = keep ? (is_q ? val * scale : val) : 0.f;
+        row[x] = keep ? (is_q ? val * scale : val) : 0.f;
+      }
+      if (!is_q) {
+#pragma unroll
+        for (int m4 = 0; m4 < 4; ++m4)
+          *reinterpret_cast<float4*>(tr + 16 * cg + 4 * m4) =
+              make_float4(row[4 * m4], row[4 * m4 + 1], row[4 * m4 + 2], row[4 * m4 + 3]);
+      } else {
+        *reinterpret_cast<uint4*>(ag + ((2 * cg) * BS + r) * 8) = tc::pack8_bf16(&row[0]);
+        *reinterpret_cast<uint4*>(ag + ((2 * cg + 1) * BS + r) * 8) = tc::pack8_bf16(&row[8]);
       }
     }
-    if (!is_q) {
-      float* tr = s.x.sol.tm + r * TM_STRIDE;
-#pragma unroll
-      for (int m4 = 0; m4 < 16; ++m4)
-        *reinterpret_cast<float4*>(tr + 4 * m4) = make_float4(row[4 * m4], row[4 * m4 + 1], row[4 * m4 + 2], row[4 * m4 + 3]);
-    } else {
-      __nv_bfloat16* ag = reinterpret_cast<__nv_bfloat16*>(P.aqk + (size_t)ch * (BS * BS * 2));
-#pragma unroll
-      for (int kc = 0; kc < 8; ++kc)
-        *reinterpret_cast<uint4*>(ag + (kc * BS + r) * 8) = tc::pack8_bf16(&row[kc * 8]);
-    }
-#pragma unroll
-    for (int jj = 0; jj < 4; ++jj)
+    // (w*v)^T image from the TMEM stash
+#pragma unroll 1
+    for (int jj = 0; jj < 4; ++jj) {
+      float z[16];
+      tc::tmem_ld16(tc::tmem_addr(tm, wid * 32, kZCol + 16 * jj), z);
+      tc::tmem_ld_wait();
 #pragma unroll
       for (int t4 = 0; t4 < 4; ++t4)
         *reinterpret_cast<float4*>(&s.x.sol.zt[((4 * jj + t4) * D + c) * 4]) =
-            make_float4(zv[jj][4 * t4], zv[jj][4 * t4 + 1], zv[jj][4 * t4 + 2], zv[jj][4 * t4 + 3]);
+            make_float4(z[4 * t4], z[4 * t4 + 1], z[4 * t4 + 2], z[4 * t4 + 3]);
+    }
   }
   tc::tc_fence_before_sync();
   __syncthreads();
@@ -416,7 +451,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
     char* ut_g = P.ut + (size_t)ch * (D * BS * 2) + c * 16;       // fp16 image [tok/8][128 dv][8]
     float val[32];
-#pragma unroll
+#pragma unroll 1
     for (int half = 0; half < 2; ++half) {
       tc::tmem_ld32(tc::tmem_addr(tm, wid * 32, half * 32), val);
       tc::tmem_ld_wait();
@@ -431,7 +466,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       reinterpret_cast<uint16_t*>(s.y.wq)[ca + (BS + 2 * i) * 8] = static_cast<uint16_t>(pk & 0xFFFFu);
       reinterpret_cast<uint16_t*>(s.y.wq)[ca + (BS + 2 * i + 1) * 8] = static_cast<uint16_t>(pk >> 16);
     }
-#pragma unroll
+#pragma unroll 1
     for (int half = 0; half < 2; ++half) {
       tc::tmem_ld32(tc::tmem_addr(tm, wid * 32, 64 + half * 32), val);
       tc::tmem_ld_wait();

@@ -235,9 +235,12 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 // D[128 x N] (+)= A[128 x K] * B[N x K]^T, A in TMEM (8 columns per 16-element K step), B a K-chunked image.
 __device__ __forceinline__ void mma_f16_ts_ktile(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr, uint32_t b_rows,
                                                  int K, uint32_t idesc, bool accumulate_first) {
+  uint64_t bd = kchunk_desc(b_addr, b_rows);
+  const uint64_t bstep = (2u * b_rows * 16u) >> 4;
+#pragma unroll
   for (int ks = 0; ks < K / 16; ++ks) {
-    const uint64_t bd = kchunk_desc(b_addr + ks * 2 * b_rows * 16, b_rows);
     mma_f16_ts(d_tmem, a_tmem + ks * 8, bd, idesc, (ks > 0 || accumulate_first) ? 1u : 0u);
+    bd += bstep;
   }
 }
 
@@ -248,21 +251,26 @@ __device__ __forceinline__ void mma_commit(uint64_t* bar) {
 }
 
 // D[128 x N] (+)= A[128 x K] * B[N x K]^T over a K-chunked bf16 image pair; K elements, 16 per MMA.
+// The descriptors are built once; each K step only bumps their 14-bit start-address fields.
 __device__ __forceinline__ void mma_bf16_ktile(uint32_t d_tmem, uint32_t a_addr, uint32_t a_rows, uint32_t b_addr,
                                                uint32_t b_rows, int K, uint32_t idesc, bool accumulate_first) {
+  uint64_t ad = kchunk_desc(a_addr, a_rows), bd = kchunk_desc(b_addr, b_rows);
+  const uint64_t astep = (2u * a_rows * 16u) >> 4, bstep = (2u * b_rows * 16u) >> 4;
+#pragma unroll
   for (int ks = 0; ks < K / 16; ++ks) {
-    const uint64_t ad = kchunk_desc(a_addr + ks * 2 * a_rows * 16, a_rows);
-    const uint64_t bd = kchunk_desc(b_addr + ks * 2 * b_rows * 16, b_rows);
     mma_bf16(d_tmem, ad, bd, idesc, (ks > 0 || accumulate_first) ? 1u : 0u);
+    ad += astep; bd += bstep;
   }
 }
 // Same for fp32 images read as tf32; 8 K elements per MMA.
 __device__ __forceinline__ void mma_tf32_ktile(uint32_t d_tmem, uint32_t a_addr, uint32_t a_rows, uint32_t b_addr,
                                                uint32_t b_rows, int K, uint32_t idesc, bool accumulate_first) {
+  uint64_t ad = kchunk_desc(a_addr, a_rows), bd = kchunk_desc(b_addr, b_rows);
+  const uint64_t astep = (2u * a_rows * 16u) >> 4, bstep = (2u * b_rows * 16u) >> 4;
+#pragma unroll
   for (int ks = 0; ks < K / 8; ++ks) {
-    const uint64_t ad = kchunk_desc(a_addr + ks * 2 * a_rows * 16, a_rows);
-    const uint64_t bd = kchunk_desc(b_addr + ks * 2 * b_rows * 16, b_rows);
     mma_tf32(d_tmem, ad, bd, idesc, (ks > 0 || accumulate_first) ? 1u : 0u);
+    ad += astep; bd += bstep;
   }
 }
 
