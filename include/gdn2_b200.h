@@ -141,7 +141,7 @@ int gdn2_selftest_mma(const float* a, const float* bt, float* out, void* stream)
  * S must be a multiple of 64 (send a ragged tail through gdn2_decode).
  *
  * Limit: the problem's scratch, gdn2_prefill_workspace_bytes(B, S, H, DK, DV, dtype, AUTO), must
- * not exceed GDN2_STATIC_SCRATCH_BYTES -- about 320 chunk-heads (B * H * S/64) at DK = DV = 128 in
+ * not exceed GDN2_STATIC_SCRATCH_BYTES -- about 450 chunk-heads (B * H * S/64) at DK = DV = 128 in
  * bf16. Larger problems return GDN2_ERR_STATIC_LIMIT and launch nothing; split them over batch,
  * heads or sequence segments, or use the two-call form. Every GPU that loads the library holds the
  * array until the process exits.
