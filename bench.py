@@ -203,15 +203,15 @@ def main():
     B, S, H, DK, DV = (CFG[x] for x in ("B", "S", "H", "DK", "DV"))
     if args.profile_case:
         # small enough for a multi-pass capture, larger than L2: prefill B=1 S=4096+37 (workspace 107 MB),
-        # decode B=32 (state 134 MB)
+        # decode B=128 (state 134 MB)
         if args.profile_case == "prefill":
             ins = device_inputs(1, 4096 + 37, H, DK, DV, dev, seed=0)
             for _ in range(3):
                 gdn2.gdn2_prefill(*ins)
         else:
-            state = torch.randn(32, H, DK, DV, device=dev) * 0.02
+            state = torch.randn(128, H, DK, DV, device=dev) * 0.02
             for n in (1, 8):
-                dq = device_inputs(32, n, H, DK, DV, dev, seed=n)
+                dq = device_inputs(128, n, H, DK, DV, dev, seed=n)
                 for _ in range(3):
                     gdn2.gdn2_decode(*dq, state)
         torch.cuda.synchronize()
