@@ -81,7 +81,7 @@ __host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK,
   L.off_kgt = off;  off = align_up(off + L.kgt_bytes * L.nch, 1024);
   L.off_ut = off;   off = align_up(off + L.ut_bytes * L.nch, 1024);
   L.off_gl = off;   off = align_up(off + L.gl_bytes * L.nch, 1024);
-  L.off_flags = off; off = align_up(off + sizeof(int) * L.nch, 1024);
+  L.off_flags = off; off = align_up(off + sizeof(int) * (2 * L.nch + 4), 1024);   // flags, compacted list, count
   L.total = off;
   return L;
 }

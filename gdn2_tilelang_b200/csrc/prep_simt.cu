@@ -20,21 +20,21 @@ namespace gdn2 {
 namespace {
 
 
+// The whole chunk-local stage for chunk n of (batch*head) bh, by one 256-thread block.
 template <typename TIn, typename TW>
-__global__ void __launch_bounds__(256)
-prep_simt_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn* __restrict__ v,
-                 const float* __restrict__ g, const TIn* __restrict__ b, const TIn* __restrict__ w,
-                 WsLayout L, WsPtrs P, int S, int H, int64_t in_bs, float scale, int only_flagged) {
+__device__ __forceinline__ void prep_simt_chunk(const TIn* __restrict__ q, const TIn* __restrict__ k,
+                                                const TIn* __restrict__ v, const float* __restrict__ g,
+                                                const TIn* __restrict__ b, const TIn* __restrict__ w,
+                                                const WsLayout& L, const WsPtrs& P, int S, int H, int64_t in_bs,
+                                                float scale, int n, int bh) {
   constexpr int BS = kChunk;
   using WT = WsTraits<TW>;
   using TV = typename WT::TV;
   constexpr int E = WT::E;
   const int DK = L.DK, DV = L.DV;
   const int NC = S / BS;
-  const int n = blockIdx.x, bh = blockIdx.y;
   const int ib = bh / H, ih = bh % H;
   const int64_t ch = (int64_t)bh * NC + n;
-  if (only_flagged && P.flags[ch] == 0) return;
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
 
   extern __shared__ float sm[];
@@ -147,16 +147,56 @@ prep_simt_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn
 }
 
 template <typename TIn, typename TW>
+__global__ void __launch_bounds__(256)
+prep_simt_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn* __restrict__ v,
+                 const float* __restrict__ g, const TIn* __restrict__ b, const TIn* __restrict__ w,
+                 WsLayout L, WsPtrs P, int S, int H, int64_t in_bs, float scale) {
+  prep_simt_chunk<TIn, TW>(q, k, v, g, b, w, L, P, S, H, in_bs, scale, blockIdx.x, blockIdx.y);
+}
+
+// Exact redo of the chunks the tensor-core kernel flagged: a fixed small grid walks the compacted list
+// (workspace ints: flags[nch], list[nch], count), so a call with nothing flagged costs two tiny launches.
+template <typename TIn, typename TW>
+__global__ void __launch_bounds__(256)
+prep_simt_flagged_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn* __restrict__ v,
+                         const float* __restrict__ g, const TIn* __restrict__ b, const TIn* __restrict__ w,
+                         WsLayout L, WsPtrs P, int S, int H, int64_t in_bs, float scale) {
+  const int NC = S / kChunk;
+  const int* list = P.flags + L.nch;
+  const int count = P.flags[2 * L.nch];
+  for (int li = blockIdx.x; li < count; li += gridDim.x) {
+    const int ch = list[li];
+    prep_simt_chunk<TIn, TW>(q, k, v, g, b, w, L, P, S, H, in_bs, scale, ch % NC, ch / NC);
+    __syncthreads();                                   // shared memory is reused by the next chunk
+  }
+}
+
+__global__ void collect_flagged_kernel(int* flags, int nch) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < nch && flags[i] != 0) flags[nch + atomicAdd(&flags[2 * nch], 1)] = i;
+}
+
+template <typename TIn, typename TW>
 int launch_typed(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
                  const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
                  bool only_flagged, cudaStream_t st) {
   const size_t smem = ((size_t)4 * kChunk * L.DK + 3 * kChunk * kChunk) * sizeof(float);
-  auto kern = prep_simt_kernel<TIn, TW>;
-  GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(S / kChunk, B * H);
-  kern<<<grid, 256, smem, st>>>(static_cast<const TIn*>(q), static_cast<const TIn*>(k), static_cast<const TIn*>(v),
-                                g, static_cast<const TIn*>(b), static_cast<const TIn*>(w), L, P, S, H, in_bs, scale,
-                                only_flagged ? 1 : 0);
+  const TIn* tq = static_cast<const TIn*>(q); const TIn* tk = static_cast<const TIn*>(k);
+  const TIn* tv = static_cast<const TIn*>(v); const TIn* tb = static_cast<const TIn*>(b);
+  const TIn* tw = static_cast<const TIn*>(w);
+  if (only_flagged) {
+    auto kern = prep_simt_flagged_kernel<TIn, TW>;
+    GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int nch = (int)L.nch;
+    GDN2_CUDA_TRY(cudaMemsetAsync(P.flags + 2 * (size_t)nch, 0, sizeof(int), st));
+    collect_flagged_kernel<<<(nch + 255) / 256, 256, 0, st>>>(P.flags, nch);
+    kern<<<nch < 296 ? nch : 296, 256, smem, st>>>(tq, tk, tv, g, tb, tw, L, P, S, H, in_bs, scale);
+  } else {
+    auto kern = prep_simt_kernel<TIn, TW>;
+    GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid(S / kChunk, B * H);
+    kern<<<grid, 256, smem, st>>>(tq, tk, tv, g, tb, tw, L, P, S, H, in_bs, scale);
+  }
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }

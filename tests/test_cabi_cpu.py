@@ -47,8 +47,8 @@ def test_status_strings(lib):
 def test_workspace_query(lib):
     f = lib.gdn2_prefill_workspace_bytes
     big = f(4, 16000, 16, 128, 128, _cabi.GDN2_BF16, _cabi.PATH_AUTO)
-    # per chunk-head: WQ 32 KiB + AQK 8 KiB + KG^T 16 KiB + U^T 16 KiB (fp16) + gamma_last 512 B (+ flag)
-    per = 32768 + 8192 + 16384 + 16384 + 512 + 4
+    # per chunk-head: WQ 32 KiB + AQK 8 KiB + KG^T 16 KiB + U^T 16 KiB (fp16) + gamma_last 512 B (+ flag and list entry)
+    per = 32768 + 8192 + 16384 + 16384 + 512 + 8
     nch = 4 * 16 * 250
     assert per * nch <= big <= per * nch + 8 * 1024
     assert f(1, 100, 1, 128, 128, _cabi.GDN2_BF16, 0) == 0          # S not a multiple of 64
