@@ -119,6 +119,7 @@ class NativeKernels:
         self.lib = load_library()
         self.prefill_path = _PATHS[os.environ.get("GDN2_B200_PREFILL_PATH", "auto")]
         self.launches = 0   # kernels launched through this object (for the benchmark's accounting)
+        self._side_streams = {}
 
     # -- helpers ---------------------------------------------------------------------------
     @staticmethod
@@ -130,6 +131,20 @@ class NativeKernels:
         if p == PATH_AUTO:
             p = PATH_TCGEN05 if (DK == 128 and DV == 128 and dtype == torch.bfloat16) else PATH_SIMT
         return p
+
+    def _segments(self, n_chunks: int, path: int) -> int:
+        """How many sequence segments the chunkwise prefill is cut into (1 = no overlap of the two stages)."""
+        if path != PATH_TCGEN05:
+            return 1
+        want = int(os.environ.get("GDN2_B200_PREFILL_SEGMENTS", "2"))
+        return max(1, min(want, n_chunks // 16))
+
+    def _side_stream(self, dev):
+        key = (dev.type, dev.index)
+        st = self._side_streams.get(key)
+        if st is None:
+            st = self._side_streams[key] = torch.cuda.Stream(device=dev, priority=-1)
+        return st
 
     # -- decode ----------------------------------------------------------------------------
     def decode(self, q, k, v, g, b, w, state, scale: float, out=None) -> torch.Tensor:
@@ -197,19 +212,47 @@ class NativeKernels:
         if initial_state is not None:
             if initial_state.dtype != torch.float32 or not initial_state.is_contiguous():
                 initial_state = initial_state.to(torch.float32).contiguous()
-        st = self._stream(q)
+        NC = S // CHUNK
+        nseg = 1 if want_chunk_states else self._segments(NC, p)
+        esz = out.element_size()
         with torch.cuda.device(dev):
-            rc = self.lib.gdn2_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
-                                          w.data_ptr(), ws.data_ptr(), nbytes, B, S, H, DK, DV, in_bs,
-                                          float(scale), code, p, st)
-            _check(self.lib, rc, "gdn2_chunk_prep")
-            rc = self.lib.gdn2_prefill_scan(ws.data_ptr(), nbytes,
-                                            None if initial_state is None else initial_state.data_ptr(),
-                                            out.data_ptr(), final_state.data_ptr(),
-                                            None if hs is None else hs.data_ptr(), B, S, H, DK, DV,
-                                            out_batch_stride, code, p, st)
-            _check(self.lib, rc, "gdn2_prefill_scan")
-        self.launches += 3 if p == PATH_TCGEN05 else 2
+            main = torch.cuda.current_stream(dev)
+            # The scan runs on only B*H thread blocks and is bound by its chunk-to-chunk chain, while the
+            # chunk-local stage is chunk-parallel. With several segments, the chunk-local stage of segment i+1
+            # runs on the caller's stream while the scan of segment i runs on a high-priority side stream.
+            bounds = [NC * i // nseg for i in range(nseg + 1)]
+            states = [torch.empty_like(final_state) for _ in range(nseg - 1)] + [final_state]
+            side = None
+            if nseg > 1:
+                side = self._side_stream(dev)
+                side.wait_stream(main)
+            state_ptr = None if initial_state is None else initial_state.data_ptr()
+            for i in range(nseg):
+                c0, c1 = bounds[i], bounds[i + 1]
+                t0, S_i = c0 * CHUNK, (c1 - c0) * CHUNK
+                if nseg == 1:
+                    ws_i, nb_i = ws, nbytes
+                else:
+                    nb_i = self.lib.gdn2_prefill_workspace_bytes(B, S_i, H, DK, DV, code, p)
+                    ws_i = torch.empty(nb_i, dtype=torch.uint8, device=dev)
+                ptrs = [x.data_ptr() + t0 * H * x.shape[-1] * x.element_size() for x in (q, k, v, g, b, w)]
+                rc = self.lib.gdn2_chunk_prep(*ptrs, ws_i.data_ptr(), nb_i, B, S_i, H, DK, DV, in_bs, float(scale),
+                                              code, p, main.cuda_stream)
+                _check(self.lib, rc, "gdn2_chunk_prep")
+                scan_stream = main
+                if side is not None:
+                    ev = torch.cuda.Event()
+                    ev.record(main)
+                    side.wait_event(ev)
+                    scan_stream = side
+                rc = self.lib.gdn2_prefill_scan(ws_i.data_ptr(), nb_i, state_ptr, out.data_ptr() + t0 * H * DV * esz,
+                                                states[i].data_ptr(), None if hs is None else hs.data_ptr(),
+                                                B, S_i, H, DK, DV, out_batch_stride, code, p, scan_stream.cuda_stream)
+                _check(self.lib, rc, "gdn2_prefill_scan")
+                state_ptr = states[i].data_ptr()
+            if side is not None:
+                main.wait_stream(side)
+        self.launches += (4 if p == PATH_TCGEN05 else 2) * nseg
         return out, final_state, hs
 
     def chunk_output(self, q, k, v, g, b, w, scale: float, chunk_states, path=None):
