@@ -64,7 +64,7 @@ struct ScanTcSmem {
   float gl[2][D];                    // gamma at the last token of chunk n (slot n & 1)
   uint64_t bar_wq[2], bar_kgt[2], bar_ut[2], bar_aqk;   // bulk-copy arrival
   uint64_t bar_m1, bar_m3, bar_m2;                      // MMA completion
-  uint64_t bar_sb, bar_un;                              // compute threads -> issuer (256 arrivals)
+  uint64_t bar_sb, bar_un, bar_unb;                     // compute threads -> issuer (256 arrivals)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -82,14 +82,28 @@ __device__ unsigned long long g_scan_timing[32];
 
 enum : uint32_t {
   kWaitWq = 0x10, kWaitUt = 0x20, kWaitAqk = 0x40, kWaitKgt = 0x80, kWaitM1 = 0x100, kWaitM2 = 0x200,
-  kWaitM3 = 0x400, kWaitSb = 0x800, kWaitUn = 0x4000
+  kWaitM3 = 0x400, kWaitSb = 0x800, kWaitUn = 0x4000, kWaitUnb = 0x8000
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc::smem_u32(bar)) : "memory");
 }
-// barrier among the 256 compute threads only (hardware barrier 1)
-__device__ __forceinline__ void compute_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+// barrier among the 256 compute threads only (hardware barrier 1), fused with an OR over one
+// predicate per thread: every thread gets the same answer
+__device__ __forceinline__ bool compute_sync_or(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "barrier.cta.red.or.pred q, 1, 256, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t"
+      "}"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
 // barrier among the 128 output threads only (hardware barrier 2)
 __device__ __forceinline__ void output_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
@@ -131,6 +145,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     }
     tc::mbar_init(&s.bar_aqk, 1); tc::mbar_init(&s.bar_m1, 1); tc::mbar_init(&s.bar_m3, 1); tc::mbar_init(&s.bar_m2, 1);
     tc::mbar_init(&s.bar_sb, kComputeThreads + kOutputThreads); tc::mbar_init(&s.bar_un, kComputeThreads);
+    tc::mbar_init(&s.bar_unb, kComputeThreads);
     s.abort_flag = 0;
     tc::mbar_init_fence();
   }
@@ -211,9 +226,11 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
           tc::mma_commit(&s.bar_m3);
         }
         TICK(6);
+        ok = ok && tc::mbar_wait(&s.bar_unb, ph, &s.abort_flag, status, kWaitUnb);
         ok = ok && tc::mbar_wait(&s.bar_aqk, ph, &s.abort_flag, status, kWaitAqk);
         TICK(7);
         if (ok) {
+          tc::tc_fence_after_sync();
           tc::mma_f16_ts_ktile(tc::tmem_addr(tm, 0, kColO), a_unb, a_aqk, BS, BS, idesc_n64, true);
           tc::mma_commit(&s.bar_m2);
         }
@@ -289,15 +306,13 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     TDECL;
     for (int n = 0; n < NC; ++n) {
       TICK(0);
-      compute_sync();                                      // publishes gl[]; makes the abort test uniform
-      if (s.abort_flag) break;
-      TICK(1);
       const int b = n & 1;
       const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
       const bool more = n + 1 < NC;
       const float gl_next = (more && tid < D) ? g_gl[(size_t)(n + 1) * D + tid] : 1.f;
 
-      // ---- Un^T = U^T - (W S)^T for this thread's 32 tokens, as fp16 (scaled) and bf16 operand images
+      // ---- Un^T = U^T - (W S)^T for this thread's 32 tokens. The fp16 image feeds the state update
+      // and is handed over first; the bf16 image feeds the output product and follows.
       tc::mbar_wait(&s.bar_ut[b], ph2, &s.abort_flag, status, kWaitUt);
       TICK(2);
       tc::mbar_wait(&s.bar_m1, ph, &s.abort_flag, status, kWaitM1);
@@ -307,35 +322,40 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         float ws[32];
         tc::tmem_ld32(t_lane + kColWs + tokp, ws);
         tc::tmem_ld_wait();
-        float p16[16], pb[16];
+        float p16[16];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int t8 = tokp / 8 + j;
           float u[8];
           unpack8_f16(*reinterpret_cast<const uint4*>(&s.ut[b][(t8 * D + dv) * 8]), u);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) u[i] = fmaf(ws[j * 8 + i], -1.f / kValScale, u[i]);     // Un / 256
+          for (int i = 0; i < 8; ++i) ws[j * 8 + i] = fmaf(ws[j * 8 + i], -1.f / kValScale, u[i]);   // Un / 256
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            p16[j * 4 + i] = pack_f16x2(u[2 * i], u[2 * i + 1]);
-            pb[j * 4 + i] = pack_bf16x2(u[2 * i] * kValScale, u[2 * i + 1] * kValScale);
-          }
+          for (int i = 0; i < 4; ++i) p16[j * 4 + i] = pack_f16x2(ws[j * 8 + 2 * i], ws[j * 8 + 2 * i + 1]);
         }
         tc::tmem_st16(t_lane + kColUn16 + tokp / 2, p16);
-        tc::tmem_st16(t_lane + kColUnb + tokp / 2, pb);
         tc::tmem_st_wait();
+        tc::tc_fence_before_sync();
+        mbar_arrive(&s.bar_un);
+        TICK(4);
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          p16[i] = pack_bf16x2(ws[2 * i] * kValScale, ws[2 * i + 1] * kValScale);
+        tc::tmem_st16(t_lane + kColUnb + tokp / 2, p16);
+        tc::tmem_st_wait();
+        tc::tc_fence_before_sync();
+        mbar_arrive(&s.bar_unb);
       }
       if (tid < D) s.gl[(n + 1) & 1][tid] = gl_next;
-      TICK(4);
-      tc::tc_fence_before_sync();
-      mbar_arrive(&s.bar_un);
       TICK(5);
 
-      // ---- new state: bf16 operand copy, optional snapshot, pre-scale for the next chunk
+      // ---- new state: the bf16 operand copy goes first (the next chunk's first product waits for
+      // it), then the optional snapshot and the pre-scale for the next chunk, which that product
+      // does not read
       tc::mbar_wait(&s.bar_m3, ph, &s.abort_flag, status, kWaitM3);
       tc::tc_fence_after_sync();
       TICK(7);
-      compute_sync();                                      // gl[(n+1)&1] written above is read below
+      if (compute_sync_or(s.abort_flag != 0)) break;       // uniform; also publishes gl[(n+1)&1]
       {
         float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
         float* fin = (!more && sT) ? sT + (size_t)bh * D * D : nullptr;
@@ -344,6 +364,19 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         tc::tmem_ld32(t_lane + dkp, xs[0]);
         tc::tmem_ld32(t_lane + dkp + 32, xs[1]);
         tc::tmem_ld_wait();
+        if (more) {
+          float pk[32];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            pk[i] = pack_bf16x2(xs[0][2 * i], xs[0][2 * i + 1]);
+            pk[16 + i] = pack_bf16x2(xs[1][2 * i], xs[1][2 * i + 1]);
+          }
+          tc::tmem_st32(t_lane + kColSb + dkp / 2, pk);
+          tc::tmem_st_wait();
+          tc::tc_fence_before_sync();
+          mbar_arrive(&s.bar_sb);
+        }
+        TICK(8);
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           const int c0 = dkp + 32 * hf;
@@ -357,10 +390,6 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
             for (int i = 0; i < 32; ++i) fin[(size_t)(c0 + i) * D + dv] = x[i];
           }
           if (more) {
-            float pk[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(x[2 * i], x[2 * i + 1]);
-            tc::tmem_st16(t_lane + kColSb + c0 / 2, pk);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               const float4 g4 = *reinterpret_cast<const float4*>(&gln[c0 + 4 * i]);
@@ -369,11 +398,8 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
             tc::tmem_st32(t_lane + c0, x);
           }
         }
-        tc::tmem_st_wait();
+        tc::tmem_st_wait();                                // ordered before the next arrival on bar_un
       }
-      TICK(8);
-      tc::tc_fence_before_sync();
-      if (more) mbar_arrive(&s.bar_sb);
       TICK(9);
     }
     if (tid == 0) TFLUSH(16);

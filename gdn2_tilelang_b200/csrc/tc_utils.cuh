@@ -50,8 +50,8 @@ constexpr long long kWaitCycles = 400LL * 1000 * 1000;
 // On the first failure `code` is OR-ed into the device status word.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           uint32_t* status_word, uint32_t code) {
+  if (mbar_try_wait(bar, parity)) return true;   // the common case costs one probe and no shared-memory load
   if (*abort_flag) return false;
-  if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
