@@ -192,51 +192,56 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     }
   } else if (wid == 8) {
     // =============================== issuer: every MMA, in critical-path order ==================
-    if (lane == 0) {
+    // The whole warp runs this loop converged (identical waits and operands on every lane); one
+    // elected lane issues each instruction.
+    {
       constexpr uint32_t idesc_n128 = tc::instr_desc(1, 128, 128);   // bf16 operands, N = 128
       constexpr uint32_t idesc_n64 = tc::instr_desc(1, 128, 64);     // bf16 operands, N = 64
       constexpr uint32_t idesc_f16 = tc::instr_desc(0, 128, 128);    // fp16 operands, N = 128
       const uint32_t a_sb = tc::tmem_addr(tm, 0, kColSb), a_un16 = tc::tmem_addr(tm, 0, kColUn16);
       const uint32_t a_unb = tc::tmem_addr(tm, 0, kColUnb);
       const uint32_t a_aqk = tc::smem_u32(s.aqk);
+      auto wait_all = [&](uint64_t* bar, uint32_t parity, uint32_t code) {
+        return __all_sync(0xffffffffu, tc::mbar_wait(bar, parity, &s.abort_flag, status, code)) != 0;
+      };
       TDECL;
       for (int n = 0; n < NC; ++n) {
         const int b = n & 1;
         const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
         TICK(0);
         // S^T (bf16) of chunk n is in place and the O accumulator has been read out
-        bool ok = tc::mbar_wait(&s.bar_sb, ph, &s.abort_flag, status, kWaitSb);
+        bool ok = wait_all(&s.bar_sb, ph, kWaitSb);
         TICK(1);
-        ok = ok && tc::mbar_wait(&s.bar_wq[b], ph2, &s.abort_flag, status, kWaitWq);
+        ok = ok && wait_all(&s.bar_wq[b], ph2, kWaitWq);
         TICK(2);
         if (ok) {
           tc::tc_fence_after_sync();
           // one N = 128 product: columns [128,192) = (W S)^T, [192,256) = (Qg S)^T
-          tc::mma_f16_ts_ktile(tc::tmem_addr(tm, 0, kColWs), a_sb, tc::smem_u32(s.wq[b]), 2 * BS, D, idesc_n128, false);
-          tc::mma_commit(&s.bar_m1);
+          tc::mma_f16_ts_ktile_warp(tc::tmem_addr(tm, 0, kColWs), a_sb, tc::smem_u32(s.wq[b]), 2 * BS, D, idesc_n128, false);
+          tc::mma_commit_warp(&s.bar_m1);
         }
         TICK(3);
-        ok = tc::mbar_wait(&s.bar_un, ph, &s.abort_flag, status, kWaitUn);
+        ok = wait_all(&s.bar_un, ph, kWaitUn);
         TICK(4);
-        ok = ok && tc::mbar_wait(&s.bar_kgt[b], ph2, &s.abort_flag, status, kWaitKgt);
+        ok = ok && wait_all(&s.bar_kgt[b], ph2, kWaitKgt);
         TICK(5);
         if (ok) {
           tc::tc_fence_after_sync();
-          tc::mma_f16_ts_ktile(tc::tmem_addr(tm, 0, 0), a_un16, tc::smem_u32(s.kgt[b]), D, BS, idesc_f16, true);
-          tc::mma_commit(&s.bar_m3);
+          tc::mma_f16_ts_ktile_warp(tc::tmem_addr(tm, 0, 0), a_un16, tc::smem_u32(s.kgt[b]), D, BS, idesc_f16, true);
+          tc::mma_commit_warp(&s.bar_m3);
         }
         TICK(6);
-        ok = ok && tc::mbar_wait(&s.bar_unb, ph, &s.abort_flag, status, kWaitUnb);
-        ok = ok && tc::mbar_wait(&s.bar_aqk, ph, &s.abort_flag, status, kWaitAqk);
+        ok = ok && wait_all(&s.bar_unb, ph, kWaitUnb);
+        ok = ok && wait_all(&s.bar_aqk, ph, kWaitAqk);
         TICK(7);
         if (ok) {
           tc::tc_fence_after_sync();
-          tc::mma_f16_ts_ktile(tc::tmem_addr(tm, 0, kColO), a_unb, a_aqk, BS, BS, idesc_n64, true);
-          tc::mma_commit(&s.bar_m2);
+          tc::mma_f16_ts_ktile_warp(tc::tmem_addr(tm, 0, kColO), a_unb, a_aqk, BS, BS, idesc_n64, true);
+          tc::mma_commit_warp(&s.bar_m2);
         }
         TICK(8);
       }
-      TFLUSH(0);
+      if (lane == 0) TFLUSH(0);
     }
   } else if (wid >= 10) {
     // =============================== output warps: O^T -> bf16 rows in global memory =============

@@ -244,6 +244,41 @@ __device__ __forceinline__ void mma_f16_ts_ktile(uint32_t d_tmem, uint32_t a_tme
   }
 }
 
+// Warp-collective forms: all 32 lanes of a converged warp execute the call with identical arguments
+// and one elected lane issues the instruction. Keeping the issuing warp converged lets the operand
+// descriptors live in uniform registers instead of being moved there before every MMA.
+__device__ __forceinline__ void mma_f16_ts_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, e;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_f16_ts_ktile_warp(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr,
+                                                      uint32_t b_rows, int K, uint32_t idesc, bool accumulate_first) {
+  uint64_t bd = kchunk_desc(b_addr, b_rows);
+  const uint64_t bstep = (2u * b_rows * 16u) >> 4;
+#pragma unroll
+  for (int ks = 0; ks < K / 16; ++ks) {
+    mma_f16_ts_warp(d_tmem, a_tmem + ks * 8, bd, idesc, (ks > 0 || accumulate_first) ? 1u : 0u);
+    bd += bstep;
+  }
+}
+__device__ __forceinline__ void mma_commit_warp(uint64_t* bar) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred e;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+      "}" ::"r"(smem_u32(bar))
+      : "memory");
+}
+
 // mbarrier arrives once every tcgen05 operation issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
