@@ -210,9 +210,9 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
         TICK(0);
         // S^T (bf16) of chunk n is in place and the O accumulator has been read out
-        bool ok = wait_all(&s.bar_sb, ph, kWaitSb);
+        bool ok = wait_all(&s.bar_wq[b], ph2, kWaitWq);
         TICK(1);
-        ok = ok && wait_all(&s.bar_wq[b], ph2, kWaitWq);
+        ok = ok && wait_all(&s.bar_sb, ph, kWaitSb);
         TICK(2);
         if (ok) {
           tc::tc_fence_after_sync();
@@ -221,9 +221,9 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
           tc::mma_commit_warp(&s.bar_m1);
         }
         TICK(3);
-        ok = wait_all(&s.bar_un, ph, kWaitUn);
+        ok = wait_all(&s.bar_kgt[b], ph2, kWaitKgt);
         TICK(4);
-        ok = ok && wait_all(&s.bar_kgt[b], ph2, kWaitKgt);
+        ok = ok && wait_all(&s.bar_un, ph, kWaitUn);
         TICK(5);
         if (ok) {
           tc::tc_fence_after_sync();
@@ -231,8 +231,8 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
           tc::mma_commit_warp(&s.bar_m3);
         }
         TICK(6);
-        ok = ok && wait_all(&s.bar_unb, ph, kWaitUnb);
         ok = ok && wait_all(&s.bar_aqk, ph, kWaitAqk);
+        ok = ok && wait_all(&s.bar_unb, ph, kWaitUnb);
         TICK(7);
         if (ok) {
           tc::tc_fence_after_sync();
@@ -320,6 +320,9 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       // and is handed over first; the bf16 image feeds the output product and follows.
       tc::mbar_wait(&s.bar_ut[b], ph2, &s.abort_flag, status, kWaitUt);
       TICK(2);
+      uint4 uraw[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) uraw[j] = *reinterpret_cast<const uint4*>(&s.ut[b][((tokp / 8 + j) * D + dv) * 8]);
       tc::mbar_wait(&s.bar_m1, ph, &s.abort_flag, status, kWaitM1);
       tc::tc_fence_after_sync();
       TICK(3);
@@ -330,9 +333,8 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         float p16[16];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int t8 = tokp / 8 + j;
           float u[8];
-          unpack8_f16(*reinterpret_cast<const uint4*>(&s.ut[b][(t8 * D + dv) * 8]), u);
+          unpack8_f16(uraw[j], u);
 #pragma unroll
           for (int i = 0; i < 8; ++i) ws[j * 8 + i] = fmaf(ws[j * 8 + i], -1.f / kValScale, u[i]);   // Un / 256
 #pragma unroll
@@ -360,7 +362,6 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       tc::mbar_wait(&s.bar_m3, ph, &s.abort_flag, status, kWaitM3);
       tc::tc_fence_after_sync();
       TICK(7);
-      if (compute_sync_or(s.abort_flag != 0)) break;       // uniform; also publishes gl[(n+1)&1]
       {
         float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
         float* fin = (!more && sT) ? sT + (size_t)bh * D * D : nullptr;
@@ -382,6 +383,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
           mbar_arrive(&s.bar_sb);
         }
         TICK(8);
+        if (compute_sync_or(s.abort_flag != 0)) break;     // uniform; also publishes gl[(n+1)&1]
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           const int c0 = dkp + 32 * hf;
