@@ -101,7 +101,8 @@ __host__ inline WsPtrs ws_pointers(void* base, const WsLayout& L) {
                 reinterpret_cast<int*>(p + L.off_flags)};
 }
 
-// Per-family element types of the workspace: TW for WQ/AQK, TV (+ scales) for KGT/UT.
+// Per-family element types of the workspace: TW for WQ, TV (+ scales) for AQK/KGT/UT
+// (AQK and KGT hold 256 * value, UT holds value / 256 in the 16-bit family).
 template <typename TW> struct WsTraits;
 template <> struct WsTraits<float> {
   using TV = float;

@@ -101,13 +101,13 @@ __device__ __forceinline__ void prep_simt_chunk(const TIn* __restrict__ q, const
   }
   // outputs that need only G, q, k: Aqk image, Qg rows, KG^T image, gamma_last; E in place
   TW* wq = reinterpret_cast<TW*>(P.wq + (size_t)ch * L.wq_bytes);
-  TW* aqk = reinterpret_cast<TW*>(P.aqk + (size_t)ch * L.aqk_bytes);
+  TV* aqk = reinterpret_cast<TV*>(P.aqk + (size_t)ch * L.aqk_bytes);
   TV* kgt = reinterpret_cast<TV*>(P.kgt + (size_t)ch * L.kgt_bytes);
   TV* ut = reinterpret_cast<TV*>(P.ut + (size_t)ch * L.ut_bytes);
   float* gl = P.gl + (size_t)ch * DK;
   for (int idx = tid; idx < BS * BS; idx += 256) {
     const int r = idx / BS, s = idx % BS;
-    aqk[kc_index<E>(r, s, BS)] = from_f32<TW>(Aq[idx]);
+    aqk[kc_index<E>(r, s, BS)] = WT::kg_store(Aq[idx]);
   }
   for (int idx = tid; idx < BS * DK; idx += 256) {
     const int t = idx / DK, c = idx % DK;

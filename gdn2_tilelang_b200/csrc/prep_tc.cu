@@ -293,7 +293,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     const uint32_t t_lo = tc::tmem_addr(tm, wid * 32, 8 * i0 * (i0 + 1));
     const uint32_t t_hi = tc::tmem_addr(tm, wid * 32, 8 * (i0 + 1) * (i0 + 2));
     float* tr = s.x.sol.tm + r * TM_STRIDE;
-    __nv_bfloat16* ag = reinterpret_cast<__nv_bfloat16*>(P.aqk + (size_t)ch * (BS * BS * 2));
+    __half* ag = reinterpret_cast<__half*>(P.aqk + (size_t)ch * (BS * BS * 2));   // fp16, 256 * Aqk
 #pragma unroll 1
     for (int cg = 0; cg < 4; ++cg) {
       float lo16[16], hi16[16], row[16];
@@ -315,8 +315,8 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
           *reinterpret_cast<float4*>(tr + 16 * cg + 4 * m4) =
               make_float4(row[4 * m4], row[4 * m4 + 1], row[4 * m4 + 2], row[4 * m4 + 3]);
       } else {
-        *reinterpret_cast<uint4*>(ag + ((2 * cg) * BS + r) * 8) = tc::pack8_bf16(&row[0]);
-        *reinterpret_cast<uint4*>(ag + ((2 * cg + 1) * BS + r) * 8) = tc::pack8_bf16(&row[8]);
+        *reinterpret_cast<uint4*>(ag + ((2 * cg) * BS + r) * 8) = tc::pack8_f16(&row[0], kValScale);
+        *reinterpret_cast<uint4*>(ag + ((2 * cg + 1) * BS + r) * 8) = tc::pack8_f16(&row[8], kValScale);
       }
     }
     // (w*v)^T image from the TMEM stash

@@ -43,7 +43,7 @@ __device__ __forceinline__ void load_chunk_operands(const WsLayout& L, const WsP
   constexpr int E = WT::E;
   const int DK = L.DK, DV = L.DV, tid = threadIdx.x;
   const TW* wq = reinterpret_cast<const TW*>(P.wq + (size_t)ch * L.wq_bytes);
-  const TW* aqk = reinterpret_cast<const TW*>(P.aqk + (size_t)ch * L.aqk_bytes);
+  const TV* aqk = reinterpret_cast<const TV*>(P.aqk + (size_t)ch * L.aqk_bytes);
   const TV* kgt = reinterpret_cast<const TV*>(P.kgt + (size_t)ch * L.kgt_bytes);
   const TV* ut = reinterpret_cast<const TV*>(P.ut + (size_t)ch * L.ut_bytes);
   for (int idx = tid; idx < kChunk * DK; idx += 256) {
@@ -53,7 +53,7 @@ __device__ __forceinline__ void load_chunk_operands(const WsLayout& L, const WsP
     if (want_kg) s.Ks[idx] = WT::kg_load(kgt[kc_index<E>(c, t, DK)]);
   }
   for (int idx = tid; idx < kChunk * kChunk; idx += 256)
-    s.As[idx] = to_f32(aqk[kc_index<E>(idx / kChunk, idx % kChunk, kChunk)]);
+    s.As[idx] = WT::kg_load(aqk[kc_index<E>(idx / kChunk, idx % kChunk, kChunk)]);
   for (int idx = tid; idx < kChunk * NV; idx += 256) {
     const int t = idx / NV, c = lo + idx % NV;
     s.Us[idx] = c < DV ? WT::u_load(ut[kc_index<E>(c, t, DV)]) : 0.f;

@@ -10,7 +10,7 @@
 //   MMA1q  O [dv, tok]  = S^T[dv,dk] * Qg[tok,dk]^T           (Qg S)^T         bf16
 //   regs   Un^T[dv,tok] = U^T - WS
 //   MMA3   ST[dv,dk]   += Un^T[dv,tok] * KG^T[dk,tok]^T       (KG^T Un)^T      fp16 (scaled, see common.cuh)
-//   MMA2   O [dv, r]   += Un^T[dv,s] * Aqk[r,s]^T             (tril(Aqk) Un)^T bf16
+//   MMA2   O [dv, r]   += Un^T[dv,s] * Aqk[r,s]^T             (tril(Aqk) Un)^T fp16 (same scaled Un^T image)
 //   regs   ST          <- gamma_C(next chunk)[dk] * ST after the bf16 copy of S^T is taken
 //
 // Only MMA1w, the Un pass, MMA3 and the state pass are on the recurrence's critical path; the
@@ -27,12 +27,12 @@
 //     double buffered so that a copy is always issued a full chunk ahead of its use.
 //   * hand-offs are mbarriers (arrive / wait), every wait is bounded (tc_utils.cuh).
 //
-//   * the A operands (S^T in bf16, Un^T in fp16 and bf16) never touch shared memory: the register
+//   * the A operands (S^T in bf16, Un^T in fp16) never touch shared memory: the register
 //     passes store them as packed 16-bit pairs into tensor memory and the MMAs read them from there,
 //     which halves the shared-memory traffic the tensor core competes for.
 //
 // TMEM columns: [0,128) fp32 state S^T; [128,192) WS; [192,256) and [256,320) the two O accumulators;
-// [320,384) S^T bf16 pairs; [384,416) Un^T/256 fp16 pairs; [416,448) Un^T bf16 pairs.
+// [320,384) S^T bf16 pairs; [384,416) Un^T/256 fp16 pairs.
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -53,18 +53,18 @@ constexpr uint32_t kAqkBytes = BS * BS * 2;      //  8 KiB
 constexpr uint32_t kKgtBytes = D * BS * 2;       // 16 KiB (fp16)
 constexpr uint32_t kUtBytes = D * BS * 2;        // 16 KiB (fp16)
 constexpr uint32_t kColWs = 128, kColO = 192;
-constexpr uint32_t kColSb = 320, kColUn16 = 384, kColUnb = 416;   // packed 16-bit A operands in TMEM
+constexpr uint32_t kColSb = 320, kColUn16 = 384;   // packed 16-bit A operands in TMEM
 
 struct ScanTcSmem {
   __nv_bfloat16 wq[2][2 * BS * D];   // B of MMA1w/q: [dk/8][128 rows: W tok 0..63, Qg tok 0..63][8]
-  __nv_bfloat16 aqk[BS * BS];        // B of MMA2: [s/8][64 r][8]
+  __half aqk[BS * BS];               // B of MMA2: [s/8][64 r][8], 256 * Aqk
   __half kgt[2][D * BS];             // B of MMA3: [tok/8][128 dk][8], 256 * KG
   __half ut[2][D * BS];              // U^T / 256: [tok/8][128 dv][8]
   __nv_bfloat16 ostage[BS * D];      // output rows [tok][dv] on their way to global memory
   float gl[2][D];                    // gamma at the last token of chunk n (slot n & 1)
   uint64_t bar_wq[2], bar_kgt[2], bar_ut[2], bar_aqk;   // bulk-copy arrival
   uint64_t bar_m1, bar_m3, bar_m2;                      // MMA completion
-  uint64_t bar_sb, bar_un, bar_unb;                     // compute threads -> issuer (256 arrivals)
+  uint64_t bar_sb, bar_un;                              // compute threads -> issuer (256 arrivals)
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -82,7 +82,7 @@ __device__ unsigned long long g_scan_timing[32];
 
 enum : uint32_t {
   kWaitWq = 0x10, kWaitUt = 0x20, kWaitAqk = 0x40, kWaitKgt = 0x80, kWaitM1 = 0x100, kWaitM2 = 0x200,
-  kWaitM3 = 0x400, kWaitSb = 0x800, kWaitUn = 0x4000, kWaitUnb = 0x8000
+  kWaitM3 = 0x400, kWaitSb = 0x800, kWaitUn = 0x4000
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -145,7 +145,6 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     }
     tc::mbar_init(&s.bar_aqk, 1); tc::mbar_init(&s.bar_m1, 1); tc::mbar_init(&s.bar_m3, 1); tc::mbar_init(&s.bar_m2, 1);
     tc::mbar_init(&s.bar_sb, kComputeThreads + kOutputThreads); tc::mbar_init(&s.bar_un, kComputeThreads);
-    tc::mbar_init(&s.bar_unb, kComputeThreads);
     s.abort_flag = 0;
     tc::mbar_init_fence();
   }
@@ -196,10 +195,9 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     // elected lane issues each instruction.
     {
       constexpr uint32_t idesc_n128 = tc::instr_desc(1, 128, 128);   // bf16 operands, N = 128
-      constexpr uint32_t idesc_n64 = tc::instr_desc(1, 128, 64);     // bf16 operands, N = 64
       constexpr uint32_t idesc_f16 = tc::instr_desc(0, 128, 128);    // fp16 operands, N = 128
+      constexpr uint32_t idesc_f16_n64 = tc::instr_desc(0, 128, 64); // fp16 operands, N = 64
       const uint32_t a_sb = tc::tmem_addr(tm, 0, kColSb), a_un16 = tc::tmem_addr(tm, 0, kColUn16);
-      const uint32_t a_unb = tc::tmem_addr(tm, 0, kColUnb);
       const uint32_t a_aqk = tc::smem_u32(s.aqk);
       auto wait_all = [&](uint64_t* bar, uint32_t parity, uint32_t code) {
         return __all_sync(0xffffffffu, tc::mbar_wait(bar, parity, &s.abort_flag, status, code)) != 0;
@@ -232,11 +230,9 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         }
         TICK(6);
         ok = ok && wait_all(&s.bar_aqk, ph, kWaitAqk);
-        ok = ok && wait_all(&s.bar_unb, ph, kWaitUnb);
         TICK(7);
         if (ok) {
-          tc::tc_fence_after_sync();
-          tc::mma_f16_ts_ktile_warp(tc::tmem_addr(tm, 0, kColO), a_unb, a_aqk, BS, BS, idesc_n64, true);
+          tc::mma_f16_ts_ktile_warp(tc::tmem_addr(tm, 0, kColO), a_un16, a_aqk, BS, BS, idesc_f16_n64, true);
           tc::mma_commit_warp(&s.bar_m2);
         }
         TICK(8);
@@ -316,8 +312,8 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       const bool more = n + 1 < NC;
       const float gl_next = (more && tid < D) ? g_gl[(size_t)(n + 1) * D + tid] : 1.f;
 
-      // ---- Un^T = U^T - (W S)^T for this thread's 32 tokens. The fp16 image feeds the state update
-      // and is handed over first; the bf16 image feeds the output product and follows.
+      // ---- Un^T / 256 = U^T / 256 - (W S)^T / 256 for this thread's 32 tokens, as the fp16 operand of
+      // both the state update and the output product
       tc::mbar_wait(&s.bar_ut[b], ph2, &s.abort_flag, status, kWaitUt);
       TICK(2);
       uint4 uraw[4];
@@ -345,13 +341,6 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         tc::tc_fence_before_sync();
         mbar_arrive(&s.bar_un);
         TICK(4);
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          p16[i] = pack_bf16x2(ws[2 * i] * kValScale, ws[2 * i + 1] * kValScale);
-        tc::tmem_st16(t_lane + kColUnb + tokp / 2, p16);
-        tc::tmem_st_wait();
-        tc::tc_fence_before_sync();
-        mbar_arrive(&s.bar_unb);
       }
       if (tid < D) s.gl[(n + 1) & 1][tid] = gl_next;
       TICK(5);

@@ -3,6 +3,7 @@
 // and access, shared-memory matrix descriptors and tcgen05.mma issue.
 #pragma once
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -307,6 +308,17 @@ __device__ __forceinline__ void mma_tf32_ktile(uint32_t d_tmem, uint32_t a_addr,
     mma_tf32(d_tmem, ad, bd, idesc, (ks > 0 || accumulate_first) ? 1u : 0u);
     ad += astep; bd += bstep;
   }
+}
+
+// pack 8 fp32, each times `mul`, into 8 fp16 (16 bytes)
+__device__ __forceinline__ uint4 pack8_f16(const float* x, float mul) {
+  uint4 r;
+  __half2 t;
+  t = __floats2half2_rn(x[0] * mul, x[1] * mul); r.x = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(x[2] * mul, x[3] * mul); r.y = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(x[4] * mul, x[5] * mul); r.z = *reinterpret_cast<uint32_t*>(&t);
+  t = __floats2half2_rn(x[6] * mul, x[7] * mul); r.w = *reinterpret_cast<uint32_t*>(&t);
+  return r;
 }
 
 // pack 8 fp32 into 8 bf16 (16 bytes)
