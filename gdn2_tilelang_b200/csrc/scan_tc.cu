@@ -219,6 +219,10 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
           tc::mma_commit_warp(&s.bar_m1);
         }
         TICK(3);
+#ifdef GDN2_SCAN_TIMING
+        wait_all(&s.bar_m1, ph, kWaitM1);
+        TICK(9);
+#endif
         ok = wait_all(&s.bar_kgt[b], ph2, kWaitKgt);
         TICK(4);
         ok = ok && wait_all(&s.bar_un, ph, kWaitUn);
@@ -304,13 +308,15 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     tc::tc_fence_before_sync();
     mbar_arrive(&s.bar_sb);
 
+    float gl_ahead = (NC > 1 && tid < D) ? g_gl[D + tid] : 1.f;
     TDECL;
     for (int n = 0; n < NC; ++n) {
       TICK(0);
       const int b = n & 1;
       const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
       const bool more = n + 1 < NC;
-      const float gl_next = (more && tid < D) ? g_gl[(size_t)(n + 1) * D + tid] : 1.f;
+      const float gl_next = gl_ahead;                      // gamma of chunk n + 1, loaded one chunk ago
+      if (n + 2 < NC && tid < D) gl_ahead = g_gl[(size_t)(n + 2) * D + tid];
 
       // ---- Un^T / 256 = U^T / 256 - (W S)^T / 256 for this thread's 32 tokens, as the fp16 operand of
       // both the state update and the output product
@@ -373,6 +379,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         }
         TICK(8);
         if (compute_sync_or(s.abort_flag != 0)) break;     // uniform; also publishes gl[(n+1)&1]
+        TICK(10);
 #pragma unroll
         for (int hf = 0; hf < 2; ++hf) {
           const int c0 = dkp + 32 * hf;
@@ -394,6 +401,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
             tc::tmem_st32(t_lane + c0, x);
           }
         }
+        TICK(11);
         tc::tmem_st_wait();                                // ordered before the next arrival on bar_un
       }
       TICK(9);

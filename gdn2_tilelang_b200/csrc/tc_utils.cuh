@@ -260,15 +260,40 @@ __device__ __forceinline__ void mma_f16_ts_warp(uint32_t d_tmem, uint32_t a_tmem
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Four consecutive K steps in one statement: one election, descriptors stepped in place.
+__device__ __forceinline__ void mma_f16_ts_k4_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint64_t b_step,
+                                                   uint32_t idesc, uint32_t accumulate_first) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, t, e;\n\t"
+      ".reg .b64 b1, b2, b3;\n\t"
+      ".reg .b32 a1, a2, a3;\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "setp.eq.b32 t, %5, %5;\n\t"
+      "add.u64 b1, %2, %3;\n\t"
+      "add.u64 b2, b1, %3;\n\t"
+      "add.u64 b3, b2, %3;\n\t"
+      "add.u32 a1, %1, 8;\n\t"
+      "add.u32 a2, %1, 16;\n\t"
+      "add.u32 a3, %1, 24;\n\t"
+      "elect.sync _|e, 0xffffffff;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %4, p;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a1], b1, %4, t;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a2], b2, %4, t;\n\t"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], [a3], b3, %4, t;\n\t"
+      "}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "l"(b_step), "r"(idesc), "r"(accumulate_first)
+      : "memory");
+}
+// D[128 x N] (+)= A[128 x K] * B[N x K]^T, A in TMEM, B a K-chunked image; K a multiple of 64.
 __device__ __forceinline__ void mma_f16_ts_ktile_warp(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_addr,
                                                       uint32_t b_rows, int K, uint32_t idesc, bool accumulate_first) {
-  uint64_t bd = kchunk_desc(b_addr, b_rows);
+  const uint64_t bd = kchunk_desc(b_addr, b_rows);
   const uint64_t bstep = (2u * b_rows * 16u) >> 4;
 #pragma unroll
-  for (int ks = 0; ks < K / 16; ++ks) {
-    mma_f16_ts_warp(d_tmem, a_tmem + ks * 8, bd, idesc, (ks > 0 || accumulate_first) ? 1u : 0u);
-    bd += bstep;
-  }
+  for (int k4 = 0; k4 < K / 64; ++k4)
+    mma_f16_ts_k4_warp(d_tmem, a_tmem + k4 * 32, bd + 4 * k4 * bstep, bstep, idesc,
+                       (k4 > 0 || accumulate_first) ? 1u : 0u);
 }
 __device__ __forceinline__ void mma_commit_warp(uint64_t* bar) {
   asm volatile(
