@@ -9,9 +9,9 @@
 //   MMA1w  WS[dv, tok]  = S^T[dv,dk] * W[tok,dk]^T            (W S)^T          bf16
 //   MMA1q  O [dv, tok]  = S^T[dv,dk] * Qg[tok,dk]^T           (Qg S)^T         bf16
 //   regs   Un^T[dv,tok] = U^T - WS
-//   MMA3   ST[dv,dk]   += Un^T[dv,tok] * KG^T[dk,tok]^T       (KG^T Un)^T      fp16 (scaled, see common.cuh)
+//   MMA3   P [dv,dk]    = Un^T[dv,tok] * KG^T[dk,tok]^T       (KG^T Un)^T      fp16 (scaled, see common.cuh)
 //   MMA2   O [dv, r]   += Un^T[dv,s] * Aqk[r,s]^T             (tril(Aqk) Un)^T fp16 (same scaled Un^T image)
-//   regs   ST          <- gamma_C(next chunk)[dk] * ST after the bf16 copy of S^T is taken
+//   regs   S^T         <- gamma_C[dk] * S^T + P   (the fp32 state lives in registers, 64 values per thread)
 //
 // Only MMA1w, the Un pass, MMA3 and the state pass are on the recurrence's critical path; the
 // kernel is organised around that:
@@ -31,7 +31,7 @@
 //     passes store them as packed 16-bit pairs into tensor memory and the MMAs read them from there,
 //     which halves the shared-memory traffic the tensor core competes for.
 //
-// TMEM columns: [0,128) fp32 state S^T; [128,192) WS; [192,256) and [256,320) the two O accumulators;
+// TMEM columns: [0,128) the update product P; [128,192) WS; [192,256) and [256,320) the two O accumulators;
 // [320,384) S^T bf16 pairs; [384,416) Un^T/256 fp16 pairs.
 #include <cuda_fp16.h>
 
@@ -61,7 +61,7 @@ struct ScanTcSmem {
   __half kgt[2][D * BS];             // B of MMA3: [tok/8][128 dk][8], 256 * KG
   __half ut[2][D * BS];              // U^T / 256: [tok/8][128 dv][8]
   __nv_bfloat16 ostage[BS * D];      // output rows [tok][dv] on their way to global memory
-  float gl[2][D];                    // gamma at the last token of chunk n (slot n & 1)
+  float gl[4][D];                    // gamma at the last token of chunk n (slot n & 3), copied with KG^T
   uint64_t bar_wq[2], bar_kgt[2], bar_ut[2], bar_aqk;   // bulk-copy arrival
   uint64_t bar_m1, bar_m3, bar_m2;                      // MMA completion
   uint64_t bar_sb, bar_un;                              // compute threads -> issuer (256 arrivals)
@@ -87,22 +87,6 @@ enum : uint32_t {
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc::smem_u32(bar)) : "memory");
-}
-// barrier among the 256 compute threads only (hardware barrier 1), fused with an OR over one
-// predicate per thread: every thread gets the same answer
-__device__ __forceinline__ bool compute_sync_or(bool pred) {
-  uint32_t r;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p, q;\n\t"
-      "setp.ne.u32 p, %1, 0;\n\t"
-      "barrier.cta.red.or.pred q, 1, 256, p;\n\t"
-      "selp.u32 %0, 1, 0, q;\n\t"
-      "}"
-      : "=r"(r)
-      : "r"((uint32_t)pred)
-      : "memory");
-  return r != 0;
 }
 // barrier among the 128 output threads only (hardware barrier 2)
 __device__ __forceinline__ void output_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
@@ -149,7 +133,6 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     tc::mbar_init_fence();
   }
   if (wid == 0) tc::tmem_alloc(&s.tmem_base, 512);
-  if (tid < D) s.gl[0][tid] = g_gl[tid];
   tc::tc_fence_before_sync();
   __syncthreads();
   tc::tc_fence_after_sync();
@@ -163,8 +146,9 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         tc::bulk_g2s(s.wq[n & 1], g_wq + (size_t)n * kWqBytes, kWqBytes, &s.bar_wq[n & 1]);
       };
       auto load_kgt = [&](int n) {
-        tc::mbar_expect_tx(&s.bar_kgt[n & 1], kKgtBytes);
+        tc::mbar_expect_tx(&s.bar_kgt[n & 1], kKgtBytes + D * 4);
         tc::bulk_g2s(s.kgt[n & 1], g_kgt + (size_t)n * kKgtBytes, kKgtBytes, &s.bar_kgt[n & 1]);
+        tc::bulk_g2s(s.gl[n & 3], g_gl + (size_t)n * D, D * 4, &s.bar_kgt[n & 1]);
       };
       auto load_ut = [&](int n) {
         tc::mbar_expect_tx(&s.bar_ut[n & 1], kUtBytes);
@@ -229,7 +213,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         TICK(5);
         if (ok) {
           tc::tc_fence_after_sync();
-          tc::mma_f16_ts_ktile_warp(tc::tmem_addr(tm, 0, 0), a_un16, tc::smem_u32(s.kgt[b]), D, BS, idesc_f16, true);
+          tc::mma_f16_ts_ktile_warp(tc::tmem_addr(tm, 0, 0), a_un16, tc::smem_u32(s.kgt[b]), D, BS, idesc_f16, false);
           tc::mma_commit_warp(&s.bar_m3);
         }
         TICK(6);
@@ -283,40 +267,31 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     const int tokp = part * 32;                           // first of this thread's 32 tokens
     const int dkp = part * 64;                            // first of this thread's 64 key channels
 
-    // initial state: this thread's share of its S^T row -> bf16 image, chunk_states[0], gamma_0-scaled TMEM copy
+    // The fp32 state: S[i] = S^T[dv][dkp + i]. It never leaves these registers between chunks.
+    float S[64];
     {
       float* h0 = hs ? hs + (((size_t)ib * NC + 0) * H + ih) * D * D : nullptr;
-      float x[16];
-#pragma unroll 1
-      for (int c0 = dkp; c0 < dkp + 64; c0 += 16) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] = s0 ? s0[((size_t)bh * D + c0 + i) * D + dv] : 0.f;
-        if (h0) {
+      for (int i = 0; i < 64; ++i) S[i] = s0 ? s0[((size_t)bh * D + dkp + i) * D + dv] : 0.f;
+      if (h0) {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) h0[(size_t)(c0 + i) * D + dv] = x[i];
-        }
-        uint32_t pk[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) pk[i] = __float_as_uint(pack_bf16x2(x[2 * i], x[2 * i + 1]));
-        tc::tmem_st8(t_lane + kColSb + c0 / 2, pk);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) x[i] *= s.gl[0][c0 + i];
-        tc::tmem_st16(t_lane + c0, x);
+        for (int i = 0; i < 64; ++i) h0[(size_t)(dkp + i) * D + dv] = S[i];
       }
+      float pk[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(S[2 * i], S[2 * i + 1]);
+      tc::tmem_st32(t_lane + kColSb + dkp / 2, pk);
       tc::tmem_st_wait();
     }
     tc::tc_fence_before_sync();
     mbar_arrive(&s.bar_sb);
 
-    float gl_ahead = (NC > 1 && tid < D) ? g_gl[D + tid] : 1.f;
     TDECL;
     for (int n = 0; n < NC; ++n) {
       TICK(0);
       const int b = n & 1;
       const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
       const bool more = n + 1 < NC;
-      const float gl_next = gl_ahead;                      // gamma of chunk n + 1, loaded one chunk ago
-      if (n + 2 < NC && tid < D) gl_ahead = g_gl[(size_t)(n + 2) * D + tid];
 
       // ---- Un^T / 256 = U^T / 256 - (W S)^T / 256 for this thread's 32 tokens, as the fp16 operand of
       // both the state update and the output product
@@ -348,63 +323,54 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         mbar_arrive(&s.bar_un);
         TICK(4);
       }
-      if (tid < D) s.gl[(n + 1) & 1][tid] = gl_next;
-      TICK(5);
 
-      // ---- new state: the bf16 operand copy goes first (the next chunk's first product waits for
-      // it), then the optional snapshot and the pre-scale for the next chunk, which that product
-      // does not read
+      // ---- new state S <- gamma_C * S + P, its bf16 operand copy for the next chunk, optional snapshot
+      tc::mbar_wait(&s.bar_kgt[b], ph2, &s.abort_flag, status, kWaitKgt);   // gamma arrived with KG^T
+      TICK(5);
       tc::mbar_wait(&s.bar_m3, ph, &s.abort_flag, status, kWaitM3);
       tc::tc_fence_after_sync();
       TICK(7);
       {
-        float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
-        float* fin = (!more && sT) ? sT + (size_t)bh * D * D : nullptr;
-        const float* gln = s.gl[(n + 1) & 1];
-        float xs[2][32];
-        tc::tmem_ld32(t_lane + dkp, xs[0]);
-        tc::tmem_ld32(t_lane + dkp + 32, xs[1]);
-        tc::tmem_ld_wait();
-        if (more) {
-          float pk[32];
+        const float* gln = s.gl[n & 3];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            pk[i] = pack_bf16x2(xs[0][2 * i], xs[0][2 * i + 1]);
-            pk[16 + i] = pack_bf16x2(xs[1][2 * i], xs[1][2 * i + 1]);
+        for (int hf = 0; hf < 2; ++hf) {
+          float pr[32];
+          tc::tmem_ld32(t_lane + dkp + 32 * hf, pr);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const float4 g4 = *reinterpret_cast<const float4*>(&gln[dkp + 32 * hf + 4 * i]);
+            S[32 * hf + 4 * i] = fmaf(g4.x, S[32 * hf + 4 * i], pr[4 * i]);
+            S[32 * hf + 4 * i + 1] = fmaf(g4.y, S[32 * hf + 4 * i + 1], pr[4 * i + 1]);
+            S[32 * hf + 4 * i + 2] = fmaf(g4.z, S[32 * hf + 4 * i + 2], pr[4 * i + 2]);
+            S[32 * hf + 4 * i + 3] = fmaf(g4.w, S[32 * hf + 4 * i + 3], pr[4 * i + 3]);
           }
-          tc::tmem_st32(t_lane + kColSb + dkp / 2, pk);
+          if (more) {
+            float pk[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) pk[i] = pack_bf16x2(S[32 * hf + 2 * i], S[32 * hf + 2 * i + 1]);
+            tc::tmem_st16(t_lane + kColSb + (dkp + 32 * hf) / 2, pk);
+          }
+        }
+        if (more) {
           tc::tmem_st_wait();
           tc::tc_fence_before_sync();
           mbar_arrive(&s.bar_sb);
         }
         TICK(8);
-        if (compute_sync_or(s.abort_flag != 0)) break;     // uniform; also publishes gl[(n+1)&1]
-        TICK(10);
+        float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
+        float* fin = (!more && sT) ? sT + (size_t)bh * D * D : nullptr;
+        if (hn) {
 #pragma unroll
-        for (int hf = 0; hf < 2; ++hf) {
-          const int c0 = dkp + 32 * hf;
-          float (&x)[32] = xs[hf];
-          if (hn) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) hn[(size_t)(c0 + i) * D + dv] = x[i];
-          }
-          if (fin) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) fin[(size_t)(c0 + i) * D + dv] = x[i];
-          }
-          if (more) {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float4 g4 = *reinterpret_cast<const float4*>(&gln[c0 + 4 * i]);
-              x[4 * i] *= g4.x; x[4 * i + 1] *= g4.y; x[4 * i + 2] *= g4.z; x[4 * i + 3] *= g4.w;
-            }
-            tc::tmem_st32(t_lane + c0, x);
-          }
+          for (int i = 0; i < 64; ++i) hn[(size_t)(dkp + i) * D + dv] = S[i];
         }
-        TICK(11);
-        tc::tmem_st_wait();                                // ordered before the next arrival on bar_un
+        if (fin) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) fin[(size_t)(dkp + i) * D + dv] = S[i];
+        }
       }
       TICK(9);
+      if (s.abort_flag) break;                             // per thread: no block-level barrier in this loop
     }
     if (tid == 0) TFLUSH(16);
   }
