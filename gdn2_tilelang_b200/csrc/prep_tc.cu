@@ -239,16 +239,15 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
 
   PTICK(2);
   // ---- 2. MMA1: D_i[128 x 16(i+1)] at TMEM columns 0, 16, 48, 96
-  if (tid == 0) {
+  if (wid == 0) {                   // the warp stays converged; one elected lane issues
     tc::tc_fence_after_sync();
 #pragma unroll 1
     for (int i = 0; i < 4; ++i) {
       const int off = 8 * i * (i + 1);
-      tc::mma_bf16_ktile(tc::tmem_addr(tm, 0, off), tc::smem_u32(s.x.ops.a_own), A_PAD,
-                         tc::smem_u32(s.x.ops.bfam) + off * 16, B_PAD, D, tc::instr_desc(1, 128, 16 * (i + 1)),
-                         false);
+      tc::mma_bf16_ktile_warp(tc::tmem_addr(tm, 0, off), tc::smem_u32(s.x.ops.a_own), A_PAD,
+                              tc::smem_u32(s.x.ops.bfam) + off * 16, B_PAD, D, tc::instr_desc(1, 128, 16 * (i + 1)));
     }
-    tc::mma_commit(&s.bar_m1);
+    tc::mma_commit_warp(&s.bar_m1);
   }
   PTICK(3);
   // value side: raw loads issued while the tensor core works
@@ -434,13 +433,12 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
 
   PTICK(7);
   // ---- 4. MMA2 (tf32): W^T at TMEM columns 0..63, U^T at 64..127
-  if (tid == 0 && !s.abort_flag) {
+  if (wid == 0 && !s.abort_flag) {
     tc::tc_fence_after_sync();
     constexpr uint32_t idesc = tc::instr_desc(2, 128, BS);
-    tc::mma_tf32_ktile(tc::tmem_addr(tm, 0, 0), tc::smem_u32(s.y.et), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc, false);
-    tc::mma_tf32_ktile(tc::tmem_addr(tm, 0, 64), tc::smem_u32(s.x.sol.zt), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc,
-                       false);
-    tc::mma_commit(&s.bar_m2);
+    tc::mma_tf32_ktile_warp(tc::tmem_addr(tm, 0, 0), tc::smem_u32(s.y.et), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc);
+    tc::mma_tf32_ktile_warp(tc::tmem_addr(tm, 0, 64), tc::smem_u32(s.x.sol.zt), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc);
+    tc::mma_commit_warp(&s.bar_m2);
   }
   tc::mbar_wait(&s.bar_m2, 0, &s.abort_flag, status, 0x2000u);
   tc::tc_fence_after_sync();

@@ -305,6 +305,54 @@ __device__ __forceinline__ void mma_commit_warp(uint64_t* bar) {
       : "memory");
 }
 
+// Both operands from shared memory, four consecutive K steps, warp-collective (one election).
+#define GDN2_DEFINE_MMA_SS_K4_WARP(NAME, KIND)                                                              \
+  __device__ __forceinline__ void NAME(uint32_t d_tmem, uint64_t a_desc, uint64_t a_step, uint64_t b_desc,  \
+                                       uint64_t b_step, uint32_t idesc, uint32_t accumulate_first) {        \
+    asm volatile(                                                                                           \
+        "{\n\t"                                                                                             \
+        ".reg .pred p, t, e;\n\t"                                                                           \
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n\t"                                                             \
+        "setp.ne.b32 p, %6, 0;\n\t"                                                                         \
+        "setp.eq.b32 t, %6, %6;\n\t"                                                                        \
+        "add.u64 a1, %1, %2;\n\t"                                                                           \
+        "add.u64 a2, a1, %2;\n\t"                                                                           \
+        "add.u64 a3, a2, %2;\n\t"                                                                           \
+        "add.u64 b1, %3, %4;\n\t"                                                                           \
+        "add.u64 b2, b1, %4;\n\t"                                                                           \
+        "add.u64 b3, b2, %4;\n\t"                                                                           \
+        "elect.sync _|e, 0xffffffff;\n\t"                                                                   \
+        "@e tcgen05.mma.cta_group::1.kind::" KIND " [%0], %1, %3, %5, p;\n\t"                               \
+        "@e tcgen05.mma.cta_group::1.kind::" KIND " [%0], a1, b1, %5, t;\n\t"                               \
+        "@e tcgen05.mma.cta_group::1.kind::" KIND " [%0], a2, b2, %5, t;\n\t"                               \
+        "@e tcgen05.mma.cta_group::1.kind::" KIND " [%0], a3, b3, %5, t;\n\t"                               \
+        "}" ::"r"(d_tmem), "l"(a_desc), "l"(a_step), "l"(b_desc), "l"(b_step), "r"(idesc),                   \
+        "r"(accumulate_first)                                                                               \
+        : "memory");                                                                                        \
+  }
+GDN2_DEFINE_MMA_SS_K4_WARP(mma_bf16_k4_warp, "f16")
+GDN2_DEFINE_MMA_SS_K4_WARP(mma_tf32_k4_warp, "tf32")
+#undef GDN2_DEFINE_MMA_SS_K4_WARP
+
+// D[128 x N] = A[128 x K] * B[N x K]^T over K-chunked images, warp-collective. KSTEP = elements per MMA
+// (16 for 16-bit operands, 8 for tf32); K a multiple of 4 * KSTEP.
+__device__ __forceinline__ void mma_bf16_ktile_warp(uint32_t d_tmem, uint32_t a_addr, uint32_t a_rows, uint32_t b_addr,
+                                                    uint32_t b_rows, int K, uint32_t idesc) {
+  const uint64_t ad = kchunk_desc(a_addr, a_rows), bd = kchunk_desc(b_addr, b_rows);
+  const uint64_t astep = (2u * a_rows * 16u) >> 4, bstep = (2u * b_rows * 16u) >> 4;
+#pragma unroll
+  for (int k4 = 0; k4 < K / 64; ++k4)
+    mma_bf16_k4_warp(d_tmem, ad + 4 * k4 * astep, astep, bd + 4 * k4 * bstep, bstep, idesc, k4 > 0 ? 1u : 0u);
+}
+__device__ __forceinline__ void mma_tf32_ktile_warp(uint32_t d_tmem, uint32_t a_addr, uint32_t a_rows, uint32_t b_addr,
+                                                    uint32_t b_rows, int K, uint32_t idesc) {
+  const uint64_t ad = kchunk_desc(a_addr, a_rows), bd = kchunk_desc(b_addr, b_rows);
+  const uint64_t astep = (2u * a_rows * 16u) >> 4, bstep = (2u * b_rows * 16u) >> 4;
+#pragma unroll
+  for (int k4 = 0; k4 < K / 32; ++k4)
+    mma_tf32_k4_warp(d_tmem, ad + 4 * k4 * astep, astep, bd + 4 * k4 * bstep, bstep, idesc, k4 > 0 ? 1u : 0u);
+}
+
 // mbarrier arrives once every tcgen05 operation issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
