@@ -4,8 +4,10 @@
 
 Workload: the serving prefill of the benchmark definition -- B=4, S=16037 (250 chunks of 64 plus a
 37-token ragged tail), H=16, DK=DV=128, bf16 q/k/v/b/w, fp32 g, fp32 state, zero initial state --
-one step = one `gdn2_prefill` over the whole batch. With N > 1 ranks (torchrun, one per GPU) the 16
-heads are split across ranks with no collective ("strong" scaling: the global problem is fixed).
+one step = one `gdn2_prefill` over the whole batch. With N > 1 ranks (torchrun, one per GPU) every
+rank runs the whole workload on its own sequences ("weak" scaling, no collective: sequences and heads
+are independent); the `head_sharded` object adds the fixed global problem with its 16 heads split
+over the ranks, the way a tensor-parallel layer calls the op.
 Inputs are seeded synthetic tensors of the stated shapes and distributions.
 
 One JSON line on rank 0:
@@ -162,7 +164,7 @@ def run_reference(args, rank, world):
     print(json.dumps({
         "impl": "reference", "metric": "gdn2_prefill_tokens_per_s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "sample": sample},
         "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -218,9 +220,9 @@ def main():
         _cabi.kernels().check_device_status(dev)
         print(f"profile case {args.profile_case} done")
         return
-    if H % world:
-        raise SystemExit(f"{H} heads do not split over {world} ranks")
-    Hl = H // world
+    # N > 1: data parallel. Every rank runs the whole workload on its own sequences (seeded by rank);
+    # the op has no cross-sequence or cross-head term, so there is no collective on the data path.
+    Hl = H
     K = _cabi.kernels()
     q, k, v, g, b, w = device_inputs(B, S, Hl, DK, DV, dev, seed=rank)
     ins = (q, k, v, g, b, w)
@@ -244,9 +246,23 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = float(t.item())
-    tokens = B * S
+    tokens = B * S * world
     value = tokens / (ms * 1e-3)
     K.check_device_status(dev)
+
+    # ---- the other way to use N GPUs: ONE copy of the workload with its heads split over the ranks
+    # (how a tensor-parallel layer calls the op); fixed global problem, still no collective
+    head_sharded = None
+    if world > 1 and H % world == 0:
+        hs_ins = device_inputs(B, S, H // world, DK, DV, dev, seed=1000 + rank)
+        barrier()
+        ms_hs = time_events(lambda: gdn2.gdn2_prefill(*hs_ins), args.steps, args.warmup, barrier)
+        t = torch.tensor([ms_hs], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_hs = float(t.item())
+        head_sharded = {"heads_per_gpu": H // world, "ms_per_step": ms_hs, "value": B * S / (ms_hs * 1e-3),
+                        "unit": "tokens/s", "scaling": "strong"}
+        del hs_ins
 
     # ---- end to end: pinned host inputs, H2D + kernels + D2H of o per step
     host = [x.cpu().pin_memory() for x in ins]
@@ -304,13 +320,13 @@ def main():
     peak, peak_kind = measured_peaks()
     dom_ms, dom_bytes = stages[dom]
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
-    whole_op_bytes = B * S * Hl * 2048.0
+    whole_op_bytes = B * S * Hl * 2048.0                  # per GPU
     roofline = {
         "bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
         "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth", "traffic": None,
         "stages_ms": {s: stages[s][0] for s in stages},
         "stages_frac": {s: stages[s][1] / (stages[s][0] * 1e-3) / 1e9 / peak for s in stages},
-        "whole_op_frac": whole_op_bytes / (ms * 1e-3) / 1e9 / peak,
+        "whole_op_frac": whole_op_bytes / (ms * 1e-3) / 1e9 / peak,       # per GPU, of its own HBM
     }
     del ws, o, fin
 
@@ -338,15 +354,16 @@ def main():
         print(json.dumps({
             "metric": "gdn2_prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "heads_per_gpu": Hl, "parallelism": f"head-sharded x{world}, no collective",
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "heads_per_gpu": Hl,
+                       "parallelism": f"data-parallel x{world}: the whole workload per GPU on its own sequences, no collective",
                        "l2": "inputs (2.1 GB) exceed L2, no flush needed", "prefill_path":
                        {1: "simt", 2: "tcgen05"}[path]},
             "clocks": clk.result,
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches * world,
-            "roofline": roofline, "decode": decode, "cpu_baseline": cpu,
+            "roofline": roofline, "decode": decode, "cpu_baseline": cpu, "head_sharded": head_sharded,
         }))
     if world > 1:
         dist.destroy_process_group()
