@@ -54,16 +54,53 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    """SM clock and throttle-reason samples while the timed region runs: NVML from a thread (a sample
+    every 2 ms), or nvidia-smi in a child process when the NVML binding is missing. Read-only."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    MASKS = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20, "hw_thermal_slowdown": 0x40}
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.gpu_index).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(uuid)
+        except Exception:
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+
+    def _nvml_loop(self, nv, h):
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while not self._stop.is_set():
+            try:
+                self._sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                mask = int(get_reasons(h))
+                for name, bit in self.MASKS.items():
+                    if mask & bit:
+                        self._reasons.add(name)
+            except Exception:
+                break
+            self._stop.wait(0.002)
 
     def __init__(self, gpu_index: int):
         self.gpu_index, self.proc = gpu_index, None
 
     def __enter__(self):
+        self._thread = None
+        try:
+            import threading
+            nv, h = self._nvml_handle()
+            self._max = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            self._sm, self._reasons, self._stop = [], set(), threading.Event()
+            self._thread = threading.Thread(target=self._nvml_loop, args=(nv, h), daemon=True)
+            self._thread.start()
+            return self
+        except Exception:
+            self._thread = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -74,6 +111,13 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+            if self._sm:
+                self.result = {"sm_mhz": statistics.median(self._sm), "sm_max_mhz": self._max,
+                               "reasons": sorted(self._reasons), "samples": len(self._sm), "source": "nvml"}
+            return
         if self.proc is None:
             return
         time.sleep(0.15)
