@@ -19,7 +19,7 @@ import torch
 from . import _cabi
 from .config import DEFAULT_KERNEL_CONFIG, GDN2Config
 
-__all__ = ["gdn2_prefill", "gdn2_decode", "gdn2_decode_step"]
+__all__ = ["gdn2_prefill", "gdn2_prefill_from_host", "gdn2_decode", "gdn2_decode_step"]
 
 
 def _check_inputs(q, k, v, g, b, w):
@@ -84,3 +84,89 @@ def gdn2_prefill(q, k, v, g, b, w, state=None, scale=None, config: GDN2Config = 
     if S > n_full:
         K.decode(*(t[:, n_full:] for t in (q, k, v, g, b, w)), state, scale, out=o[:, n_full:])
     return o, state
+
+
+@torch.no_grad()
+def gdn2_prefill_from_host(q, k, v, g, b, w, state=None, scale=None, config: GDN2Config = DEFAULT_KERNEL_CONFIG,
+                           device=None, out=None):
+    """``gdn2_prefill`` for prompts whose tensors live in host memory (pinned, for the copies to be
+    asynchronous). No counterpart in the reference, whose callers upload first and call ``gdn2_prefill``.
+
+    The batch is streamed one sequence at a time through double-buffered device inputs: the upload of
+    sequence i + 1 and the download of the outputs of sequence i - 1 run on their own CUDA streams while
+    sequence i is computed, so the call costs about as much as its host-to-device traffic alone instead
+    of upload + kernels + download one after the other. Sequences are independent, so the results are
+    those of one ``gdn2_prefill`` over the whole batch.
+
+    Returns ``(o, state)``: ``o`` [B, S, H, DV] in host memory (``out`` if given, else a new pinned
+    tensor), complete when the current stream reaches the end of this call; ``state`` [B, H, DK, DV]
+    float32 on the device. ``state`` (initial, optional) may live on either side.
+    """
+    config.validate()
+    B, S, H, DK, DV = _check_inputs(q, k, v, g, b, w)
+    dev = torch.device(device if device is not None else "cuda")
+    if dev.type != "cuda":                                 # host-logic tests: nothing to overlap
+        o, st = gdn2_prefill(q, k, v, g, b, w, state, scale, config)
+        if out is not None:
+            out.copy_(o)
+            o = out
+        return o, st
+    if dev.index is None:
+        dev = torch.device("cuda", torch.cuda.current_device())
+    ins = (q, k, v, g, b, w)
+    if out is None:
+        out = torch.empty(B, S, H, DV, dtype=v.dtype).pin_memory()
+    elif out.shape != (B, S, H, DV) or out.dtype != v.dtype or out.device.type != "cpu":
+        raise ValueError("out must be a host tensor of shape [B, S, H, DV] in v.dtype")
+    if state is not None and state.shape != (B, H, DK, DV):
+        raise ValueError(f"state must have shape {(B, H, DK, DV)}, got {tuple(state.shape)}")
+
+    with torch.cuda.device(dev):
+        main = torch.cuda.current_stream(dev)
+        up, down = _transfer_streams(dev)
+        slots = [[torch.empty((1,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for t in ins] for _ in range(2)]
+        state_out = torch.empty(B, H, DK, DV, dtype=config.state_dtype, device=dev)
+        if state is not None:
+            state_out.copy_(state, non_blocking=True)
+        uploaded = [torch.cuda.Event() for _ in range(B)]
+        consumed = [torch.cuda.Event() for _ in range(B)]      # sequence i's input slot may be overwritten
+        computed = [torch.cuda.Event() for _ in range(B)]
+        outputs = []                                            # device outputs stay alive until the call ends
+        up.wait_stream(main)                                    # the buffers above exist before anything lands in them
+        down.wait_stream(main)
+
+        def upload(i):
+            with torch.cuda.stream(up):
+                if i >= 2:
+                    up.wait_event(consumed[i - 2])
+                for d, h in zip(slots[i & 1], ins):
+                    d.copy_(h[i:i + 1], non_blocking=True)
+                uploaded[i].record(up)
+
+        upload(0)
+        for i in range(B):
+            if i + 1 < B:
+                upload(i + 1)
+            main.wait_event(uploaded[i])
+            st_in = state_out[i:i + 1] if state is not None else None
+            o_i, st_i = gdn2_prefill(*slots[i & 1], st_in, scale, config)
+            outputs.append(o_i)
+            state_out[i:i + 1].copy_(st_i)
+            consumed[i].record(main)
+            computed[i].record(main)
+            with torch.cuda.stream(down):
+                down.wait_event(computed[i])
+                out[i:i + 1].copy_(o_i, non_blocking=True)
+        main.wait_stream(down)
+        main.wait_stream(up)
+    return out, state_out
+
+
+_TRANSFER_STREAMS: dict = {}
+
+
+def _transfer_streams(dev):
+    key = (dev.type, dev.index)
+    if key not in _TRANSFER_STREAMS:
+        _TRANSFER_STREAMS[key] = (torch.cuda.Stream(dev), torch.cuda.Stream(dev))
+    return _TRANSFER_STREAMS[key]

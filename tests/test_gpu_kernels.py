@@ -213,6 +213,24 @@ def test_prefill_ragged_d128_bf16(K):
     assert orc.rel_fro_err(state.cpu(), s_ref) < STATE_FRO
 
 
+def test_prefill_from_host_streams_sequences(K):
+    B, S, H, D = 3, 64 * 6 + 21, 4, 128
+    dev, host = bf16_inputs(B, S, H, D, D, seed=15)
+    s0 = torch.randn(B, H, D, D, device="cuda") * 0.1
+    o_ref, s_ref = gdn2.gdn2_prefill(*dev, s0)
+    pinned = [t.cpu().pin_memory() for t in dev]
+    o, s = gdn2.gdn2_prefill_from_host(*pinned, s0.cpu())
+    torch.cuda.synchronize()
+    assert o.device.type == "cpu" and o.is_pinned() and s.is_cuda
+    assert torch.equal(o, o_ref.cpu())                       # same kernels on the same values
+    assert torch.equal(s, s_ref)
+    o2, s2 = gdn2.gdn2_prefill_from_host(*pinned)            # no initial state
+    o_ref2, s_ref2 = gdn2.gdn2_prefill(*dev)
+    torch.cuda.synchronize()
+    assert torch.equal(o2, o_ref2.cpu()) and torch.equal(s2, s_ref2)
+    K.check_device_status()
+
+
 def test_fast_decay_d128_bf16_takes_exact_path(K):
     dev, host = bf16_inputs(1, 128, 2, 128, 128, seed=17, gate="softplus", decay_scale=30.0)
     o_ref, s_ref = orc.recurrence(*host)

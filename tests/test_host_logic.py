@@ -72,6 +72,17 @@ def test_segmented_prefill_equals_one_pass(fake):
     assert orc.rel_max_err(state, s_all) < 2e-5
 
 
+def test_prefill_from_host_without_a_gpu_equals_prefill(fake):
+    ins = orc.make_inputs(2, 100, 3, 32, 24, gate="softplus")
+    s0 = torch.randn(2, 3, 32, 24)
+    o_ref, s_ref = gdn2.gdn2_prefill(*ins, s0)
+    out = torch.empty_like(o_ref)
+    o, s = gdn2.gdn2_prefill_from_host(*ins, s0, device="cpu", out=out)
+    assert o is out and torch.equal(o, o_ref) and torch.equal(s, s_ref)
+    with pytest.raises(ValueError):
+        gdn2.gdn2_prefill_from_host(*ins, torch.zeros(1, 3, 32, 24), device="cpu")
+
+
 def test_decode_step_shapes_and_in_place_state(fake):
     q, k, v, g, b, w = orc.make_inputs(2, 1, 3, 32, 24, gate="softplus")
     s0 = golden_state(2, 3, 32, 24, 4, 0.3)
