@@ -1,6 +1,9 @@
 // Chunk-local stage of the chunkwise forward, tensor-core (tcgen05 / TMEM) family, for
-// DK = DV = 128 and bf16 inputs. One 128-thread block per (chunk, batch*head), two blocks per SM;
-// thread c owns key channel c and value channel c, so the cumulative decay is a private running sum.
+// DK = DV = 128 and bf16 inputs. One 256-thread block per (chunk, batch*head), two blocks per SM.
+// Thread (c, hf) owns key channel c and value channel c for the tokens of half hf of the chunk
+// (32 tokens = two 16-token sub-blocks), so the cumulative decay is a private running sum plus one
+// prefix exchanged through shared memory. Two threads per channel, rather than one, double the warps
+// an SM has to hide latency with at the same shared-memory footprint.
 //
 // What the reference spreads over five kernels (cumsum, intra_diag, inter_blocks, solve, wy:
 // gdn2/forward.py:65-535 of the reference project) is one kernel here, and the intermediates it
@@ -36,6 +39,7 @@ namespace {
 
 constexpr int D = 128;
 constexpr int BS = kChunk;
+constexpr int kThreads = 256;
 constexpr int A_PAD = 129;        // rows per K chunk of a 128-row bf16 image, +1 pad row: kills bank conflicts
 constexpr int B_PAD = 161;        // 160 key rows (16 + 32 + 48 + 64) + 1 pad row
 constexpr int TM_STRIDE = 68;     // floats per Tm row (row-major, padded against bank conflicts)
@@ -46,7 +50,7 @@ constexpr uint32_t kQgCol = 160;  // TMEM columns [160,192): packed Qg of the th
 
 #ifdef GDN2_SCAN_TIMING
 __device__ unsigned long long g_prep_timing[16];
-#define PTICK(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) { long long now_ = clock64(); g_prep_timing[i] = now_ - tprev; tprev = now_; } } while (0)
+#define PTICK(i) do { if (blockIdx.x == 100 && blockIdx.y == 32 && tid == 0) { long long now_ = clock64(); g_prep_timing[i] = now_ - tprev; tprev = now_; } } while (0)
 #else
 #define PTICK(i) do {} while (0)
 #endif
@@ -67,6 +71,7 @@ struct PrepTcSmem {
     float et[16 * D * 4];                    // A of MMA2: E^T  [tok/4][128 dk][4]
     __nv_bfloat16 wq[16 * A_PAD * 8];        // staging of the WQ record: [dk/8][129][8]
   } y;
+  float pre[2][3][D];                        // per half and channel: first-row G of its two sub-blocks, its total (relative)
   uint64_t bar_m1, bar_m2;
   uint32_t tmem_base;
   int abort_flag;
@@ -83,7 +88,27 @@ __device__ __forceinline__ float pick4(int j, float a0, float a1, float a2, floa
   return j == 0 ? a0 : j == 1 ? a1 : j == 2 ? a2 : a3;
 }
 
-__global__ void __launch_bounds__(128, 2)
+// Raw values of one channel for 8 consecutive tokens, converted only when consumed.
+struct Raw8 {
+  float g[8];
+  __nv_bfloat16 k[8], q[8], b[8];
+};
+__device__ __forceinline__ void load_raw8(Raw8& r, const float* gp, const __nv_bfloat16* kp, const __nv_bfloat16* qp,
+                                          const __nv_bfloat16* bp, size_t rstride) {
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const size_t off = u * rstride;
+    r.g[u] = __ldg(gp + off); r.k[u] = __ldg(kp + off); r.q[u] = __ldg(qp + off); r.b[u] = __ldg(bp + off);
+  }
+}
+
+// Per-sub-block constants of the gating step.
+struct SubConst {
+  float ref, refn, gam_ref, kg_c, cc_a, cc_b;
+  int j, off_j;
+};
+
+__global__ void __launch_bounds__(kThreads, 2)
 prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
                const __nv_bfloat16* __restrict__ b, const __nv_bfloat16* __restrict__ w, WsPtrs P, int S, int H,
@@ -95,49 +120,54 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const int ib = bh / H, ih = bh % H;
   const int64_t ch = (int64_t)bh * NC + n;
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
-  const int c = tid;
+  const int c = tid & (D - 1);                                          // channel = TMEM lane
+  const int hf = tid >> 7;                                              // token half: tokens [32 hf, 32 hf + 32)
+  const int lq = wid & 3;                                               // TMEM lane quarter of this warp
   const size_t row0 = ((size_t)ib * in_bs + (size_t)n * BS) * H + ih;   // token row of t = 0
   const size_t rstride = (size_t)H * D;                                 // elements between tokens
-  const float* gp = g + row0 * D + c;
+  const size_t hoff = (size_t)(32 * hf) * rstride;                      // first token of this thread's half
+  const float* gp = g + row0 * D + c + hoff;
 #ifdef GDN2_SCAN_TIMING
   long long tprev = clock64();
 #endif
 
   // Pull the whole input tile of this chunk-head towards L2 before anything depends on it: 64 rows x
-  // (5 x 256 B + 512 B) = 896 128-byte lines, 7 per thread.
+  // (5 x 256 B + 512 B) = 896 128-byte lines, 3.5 per thread.
   {
     const char* base[6] = {reinterpret_cast<const char*>(g + row0 * D), reinterpret_cast<const char*>(k + row0 * D),
                            reinterpret_cast<const char*>(q + row0 * D), reinterpret_cast<const char*>(b + row0 * D),
                            reinterpret_cast<const char*>(v + row0 * D), reinterpret_cast<const char*>(w + row0 * D)};
 #pragma unroll
-    for (int i = 0; i < 7; ++i) {
-      const int line = tid + 128 * i;                     // 0..895: g takes lines [0,256), then 128 per bf16 tensor
-      const int ten = line < 256 ? 0 : 1 + ((line - 256) >> 7);
-      const int rem = line < 256 ? line : (line - 256) & 127;
-      const int per_row = ten == 0 ? 4 : 2;
-      const int rowi = rem / per_row, seg = rem % per_row;
-      const char* ptr = base[ten] + (size_t)rowi * rstride * (ten == 0 ? 4 : 2) + seg * 128;
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+    for (int i = 0; i < 4; ++i) {
+      const int line = tid + kThreads * i;                // 0..895: g takes lines [0,256), then 128 per bf16 tensor
+      if (line < 896) {
+        const int ten = line < 256 ? 0 : 1 + ((line - 256) >> 7);
+        const int rem = line < 256 ? line : (line - 256) & 127;
+        const int per_row = ten == 0 ? 4 : 2;
+        const int rowi = rem / per_row, seg = rem % per_row;
+        const char* ptr = base[ten] + (size_t)rowi * rstride * (ten == 0 ? 4 : 2) + seg * 128;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+      }
     }
   }
 
-  // ---- 1a. G at the first row of every sub-block and at the last token; decay-span check
-  float ref0 = 0.f, ref1 = 0.f, ref2 = 0.f, ref3 = 0.f, g_last;
+  // ---- 1a. G at the first row of every sub-block and at the last token; decay-span check.
+  //          Each thread sums its own half; the halves meet through shared memory.
+  float ref0, ref1, ref2, ref3, g_last, run0;
   bool bad = false;
   {
-    float gv[BS];
+    float gv[32];
 #pragma unroll
-    for (int t = 0; t < BS; ++t) gv[t] = __ldg(gp + t * rstride) * kLog2e;     // 64 independent loads in flight
-    float run = 0.f;
+    for (int t = 0; t < 32; ++t) gv[t] = __ldg(gp + t * rstride) * kLog2e;     // 32 independent loads in flight
+    float run = 0.f, first[2];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float first = run + gv[16 * j];
+    for (int j = 0; j < 2; ++j) {
+      first[j] = run + gv[16 * j];
 #pragma unroll
       for (int u = 0; u < 16; ++u) run += gv[16 * j + u];
-      bad |= !((first - run) <= kMaxSpanLog2);
-      if (j == 0) ref0 = first; else if (j == 1) ref1 = first; else if (j == 2) ref2 = first; else ref3 = first;
+      bad |= !((first[j] - run) <= kMaxSpanLog2);
     }
-    g_last = run;
+    s.pre[hf][0][c] = first[0]; s.pre[hf][1][c] = first[1]; s.pre[hf][2][c] = run;
   }
   if (tid == 0) {
     tc::mbar_init(&s.bar_m1, 1);
@@ -149,6 +179,13 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (tid == 0) P.flags[ch] = any_bad ? 1 : 0;
   if (any_bad) return;              // the exact kernel redoes this chunk; nothing allocated yet
+  {
+    const float tot0 = s.pre[0][2][c];
+    ref0 = s.pre[0][0][c]; ref1 = s.pre[0][1][c];
+    ref2 = tot0 + s.pre[1][0][c]; ref3 = tot0 + s.pre[1][1][c];
+    g_last = tot0 + s.pre[1][2][c];
+    run0 = hf ? tot0 : 0.f;
+  }
   if (wid == 0) tc::tmem_alloc(&s.tmem_base, kTmemCols);
   tc::tc_fence_before_sync();
   __syncthreads();
@@ -156,66 +193,58 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const uint32_t tm = s.tmem_base;
 
   PTICK(1);
-  // ---- 1b. gated operands of channel c, one 16-token sub-block per iteration; the next sub-block's
-  //          64 loads are issued (raw, unconverted) before the current one is processed
+  // ---- 1b. gated operands of channel c for this thread's 32 tokens, in four groups of 8; the next
+  //          group's 32 loads are issued (raw, unconverted) before the current one is processed
   {
-    const __nv_bfloat16* qp = q + row0 * D + c;
-    const __nv_bfloat16* kp = k + row0 * D + c;
-    const __nv_bfloat16* bp = b + row0 * D + c;
+    const __nv_bfloat16* qp = q + row0 * D + c + hoff;
+    const __nv_bfloat16* kp = k + row0 * D + c + hoff;
+    const __nv_bfloat16* bp = b + row0 * D + c + hoff;
     const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
     const int cb = (c >> 3) * B_PAD * 8 + (c & 7);
     char* kgt_g = P.kgt + (size_t)ch * (D * BS * 2) + c * 16;   // fp16 image [tok/8][128 dk][8]
-    float gc[16], gn[16];
-    __nv_bfloat16 kc[16], qc[16], bc[16], kn_[16], qn_[16], bn_[16];
+    float run = run0;
+    SubConst sc;
+
+    auto sub_consts = [&](int j) {
+      sc.j = j;
+      sc.off_j = 8 * j * (j + 1);                               // first row of B_j: 0, 16, 48, 96
+      sc.ref = pick4(j, ref0, ref1, ref2, ref3);
+      sc.refn = pick4(j, ref1, ref2, ref3, 0.f);                // ref of the next sub-block (unused for j = 3)
+      sc.gam_ref = ex2(sc.ref);
+      sc.kg_c = (j < 3) ? ex2(g_last - sc.refn) : 1.f;
+      sc.cc_a = ex2(pick4(j, ref2, ref3, 0.f, 0.f) - sc.refn);  // B_{j+2} relative to B_{j+1}
+      sc.cc_b = ex2(ref3 - sc.refn);                            // B_{j+3} relative to B_{j+1} (j = 0 only)
+    };
+    // one group: tokens t0 .. t0 + 7 (t0 a multiple of 8)
+    auto gate8 = [&](const Raw8& r, int t0) {
+      const int j = sc.j;
+      uint32_t qgp[4], kgp[4];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) {
-      const size_t off = u * rstride;
-      gc[u] = __ldg(gp + off); kc[u] = __ldg(kp + off); qc[u] = __ldg(qp + off); bc[u] = __ldg(bp + off);
-    }
-    float run = 0.f;
-#pragma unroll 1
-    for (int j = 0; j < 4; ++j) {
-      if (j < 3) {
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const size_t off = (16 * (j + 1) + u) * rstride;
-          gn[u] = __ldg(gp + off); kn_[u] = __ldg(kp + off); qn_[u] = __ldg(qp + off); bn_[u] = __ldg(bp + off);
-        }
-      }
-      const int off_j = 8 * j * (j + 1);                       // first row of B_j: 0, 16, 48, 96
-      const float ref = pick4(j, ref0, ref1, ref2, ref3);
-      const float refn = pick4(j, ref1, ref2, ref3, 0.f);      // ref of the next sub-block (unused for j = 3)
-      const float gam_ref = ex2(ref);
-      const float kg_c = (j < 3) ? ex2(g_last - refn) : 1.f;
-      const float cc_a = ex2(pick4(j, ref2, ref3, 0.f, 0.f) - refn);   // B_{j+2} relative to B_{j+1}
-      const float cc_b = ex2(ref3 - refn);                               // B_{j+3} relative to B_{j+1} (j = 0 only)
-      uint32_t qgp[8], kgp[8];
-#pragma unroll
-      for (int t4 = 0; t4 < 4; ++t4) {
+      for (int t4 = 0; t4 < 2; ++t4) {
         float e4[4], kg4[4], qg4[4];
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const int uu = 4 * t4 + u;
-          const int t = 16 * j + uu;
-          run += gc[uu] * kLog2e;
-          const float kf = __bfloat162float(kc[uu]), qf = __bfloat162float(qc[uu]);
-          const float a = ex2(run - ref);                     // <= 1
-          const float co = ex2(ref - run);                    // >= 1, bounded by the span check
-          const float nx = (j < 3) ? ex2(refn - run) : ex2(g_last - run);   // <= 1
-          const float e = __bfloat162float(bc[uu]) * kf;
+          const int t = t0 + uu;
+          run += r.g[uu] * kLog2e;
+          const float kf = __bfloat162float(r.k[uu]), qf = __bfloat162float(r.q[uu]);
+          const float a = ex2(run - sc.ref);                  // <= 1
+          const float co = ex2(sc.ref - run);                 // >= 1, bounded by the span check
+          const float nx = (j < 3) ? ex2(sc.refn - run) : ex2(g_last - run);   // <= 1
+          const float e = __bfloat162float(r.b[uu]) * kf;
           s.x.ops.a_own[ca + t * 8] = __float2bfloat16_rn(e * a);
           s.x.ops.a_own[ca + (BS + t) * 8] = __float2bfloat16_rn(qf * a);
-          s.x.ops.bfam[cb + (off_j + t) * 8] = __float2bfloat16_rn(kf * co);
+          s.x.ops.bfam[cb + (sc.off_j + t) * 8] = __float2bfloat16_rn(kf * co);
           const float kn = kf * nx;
           if (j < 3) s.x.ops.bfam[cb + (8 * (j + 1) * (j + 2) + t) * 8] = __float2bfloat16_rn(kn);
-          if (j < 2) s.x.ops.bfam[cb + (8 * (j + 2) * (j + 3) + t) * 8] = __float2bfloat16_rn(kn * cc_a);
-          if (j < 1) s.x.ops.bfam[cb + (96 + t) * 8] = __float2bfloat16_rn(kn * cc_b);
-          const float gam = a * gam_ref;
+          if (j < 2) s.x.ops.bfam[cb + (8 * (j + 2) * (j + 3) + t) * 8] = __float2bfloat16_rn(kn * sc.cc_a);
+          if (j < 1) s.x.ops.bfam[cb + (96 + t) * 8] = __float2bfloat16_rn(kn * sc.cc_b);
+          const float gam = a * sc.gam_ref;
           e4[u] = tf32_rn(e * gam);
           qg4[u] = scale * qf * gam;
-          kg4[u] = kn * kg_c * kValScale;
+          kg4[u] = kn * sc.kg_c * kValScale;
         }
-        const int tq = 4 * j + t4;                              // token quad index
+        const int tq = (t0 >> 2) + t4;                          // token quad index
         *reinterpret_cast<float4*>(&s.y.et[(tq * D + c) * 4]) = make_float4(e4[0], e4[1], e4[2], e4[3]);
         __half2 h01 = __floats2half2_rn(kg4[0], kg4[1]), h23 = __floats2half2_rn(kg4[2], kg4[3]);
         kgp[2 * t4] = *reinterpret_cast<uint32_t*>(&h01);
@@ -224,14 +253,27 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         qgp[2 * t4] = *reinterpret_cast<uint32_t*>(&p01);
         qgp[2 * t4 + 1] = *reinterpret_cast<uint32_t*>(&p23);
       }
-      tc::tmem_st8(tc::tmem_addr(tm, wid * 32, kQgCol + 8 * j), qgp);
-      *reinterpret_cast<uint4*>(kgt_g + (size_t)(2 * j) * D * 16) = make_uint4(kgp[0], kgp[1], kgp[2], kgp[3]);
-      *reinterpret_cast<uint4*>(kgt_g + (size_t)(2 * j + 1) * D * 16) = make_uint4(kgp[4], kgp[5], kgp[6], kgp[7]);
-#pragma unroll
-      for (int u = 0; u < 16; ++u) { gc[u] = gn[u]; kc[u] = kn_[u]; qc[u] = qn_[u]; bc[u] = bn_[u]; }
+      tc::tmem_st4(tc::tmem_addr(tm, lq * 32, kQgCol + (t0 >> 1)), qgp);
+      *reinterpret_cast<uint4*>(kgt_g + (size_t)(t0 >> 3) * D * 16) = make_uint4(kgp[0], kgp[1], kgp[2], kgp[3]);
+    };
+
+    Raw8 ra, rb;
+    load_raw8(ra, gp, kp, qp, bp, rstride);
+#pragma unroll 1
+    for (int sb = 0; sb < 2; ++sb) {                            // this thread's two sub-blocks
+      const int t0 = 32 * hf + 16 * sb;
+      const size_t o8 = (size_t)(16 * sb + 8) * rstride;
+      load_raw8(rb, gp + o8, kp + o8, qp + o8, bp + o8, rstride);
+      sub_consts(2 * hf + sb);
+      gate8(ra, t0);
+      if (sb == 0) {
+        const size_t o16 = (size_t)16 * rstride;
+        load_raw8(ra, gp + o16, kp + o16, qp + o16, bp + o16, rstride);
+      }
+      gate8(rb, t0 + 8);
     }
     tc::tmem_st_wait();
-    P.gl[(size_t)ch * D + c] = ex2(g_last);
+    if (hf == 1) P.gl[(size_t)ch * D + c] = ex2(g_last);
   }
   tc::fence_async_smem();
   tc::tc_fence_before_sync();
@@ -254,27 +296,20 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   // z = w*v of this thread's value channel waits in TMEM columns [192,256) of its own lane until the
   // MMA1 operands are dead and (w*v)^T can take their place in shared memory
   {
-    const __nv_bfloat16* vp = v + row0 * D + c;
-    const __nv_bfloat16* wp = w + row0 * D + c;
+    const __nv_bfloat16* vp = v + row0 * D + c + hoff;
+    const __nv_bfloat16* wp = w + row0 * D + c + hoff;
     __nv_bfloat16 vr[16], wr[16], vn[16], wn[16];         // raw values: converted one group behind the loads
 #pragma unroll
     for (int u = 0; u < 16; ++u) { vr[u] = __ldg(vp + u * rstride); wr[u] = __ldg(wp + u * rstride); }
-#pragma unroll 1
-    for (int jj = 0; jj < 4; ++jj) {
-      if (jj < 3) {
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          const size_t off = (16 * (jj + 1) + u) * rstride;
-          vn[u] = __ldg(vp + off); wn[u] = __ldg(wp + off);
-        }
-      }
-      float z[16];
+    for (int u = 0; u < 16; ++u) { vn[u] = __ldg(vp + (16 + u) * rstride); wn[u] = __ldg(wp + (16 + u) * rstride); }
+    float z[16];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) z[u] = tf32_rn(__bfloat162float(vr[u]) * __bfloat162float(wr[u]));
-      tc::tmem_st16(tc::tmem_addr(tm, wid * 32, kZCol + 16 * jj), z);
+    for (int u = 0; u < 16; ++u) z[u] = tf32_rn(__bfloat162float(vr[u]) * __bfloat162float(wr[u]));
+    tc::tmem_st16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * hf), z);
 #pragma unroll
-      for (int u = 0; u < 16; ++u) { vr[u] = vn[u]; wr[u] = wn[u]; }
-    }
+    for (int u = 0; u < 16; ++u) z[u] = tf32_rn(__bfloat162float(vn[u]) * __bfloat162float(wn[u]));
+    tc::tmem_st16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * hf + 16), z);
     tc::tmem_st_wait();
   }
   PTICK(4);
@@ -282,19 +317,20 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::tc_fence_after_sync();
   PTICK(5);
 
-  // ---- 2b. read back: lane = row (0..63 Tm, 64..127 Aqk); a warp spans sub-blocks i0 and i0+1.
+  // ---- 2b. read back: lane = row (0..63 Tm, 64..127 Aqk); a warp spans sub-blocks i0 and i0+1, and
+  //          the two threads of a row split the four 16-column groups.
   //          The MMA1 operands are dead now: Tm, Ai and (w*v)^T take their place.
   {
-    const int r = tid & 63;
-    const bool is_q = tid >= 64;
-    const int i0 = 2 * (wid & 1);
+    const int r = c & 63;
+    const bool is_q = c >= 64;
+    const int i0 = 2 * (lq & 1);
     const bool hi = lane >= 16;
-    const uint32_t t_lo = tc::tmem_addr(tm, wid * 32, 8 * i0 * (i0 + 1));
-    const uint32_t t_hi = tc::tmem_addr(tm, wid * 32, 8 * (i0 + 1) * (i0 + 2));
+    const uint32_t t_lo = tc::tmem_addr(tm, lq * 32, 8 * i0 * (i0 + 1));
+    const uint32_t t_hi = tc::tmem_addr(tm, lq * 32, 8 * (i0 + 1) * (i0 + 2));
     float* tr = s.x.sol.tm + r * TM_STRIDE;
     __half* ag = reinterpret_cast<__half*>(P.aqk + (size_t)ch * (BS * BS * 2));   // fp16, 256 * Aqk
 #pragma unroll 1
-    for (int cg = 0; cg < 4; ++cg) {
+    for (int cg = 2 * hf; cg < 2 * hf + 2; ++cg) {
       float lo16[16], hi16[16], row[16];
 #pragma unroll
       for (int x = 0; x < 16; ++x) { lo16[x] = 0.f; hi16[x] = 0.f; }
@@ -318,11 +354,11 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         *reinterpret_cast<uint4*>(ag + ((2 * cg + 1) * BS + r) * 8) = tc::pack8_f16(&row[8], kValScale);
       }
     }
-    // (w*v)^T image from the TMEM stash
+    // (w*v)^T image from the TMEM stash: each thread moves the 32 tokens it produced
 #pragma unroll 1
-    for (int jj = 0; jj < 4; ++jj) {
+    for (int jj = 2 * hf; jj < 2 * hf + 2; ++jj) {
       float z[16];
-      tc::tmem_ld16(tc::tmem_addr(tm, wid * 32, kZCol + 16 * jj), z);
+      tc::tmem_ld16(tc::tmem_addr(tm, lq * 32, kZCol + 16 * jj), z);
       tc::tmem_ld_wait();
 #pragma unroll
       for (int t4 = 0; t4 < 4; ++t4)
@@ -357,12 +393,12 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         x[r] = (r == j ? 1.f : 0.f) - (a0 + a1);            // rows above j stay 0, row j is 1
         aim[AI(16 * i + r, 16 * i + j)] = tf32_rn(x[r]);
       }
-    } else {
-      // zero the blocks above the diagonal: 6 blocks x 256 entries over 64 threads
-      const int z = tid - BS;
+    } else if (tid >= 128) {
+      // zero the blocks above the diagonal: 6 blocks x 256 entries over 128 threads
+      const int z = tid - 128;
 #pragma unroll
-      for (int e = 0; e < 24; ++e) {
-        const int idx = z + 64 * e;                         // 0..1535
+      for (int e = 0; e < 12; ++e) {
+        const int idx = z + 128 * e;                        // 0..1535
         const int blk = idx >> 8, rr = (idx >> 4) & 15, cc = idx & 15;
         const int bi = blk < 3 ? 0 : blk < 5 ? 1 : 2;       // (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
         const int bj = blk < 3 ? blk + 1 : blk < 5 ? blk - 1 : 3;
@@ -391,9 +427,9 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         }
       }
     };
-    // N_ik = D_i T_ik, in place over T_ik: warp w takes pairs w and w + 4 of (1,0) (2,0) (2,1) (3,0) (3,1) (3,2)
-#pragma unroll 1
-    for (int pidx = wid; pidx < 6; pidx += 4) {
+    // N_ik = D_i T_ik, in place over T_ik: warp w < 6 takes pair w of (1,0) (2,0) (2,1) (3,0) (3,1) (3,2)
+    if (wid < 6) {
+      const int pidx = wid;
       const int bi = pidx < 1 ? 1 : pidx < 3 ? 2 : 3;
       const int bk = pidx < 1 ? 0 : pidx < 3 ? pidx - 1 : pidx - 3;
       float acc[2][4] = {};
@@ -407,7 +443,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       }
     }
     __syncthreads();
-    // X_ij, distance d = i - j = 1, 2, 3; warp w takes block (w + d, w)
+    // X_ij, distance d = i - j = 1, 2, 3; warp w < 4 - d takes block (w + d, w)
 #pragma unroll 1
     for (int d = 1; d < 4; ++d) {
       if (wid + d < 4) {
@@ -444,41 +480,39 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::tc_fence_after_sync();
   PTICK(8);
 
-  // ---- 5. W and Qg rows into the WQ staging image (E^T is dead now), U^T straight to global
+  // ---- 5. W and Qg rows into the WQ staging image (E^T is dead now), U^T straight to global; each
+  //         thread handles the 32 tokens of its half
   {
     const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
     char* ut_g = P.ut + (size_t)ch * (D * BS * 2) + c * 16;       // fp16 image [tok/8][128 dv][8]
     float val[32];
-#pragma unroll 1
-    for (int half = 0; half < 2; ++half) {
-      tc::tmem_ld32(tc::tmem_addr(tm, wid * 32, half * 32), val);
-      tc::tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) s.y.wq[ca + (half * 32 + i) * 8] = __float2bfloat16_rn(val[i]);
-    }
-    tc::tmem_ld32(tc::tmem_addr(tm, wid * 32, kQgCol), val);
+    tc::tmem_ld32(tc::tmem_addr(tm, lq * 32, 32 * hf), val);
     tc::tmem_ld_wait();
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const uint32_t pk = __float_as_uint(val[i]);
-      reinterpret_cast<uint16_t*>(s.y.wq)[ca + (BS + 2 * i) * 8] = static_cast<uint16_t>(pk & 0xFFFFu);
-      reinterpret_cast<uint16_t*>(s.y.wq)[ca + (BS + 2 * i + 1) * 8] = static_cast<uint16_t>(pk >> 16);
-    }
-#pragma unroll 1
-    for (int half = 0; half < 2; ++half) {
-      tc::tmem_ld32(tc::tmem_addr(tm, wid * 32, 64 + half * 32), val);
+    for (int i = 0; i < 32; ++i) s.y.wq[ca + (32 * hf + i) * 8] = __float2bfloat16_rn(val[i]);
+    {
+      float qv[16];
+      tc::tmem_ld16(tc::tmem_addr(tm, lq * 32, kQgCol + 16 * hf), qv);
       tc::tmem_ld_wait();
 #pragma unroll
-      for (int i8 = 0; i8 < 4; ++i8) {
-        uint32_t pk[4];
-#pragma unroll
-        for (int x = 0; x < 4; ++x) {
-          __half2 h = __floats2half2_rn(val[8 * i8 + 2 * x] * (1.f / kValScale),
-                                        val[8 * i8 + 2 * x + 1] * (1.f / kValScale));
-          pk[x] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        *reinterpret_cast<uint4*>(ut_g + (size_t)(half * 4 + i8) * D * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t pk = __float_as_uint(qv[i]);
+        reinterpret_cast<uint16_t*>(s.y.wq)[ca + (BS + 32 * hf + 2 * i) * 8] = static_cast<uint16_t>(pk & 0xFFFFu);
+        reinterpret_cast<uint16_t*>(s.y.wq)[ca + (BS + 32 * hf + 2 * i + 1) * 8] = static_cast<uint16_t>(pk >> 16);
       }
+    }
+    tc::tmem_ld32(tc::tmem_addr(tm, lq * 32, 64 + 32 * hf), val);
+    tc::tmem_ld_wait();
+#pragma unroll
+    for (int i8 = 0; i8 < 4; ++i8) {
+      uint32_t pk[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        __half2 h = __floats2half2_rn(val[8 * i8 + 2 * x] * (1.f / kValScale),
+                                      val[8 * i8 + 2 * x + 1] * (1.f / kValScale));
+        pk[x] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      *reinterpret_cast<uint4*>(ut_g + (size_t)(hf * 4 + i8) * D * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
   }
   tc::fence_async_smem();
@@ -506,9 +540,10 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
   GDN2_CUDA_TRY(cudaFuncSetAttribute(prep_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(S / BS, B * H);
   using bf16 = __nv_bfloat16;
-  prep_tc_kernel<<<grid, 128, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
-                                          static_cast<const bf16*>(v), g, static_cast<const bf16*>(b),
-                                          static_cast<const bf16*>(w), P, S, H, in_bs, scale, device_status_word());
+  prep_tc_kernel<<<grid, kThreads, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
+                                               static_cast<const bf16*>(v), g, static_cast<const bf16*>(b),
+                                               static_cast<const bf16*>(w), P, S, H, in_bs, scale,
+                                               device_status_word());
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }
