@@ -91,14 +91,19 @@ __device__ __forceinline__ float pick4(int j, float a0, float a1, float a2, floa
 // Raw values of one channel for 8 consecutive tokens, converted only when consumed.
 struct Raw8 {
   float g[8];
-  __nv_bfloat16 k[8], q[8], b[8];
+  uint32_t k[8], q[8], b[8];              // bf16 bit patterns, zero-extended: one register each, no packing
 };
+// 16-bit load into a full register, and its value as fp32 (a bf16 is the top half of an fp32)
+__device__ __forceinline__ uint32_t ldg_u16(const __nv_bfloat16* p) {
+  return static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned short*>(p)));
+}
+__device__ __forceinline__ float bf16_bits_to_f32(uint32_t x) { return __uint_as_float(x << 16); }
 __device__ __forceinline__ void load_raw8(Raw8& r, const float* gp, const __nv_bfloat16* kp, const __nv_bfloat16* qp,
                                           const __nv_bfloat16* bp, size_t rstride) {
 #pragma unroll
   for (int u = 0; u < 8; ++u) {
     const size_t off = u * rstride;
-    r.g[u] = __ldg(gp + off); r.k[u] = __ldg(kp + off); r.q[u] = __ldg(qp + off); r.b[u] = __ldg(bp + off);
+    r.g[u] = __ldg(gp + off); r.k[u] = ldg_u16(kp + off); r.q[u] = ldg_u16(qp + off); r.b[u] = ldg_u16(bp + off);
   }
 }
 
@@ -134,9 +139,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   // Pull the whole input tile of this chunk-head towards L2 before anything depends on it: 64 rows x
   // (5 x 256 B + 512 B) = 896 128-byte lines, 3.5 per thread.
   {
-    const char* base[6] = {reinterpret_cast<const char*>(g + row0 * D), reinterpret_cast<const char*>(k + row0 * D),
-                           reinterpret_cast<const char*>(q + row0 * D), reinterpret_cast<const char*>(b + row0 * D),
-                           reinterpret_cast<const char*>(v + row0 * D), reinterpret_cast<const char*>(w + row0 * D)};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int line = tid + kThreads * i;                // 0..895: g takes lines [0,256), then 128 per bf16 tensor
@@ -145,7 +147,10 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         const int rem = line < 256 ? line : (line - 256) & 127;
         const int per_row = ten == 0 ? 4 : 2;
         const int rowi = rem / per_row, seg = rem % per_row;
-        const char* ptr = base[ten] + (size_t)rowi * rstride * (ten == 0 ? 4 : 2) + seg * 128;
+        const void* tb = ten == 0 ? (const void*)g : ten == 1 ? (const void*)k : ten == 2 ? (const void*)q
+                       : ten == 3 ? (const void*)b : ten == 4 ? (const void*)v : (const void*)w;
+        const size_t es = ten == 0 ? 4 : 2;
+        const char* ptr = static_cast<const char*>(tb) + (row0 * D + (size_t)rowi * rstride) * es + seg * 128;
         asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
       }
     }
@@ -227,11 +232,11 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
           const int uu = 4 * t4 + u;
           const int t = t0 + uu;
           run += r.g[uu] * kLog2e;
-          const float kf = __bfloat162float(r.k[uu]), qf = __bfloat162float(r.q[uu]);
+          const float kf = bf16_bits_to_f32(r.k[uu]), qf = bf16_bits_to_f32(r.q[uu]);
           const float a = ex2(run - sc.ref);                  // <= 1
           const float co = ex2(sc.ref - run);                 // >= 1, bounded by the span check
           const float nx = (j < 3) ? ex2(sc.refn - run) : ex2(g_last - run);   // <= 1
-          const float e = __bfloat162float(r.b[uu]) * kf;
+          const float e = bf16_bits_to_f32(r.b[uu]) * kf;
           s.x.ops.a_own[ca + t * 8] = __float2bfloat16_rn(e * a);
           s.x.ops.a_own[ca + (BS + t) * 8] = __float2bfloat16_rn(qf * a);
           s.x.ops.bfam[cb + (sc.off_j + t) * 8] = __float2bfloat16_rn(kf * co);
@@ -298,17 +303,17 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   {
     const __nv_bfloat16* vp = v + row0 * D + c + hoff;
     const __nv_bfloat16* wp = w + row0 * D + c + hoff;
-    __nv_bfloat16 vr[16], wr[16], vn[16], wn[16];         // raw values: converted one group behind the loads
+    uint32_t vr[16], wr[16], vn[16], wn[16];              // raw bf16 bits: converted one group behind the loads
 #pragma unroll
-    for (int u = 0; u < 16; ++u) { vr[u] = __ldg(vp + u * rstride); wr[u] = __ldg(wp + u * rstride); }
+    for (int u = 0; u < 16; ++u) { vr[u] = ldg_u16(vp + u * rstride); wr[u] = ldg_u16(wp + u * rstride); }
 #pragma unroll
-    for (int u = 0; u < 16; ++u) { vn[u] = __ldg(vp + (16 + u) * rstride); wn[u] = __ldg(wp + (16 + u) * rstride); }
+    for (int u = 0; u < 16; ++u) { vn[u] = ldg_u16(vp + (16 + u) * rstride); wn[u] = ldg_u16(wp + (16 + u) * rstride); }
     float z[16];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) z[u] = tf32_rn(__bfloat162float(vr[u]) * __bfloat162float(wr[u]));
+    for (int u = 0; u < 16; ++u) z[u] = tf32_rn(bf16_bits_to_f32(vr[u]) * bf16_bits_to_f32(wr[u]));
     tc::tmem_st16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * hf), z);
 #pragma unroll
-    for (int u = 0; u < 16; ++u) z[u] = tf32_rn(__bfloat162float(vn[u]) * __bfloat162float(wn[u]));
+    for (int u = 0; u < 16; ++u) z[u] = tf32_rn(bf16_bits_to_f32(vn[u]) * bf16_bits_to_f32(wn[u]));
     tc::tmem_st16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * hf + 16), z);
     tc::tmem_st_wait();
   }
