@@ -113,6 +113,9 @@ struct SubConst {
   int j, off_j;
 };
 
+// HT > 0: the number of heads is a compile-time constant, so every token offset of the strided channel
+// loads folds into the load instruction's immediate; HT = 0 takes it from the argument.
+template <int HT>
 __global__ void __launch_bounds__(kThreads, 2)
 prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
@@ -129,7 +132,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const int hf = tid >> 7;                                              // token half: tokens [32 hf, 32 hf + 32)
   const int lq = wid & 3;                                               // TMEM lane quarter of this warp
   const size_t row0 = ((size_t)ib * in_bs + (size_t)n * BS) * H + ih;   // token row of t = 0
-  const size_t rstride = (size_t)H * D;                                 // elements between tokens
+  const size_t rstride = HT > 0 ? (size_t)HT * D : (size_t)H * D;       // elements between tokens
   const size_t hoff = (size_t)(32 * hf) * rstride;                      // first token of this thread's half
   const float* gp = g + row0 * D + c + hoff;
 #ifdef GDN2_SCAN_TIMING
@@ -318,7 +321,9 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     tc::tmem_st_wait();
   }
   PTICK(4);
-  tc::mbar_wait(&s.bar_m1, 0, &s.abort_flag, status, 0x1000u);
+  // one warp polls the MMA barrier; the rest sleep at the block barrier instead of spending issue slots
+  if (wid == 0) tc::mbar_wait(&s.bar_m1, 0, &s.abort_flag, status, 0x1000u);
+  __syncthreads();
   tc::tc_fence_after_sync();
   PTICK(5);
 
@@ -481,7 +486,8 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     tc::mma_tf32_ktile_warp(tc::tmem_addr(tm, 0, 64), tc::smem_u32(s.x.sol.zt), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc);
     tc::mma_commit_warp(&s.bar_m2);
   }
-  tc::mbar_wait(&s.bar_m2, 0, &s.abort_flag, status, 0x2000u);
+  if (wid == 0) tc::mbar_wait(&s.bar_m2, 0, &s.abort_flag, status, 0x2000u);
+  __syncthreads();
   tc::tc_fence_after_sync();
   PTICK(8);
 
@@ -542,15 +548,23 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
                    cudaStream_t st) {
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
   const size_t smem = sizeof(PrepTcSmem) + 128;
-  GDN2_CUDA_TRY(cudaFuncSetAttribute(prep_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(S / BS, B * H);
   using bf16 = __nv_bfloat16;
-  prep_tc_kernel<<<grid, kThreads, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
-                                               static_cast<const bf16*>(v), g, static_cast<const bf16*>(b),
-                                               static_cast<const bf16*>(w), P, S, H, in_bs, scale,
-                                               device_status_word());
-  GDN2_CUDA_TRY(cudaGetLastError());
-  return GDN2_OK;
+  auto launch = [&](auto kern) -> int {
+    GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, kThreads, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
+                                       static_cast<const bf16*>(v), g, static_cast<const bf16*>(b),
+                                       static_cast<const bf16*>(w), P, S, H, in_bs, scale, device_status_word());
+    GDN2_CUDA_TRY(cudaGetLastError());
+    return GDN2_OK;
+  };
+  switch (H) {                                  // common head counts, whole and sharded
+    case 16: return launch(prep_tc_kernel<16>);
+    case 8: return launch(prep_tc_kernel<8>);
+    case 4: return launch(prep_tc_kernel<4>);
+    case 2: return launch(prep_tc_kernel<2>);
+    default: return launch(prep_tc_kernel<0>);
+  }
 }
 
 #ifdef GDN2_SCAN_TIMING
