@@ -23,7 +23,7 @@
 //  3. (I + Tm)^-1 by 16x16 blocks: the four diagonal blocks by forward substitution in registers,
 //     the off-diagonal blocks from 16 small products on warp-level register fragments.
 //  4. MMA2 (tf32, transposed so channels are M): W^T = E^T * Ai^T, U^T = (w*v)^T * Ai^T.
-//  5. Outputs in the scan's operand layout (common.cuh): WQ via shared staging + bulk stores, AQK,
+//  5. Outputs in the scan's operand layout (common.cuh): WQ via shared staging + coalesced stores, AQK,
 //     KG^T and U^T (scaled fp16), gamma_last with 128-bit coalesced global stores.
 //
 // Shared memory is two regions reused over the block's life so that two blocks fit on an SM:
@@ -526,19 +526,24 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       *reinterpret_cast<uint4*>(ut_g + (size_t)(hf * 4 + i8) * D * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
   }
-  tc::fence_async_smem();
   tc::tc_fence_before_sync();
   __syncthreads();
   PTICK(9);
-  if (tid < 16 && !s.abort_flag) {
-    char* g_wq = P.wq + (size_t)ch * (2 * BS * D * 2) + (size_t)tid * (2 * BS * 16);
-    tc::bulk_s2g(g_wq, reinterpret_cast<const char*>(s.y.wq) + tid * A_PAD * 16, 2 * BS * 16);
-    tc::bulk_commit();
-    tc::bulk_wait_read_all();
-  }
-  __syncthreads();
-  PTICK(10);
   if (wid == 0) tc::tmem_dealloc(tm, kTmemCols);
+  // WQ record: 16 K chunks x 128 rows x 16 bytes; every thread copies 8 pieces with 128-bit accesses
+  // (16 consecutive threads cover 256 contiguous bytes) and the block ends without waiting on them
+  if (!s.abort_flag) {
+    char* g_wq = P.wq + (size_t)ch * (2 * BS * D * 2);
+    const char* stage = reinterpret_cast<const char*>(s.y.wq);
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+      const int piece = tid + kThreads * x;                 // 0..2047
+      const int kc = piece >> 7, row = piece & 127;
+      *reinterpret_cast<uint4*>(g_wq + (size_t)piece * 16) =
+          *reinterpret_cast<const uint4*>(stage + (kc * A_PAD + row) * 16);
+    }
+  }
+  PTICK(10);
 }
 
 }  // namespace
