@@ -30,6 +30,8 @@
 //   X (72.5 KiB): MMA1 operands, then Tm + Ai + (w*v)^T;   Y (32.25 KiB): E^T, then the WQ staging.
 // Qg = scale*q*gamma is produced in step 1 but only needed in step 5; it waits in 32 spare TMEM
 // columns of the thread's own lane (packed bf16 pairs).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "tc_utils.cuh"
 
@@ -109,7 +111,7 @@ __device__ __forceinline__ void load_raw8(Raw8& r, const float* gp, const __nv_b
 
 // Per-sub-block constants of the gating step.
 struct SubConst {
-  float ref, refn, gam_ref, kg_c, cc_a, cc_b;
+  float ref, refn, gam_ref, kg_c, cc_a, cc_b, nx_c;
   int j, off_j;
 };
 
@@ -178,8 +180,8 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     s.pre[hf][0][c] = first[0]; s.pre[hf][1][c] = first[1]; s.pre[hf][2][c] = run;
   }
   if (tid == 0) {
-    tc::mbar_init(&s.bar_m1, 1);
-    tc::mbar_init(&s.bar_m2, 1);
+    tc::mbar_init(&s.bar_m1, 4);     // one commit per issuing warp
+    tc::mbar_init(&s.bar_m2, 2);
     s.abort_flag = 0;
     tc::mbar_init_fence();
   }
@@ -219,6 +221,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       sc.ref = pick4(j, ref0, ref1, ref2, ref3);
       sc.refn = pick4(j, ref1, ref2, ref3, 0.f);                // ref of the next sub-block (unused for j = 3)
       sc.gam_ref = ex2(sc.ref);
+      sc.nx_c = ex2(((j < 3) ? sc.refn : g_last) - sc.ref);    // 2^(refn - run) = nx_c * 2^(ref - run)
       sc.kg_c = (j < 3) ? ex2(g_last - sc.refn) : 1.f;
       sc.cc_a = ex2(pick4(j, ref2, ref3, 0.f, 0.f) - sc.refn);  // B_{j+2} relative to B_{j+1}
       sc.cc_b = ex2(ref3 - sc.refn);                            // B_{j+3} relative to B_{j+1} (j = 0 only)
@@ -238,7 +241,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
           const float kf = bf16_bits_to_f32(r.k[uu]), qf = bf16_bits_to_f32(r.q[uu]);
           const float a = ex2(run - sc.ref);                  // <= 1
           const float co = ex2(sc.ref - run);                 // >= 1, bounded by the span check
-          const float nx = (j < 3) ? ex2(sc.refn - run) : ex2(g_last - run);   // <= 1
+          const float nx = sc.nx_c * co;                      // 2^(refn - run) (2^(g_last - run) for j = 3), <= 1
           const float e = bf16_bits_to_f32(r.b[uu]) * kf;
           s.x.ops.a_own[ca + t * 8] = __float2bfloat16_rn(e * a);
           s.x.ops.a_own[ca + (BS + t) * 8] = __float2bfloat16_rn(qf * a);
@@ -289,14 +292,14 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
 
   PTICK(2);
   // ---- 2. MMA1: D_i[128 x 16(i+1)] at TMEM columns 0, 16, 48, 96
-  if (wid == 0) {                   // the warp stays converged; one elected lane issues
+  //         The four products are independent: warps 0..3 issue one each (converged, one elected
+  //         lane) and commit it, so no warp falls far behind the others before the value-side loads.
+  if (wid < 4) {
     tc::tc_fence_after_sync();
-#pragma unroll 1
-    for (int i = 0; i < 4; ++i) {
-      const int off = 8 * i * (i + 1);
-      tc::mma_bf16_ktile_warp(tc::tmem_addr(tm, 0, off), tc::smem_u32(s.x.ops.a_own), A_PAD,
-                              tc::smem_u32(s.x.ops.bfam) + off * 16, B_PAD, D, tc::instr_desc(1, 128, 16 * (i + 1)));
-    }
+    const int i = wid;
+    const int off = 8 * i * (i + 1);
+    tc::mma_bf16_ktile_warp(tc::tmem_addr(tm, 0, off), tc::smem_u32(s.x.ops.a_own), A_PAD,
+                            tc::smem_u32(s.x.ops.bfam) + off * 16, B_PAD, D, tc::instr_desc(1, 128, 16 * (i + 1)));
     tc::mma_commit_warp(&s.bar_m1);
   }
   PTICK(3);
@@ -479,11 +482,11 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
 
   PTICK(7);
   // ---- 4. MMA2 (tf32): W^T at TMEM columns 0..63, U^T at 64..127
-  if (wid == 0 && !s.abort_flag) {
+  if (wid < 2 && !s.abort_flag) {  // warp 0: W^T, warp 1: U^T
     tc::tc_fence_after_sync();
     constexpr uint32_t idesc = tc::instr_desc(2, 128, BS);
-    tc::mma_tf32_ktile_warp(tc::tmem_addr(tm, 0, 0), tc::smem_u32(s.y.et), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc);
-    tc::mma_tf32_ktile_warp(tc::tmem_addr(tm, 0, 64), tc::smem_u32(s.x.sol.zt), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc);
+    tc::mma_tf32_ktile_warp(tc::tmem_addr(tm, 0, 64 * wid), tc::smem_u32(wid == 0 ? s.y.et : s.x.sol.zt), D,
+                            tc::smem_u32(s.x.sol.ai), BS, BS, idesc);
     tc::mma_commit_warp(&s.bar_m2);
   }
   if (wid == 0) tc::mbar_wait(&s.bar_m2, 0, &s.abort_flag, status, 0x2000u);
@@ -552,7 +555,10 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
                    const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
                    cudaStream_t st) {
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
-  const size_t smem = sizeof(PrepTcSmem) + 128;
+  size_t smem = sizeof(PrepTcSmem) + 128;
+#ifdef GDN2_SCAN_TIMING
+  if (getenv("GDN2_EXP_ONE_BLOCK")) smem = 120 * 1024;    // experiment: one resident block per SM
+#endif
   dim3 grid(S / BS, B * H);
   using bf16 = __nv_bfloat16;
   auto launch = [&](auto kern) -> int {
