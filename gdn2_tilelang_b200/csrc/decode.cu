@@ -21,8 +21,14 @@
 
 namespace gdn2 {
 
+// decode_blocked.cu: blocks of up to 8 tokens without a per-token dependent sweep (DK = DV = 128)
+template <typename T>
+int launch_decode_blocked(const T* q, const T* k, const T* v, const float* g, const T* b, const T* w, float* state,
+                          T* o, int B, int n, int H, int64_t in_bs, int64_t o_bs, float scale, cudaStream_t st);
+
 namespace {
 
+constexpr int kBlockedMinTokens = 4;   // from here on the blocked form wins over the token-by-token sweeps
 constexpr int kTokBatch = 8;   // token vectors staged in shared memory per barrier round
 
 // packed fp32 pairs (Blackwell): two FMAs / multiplies per instruction on 64-bit register pairs
@@ -210,7 +216,9 @@ int launch_typed(const void* q, const void* k, const void* v, const float* g, co
   const T* tq = static_cast<const T*>(q); const T* tk = static_cast<const T*>(k);
   const T* tv = static_cast<const T*>(v); const T* tb = static_cast<const T*>(b);
   const T* tw = static_cast<const T*>(w); T* to = static_cast<T*>(o);
-  if (DK == 128 && DV == 128) {
+  if (DK == 128 && DV == 128 && n >= kBlockedMinTokens) {
+    return launch_decode_blocked<T>(tq, tk, tv, g, tb, tw, state, to, B, n, H, in_bs, o_bs, scale, st);
+  } else if (DK == 128 && DV == 128) {
     decode_d128_kernel<T><<<B * H, 128, 0, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, in_bs, o_bs, scale);
   } else {
     dim3 grid((DV + 31) / 32, B * H);

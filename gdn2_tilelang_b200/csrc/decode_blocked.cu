@@ -1,0 +1,458 @@
+// Recurrent decode of several tokens at once, DK = DV = 128: the n-token recurrence of
+// decode_multi_kernel (gdn2/inference.py:199-303 of the reference project) evaluated in blocks of up
+// to 8 tokens without a per-token dependent sweep over the state.
+//
+// With A_t = exp(g_1 + .. + g_t) per key channel (A_t / A_s <= 1 for s <= t, so nothing can overflow):
+//     u_t = w_t*v_t - (b_t*k_t*A_t)^T S_0 - sum_{s<t} Akk[t,s] u_s      Akk[t,s] = sum_c b_t k_t k_s A_t/A_s
+//     o_t = (scale*q_t*A_t)^T S_0 + sum_{s<=t} Aqk[t,s] u_s              Aqk[t,s] = scale * sum_c q_t k_s A_t/A_s
+//     S_8 = diag(A_8) S_0 + sum_s (k_s * A_8/A_s) u_s^T
+// which is the token-by-token recurrence S <- diag(exp g) S; u = w*v - S^T(b*k); S <- S + k u^T;
+// o = scale S^T q with the sums regrouped: two sweeps over the state tile with 64 and 36 independent
+// accumulation chains per thread instead of 2 n sweeps that each wait for a cross-thread reduction.
+//
+// Persistent blocks, one per SM, walk over the (batch, head) tiles with three kinds of warps:
+//   * one copy thread brings a tile's 64 KiB of fp32 state into shared memory by bulk copies (TMA) two
+//     tiles ahead and sends the updated tile back the same way: HBM traffic is the state once in, once
+//     out, and no compute thread ever waits on a global load of it;
+//   * four table warps (thread = channel) read the token vectors of the next step and build its
+//     coefficient tables and the 8 x 8 pair matrices while the current step is swept;
+//   * eight sweep warps do the two sweeps in place: warp w owns value columns 16w .. 16w+15, lane
+//     (rgl = lane >> 2, cq = lane & 3) columns 16w + 4cq .. +3 of key rows 16 rgl .. 16 rgl + 15.
+// Hand-offs are mbarriers with bounded waits.
+// Per-row coefficients sit in shared memory as duplicated pairs so the packed f32x2 FMAs take them
+// as they are.
+#include "common.cuh"
+#include "tc_utils.cuh"
+
+namespace gdn2 {
+
+namespace {
+
+constexpr int D = 128;
+constexpr int NB = 8;                       // tokens per block step
+constexpr int kGroupFloats = 16 * D + 16;   // 16 state rows + 64 bytes: adjacent row groups land 64 B apart mod 128
+constexpr int kTileFloats = 8 * kGroupFloats;
+constexpr uint32_t kGroupBytes = 16 * D * 4;
+constexpr int kCoefRows = 136;              // 128 rows + one slot per 16-row group
+__device__ __forceinline__ int crow(int r) { return r + (r >> 4); }
+
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+  return d;
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+struct Tables {
+  // per key row, duplicated pairs (x, x): chunks 0..3 = b*k*A_t for t < 8, chunks 4..7 = scale*q*A_t
+  float4 c1[8][kCoefRows];
+  // chunks 0..3: k * A_8/A_s for s < 8 (duplicated pairs); chunk 4: (A_8, A_8, 0, 0)
+  float4 c2[5][kCoefRows];
+  float wv[NB][D];                    // w * v
+  float akk[NB][NB];                  // strictly lower
+  float aqk[NB][NB];                  // lower incl. diagonal, scale folded in
+};
+
+struct alignas(128) BlockedSmem {
+  float tile[2][kTileFloats];         // the state of two (batch, head) tiles
+  Tables tab[2];                      // coefficient tables of two consecutive steps
+  float part[4][64];                  // per 32-channel group: partial sums of the 64 pair entries
+  uint64_t tile_full[2], tile_done[2];   // copy thread -> sweep warps (bytes landed); sweep warps -> copy thread
+  uint64_t tab_full[2], tab_empty[2];    // table warps -> sweep warps; sweep warps -> table warps
+  int abort_flag;
+};
+
+constexpr int kSweepThreads = 256;    // warps 0..7
+constexpr int kTableThreads = 128;    // warps 8..11
+constexpr int kAllThreads = kSweepThreads + kTableThreads + 32;   // + warp 12: one thread drives the bulk copies
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc::smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void table_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// the same barrier fused with an OR over one predicate per thread: every table thread gets the same answer
+__device__ __forceinline__ bool table_sync_or(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "barrier.cta.red.or.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t"
+      "}"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
+#ifdef GDN2_SCAN_TIMING
+__device__ unsigned long long g_dec_timing[32];
+#define DTICK(i) do { if (blockIdx.x == 0 && lane == 0) { long long now_ = clock64(); dacc[i] += now_ - dprev; dprev = now_; } } while (0)
+#define DDECL long long dacc[12] = {0}; long long dprev = clock64()
+#define DFLUSH(off) do { if (blockIdx.x == 0 && lane == 0) for (int i_ = 0; i_ < 12; ++i_) g_dec_timing[off + i_] = dacc[i_]; } while (0)
+#else
+#define DTICK(i) do {} while (0)
+#define DDECL do {} while (0)
+#define DFLUSH(off) do {} while (0)
+#endif
+
+enum : uint32_t { kWaitTile = 0x10000u, kWaitTab = 0x20000u, kWaitEmpty = 0x40000u, kWaitDone = 0x80000u };
+
+template <typename T>
+__global__ void __launch_bounds__(kAllThreads, 1)
+decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
+                      const float* __restrict__ g, const T* __restrict__ b, const T* __restrict__ w,
+                      float* __restrict__ state, T* __restrict__ o, int ntiles, int n, int H, int64_t in_bs,
+                      int64_t o_bs, float scale, uint32_t* status) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  BlockedSmem& s = *reinterpret_cast<BlockedSmem*>(smem_raw);
+  const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&s.tile_full[i], 1);
+      tc::mbar_init(&s.tile_done[i], kSweepThreads);
+      tc::mbar_init(&s.tab_full[i], kTableThreads);
+      tc::mbar_init(&s.tab_empty[i], kSweepThreads);
+    }
+    s.abort_flag = 0;
+    tc::mbar_init_fence();
+  }
+  __syncthreads();
+
+  if (wid == 12) {
+    // =============================== copy thread: tiles in, tiles out ==========================
+    if (lane == 0) {
+      auto load_tile = [&](int tile, int buf) {          // 8 bulk copies of 16 rows each
+        tc::mbar_expect_tx(&s.tile_full[buf], 8 * kGroupBytes);
+        const float* src = state + (size_t)tile * D * D;
+#pragma unroll
+        for (int gidx = 0; gidx < 8; ++gidx)
+          tc::bulk_g2s(&s.tile[buf][gidx * kGroupFloats], src + gidx * 16 * D, kGroupBytes, &s.tile_full[buf]);
+      };
+      const int first = blockIdx.x, stride = gridDim.x;
+      if (first < ntiles) load_tile(first, 0);
+      if (first + stride < ntiles) load_tile(first + stride, 1);
+      int it = 0;
+      for (int tile = first; tile < ntiles; tile += stride, ++it) {
+        const int buf = it & 1;
+        if (!tc::mbar_wait(&s.tile_done[buf], (it >> 1) & 1, &s.abort_flag, status, kWaitDone)) break;
+        float* dst = state + (size_t)tile * D * D;
+#pragma unroll
+        for (int gidx = 0; gidx < 8; ++gidx)
+          tc::bulk_s2g(dst + gidx * 16 * D, &s.tile[buf][gidx * kGroupFloats], kGroupBytes);
+        tc::bulk_commit();
+        if (tile + 2 * stride < ntiles) {
+          tc::bulk_wait_read_all();                      // the buffer may be overwritten once the store has read it
+          load_tile(tile + 2 * stride, buf);
+        }
+      }
+      tc::bulk_wait_all();
+    }
+  } else if (wid >= 8) {
+    // =============================== table warps: thread = key / value channel =================
+    const int c = tid - kSweepThreads;
+    const int pw_ = wid - 8;                             // 32-channel group
+    int step = 0;
+    DDECL;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+      const int ib = tile / H, ih = tile % H;
+      for (int t0 = 0; t0 < n; t0 += NB, ++step) {
+        const int nb = min(NB, n - t0);
+        Tables& tb = s.tab[step & 1];
+        DTICK(0);
+        // all 48 loads of the step are issued before any is used (padding tokens re-read the last real one)
+        float graw[NB];
+        T kraw[NB], braw[NB], qraw[NB], wraw[NB], vraw[NB];
+#pragma unroll
+        for (int t = 0; t < NB; ++t) {
+          const int tt = t < nb ? t : nb - 1;
+          const size_t tok = (((size_t)ib * in_bs + (t0 + tt)) * H + ih) * D + c;
+          graw[t] = g[tok]; kraw[t] = k[tok]; braw[t] = b[tok]; qraw[t] = q[tok]; wraw[t] = w[tok]; vraw[t] = v[tok];
+        }
+        float G[NB], kk[NB], bk[NB], qs[NB], wvv[NB];
+        float run = 0.f;
+#pragma unroll
+        for (int t = 0; t < NB; ++t) {
+          const bool real = t < nb;                      // padding token: no decay, no write, no read
+          run += real ? graw[t] * kLog2e : 0.f;
+          kk[t] = real ? to_f32(kraw[t]) : 0.f;
+          bk[t] = real ? to_f32(braw[t]) * kk[t] : 0.f;
+          qs[t] = real ? to_f32(qraw[t]) * scale : 0.f;
+          wvv[t] = real ? to_f32(wraw[t]) * to_f32(vraw[t]) : 0.f;
+          G[t] = run;                                    // log2 of A_t
+        }
+        // the sweep warps have finished with this table buffer (two steps ago)
+        DTICK(1);
+        const bool okw = tc::mbar_wait(&s.tab_empty[step & 1], ((step >> 1) & 1) ^ 1, &s.abort_flag, status, kWaitEmpty);
+        // uniform over the table warps; it also orders this step after the reads of the previous step's partial sums
+        if (table_sync_or(!okw)) break;
+        DTICK(2);
+        {
+          const int pr = crow(c);
+          float c1v[16], c2v[8];
+#pragma unroll
+          for (int t = 0; t < NB; ++t) {
+            const float At = ex2(G[t]);
+            c1v[t] = bk[t] * At;
+            c1v[8 + t] = qs[t] * At;
+            c2v[t] = kk[t] * ex2(G[NB - 1] - G[t]);
+            tb.wv[t][c] = wvv[t];
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) tb.c1[j][pr] = make_float4(c1v[2 * j], c1v[2 * j], c1v[2 * j + 1], c1v[2 * j + 1]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) tb.c2[j][pr] = make_float4(c2v[2 * j], c2v[2 * j], c2v[2 * j + 1], c2v[2 * j + 1]);
+          const float An = ex2(G[NB - 1]);
+          tb.c2[4][pr] = make_float4(An, An, 0.f, 0.f);
+        }
+        // Slot (t, sx) holds the Akk[t, sx] term for sx < t and the Aqk[sx, t] term for sx >= t (the upper
+        // triangle is free). Summing over the warp's 32 channels: each step halves what a lane keeps.
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+          float term[32];
+#pragma unroll
+          for (int tt = 0; tt < 4; ++tt) {
+            const int t = 4 * hb + tt;
+#pragma unroll
+            for (int sx = 0; sx < NB; ++sx) {
+              float val;
+              if (sx < t) val = bk[t] * kk[sx] * ex2(G[t] - G[sx]);          // Akk[t, sx], A_t / A_s <= 1
+              else if (sx == t) val = qs[t] * kk[t];                          // Aqk[t, t]
+              else val = qs[sx] * kk[t] * ex2(G[sx] - G[t]);                  // Aqk[sx, t]
+              term[tt * 8 + sx] = val;
+            }
+          }
+#pragma unroll
+          for (int m = 0; m < 5; ++m) {
+            const int half = 16 >> m;                    // values kept after this step
+            const int bit = 16 >> m;
+            const bool up = (lane & bit) != 0;
+#pragma unroll
+            for (int x = 0; x < half; ++x) {
+              const float send = up ? term[x] : term[x + half];
+              const float keep = up ? term[x + half] : term[x];
+              term[x] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+            }
+          }
+          int idx = 0;                                   // the lane bit tested at step m chose the upper half of 16 >> m entries
+#pragma unroll
+          for (int m = 0; m < 5; ++m) idx += ((lane >> (4 - m)) & 1) * (16 >> m);
+          s.part[pw_][32 * hb + idx] = term[0];
+        }
+        DTICK(3);
+        table_sync();
+        if (c < 64) {
+          const float sum = s.part[0][c] + s.part[1][c] + s.part[2][c] + s.part[3][c];
+          const int t = c >> 3, sx = c & 7;
+          if (sx < t) tb.akk[t][sx] = sum;               // Akk[t, sx]
+          else tb.aqk[sx][t] = sum;                      // slot (t, sx) with sx >= t holds Aqk[sx, t]
+        }
+        mbar_arrive(&s.tab_full[step & 1]);
+        DTICK(4);
+      }
+      if (s.abort_flag) break;
+    }
+    if (wid == 8) DFLUSH(0);
+  } else {
+    // =============================== sweep warps ================================================
+    const int rgl = lane >> 2, cq = lane & 3;
+    const int col0 = 16 * wid + 4 * cq;
+    int it = 0, step = 0;
+    DDECL;
+    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
+      const int buf = it & 1;
+      const int ib = tile / H, ih = tile % H;
+      float* S = s.tile[buf];
+      bool ok = true;
+      for (int t0 = 0; t0 < n; t0 += NB, ++step) {
+        const int nb = min(NB, n - t0);
+        const Tables& tb = s.tab[step & 1];
+        DTICK(0);
+        ok = tc::mbar_wait(&s.tab_full[step & 1], (step >> 1) & 1, &s.abort_flag, status, kWaitTab);
+        DTICK(1);
+        if (ok && t0 == 0) ok = tc::mbar_wait(&s.tile_full[buf], (it >> 1) & 1, &s.abort_flag, status, kWaitTile);
+        if (!ok) break;
+        DTICK(2);
+
+        // ---- sweep 1: the 16 products (8 erase rows, 8 query rows) of S_0 for this thread's rows and columns
+        float2 acc[16][2];
+#pragma unroll
+        for (int p = 0; p < 16; ++p) { acc[p][0] = make_float2(0.f, 0.f); acc[p][1] = make_float2(0.f, 0.f); }
+        const float* Srow = S + rgl * kGroupFloats + col0;
+        const int cr0 = 17 * rgl;
+#pragma unroll 2
+        for (int i = 0; i < 16; ++i) {
+          const float4 sv = *reinterpret_cast<const float4*>(Srow + i * D);
+          const float2 s01 = make_float2(sv.x, sv.y), s23 = make_float2(sv.z, sv.w);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float4 cf = tb.c1[j][cr0 + i];
+            acc[2 * j][0] = ffma2(s01, make_float2(cf.x, cf.y), acc[2 * j][0]);
+            acc[2 * j][1] = ffma2(s23, make_float2(cf.x, cf.y), acc[2 * j][1]);
+            acc[2 * j + 1][0] = ffma2(s01, make_float2(cf.z, cf.w), acc[2 * j + 1][0]);
+            acc[2 * j + 1][1] = ffma2(s23, make_float2(cf.z, cf.w), acc[2 * j + 1][1]);
+          }
+        }
+        DTICK(3);
+        // reduce over the 8 row groups. Index = half*32 + column*8 + t (half 0: erase products, 1: query
+        // products); lane (rgl) ends with the 8 values of half rgl >> 2, column rgl & 3.
+        float pv[8];
+        {
+          float val[64];
+#pragma unroll
+          for (int p = 0; p < 16; ++p) {
+            const int base = (p >> 3) * 32 + (p & 7);
+            val[base + 0 * 8] = acc[p][0].x; val[base + 1 * 8] = acc[p][0].y;
+            val[base + 2 * 8] = acc[p][1].x; val[base + 3 * 8] = acc[p][1].y;
+          }
+#pragma unroll
+          for (int m = 0; m < 3; ++m) {
+            const int half = 32 >> m;
+            const int bit = 16 >> m;                     // lane bits 4, 3, 2 = rgl bits 2, 1, 0
+            const bool up = (lane & bit) != 0;
+#pragma unroll
+            for (int x = 0; x < half; ++x) {
+              const float send = up ? val[x] : val[x + half];
+              const float keep = up ? val[x + half] : val[x];
+              val[x] = keep + __shfl_xor_sync(0xffffffffu, send, bit);
+            }
+          }
+#pragma unroll
+          for (int t = 0; t < 8; ++t) pv[t] = val[t];
+        }
+        DTICK(4);
+        // ---- forward substitution for u on the lanes that hold the erase products; the lanes that hold
+        //      the query products of the same column take u from them and form the outputs
+        const bool has_q = (rgl & 4) != 0;
+        const int mycol = col0 + (rgl & 3);
+        float u[8];
+        {
+          float4 ak[NB][2];                              // rows of Akk, fetched ahead of the dependent chain
+#pragma unroll
+          for (int t = 1; t < NB; ++t) {
+            ak[t][0] = *reinterpret_cast<const float4*>(&tb.akk[t][0]);
+            if (t > 4) ak[t][1] = *reinterpret_cast<const float4*>(&tb.akk[t][4]);
+          }
+          float wvt[NB];
+#pragma unroll
+          for (int t = 0; t < NB; ++t) wvt[t] = tb.wv[t][mycol];
+#pragma unroll
+          for (int t = 0; t < NB; ++t) {
+            float x = wvt[t] - pv[t];
+            const float arow[8] = {ak[t][0].x, ak[t][0].y, ak[t][0].z, ak[t][0].w, ak[t][1].x, ak[t][1].y, ak[t][1].z, ak[t][1].w};
+#pragma unroll
+            for (int sx = 0; sx < t; ++sx) x = fmaf(-arow[sx], u[sx], x);
+            u[t] = x;                                    // meaningful on the erase lanes only
+          }
+#pragma unroll
+          for (int t = 0; t < NB; ++t) {
+            const float other = __shfl_xor_sync(0xffffffffu, u[t], 16);
+            if (has_q) u[t] = other;
+          }
+        }
+        if (has_q) {
+#pragma unroll
+          for (int t = 0; t < NB; ++t) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&tb.aqk[t][0]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&tb.aqk[t][4]);
+            const float arow[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            float ov = pv[t];
+#pragma unroll
+            for (int sx = 0; sx <= t; ++sx) ov = fmaf(arow[sx], u[sx], ov);
+            if (t < nb) o[(((size_t)ib * o_bs + (t0 + t)) * H + ih) * D + mycol] = from_f32<T>(ov);
+          }
+        }
+        DTICK(5);
+        // gather u of the thread's four columns from the lanes that share cq (rgl bits 0 and 1 = lane bits 2, 3)
+        float2 u01[8], u23[8];
+#pragma unroll
+        for (int t = 0; t < NB; ++t) {
+          const float o4 = __shfl_xor_sync(0xffffffffu, u[t], 4);      // column (rgl & 3) ^ 1
+          const float e = (rgl & 1) ? o4 : u[t];                       // even column of my pair
+          const float od = (rgl & 1) ? u[t] : o4;                      // odd column of my pair
+          const float e2 = __shfl_xor_sync(0xffffffffu, e, 8);         // the other pair
+          const float od2 = __shfl_xor_sync(0xffffffffu, od, 8);
+          if (rgl & 2) { u01[t] = make_float2(e2, od2); u23[t] = make_float2(e, od); }
+          else { u01[t] = make_float2(e, od); u23[t] = make_float2(e2, od2); }
+        }
+        DTICK(6);
+        // ---- sweep 2: S <- A_8 * S + sum_s (k_s A_8/A_s) u_s^T, in place
+        {
+          float* Sw = S + rgl * kGroupFloats + col0;
+#pragma unroll 4
+          for (int i = 0; i < 16; ++i) {
+            const float4 sv = *reinterpret_cast<const float4*>(Sw + i * D);
+            const float4 ga = tb.c2[4][cr0 + i];
+            float2 n01 = fmul2(make_float2(ga.x, ga.y), make_float2(sv.x, sv.y));
+            float2 n23 = fmul2(make_float2(ga.x, ga.y), make_float2(sv.z, sv.w));
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float4 cf = tb.c2[j][cr0 + i];
+              n01 = ffma2(make_float2(cf.x, cf.y), u01[2 * j], n01);
+              n23 = ffma2(make_float2(cf.x, cf.y), u23[2 * j], n23);
+              n01 = ffma2(make_float2(cf.z, cf.w), u01[2 * j + 1], n01);
+              n23 = ffma2(make_float2(cf.z, cf.w), u23[2 * j + 1], n23);
+            }
+            *reinterpret_cast<float4*>(Sw + i * D) = make_float4(n01.x, n01.y, n23.x, n23.y);
+          }
+        }
+        mbar_arrive(&s.tab_empty[step & 1]);             // this step's tables may be overwritten
+        DTICK(7);
+      }
+      if (!ok) break;
+      tc::fence_async_smem();                            // the tile's new values are visible to the bulk store
+      mbar_arrive(&s.tile_done[buf]);
+    }
+    if (wid == 0) DFLUSH(16);
+  }
+}
+
+}  // namespace
+
+template <typename T>
+int launch_decode_blocked(const T* q, const T* k, const T* v, const float* g, const T* b, const T* w, float* state,
+                          T* o, int B, int n, int H, int64_t in_bs, int64_t o_bs, float scale, cudaStream_t st) {
+  const size_t smem = sizeof(BlockedSmem) + 128;
+  GDN2_CUDA_TRY(cudaFuncSetAttribute(decode_blocked_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int ntiles = B * H;
+  const int sms = device_sm_count();
+  const int grid = ntiles < sms ? ntiles : sms;
+  decode_blocked_kernel<T><<<grid, kAllThreads, smem, st>>>(q, k, v, g, b, w, state, o, ntiles, n, H, in_bs, o_bs, scale,
+                                                         device_status_word());
+  GDN2_CUDA_TRY(cudaGetLastError());
+  return GDN2_OK;
+}
+
+#ifdef GDN2_SCAN_TIMING
+extern "C" int gdn2_debug_decode_timing(unsigned long long* out32) {
+  return cudaMemcpyFromSymbol(out32, g_dec_timing, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -6;
+}
+#endif
+
+template int launch_decode_blocked<float>(const float*, const float*, const float*, const float*, const float*,
+                                          const float*, float*, float*, int, int, int, int64_t, int64_t, float,
+                                          cudaStream_t);
+template int launch_decode_blocked<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*,
+                                                  const float*, const __nv_bfloat16*, const __nv_bfloat16*, float*,
+                                                  __nv_bfloat16*, int, int, int, int64_t, int64_t, float, cudaStream_t);
+template int launch_decode_blocked<__half>(const __half*, const __half*, const __half*, const float*, const __half*,
+                                           const __half*, float*, __half*, int, int, int, int64_t, int64_t, float,
+                                           cudaStream_t);
+
+}  // namespace gdn2

@@ -93,7 +93,14 @@ def test_decode_multi_equals_repeated_single(K):
     om = gdn2.gdn2_decode(*dev, sm)
     s1 = s0.clone()
     o1 = torch.cat([gdn2.gdn2_decode(*(t[:, i:i + 1] for t in dev), s1) for i in range(12)], 1)
-    assert torch.equal(om, o1) and torch.equal(sm, s1)      # same kernel arithmetic per token: bit-exact
+    # n >= 4 takes the blocked kernel (sums regrouped), single tokens the sweep kernel: equal up to fp32
+    # reassociation, and up to one bf16 step in the rounded outputs
+    assert orc.rel_max_err(sm.cpu(), s1.cpu()) < 1e-5
+    assert orc.rel_max_err(om.float().cpu(), o1.float().cpu()) < 8e-3
+    s3, s4 = s0.clone(), s0.clone()
+    o3 = gdn2.gdn2_decode(*(t[:, :3] for t in dev), s3)      # n = 3: the sweep kernel, bit-exact with single steps
+    o4 = torch.cat([gdn2.gdn2_decode(*(t[:, i:i + 1] for t in dev), s4) for i in range(3)], 1)
+    assert torch.equal(o3, o4) and torch.equal(s3, s4)
     st = s0.clone()
     os_ = gdn2.gdn2_decode_step(*(t[:, 0] for t in dev), st)
     assert torch.equal(os_, o1[:, 0])
