@@ -106,6 +106,23 @@ def test_decode_multi_equals_repeated_single(K):
     assert torch.equal(os_, o1[:, 0])
 
 
+@pytest.mark.parametrize("n", [4, 5, 9, 16, 23])
+@pytest.mark.parametrize("decay_scale", [1.0, 40.0])
+def test_decode_blocked_lengths_and_fast_decay_fp32(K, n, decay_scale):
+    """n >= 4 at DK = DV = 128 takes the blocked kernel: every block length, padded last blocks, and gates
+    strong enough that a factorised decay would overflow (here every ratio stays <= 1)."""
+    B, H, D = 2, 3, 128
+    ins = orc.make_inputs(B, n, H, D, D, seed=40 + n, gate="softplus", decay_scale=decay_scale)
+    s0 = golden_state(B, H, D, D, n, 0.3)
+    state = s0.to(DEV)
+    o = gdn2.gdn2_decode(*cuda(*ins), state)
+    s_ref = s0.clone()
+    o_ref = orc.decode(*ins, s_ref)
+    assert torch.isfinite(o).all() and torch.isfinite(state).all()
+    assert orc.rel_max_err(o.cpu(), o_ref) < 2e-5
+    assert orc.rel_max_err(state.cpu(), s_ref) < 2e-5
+
+
 def test_decode_zero_gates_only_decay(K):
     dev, host = bf16_inputs(2, 9, 4, 128, 128, seed=5)
     q, k, v, g, b, w = dev
