@@ -255,6 +255,27 @@ def test_prefill_from_host_streams_sequences(K):
     K.check_device_status()
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_fp16_inputs_prefill_and_decode(K, D):
+    """fp16 tensors (the third dtype the reference accepts) go through the SIMT family with fp32 records."""
+    B, S, H = 2, 64 * 3 + 11, 3
+    q, k, v, g, b, w = orc.make_inputs(B, S, H, D, D, seed=31, gate="softplus")
+    host = tuple(t.half().float() for t in (q, k, v)) + (g, b.half().float(), w.half().float())
+    dev = tuple(t.half().to(DEV) for t in (q, k, v)) + (g.to(DEV), b.half().to(DEV), w.half().to(DEV))
+    o, state = gdn2.gdn2_prefill(*dev)
+    o_ref, s_ref = orc.prefill(*host)
+    assert o.dtype == torch.float16
+    assert orc.max_abs_err(o.float().cpu(), o_ref) < 5e-3          # fp16 output rounding only
+    assert orc.rel_fro_err(state.cpu(), s_ref) < 1e-4
+    st = state.clone()
+    o2 = gdn2.gdn2_decode(*(t[:, :9] for t in dev), st)
+    s2 = s_ref.clone()
+    o2_ref = orc.decode(*(t[:, :9] for t in host), s2)
+    assert o2.dtype == torch.float16
+    assert orc.max_abs_err(o2.float().cpu(), o2_ref) < 5e-3
+    assert orc.rel_fro_err(st.cpu(), s2) < 1e-4
+
+
 def test_fast_decay_d128_bf16_takes_exact_path(K):
     dev, host = bf16_inputs(1, 128, 2, 128, 128, seed=17, gate="softplus", decay_scale=30.0)
     o_ref, s_ref = orc.recurrence(*host)
