@@ -1,9 +1,14 @@
 // Chunk-local stage of the chunkwise forward, tensor-core (tcgen05 / TMEM) family, for
 // DK = DV = 128 and bf16 inputs. One 256-thread block per (chunk, batch*head), two blocks per SM.
-// Thread (c, hf) owns key channel c and value channel c for the tokens of half hf of the chunk
-// (32 tokens = two 16-token sub-blocks), so the cumulative decay is a private running sum plus one
-// prefix exchanged through shared memory. Two threads per channel, rather than one, double the warps
-// an SM has to hide latency with at the same shared-memory footprint.
+// Two thread mappings are used:
+//   * gating (steps 1, value side): thread = (channel pair cp, 16-token sub-block sbk). Two adjacent
+//     channels per thread turn every 16-bit load, convert and shared-memory store into a packed 32-bit one,
+//     and the cumulative decay of a channel is a private running sum plus one prefix per sub-block
+//     exchanged through shared memory. A warp holds one sub-block, so its constants are warp-uniform.
+//   * everything that reads MMA results (steps 2b, 5): thread = (TMEM lane = row or channel, half of the
+//     columns or tokens), because a warp can only address its own 32 lanes of tensor memory.
+// What a gating thread produces for later steps (Qg, w*v) waits in spare TMEM columns of whatever lane the
+// thread owns: the stash is private scratch, read back by the same thread.
 //
 // What the reference spreads over five kernels (cumsum, intra_diag, inter_blocks, solve, wy:
 // gdn2/forward.py:65-535 of the reference project) is one kernel here, and the intermediates it
@@ -29,7 +34,7 @@
 // Shared memory is two regions reused over the block's life so that two blocks fit on an SM:
 //   X (72.5 KiB): MMA1 operands, then Tm + Ai + (w*v)^T;   Y (32.25 KiB): E^T, then the WQ staging.
 // Qg = scale*q*gamma is produced in step 1 but only needed in step 5; it waits in 32 spare TMEM
-// columns of the thread's own lane (packed bf16 pairs).
+// columns (packed bf16 pairs: the two channels of one token per word).
 #include <cstdlib>
 
 #include "common.cuh"
@@ -73,7 +78,7 @@ struct PrepTcSmem {
     float et[16 * D * 4];                    // A of MMA2: E^T  [tok/4][128 dk][4]
     __nv_bfloat16 wq[16 * A_PAD * 8];        // staging of the WQ record: [dk/8][129][8]
   } y;
-  float pre[2][3][D];                        // per half and channel: first-row G of its two sub-blocks, its total (relative)
+  float pre[4][2][D];                        // per sub-block and channel: G at its first row and its total, both relative to its start
   uint64_t bar_m1, bar_m2;
   uint32_t tmem_base;
   int abort_flag;
@@ -86,34 +91,40 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float pick4(int j, float a0, float a1, float a2, float a3) {
-  return j == 0 ? a0 : j == 1 ? a1 : j == 2 ? a2 : a3;
-}
 
-// Raw values of one channel for 8 consecutive tokens, converted only when consumed.
-struct Raw8 {
-  float g[8];
-  uint32_t k[8], q[8], b[8];              // bf16 bit patterns, zero-extended: one register each, no packing
+// Raw values of one channel pair for 4 consecutive tokens, converted only when consumed: g as two floats,
+// k, q, b as the two bf16 bit patterns in one 32-bit word (low half = even channel).
+struct Raw4 {
+  float2 g[4];
+  uint32_t k[4], q[4], b[4];
 };
-// 16-bit load into a full register, and its value as fp32 (a bf16 is the top half of an fp32)
-__device__ __forceinline__ uint32_t ldg_u16(const __nv_bfloat16* p) {
-  return static_cast<uint32_t>(__ldg(reinterpret_cast<const unsigned short*>(p)));
-}
-__device__ __forceinline__ float bf16_bits_to_f32(uint32_t x) { return __uint_as_float(x << 16); }
-__device__ __forceinline__ void load_raw8(Raw8& r, const float* gp, const __nv_bfloat16* kp, const __nv_bfloat16* qp,
-                                          const __nv_bfloat16* bp, size_t rstride) {
+__device__ __forceinline__ void load_raw4(Raw4& r, const float2* gp, const uint32_t* kp, const uint32_t* qp,
+                                          const uint32_t* bp, size_t pstride) {
 #pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    const size_t off = u * rstride;
-    r.g[u] = __ldg(gp + off); r.k[u] = ldg_u16(kp + off); r.q[u] = ldg_u16(qp + off); r.b[u] = ldg_u16(bp + off);
+  for (int u = 0; u < 4; ++u) {
+    const size_t off = u * pstride;
+    r.g[u] = __ldg(gp + off); r.k[u] = __ldg(kp + off); r.q[u] = __ldg(qp + off); r.b[u] = __ldg(bp + off);
   }
 }
-
-// Per-sub-block constants of the gating step.
-struct SubConst {
-  float ref, refn, gam_ref, kg_c, cc_a, cc_b, nx_c;
-  int j, off_j;
-};
+// the two bf16 values of a packed word as fp32 (a bf16 is the top half of an fp32)
+__device__ __forceinline__ float2 bf16x2_bits_to_f32(uint32_t x) {
+  return make_float2(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t pack_bf16x2_rn(float lo, float hi) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ uint32_t pack_f16x2_rn(float lo, float hi) {
+  __half2 t = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+__device__ __forceinline__ float2 ex2(float2 x) { return make_float2(ex2(x.x), ex2(x.y)); }
+__device__ __forceinline__ float2 operator-(float2 a, float2 b) { return make_float2(a.x - b.x, a.y - b.y); }
+__device__ __forceinline__ float2 operator+(float2 a, float2 b) { return make_float2(a.x + b.x, a.y + b.y); }
+__device__ __forceinline__ float2 operator*(float2 a, float2 b) { return make_float2(a.x * b.x, a.y * b.y); }
+__device__ __forceinline__ float2 pick4(int j, float2 a0, float2 a1, float2 a2, float2 a3) {
+  return j == 0 ? a0 : j == 1 ? a1 : j == 2 ? a2 : a3;
+}
 
 // HT > 0: the number of heads is a compile-time constant, so every token offset of the strided channel
 // loads folds into the load instruction's immediate; HT = 0 takes it from the argument.
@@ -130,13 +141,18 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const int ib = bh / H, ih = bh % H;
   const int64_t ch = (int64_t)bh * NC + n;
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
-  const int c = tid & (D - 1);                                          // channel = TMEM lane
-  const int hf = tid >> 7;                                              // token half: tokens [32 hf, 32 hf + 32)
+  const int c = tid & (D - 1);                                          // lane-true mapping: channel / row = TMEM lane
+  const int hf = tid >> 7;                                              // ... and half of the tokens or columns
   const int lq = wid & 3;                                               // TMEM lane quarter of this warp
+  // gating mapping: thread = (channel pair cp, 16-token sub-block sbk); a warp has one sub-block
+  const int cp = tid & 63;                                              // channels 2 cp, 2 cp + 1
+  const int sbk = tid >> 6;
+  const int c0 = 2 * cp;
   const size_t row0 = ((size_t)ib * in_bs + (size_t)n * BS) * H + ih;   // token row of t = 0
   const size_t rstride = HT > 0 ? (size_t)HT * D : (size_t)H * D;       // elements between tokens
-  const size_t hoff = (size_t)(32 * hf) * rstride;                      // first token of this thread's half
-  const float* gp = g + row0 * D + c + hoff;
+  const size_t pstride = rstride / 2;                                   // channel pairs between tokens
+  const size_t soff = (size_t)(16 * sbk) * rstride;                     // first token of this thread's sub-block
+  const float2* gp = reinterpret_cast<const float2*>(g + row0 * D + soff) + cp;
 #ifdef GDN2_SCAN_TIMING
   long long tprev = clock64();
 #endif
@@ -162,22 +178,20 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   }
 
   // ---- 1a. G at the first row of every sub-block and at the last token; decay-span check.
-  //          Each thread sums its own half; the halves meet through shared memory.
-  float ref0, ref1, ref2, ref3, g_last, run0;
+  //          Each thread sums its own sub-block (two channels); the four meet through shared memory.
+  float2 ref0, ref1, ref2, ref3, g_last, run0;
   bool bad = false;
   {
-    float gv[32];
+    float2 gv[16];
 #pragma unroll
-    for (int t = 0; t < 32; ++t) gv[t] = __ldg(gp + t * rstride) * kLog2e;     // 32 independent loads in flight
-    float run = 0.f, first[2];
+    for (int t = 0; t < 16; ++t) gv[t] = __ldg(gp + t * pstride);                 // 16 independent loads in flight
+    float2 run = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      first[j] = run + gv[16 * j];
-#pragma unroll
-      for (int u = 0; u < 16; ++u) run += gv[16 * j + u];
-      bad |= !((first[j] - run) <= kMaxSpanLog2);
-    }
-    s.pre[hf][0][c] = first[0]; s.pre[hf][1][c] = first[1]; s.pre[hf][2][c] = run;
+    for (int u = 0; u < 16; ++u) { run.x = fmaf(gv[u].x, kLog2e, run.x); run.y = fmaf(gv[u].y, kLog2e, run.y); }
+    const float2 first = make_float2(gv[0].x * kLog2e, gv[0].y * kLog2e);
+    bad = !((first.x - run.x) <= kMaxSpanLog2) || !((first.y - run.y) <= kMaxSpanLog2);
+    *reinterpret_cast<float2*>(&s.pre[sbk][0][c0]) = first;
+    *reinterpret_cast<float2*>(&s.pre[sbk][1][c0]) = run;
   }
   if (tid == 0) {
     tc::mbar_init(&s.bar_m1, 4);     // one commit per issuing warp
@@ -190,11 +204,14 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   if (tid == 0) P.flags[ch] = any_bad ? 1 : 0;
   if (any_bad) return;              // the exact kernel redoes this chunk; nothing allocated yet
   {
-    const float tot0 = s.pre[0][2][c];
-    ref0 = s.pre[0][0][c]; ref1 = s.pre[0][1][c];
-    ref2 = tot0 + s.pre[1][0][c]; ref3 = tot0 + s.pre[1][1][c];
-    g_last = tot0 + s.pre[1][2][c];
-    run0 = hf ? tot0 : 0.f;
+    const float2 f0 = *reinterpret_cast<const float2*>(&s.pre[0][0][c0]), t0_ = *reinterpret_cast<const float2*>(&s.pre[0][1][c0]);
+    const float2 f1 = *reinterpret_cast<const float2*>(&s.pre[1][0][c0]), t1_ = *reinterpret_cast<const float2*>(&s.pre[1][1][c0]);
+    const float2 f2 = *reinterpret_cast<const float2*>(&s.pre[2][0][c0]), t2_ = *reinterpret_cast<const float2*>(&s.pre[2][1][c0]);
+    const float2 f3 = *reinterpret_cast<const float2*>(&s.pre[3][0][c0]), t3_ = *reinterpret_cast<const float2*>(&s.pre[3][1][c0]);
+    const float2 p1 = t0_, p2 = t0_ + t1_, p3 = p2 + t2_;
+    ref0 = f0; ref1 = p1 + f1; ref2 = p2 + f2; ref3 = p3 + f3;
+    g_last = p3 + t3_;
+    run0 = pick4(sbk, make_float2(0.f, 0.f), p1, p2, p3);
   }
   if (wid == 0) tc::tmem_alloc(&s.tmem_base, kTmemCols);
   tc::tc_fence_before_sync();
@@ -203,88 +220,84 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const uint32_t tm = s.tmem_base;
 
   PTICK(1);
-  // ---- 1b. gated operands of channel c for this thread's 32 tokens, in four groups of 8; the next
-  //          group's 32 loads are issued (raw, unconverted) before the current one is processed
+  // ---- 1b. gated operands of the channel pair for this thread's 16 tokens, in four groups of 4; the next
+  //          group's 16 loads are issued (raw, unconverted) before the current one is processed. Two
+  //          channels per thread: every 16-bit operand leaves as a packed pair (one convert, one store).
   {
-    const __nv_bfloat16* qp = q + row0 * D + c + hoff;
-    const __nv_bfloat16* kp = k + row0 * D + c + hoff;
-    const __nv_bfloat16* bp = b + row0 * D + c + hoff;
-    const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
-    const int cb = (c >> 3) * B_PAD * 8 + (c & 7);
-    char* kgt_g = P.kgt + (size_t)ch * (D * BS * 2) + c * 16;   // fp16 image [tok/8][128 dk][8]
-    float run = run0;
-    SubConst sc;
+    const uint32_t* qp = reinterpret_cast<const uint32_t*>(q + row0 * D + soff) + cp;
+    const uint32_t* kp = reinterpret_cast<const uint32_t*>(k + row0 * D + soff) + cp;
+    const uint32_t* bp = reinterpret_cast<const uint32_t*>(b + row0 * D + soff) + cp;
+    uint32_t* a_own32 = reinterpret_cast<uint32_t*>(s.x.ops.a_own) + (cp >> 2) * A_PAD * 4 + (cp & 3);
+    uint32_t* bfam32 = reinterpret_cast<uint32_t*>(s.x.ops.bfam) + (cp >> 2) * B_PAD * 4 + (cp & 3);
+    char* kgt_g = P.kgt + (size_t)ch * (D * BS * 2) + c0 * 16;   // fp16 image [tok/8][128 dk][8]
+    const int j = sbk;                                          // warp-uniform
+    const int off_j = 8 * j * (j + 1);                          // first row of B_j: 0, 16, 48, 96
+    const int off_j1 = 8 * (j + 1) * (j + 2), off_j2 = 8 * (j + 2) * (j + 3);
+    const float2 zero2 = make_float2(0.f, 0.f);
+    const float2 ref = pick4(j, ref0, ref1, ref2, ref3);
+    const float2 refn = pick4(j, ref1, ref2, ref3, zero2);      // ref of the next sub-block (unused for j = 3)
+    const float2 gam_ref = ex2(ref);
+    const float2 nx_c = ex2(((j < 3) ? refn : g_last) - ref);  // 2^(refn - run) = nx_c * 2^(ref - run)
+    const float2 kg_c = (j < 3) ? ex2(g_last - refn) : make_float2(1.f, 1.f);
+    const float2 cc_a = ex2(pick4(j, ref2, ref3, zero2, zero2) - refn);   // B_{j+2} relative to B_{j+1}
+    const float2 cc_b = ex2(ref3 - refn);                      // B_{j+3} relative to B_{j+1} (j = 0 only)
+    float2 run = run0;
+    uint32_t kgx[4], kgy[4];                                    // fp16 pairs of KG for 8 tokens of each channel
 
-    auto sub_consts = [&](int j) {
-      sc.j = j;
-      sc.off_j = 8 * j * (j + 1);                               // first row of B_j: 0, 16, 48, 96
-      sc.ref = pick4(j, ref0, ref1, ref2, ref3);
-      sc.refn = pick4(j, ref1, ref2, ref3, 0.f);                // ref of the next sub-block (unused for j = 3)
-      sc.gam_ref = ex2(sc.ref);
-      sc.nx_c = ex2(((j < 3) ? sc.refn : g_last) - sc.ref);    // 2^(refn - run) = nx_c * 2^(ref - run)
-      sc.kg_c = (j < 3) ? ex2(g_last - sc.refn) : 1.f;
-      sc.cc_a = ex2(pick4(j, ref2, ref3, 0.f, 0.f) - sc.refn);  // B_{j+2} relative to B_{j+1}
-      sc.cc_b = ex2(ref3 - sc.refn);                            // B_{j+3} relative to B_{j+1} (j = 0 only)
-    };
-    // one group: tokens t0 .. t0 + 7 (t0 a multiple of 8)
-    auto gate8 = [&](const Raw8& r, int t0) {
-      const int j = sc.j;
-      uint32_t qgp[4], kgp[4];
+    // one group: tokens t0 .. t0 + 3 of the chunk (t0 a multiple of 4); hi = second group of an 8-token pair
+    auto gate4 = [&](const Raw4& r, int t0, int hi) {
+      float e4x[4], e4y[4], kx[4], ky[4];
+      uint32_t qgp[4];
 #pragma unroll
-      for (int t4 = 0; t4 < 2; ++t4) {
-        float e4[4], kg4[4], qg4[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int uu = 4 * t4 + u;
-          const int t = t0 + uu;
-          run += r.g[uu] * kLog2e;
-          const float kf = bf16_bits_to_f32(r.k[uu]), qf = bf16_bits_to_f32(r.q[uu]);
-          const float a = ex2(run - sc.ref);                  // <= 1
-          const float co = ex2(sc.ref - run);                 // >= 1, bounded by the span check
-          const float nx = sc.nx_c * co;                      // 2^(refn - run) (2^(g_last - run) for j = 3), <= 1
-          const float e = bf16_bits_to_f32(r.b[uu]) * kf;
-          s.x.ops.a_own[ca + t * 8] = __float2bfloat16_rn(e * a);
-          s.x.ops.a_own[ca + (BS + t) * 8] = __float2bfloat16_rn(qf * a);
-          s.x.ops.bfam[cb + (sc.off_j + t) * 8] = __float2bfloat16_rn(kf * co);
-          const float kn = kf * nx;
-          if (j < 3) s.x.ops.bfam[cb + (8 * (j + 1) * (j + 2) + t) * 8] = __float2bfloat16_rn(kn);
-          if (j < 2) s.x.ops.bfam[cb + (8 * (j + 2) * (j + 3) + t) * 8] = __float2bfloat16_rn(kn * sc.cc_a);
-          if (j < 1) s.x.ops.bfam[cb + (96 + t) * 8] = __float2bfloat16_rn(kn * sc.cc_b);
-          const float gam = a * sc.gam_ref;
-          e4[u] = tf32_rn(e * gam);
-          qg4[u] = scale * qf * gam;
-          kg4[u] = kn * sc.kg_c * kValScale;
-        }
-        const int tq = (t0 >> 2) + t4;                          // token quad index
-        *reinterpret_cast<float4*>(&s.y.et[(tq * D + c) * 4]) = make_float4(e4[0], e4[1], e4[2], e4[3]);
-        __half2 h01 = __floats2half2_rn(kg4[0], kg4[1]), h23 = __floats2half2_rn(kg4[2], kg4[3]);
-        kgp[2 * t4] = *reinterpret_cast<uint32_t*>(&h01);
-        kgp[2 * t4 + 1] = *reinterpret_cast<uint32_t*>(&h23);
-        __nv_bfloat162 p01 = __floats2bfloat162_rn(qg4[0], qg4[1]), p23 = __floats2bfloat162_rn(qg4[2], qg4[3]);
-        qgp[2 * t4] = *reinterpret_cast<uint32_t*>(&p01);
-        qgp[2 * t4 + 1] = *reinterpret_cast<uint32_t*>(&p23);
+      for (int u = 0; u < 4; ++u) {
+        const int t = t0 + u;
+        run.x = fmaf(r.g[u].x, kLog2e, run.x); run.y = fmaf(r.g[u].y, kLog2e, run.y);
+        const float2 kf = bf16x2_bits_to_f32(r.k[u]), qf = bf16x2_bits_to_f32(r.q[u]);
+        const float2 a = ex2(run - ref);                      // <= 1
+        const float2 co = ex2(ref - run);                     // >= 1, bounded by the span check
+        const float2 nx = nx_c * co;                          // 2^(refn - run) (2^(g_last - run) for j = 3), <= 1
+        const float2 e = bf16x2_bits_to_f32(r.b[u]) * kf;
+        a_own32[t * 4] = pack_bf16x2_rn(e.x * a.x, e.y * a.y);
+        a_own32[(BS + t) * 4] = pack_bf16x2_rn(qf.x * a.x, qf.y * a.y);
+        bfam32[(off_j + t) * 4] = pack_bf16x2_rn(kf.x * co.x, kf.y * co.y);
+        const float2 kn = kf * nx;
+        if (j < 3) bfam32[(off_j1 + t) * 4] = pack_bf16x2_rn(kn.x, kn.y);
+        if (j < 2) bfam32[(off_j2 + t) * 4] = pack_bf16x2_rn(kn.x * cc_a.x, kn.y * cc_a.y);
+        if (j < 1) bfam32[(96 + t) * 4] = pack_bf16x2_rn(kn.x * cc_b.x, kn.y * cc_b.y);
+        const float2 gam = a * gam_ref;
+        e4x[u] = tf32_rn(e.x * gam.x); e4y[u] = tf32_rn(e.y * gam.y);
+        qgp[u] = pack_bf16x2_rn(scale * qf.x * gam.x, scale * qf.y * gam.y);
+        kx[u] = kn.x * kg_c.x * kValScale; ky[u] = kn.y * kg_c.y * kValScale;
       }
-      tc::tmem_st4(tc::tmem_addr(tm, lq * 32, kQgCol + (t0 >> 1)), qgp);
-      *reinterpret_cast<uint4*>(kgt_g + (size_t)(t0 >> 3) * D * 16) = make_uint4(kgp[0], kgp[1], kgp[2], kgp[3]);
+      const int tq = t0 >> 2;                                   // token quad index
+      *reinterpret_cast<float4*>(&s.y.et[(tq * D + c0) * 4]) = make_float4(e4x[0], e4x[1], e4x[2], e4x[3]);
+      *reinterpret_cast<float4*>(&s.y.et[(tq * D + c0 + 1) * 4]) = make_float4(e4y[0], e4y[1], e4y[2], e4y[3]);
+      tc::tmem_st4(tc::tmem_addr(tm, lq * 32, kQgCol + 16 * (sbk >> 1) + (t0 & 15)), qgp);
+      kgx[2 * hi] = pack_f16x2_rn(kx[0], kx[1]); kgx[2 * hi + 1] = pack_f16x2_rn(kx[2], kx[3]);
+      kgy[2 * hi] = pack_f16x2_rn(ky[0], ky[1]); kgy[2 * hi + 1] = pack_f16x2_rn(ky[2], ky[3]);
+      if (hi) {
+        char* dst = kgt_g + (size_t)(t0 >> 3) * D * 16;
+        *reinterpret_cast<uint4*>(dst) = make_uint4(kgx[0], kgx[1], kgx[2], kgx[3]);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(kgy[0], kgy[1], kgy[2], kgy[3]);
+      }
     };
 
-    Raw8 ra, rb;
-    load_raw8(ra, gp, kp, qp, bp, rstride);
+    Raw4 ra, rb;
+    load_raw4(ra, gp, kp, qp, bp, pstride);
 #pragma unroll 1
-    for (int sb = 0; sb < 2; ++sb) {                            // this thread's two sub-blocks
-      const int t0 = 32 * hf + 16 * sb;
-      const size_t o8 = (size_t)(16 * sb + 8) * rstride;
-      load_raw8(rb, gp + o8, kp + o8, qp + o8, bp + o8, rstride);
-      sub_consts(2 * hf + sb);
-      gate8(ra, t0);
-      if (sb == 0) {
-        const size_t o16 = (size_t)16 * rstride;
-        load_raw8(ra, gp + o16, kp + o16, qp + o16, bp + o16, rstride);
+    for (int s2 = 0; s2 < 2; ++s2) {                            // two 8-token halves of the sub-block
+      const int t0 = 16 * sbk + 8 * s2;
+      const size_t o4 = (size_t)(8 * s2 + 4) * pstride;
+      load_raw4(rb, gp + o4, kp + o4, qp + o4, bp + o4, pstride);
+      gate4(ra, t0, 0);
+      if (s2 == 0) {
+        const size_t o8 = (size_t)8 * pstride;
+        load_raw4(ra, gp + o8, kp + o8, qp + o8, bp + o8, pstride);
       }
-      gate8(rb, t0 + 8);
+      gate4(rb, t0 + 4, 1);
     }
     tc::tmem_st_wait();
-    if (hf == 1) P.gl[(size_t)ch * D + c] = ex2(g_last);
+    if (sbk == 3) *reinterpret_cast<float2*>(&P.gl[(size_t)ch * D + c0]) = ex2(g_last);
   }
   tc::fence_async_smem();
   tc::tc_fence_before_sync();
@@ -304,23 +317,22 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   }
   PTICK(3);
   // value side: raw loads issued while the tensor core works
-  // z = w*v of this thread's value channel waits in TMEM columns [192,256) of its own lane until the
+  // z = w*v of this thread's two value channels waits in TMEM columns [192,256) of its own lane until the
   // MMA1 operands are dead and (w*v)^T can take their place in shared memory
   {
-    const __nv_bfloat16* vp = v + row0 * D + c + hoff;
-    const __nv_bfloat16* wp = w + row0 * D + c + hoff;
-    uint32_t vr[16], wr[16], vn[16], wn[16];              // raw bf16 bits: converted one group behind the loads
+    const uint32_t* vp = reinterpret_cast<const uint32_t*>(v + row0 * D + soff) + cp;
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(w + row0 * D + soff) + cp;
+    uint32_t vr[16], wr[16];                              // raw bf16 pairs: all 32 loads in flight, then converted
 #pragma unroll
-    for (int u = 0; u < 16; ++u) { vr[u] = ldg_u16(vp + u * rstride); wr[u] = ldg_u16(wp + u * rstride); }
+    for (int u = 0; u < 16; ++u) { vr[u] = __ldg(vp + u * pstride); wr[u] = __ldg(wp + u * pstride); }
+    float zx[16], zy[16];
 #pragma unroll
-    for (int u = 0; u < 16; ++u) { vn[u] = ldg_u16(vp + (16 + u) * rstride); wn[u] = ldg_u16(wp + (16 + u) * rstride); }
-    float z[16];
-#pragma unroll
-    for (int u = 0; u < 16; ++u) z[u] = tf32_rn(bf16_bits_to_f32(vr[u]) * bf16_bits_to_f32(wr[u]));
-    tc::tmem_st16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * hf), z);
-#pragma unroll
-    for (int u = 0; u < 16; ++u) z[u] = tf32_rn(bf16_bits_to_f32(vn[u]) * bf16_bits_to_f32(wn[u]));
-    tc::tmem_st16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * hf + 16), z);
+    for (int u = 0; u < 16; ++u) {
+      const float2 vf = bf16x2_bits_to_f32(vr[u]), wf = bf16x2_bits_to_f32(wr[u]);
+      zx[u] = tf32_rn(vf.x * wf.x); zy[u] = tf32_rn(vf.y * wf.y);
+    }
+    tc::tmem_st16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * (sbk >> 1)), zx);
+    tc::tmem_st16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * (sbk >> 1) + 16), zy);
     tc::tmem_st_wait();
   }
   PTICK(4);
@@ -367,16 +379,20 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         *reinterpret_cast<uint4*>(ag + ((2 * cg + 1) * BS + r) * 8) = tc::pack8_f16(&row[8], kValScale);
       }
     }
-    // (w*v)^T image from the TMEM stash: each thread moves the 32 tokens it produced
-#pragma unroll 1
-    for (int jj = 2 * hf; jj < 2 * hf + 2; ++jj) {
-      float z[16];
-      tc::tmem_ld16(tc::tmem_addr(tm, lq * 32, kZCol + 16 * jj), z);
+    // (w*v)^T image from the TMEM stash: each thread moves the 16 tokens x 2 channels it produced
+    {
+      float zx[16], zy[16];
+      tc::tmem_ld16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * (sbk >> 1)), zx);
+      tc::tmem_ld16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * (sbk >> 1) + 16), zy);
       tc::tmem_ld_wait();
 #pragma unroll
-      for (int t4 = 0; t4 < 4; ++t4)
-        *reinterpret_cast<float4*>(&s.x.sol.zt[((4 * jj + t4) * D + c) * 4]) =
-            make_float4(z[4 * t4], z[4 * t4 + 1], z[4 * t4 + 2], z[4 * t4 + 3]);
+      for (int t4 = 0; t4 < 4; ++t4) {
+        const int tq = 4 * sbk + t4;
+        *reinterpret_cast<float4*>(&s.x.sol.zt[(tq * D + c0) * 4]) =
+            make_float4(zx[4 * t4], zx[4 * t4 + 1], zx[4 * t4 + 2], zx[4 * t4 + 3]);
+        *reinterpret_cast<float4*>(&s.x.sol.zt[(tq * D + c0 + 1) * 4]) =
+            make_float4(zy[4 * t4], zy[4 * t4 + 1], zy[4 * t4 + 2], zy[4 * t4 + 3]);
+      }
     }
   }
   tc::tc_fence_before_sync();
@@ -504,16 +520,13 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     tc::tmem_ld_wait();
 #pragma unroll
     for (int i = 0; i < 32; ++i) s.y.wq[ca + (32 * hf + i) * 8] = __float2bfloat16_rn(val[i]);
-    {
+    {   // Qg rows from this thread's gating stash: word t = the two channels 2 cp, 2 cp + 1 of token 16 sbk + t
       float qv[16];
-      tc::tmem_ld16(tc::tmem_addr(tm, lq * 32, kQgCol + 16 * hf), qv);
+      tc::tmem_ld16(tc::tmem_addr(tm, lq * 32, kQgCol + 16 * (sbk >> 1)), qv);
       tc::tmem_ld_wait();
+      uint32_t* wq32 = reinterpret_cast<uint32_t*>(s.y.wq) + (cp >> 2) * A_PAD * 4 + (cp & 3);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const uint32_t pk = __float_as_uint(qv[i]);
-        reinterpret_cast<uint16_t*>(s.y.wq)[ca + (BS + 32 * hf + 2 * i) * 8] = static_cast<uint16_t>(pk & 0xFFFFu);
-        reinterpret_cast<uint16_t*>(s.y.wq)[ca + (BS + 32 * hf + 2 * i + 1) * 8] = static_cast<uint16_t>(pk >> 16);
-      }
+      for (int i = 0; i < 16; ++i) wq32[(BS + 16 * sbk + i) * 4] = __float_as_uint(qv[i]);
     }
     tc::tmem_ld32(tc::tmem_addr(tm, lq * 32, 64 + 32 * hf), val);
     tc::tmem_ld_wait();
