@@ -26,7 +26,7 @@ from .config import DEFAULT_KERNEL_CONFIG, GDN2Config, GatedDeltaNet2Config
 from .forward import chunk_gdn2_fwd
 from .inference import gdn2_decode, gdn2_prefill
 
-__all__ = ["gdn2_attention", "GatedDeltaNet2", "GDN2Cache", "resolve_backend"]
+__all__ = ["gdn2_attention", "GatedDeltaNet2", "GDN2Cache", "GraphedStep", "resolve_backend"]
 
 _BACKENDS = ("auto", "cuda", "tilelang", "torch")
 
@@ -250,3 +250,56 @@ class GatedDeltaNet2(nn.Module):
             conv_state = torch.zeros(batch_size, channels, self.cfg.conv_size - 1, device=device,
                                      dtype=self.o_proj.weight.dtype)
         return GDN2Cache(state, conv_state)
+
+
+class GraphedStep:
+    """One-token ``GatedDeltaNet2.step`` captured in a CUDA graph (no counterpart in the reference).
+
+    ``step`` is some forty small launches (projections, convolutions, gates, the decode kernel, the gated
+    norm); at batch sizes where each of them takes microseconds the host's launch cost sets the latency.
+    Capturing them once and replaying the graph makes a step one launch. The cache is updated in place
+    (``recurrent_state`` by the decode kernel, ``conv_state`` by a copy), so the ``GDN2Cache`` given here
+    is THE cache of the sequence from then on; its tensors must not be replaced, only written into.
+
+    >>> cache = layer.prefill(prompt)[1]
+    >>> step = GraphedStep(layer, cache)
+    >>> y = step(x_t)            # [B, hidden] -> [B, hidden]; a view of a static buffer, valid until the next call
+    """
+
+    def __init__(self, layer: "GatedDeltaNet2", cache: GDN2Cache, warmup: int = 2):
+        state = cache.recurrent_state
+        if not state.is_cuda:
+            raise ValueError("GraphedStep needs a cache on a CUDA device")
+        self.layer, self.cache = layer, cache
+        B = state.shape[0]
+        weight = layer.o_proj.weight
+        self.x = torch.zeros(B, layer.cfg.hidden_size, device=state.device, dtype=weight.dtype)
+        keep_state = state.clone()
+        keep_conv = None if cache.conv_state is None else cache.conv_state.clone()
+        side = torch.cuda.Stream(state.device)
+        side.wait_stream(torch.cuda.current_stream(state.device))
+        with torch.cuda.stream(side):                     # library handles and workspaces come to life here
+            for _ in range(max(1, warmup)):
+                self._step_in_place()
+        torch.cuda.current_stream(state.device).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = self._step_in_place()
+        state.copy_(keep_state)                           # the warm-up and the capture advanced the cache
+        if keep_conv is not None:
+            cache.conv_state.copy_(keep_conv)
+
+    @torch.no_grad()
+    def _step_in_place(self):
+        layer, cache = self.layer, self.cache
+        x = self.x.unsqueeze(1)
+        q, k, v, g, b, w, conv = layer._front(x, cache.conv_state, cached=layer.q_conv is not None)
+        if conv is not None:
+            cache.conv_state.copy_(conv)
+        o = gdn2_decode(q, k, v, g, b, w, cache.recurrent_state, scale=layer.scale)
+        return layer._back(x, o)[:, 0]
+
+    def __call__(self, hidden_states):
+        self.x.copy_(hidden_states)
+        self.graph.replay()
+        return self.out

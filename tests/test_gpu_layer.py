@@ -51,3 +51,21 @@ def test_layer_bf16_d128_vs_oracle():
     assert orc.rel_max_err(got, ref) < 5e-2
     assert orc.rel_fro_err(cache.recurrent_state.cpu(), state) < 2e-2
     assert cache.conv_state.dtype == torch.bfloat16 and cache.recurrent_state.dtype == torch.float32
+
+
+def test_graphed_step_equals_eager_steps():
+    """The captured one-token step replays the same kernels: identical outputs and cache, token after token."""
+    cfg = gdn2.GatedDeltaNet2Config(hidden_size=256, num_heads=4, num_kv_heads=2)
+    layer = gdn2.GatedDeltaNet2(cfg).to(torch.bfloat16).eval().to(DEV)
+    x = (torch.randn(3, 40, 256, generator=torch.Generator().manual_seed(8)) * 0.5).bfloat16().to(DEV)
+    _, cache_a = layer.prefill(x[:, :24])
+    _, cache_b = layer.prefill(x[:, :24])
+    step = gdn2.GraphedStep(layer, cache_b)
+    assert torch.equal(cache_a.recurrent_state, cache_b.recurrent_state)      # the capture left the cache as it was
+    assert torch.equal(cache_a.conv_state, cache_b.conv_state)
+    for t in range(24, 40):
+        want, cache_a = layer.step(x[:, t], cache_a)
+        got = step(x[:, t]).clone()
+        assert torch.equal(got, want), t
+    assert torch.equal(cache_a.recurrent_state, cache_b.recurrent_state)
+    assert torch.equal(cache_a.conv_state, cache_b.conv_state)
