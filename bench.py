@@ -229,6 +229,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg")
     ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg")
+    ap.add_argument("--skip-layer", action="store_true", help="omit the layer leg (launch-list captures)")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the end-to-end leg (launch-list captures)")
     ap.add_argument("--profile-case", choices=["prefill", "decode"],
                     help="run a small case a profiler can capture (3 iterations, no JSON line) and exit")
@@ -394,6 +395,39 @@ def main():
                                "total_gbs": (2 * Bd * H * DK * DV * 4 + Bd * n * H * 2048) / (ms_d * 1e-3) / 1e9}
         del state
 
+    # ---- the layer around the op (hidden 2048, 16 heads, 8 kv heads, D = 128, bf16): prefill of
+    # [2, 4096, hidden], then 128 one-token steps, eager and replayed from a CUDA graph
+    layer_leg = None
+    if rank == 0 and world == 1 and not args.skip_layer:
+        cfg = gdn2.GatedDeltaNet2Config(hidden_size=2048, num_heads=16, num_kv_heads=8)
+        gen = torch.Generator(device=dev).manual_seed(0)
+        layer = gdn2.GatedDeltaNet2(cfg).to(torch.bfloat16).eval().to(dev)
+        with torch.no_grad():
+            for prm in layer.parameters():
+                if prm.dim() == 2:
+                    prm.copy_(torch.randn(prm.shape, device=dev, generator=gen) * 0.02)
+        x = torch.randn(2, 4096, 2048, device=dev, generator=gen).bfloat16()
+        ms_pre = time_events(lambda: layer.prefill(x), 5, 3, torch.cuda.synchronize)
+        _, cache = layer.prefill(x)
+        xt = torch.randn(2, 2048, device=dev, generator=gen).bfloat16()
+
+        def eager_steps():
+            for _ in range(128):
+                layer.step(xt, cache)
+
+        ms_eager = time_events(eager_steps, 3, 1, torch.cuda.synchronize)
+        step = gdn2.GraphedStep(layer, cache)
+
+        def graphed_steps():
+            for _ in range(128):
+                step(xt)
+
+        ms_graph = time_events(graphed_steps, 3, 1, torch.cuda.synchronize)
+        layer_leg = {"config": "hidden 2048, H=16, HK=8, DK=DV=128, bf16, x [2,4096,2048]",
+                     "prefill_ms": ms_pre, "prefill_tokens_per_s": 2 * 4096 / (ms_pre * 1e-3),
+                     "step_us_eager": ms_eager * 1e3 / 128, "step_us_cuda_graph": ms_graph * 1e3 / 128}
+        del layer, x, cache, step
+
     cpu = None
     if rank == 0 and world == 1 and not args.skip_cpu:
         threads = os.cpu_count() or 1
@@ -413,7 +447,8 @@ def main():
             "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches * world,
-            "roofline": roofline, "decode": decode, "cpu_baseline": cpu, "head_sharded": head_sharded,
+            "roofline": roofline, "decode": decode, "layer": layer_leg, "cpu_baseline": cpu,
+            "head_sharded": head_sharded,
         }))
     if world > 1:
         dist.destroy_process_group()

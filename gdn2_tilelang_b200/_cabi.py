@@ -42,7 +42,19 @@ SIGNATURES = {
     "gdn2_check_device_status": (_int, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
     "gdn2_selftest_mma": (_int, [_vp, _vp, _vp, _vp]),
     "gdn2_prefill_static": (_int, [_vp] * 9 + [_i64] * 7 + [_f32, _int, _vp]),
+    "gdn2_layer_front": (_int, [_vp, _int, _vp]),
+    "gdn2_layer_back": (_int, [_vp] * 4 + [_i64] * 5 + [_f32, _int, _vp]),
 }
+
+
+class LayerFrontArgs(ctypes.Structure):
+    """``gdn2_layer_front_args`` of include/gdn2_b200.h."""
+
+    _fields_ = ([(n, _vp) for n in ("proj", "conv_state", "conv_weight", "conv_bias", "A_log", "dt_bias",
+                                    "q", "k", "v", "g", "b", "w", "new_conv_state")]
+                + [(n, _i64) for n in ("B", "S", "H", "HK", "DK", "DV", "K", "NP",
+                                       "off_q", "off_k", "off_v", "off_b", "off_w", "off_f")]
+                + [("erase_scale", _f32)])
 
 _lock = threading.Lock()
 _lib = None
@@ -289,6 +301,44 @@ class NativeKernels:
         if rc != 0:
             raise GDN2KernelError(f"device status word = {detail.value:#x}: "
                                   f"{self.lib.gdn2_status_string(rc).decode()}")
+
+    def layer_front(self, proj, offsets, conv_state, conv_weight, conv_bias, A_log, dt_bias, H, HK, DK, DV, K,
+                    erase_scale, want_conv_state):
+        """Fused pre-processing of the layer: ``proj [B, S, NP]`` -> ``(q, k, v, g, b, w, new_conv_state)``.
+        ``offsets`` = columns of the q, k, v, b, w, f projections inside ``proj``."""
+        _require_cuda(proj)
+        B, S, NP = proj.shape
+        dt, dev = proj.dtype, proj.device
+        q = torch.empty(B, S, H, DK, dtype=dt, device=dev)
+        k, b = torch.empty_like(q), torch.empty_like(q)
+        g = torch.empty(B, S, H, DK, dtype=torch.float32, device=dev)
+        v = torch.empty(B, S, H, DV, dtype=dt, device=dev)
+        w = torch.empty_like(v)
+        new_conv = None
+        if K > 1 and want_conv_state:
+            new_conv = torch.empty(B, 2 * HK * DK + H * DV, K - 1, dtype=dt, device=dev)
+        ptr = lambda t: None if t is None else t.data_ptr()
+        a = LayerFrontArgs(ptr(proj), ptr(conv_state), ptr(conv_weight), ptr(conv_bias), ptr(A_log), ptr(dt_bias),
+                           ptr(q), ptr(k), ptr(v), ptr(g), ptr(b), ptr(w), ptr(new_conv),
+                           B, S, H, HK, DK, DV, K, NP, *offsets, erase_scale)
+        with torch.cuda.device(dev):
+            rc = self.lib.gdn2_layer_front(ctypes.byref(a), dtype_code(dt), self._stream(proj))
+        _check(self.lib, rc, "gdn2_layer_front")
+        self.launches += 2 if new_conv is not None else 1
+        return q, k, v, g, b, w, new_conv
+
+    def layer_back(self, o, proj, norm_weight, off_gate, eps):
+        """Fused gated RMSNorm: ``o [B, S, H, DV]`` and the o_gate columns of ``proj`` -> ``[B, S, H*DV]``."""
+        _require_cuda(o, proj)
+        B, S, H, DV = o.shape
+        out = torch.empty(B, S, H * DV, dtype=o.dtype, device=o.device)
+        with torch.cuda.device(o.device):
+            rc = self.lib.gdn2_layer_back(o.data_ptr(), proj.data_ptr(), norm_weight.data_ptr(), out.data_ptr(),
+                                          B * S, H, DV, proj.shape[-1], off_gate, eps, dtype_code(o.dtype),
+                                          self._stream(o))
+        _check(self.lib, rc, "gdn2_layer_back")
+        self.launches += 1
+        return out
 
     def selftest_mma(self, a: torch.Tensor, bt: torch.Tensor) -> torch.Tensor:
         _require_cuda(a, bt)

@@ -22,6 +22,7 @@ import torch
 import torch.nn.functional as F
 from torch import nn
 
+from . import _cabi
 from .config import DEFAULT_KERNEL_CONFIG, GDN2Config, GatedDeltaNet2Config
 from .forward import chunk_gdn2_fwd
 from .inference import gdn2_decode, gdn2_prefill
@@ -162,10 +163,48 @@ class GatedDeltaNet2(nn.Module):
     def _expand(self, x):
         return x if self.head_repeat == 1 else x.repeat_interleave(self.head_repeat, dim=-2)
 
+    def _fused_tables(self):
+        """Concatenated projection weight ``[NP, hidden]`` (q | k | v | b | w | f | o_gate), its column
+        offsets, and the convolution weight ``[CC, K]`` / bias ``[CC]`` (q | k | v); rebuilt when a
+        parameter changes."""
+        lin = (self.q_proj, self.k_proj, self.v_proj, self.b_proj, self.w_proj, self.f_proj, self.o_gate_proj)
+        convs = () if self.q_conv is None else (self.q_conv.conv, self.k_conv.conv, self.v_conv.conv)
+        params = [m.weight for m in lin] + [c.weight for c in convs] + [c.bias for c in convs if c.bias is not None]
+        key = tuple((p.data_ptr(), p._version, p.dtype) for p in params)
+        if getattr(self, "_fused_key", None) != key:
+            w_cat = torch.cat([m.weight for m in lin], 0).contiguous()
+            sizes = [m.weight.shape[0] for m in lin]
+            offs = [sum(sizes[:i]) for i in range(len(sizes))]
+            cw = cb = None
+            if convs:
+                cw = torch.cat([c.weight.reshape(c.weight.shape[0], -1) for c in convs], 0).contiguous()
+                if all(c.bias is not None for c in convs):
+                    cb = torch.cat([c.bias for c in convs], 0).contiguous()
+            self._fused_key, self._fused = key, (w_cat, offs, cw, cb)
+        return self._fused
+
+    def _use_fused(self, x) -> bool:
+        return (x.is_cuda and self.head_dim_k <= 256 and self.head_dim_v <= 256
+                and self.q_proj.weight.dtype == x.dtype and self.q_proj.bias is None)
+
     def _front(self, x, conv_state, cached: bool):
-        """Everything before the attention kernels. Returns ``(q, k, v, g, b, w, new_conv_state)``."""
+        """Everything before the attention kernels. Returns ``(q, k, v, g, b, w, new_conv_state, proj)``;
+        ``proj`` is the fused projection buffer (its o_gate columns feed ``_back``) or ``None``."""
         B, S, _ = x.shape
         H, HK, DK, DV = self.num_heads, self.num_kv_heads, self.head_dim_k, self.head_dim_v
+        if self._use_fused(x):
+            # one GEMM for the seven input projections, then one kernel for everything element-wise
+            w_cat, offs, cw, cb = self._fused_tables()
+            proj = F.linear(x, w_cat)
+            K = self.cfg.conv_size if self.q_conv is not None else 0
+            state = None
+            if cached and conv_state is not None:
+                state = conv_state if conv_state.dtype == x.dtype else conv_state.to(x.dtype)
+                state = state.contiguous()
+            q, k, v, g, b, w, new_conv = _cabi.kernels().layer_front(
+                proj, offs[:6], state, cw, cb, self.A_log.detach().to(x.dtype), self.dt_bias.detach().to(x.dtype).contiguous(),
+                H, HK, DK, DV, K, float(self.erase_scale), want_conv_state=True)
+            return q, k, v, g, b, w, new_conv, proj
         q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
         new_conv = None
         if self.q_conv is not None:
@@ -187,10 +226,15 @@ class GatedDeltaNet2(nn.Module):
         b = torch.sigmoid(self.b_proj(x).view(B, S, HK, DK)) * self.erase_scale
         w = torch.sigmoid(self.w_proj(x).view(B, S, H, DV))
         q, k, b, g = (self._expand(t) for t in (q, k, b, g))
-        return q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), b.contiguous(), w.contiguous(), new_conv
+        return q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), b.contiguous(), w.contiguous(), new_conv, None
 
-    def _back(self, x, o):
+    def _back(self, x, o, proj=None):
         B, S, _ = x.shape
+        if proj is not None:
+            off_gate = self._fused_tables()[1][6]
+            normed = _cabi.kernels().layer_back(o.contiguous(), proj, self.o_norm.weight.detach().to(o.dtype),
+                                                off_gate, float(self.o_norm.eps))
+            return self._reduce(self.o_proj(normed))
         gate = self.o_gate_proj(x).view(B, S, self.num_heads, self.head_dim_v)
         o = self.o_norm(o, gate).reshape(B, S, self.num_heads * self.head_dim_v)
         return self._reduce(self.o_proj(o))
@@ -203,12 +247,12 @@ class GatedDeltaNet2(nn.Module):
     @torch.no_grad()
     def forward(self, hidden_states, cache: GDN2Cache | None = None, use_cache: bool = False, cu_seqlens=None):
         """Full-sequence forward. Returns ``(output [B, S, hidden], GDN2Cache | None)``."""
-        q, k, v, g, b, w, conv = self._front(hidden_states, None, cached=False)
+        q, k, v, g, b, w, conv, proj = self._front(hidden_states, None, cached=False)
         o, final_state = gdn2_attention(
             q, k, v, g, b, w, scale=self.scale,
             initial_state=cache.recurrent_state if cache is not None else None,
             output_final_state=use_cache, config=self.cfg.kernel, cu_seqlens=cu_seqlens)
-        out = self._back(hidden_states, o)
+        out = self._back(hidden_states, o, proj)
         return out, (GDN2Cache(final_state, conv if use_cache else None) if use_cache else None)
 
     @torch.no_grad()
@@ -216,21 +260,21 @@ class GatedDeltaNet2(nn.Module):
         """Prefill a prompt (or a segment of one) and return ``(output, cache)`` to decode from."""
         if cache is None:
             cache = self.init_cache(hidden_states.shape[0], device=hidden_states.device)
-        q, k, v, g, b, w, conv = self._front(hidden_states, cache.conv_state, cached=self.q_conv is not None)
+        q, k, v, g, b, w, conv, proj = self._front(hidden_states, cache.conv_state, cached=self.q_conv is not None)
         if conv is not None:
             cache.conv_state = conv
         o, state = gdn2_prefill(q, k, v, g, b, w, cache.recurrent_state, scale=self.scale, config=self.cfg.kernel)
         cache.recurrent_state = state
-        return self._back(hidden_states, o), cache
+        return self._back(hidden_states, o, proj), cache
 
     @torch.no_grad()
     def decode(self, hidden_states, cache: GDN2Cache):
         """Decode ``n`` tokens ``[B, n, hidden]``; ``cache.recurrent_state`` is updated in place."""
-        q, k, v, g, b, w, conv = self._front(hidden_states, cache.conv_state, cached=self.q_conv is not None)
+        q, k, v, g, b, w, conv, proj = self._front(hidden_states, cache.conv_state, cached=self.q_conv is not None)
         if conv is not None:
             cache.conv_state = conv
         o = gdn2_decode(q, k, v, g, b, w, cache.recurrent_state, scale=self.scale)
-        return self._back(hidden_states, o), cache
+        return self._back(hidden_states, o, proj), cache
 
     @torch.no_grad()
     def step(self, hidden_states, cache: GDN2Cache):
@@ -293,11 +337,11 @@ class GraphedStep:
     def _step_in_place(self):
         layer, cache = self.layer, self.cache
         x = self.x.unsqueeze(1)
-        q, k, v, g, b, w, conv = layer._front(x, cache.conv_state, cached=layer.q_conv is not None)
+        q, k, v, g, b, w, conv, proj = layer._front(x, cache.conv_state, cached=layer.q_conv is not None)
         if conv is not None:
             cache.conv_state.copy_(conv)
         o = gdn2_decode(q, k, v, g, b, w, cache.recurrent_state, scale=layer.scale)
-        return layer._back(x, o)[:, 0]
+        return layer._back(x, o, proj)[:, 0]
 
     def __call__(self, hidden_states):
         self.x.copy_(hidden_states)

@@ -1,0 +1,244 @@
+// Element-wise stages of the GatedDeltaNet2 layer around the attention kernels, fused:
+//
+//   front: from ONE projection buffer P = x W_cat^T (columns q | k | v | b | w | f | o_gate) to the six
+//          kernel inputs -- causal depthwise convolution + SiLU on q, k, v (with the cached last
+//          conv_size-1 columns when decoding), L2 normalisation of q and k per head, the decay
+//          g = -exp(A_log) * softplus(f + dt_bias), the gates b = erase_scale * sigmoid(.), w = sigmoid(.),
+//          and the grouped-query expansion (a kv head written to its head_repeat value heads);
+//   tail:  the new convolution cache (the last conv_size-1 pre-convolution columns of q | k | v);
+//   back:  per-head RMSNorm of the attention output times SiLU(o_gate).
+//
+// These replace the torch operator chains of _ShortConv, F.normalize, the gate expressions and
+// _GatedRMSNorm (gdn2/attention.py:186-229, 290-297, 323-340 of the reference project): about 25 launches
+// and as many round trips through HBM per call become three. All arithmetic is fp32 with one rounding to
+// the storage type at the end. One warp per (token, kv head) in front, per (token, value head) in back.
+#include "common.cuh"
+
+namespace gdn2 {
+
+namespace {
+
+constexpr int kWarps = 4;
+
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+// value at time tt (may be negative: the cached columns, or zero) of projection column `col`, whose
+// position among the convolved channels q | k | v is `cch`
+template <typename T>
+__device__ __forceinline__ float tap(const T* P, const T* conv_state, int64_t b, int tt, int S, int NP, int col, int cch,
+                                     int CC, int K) {
+  if (tt >= 0) return to_f32(P[((size_t)b * S + tt) * NP + col]);
+  if (conv_state == nullptr) return 0.f;
+  return to_f32(conv_state[((size_t)b * CC + cch) * (K - 1) + (K - 1 + tt)]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(32 * kWarps)
+layer_front_kernel(gdn2_layer_front_args a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t item = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  if (item >= a.B * a.S * a.HK) return;
+  const int hk = (int)(item % a.HK);
+  const int64_t bt = item / a.HK;
+  const int t = (int)(bt % a.S);
+  const int64_t b = bt / a.S;
+  const int S = (int)a.S, NP = (int)a.NP, K = (int)a.K, DK = (int)a.DK, DV = (int)a.DV, H = (int)a.H, HK = (int)a.HK;
+  const int rep = H / HK;
+  const int Cqk = HK * DK, Cv = H * DV, CC = 2 * Cqk + Cv;
+  const T* P = static_cast<const T*>(a.proj);
+  const T* cs = static_cast<const T*>(a.conv_state);
+  const T* cw = static_cast<const T*>(a.conv_weight);   // [CC, K], channels q | k | v
+  const T* cb = static_cast<const T*>(a.conv_bias);     // [CC] or null
+  const size_t prow = ((size_t)b * S + t) * NP;
+
+  // ---- q and k: convolution + SiLU, then L2 normalisation over the head
+  for (int which = 0; which < 2; ++which) {
+    const int col0 = (which == 0 ? (int)a.off_q : (int)a.off_k) + hk * DK;
+    const int cch0 = which * Cqk + hk * DK;
+    float ss = 0.f;
+    float vals[8];                                       // DK <= 256: up to 8 channels per lane
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + 32 * i;
+      float y = 0.f;
+      if (c < DK) {
+        if (K > 0) {
+          y = cb ? to_f32(cb[cch0 + c]) : 0.f;
+          for (int j = 0; j < K; ++j)
+            y = fmaf(to_f32(cw[(size_t)(cch0 + c) * K + j]), tap(P, cs, b, t - (K - 1) + j, S, NP, col0 + c, cch0 + c, CC, K), y);
+          y = silu(y);
+        } else {
+          y = to_f32(P[prow + col0 + c]);
+        }
+        ss = fmaf(y, y, ss);
+      }
+      vals[i] = y;
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+    T* dst = static_cast<T*>(which == 0 ? a.q : a.k);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int c = lane + 32 * i;
+      if (c < DK) {
+        const T o = from_f32<T>(vals[i] * inv);
+        for (int r = 0; r < rep; ++r) dst[(((size_t)b * S + t) * H + hk * rep + r) * DK + c] = o;
+      }
+    }
+  }
+  // ---- erase gate b and decay g for the kv head, written to its value heads
+  {
+    const T* A_log = static_cast<const T*>(a.A_log);
+    const T* dtb = static_cast<const T*>(a.dt_bias);
+    const float nega = -__expf(to_f32(A_log[hk]));
+    T* bd = static_cast<T*>(a.b);
+    for (int c = lane; c < DK; c += 32) {
+      const T bo = from_f32<T>(to_f32(from_f32<T>(sigmoidf_(to_f32(P[prow + a.off_b + hk * DK + c])))) * a.erase_scale);
+      const float go = nega * softplusf_(to_f32(P[prow + a.off_f + hk * DK + c]) + to_f32(dtb[hk * DK + c]));
+      for (int r = 0; r < rep; ++r) {
+        const size_t o = (((size_t)b * S + t) * H + hk * rep + r) * DK + c;
+        bd[o] = bo;
+        a.g[o] = go;
+      }
+    }
+  }
+  // ---- v (convolution + SiLU) and the write gate w for the value heads of this kv head
+  {
+    T* vd = static_cast<T*>(a.v);
+    T* wd = static_cast<T*>(a.w);
+    for (int r = 0; r < rep; ++r) {
+      const int h = hk * rep + r;
+      for (int c = lane; c < DV; c += 32) {
+        const int col = (int)a.off_v + h * DV + c;
+        const int cch = 2 * Cqk + h * DV + c;
+        float y;
+        if (K > 0) {
+          y = cb ? to_f32(cb[cch]) : 0.f;
+          for (int j = 0; j < K; ++j)
+            y = fmaf(to_f32(cw[(size_t)cch * K + j]), tap(P, cs, b, t - (K - 1) + j, S, NP, col, cch, CC, K), y);
+          y = silu(y);
+        } else {
+          y = to_f32(P[prow + col]);
+        }
+        const size_t o = (((size_t)b * S + t) * H + h) * DV + c;
+        vd[o] = from_f32<T>(y);
+        wd[o] = from_f32<T>(sigmoidf_(to_f32(P[prow + a.off_w + h * DV + c])));
+      }
+    }
+  }
+}
+
+// new_conv[b, cch, s] = pre-convolution value at time S - (K-1) + s (from P, the old cache, or zero)
+template <typename T>
+__global__ void layer_conv_tail_kernel(gdn2_layer_front_args a) {
+  const int K = (int)a.K, S = (int)a.S, NP = (int)a.NP;
+  const int Cqk = (int)(a.HK * a.DK), Cv = (int)(a.H * a.DV), CC = 2 * Cqk + Cv;
+  const int64_t total = a.B * CC * (K - 1);
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const int sidx = (int)(idx % (K - 1));
+  const int cch = (int)((idx / (K - 1)) % CC);
+  const int64_t b = idx / ((int64_t)(K - 1) * CC);
+  const int col = cch < Cqk ? (int)a.off_q + cch : cch < 2 * Cqk ? (int)a.off_k + (cch - Cqk) : (int)a.off_v + (cch - 2 * Cqk);
+  const int tt = S - (K - 1) + sidx;
+  static_cast<T*>(a.new_conv_state)[idx] =
+      from_f32<T>(tap(static_cast<const T*>(a.proj), static_cast<const T*>(a.conv_state), b, tt, S, NP, col, cch, CC, K));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(32 * kWarps)
+layer_back_kernel(const T* __restrict__ o, const T* __restrict__ proj, const T* __restrict__ weight, T* __restrict__ out,
+                  int64_t BS, int H, int DV, int NP, int off_gate, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int64_t item = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  if (item >= BS * H) return;
+  const int h = (int)(item % H);
+  const int64_t bt = item / H;
+  const T* orow = o + (size_t)item * DV;
+  const T* grow = proj + (size_t)bt * NP + off_gate + h * DV;
+  float x[8], ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = lane + 32 * i;
+    x[i] = c < DV ? to_f32(orow[c]) : 0.f;
+    ss = fmaf(x[i], x[i], ss);
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)DV + eps);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = lane + 32 * i;
+    if (c < DV) out[(size_t)item * DV + c] = from_f32<T>(x[i] * r * to_f32(weight[c]) * silu(to_f32(grow[c])));
+  }
+}
+
+template <typename T>
+int launch_front_typed(const gdn2_layer_front_args& a, cudaStream_t st) {
+  const int64_t items = a.B * a.S * a.HK;
+  layer_front_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
+  GDN2_CUDA_TRY(cudaGetLastError());
+  if (a.K > 1 && a.new_conv_state) {
+    const int64_t total = a.B * (2 * a.HK * a.DK + a.H * a.DV) * (a.K - 1);
+    layer_conv_tail_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a);
+    GDN2_CUDA_TRY(cudaGetLastError());
+  }
+  return GDN2_OK;
+}
+
+template <typename T>
+int launch_back_typed(const void* o, const void* proj, const void* weight, void* out, int64_t BS, int H, int DV, int NP,
+                      int off_gate, float eps, cudaStream_t st) {
+  const int64_t items = BS * H;
+  layer_back_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(
+      static_cast<const T*>(o), static_cast<const T*>(proj), static_cast<const T*>(weight), static_cast<T*>(out), BS, H,
+      DV, NP, off_gate, eps);
+  GDN2_CUDA_TRY(cudaGetLastError());
+  return GDN2_OK;
+}
+
+}  // namespace
+
+}  // namespace gdn2
+
+extern "C" {
+
+int gdn2_layer_front(const gdn2_layer_front_args* args, int dtype, void* stream) {
+  using namespace gdn2;
+  if (!args) return GDN2_ERR_NULL_POINTER;
+  const gdn2_layer_front_args& a = *args;
+  if (!a.proj || !a.q || !a.k || !a.v || !a.g || !a.b || !a.w || !a.A_log || !a.dt_bias) return GDN2_ERR_NULL_POINTER;
+  if (a.B <= 0 || a.S <= 0 || a.H <= 0 || a.HK <= 0 || a.H % a.HK != 0 || a.DK <= 0 || a.DV <= 0 || a.DK > 256 ||
+      a.DV > 256 || a.K < 0 || a.K > 16 || a.NP <= 0)
+    return GDN2_ERR_BAD_SHAPE;
+  if (a.K > 0 && !a.conv_weight) return GDN2_ERR_NULL_POINTER;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case GDN2_F32: return launch_front_typed<float>(a, st);
+    case GDN2_BF16: return launch_front_typed<__nv_bfloat16>(a, st);
+    case GDN2_F16: return launch_front_typed<__half>(a, st);
+    default: return GDN2_ERR_BAD_DTYPE;
+  }
+}
+
+int gdn2_layer_back(const void* o, const void* proj, const void* norm_weight, void* out, int64_t BS, int64_t H,
+                    int64_t DV, int64_t NP, int64_t off_gate, float eps, int dtype, void* stream) {
+  using namespace gdn2;
+  if (!o || !proj || !norm_weight || !out) return GDN2_ERR_NULL_POINTER;
+  if (BS <= 0 || H <= 0 || DV <= 0 || DV > 256 || NP <= 0 || off_gate < 0) return GDN2_ERR_BAD_SHAPE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case GDN2_F32: return launch_back_typed<float>(o, proj, norm_weight, out, BS, (int)H, (int)DV, (int)NP, (int)off_gate, eps, st);
+    case GDN2_BF16: return launch_back_typed<__nv_bfloat16>(o, proj, norm_weight, out, BS, (int)H, (int)DV, (int)NP, (int)off_gate, eps, st);
+    case GDN2_F16: return launch_back_typed<__half>(o, proj, norm_weight, out, BS, (int)H, (int)DV, (int)NP, (int)off_gate, eps, st);
+    default: return GDN2_ERR_BAD_DTYPE;
+  }
+}
+
+}  // extern "C"

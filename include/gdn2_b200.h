@@ -159,6 +159,41 @@ int gdn2_prefill_static(const void* q, const void* k, const void* v, const float
                         int64_t in_batch_stride, int64_t o_batch_stride, float scale, int dtype,
                         void* stream);
 
+/*
+ * Element-wise stages of the GatedDeltaNet2 layer, fused. The caller computes ONE projection buffer
+ * proj [B, S, NP] = x W_cat^T whose columns hold, at the given offsets, the q, k, v, b, w, f and o_gate
+ * projections (q, k, b, f: HK*DK columns each; v, w, o_gate: H*DV columns each).
+ *
+ * gdn2_layer_front writes the six kernel inputs in the layout of gdn2_prefill / gdn2_decode:
+ *   q, k, b [B, S, H, DK] and v, w [B, S, H, DV] in `dtype`, g [B, S, H, DK] fp32, with
+ *   q, k = l2norm(silu(conv(proj_q,k)))  v = silu(conv(proj_v))  (depthwise causal convolution of K taps:
+ *   conv_weight [2*HK*DK + H*DV, K], conv_bias [same] or NULL, channels ordered q | k | v; K = 0 skips it),
+ *   b = erase_scale * sigmoid(proj_b)  w = sigmoid(proj_w)  g = -exp(A_log[hk]) * softplus(proj_f + dt_bias[hk]),
+ *   every kv head hk written to its H/HK value heads. conv_state [B, 2*HK*DK + H*DV, K-1] (or NULL = zeros)
+ *   supplies the columns before the first token; new_conv_state (or NULL) receives the last K-1
+ *   pre-convolution columns. A_log [HK] and dt_bias [HK, DK] are in `dtype`.
+ * gdn2_layer_back writes out [B*S, H*DV] = rmsnorm_per_head(o) * norm_weight[DV] * silu(proj_o_gate).
+ * Replaces the operator chains of _ShortConv, F.normalize, the gate expressions, repeat_interleave and
+ * _GatedRMSNorm (gdn2/attention.py:186-229, 290-297, 323-340, 352-354).
+ */
+typedef struct gdn2_layer_front_args {
+  const void* proj;            /* [B, S, NP] */
+  const void* conv_state;      /* [B, CC, K-1] or NULL */
+  const void* conv_weight;     /* [CC, K] */
+  const void* conv_bias;       /* [CC] or NULL */
+  const void* A_log;           /* [HK] */
+  const void* dt_bias;         /* [HK, DK] */
+  void* q; void* k; void* v; float* g; void* b; void* w;
+  void* new_conv_state;        /* [B, CC, K-1] or NULL */
+  int64_t B, S, H, HK, DK, DV, K, NP;
+  int64_t off_q, off_k, off_v, off_b, off_w, off_f;
+  float erase_scale;
+} gdn2_layer_front_args;
+
+int gdn2_layer_front(const gdn2_layer_front_args* args, int dtype, void* stream);
+int gdn2_layer_back(const void* o, const void* proj, const void* norm_weight, void* out, int64_t BS, int64_t H,
+                    int64_t DV, int64_t NP, int64_t off_gate, float eps, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -69,3 +69,31 @@ def test_graphed_step_equals_eager_steps():
         assert torch.equal(got, want), t
     assert torch.equal(cache_a.recurrent_state, cache_b.recurrent_state)
     assert torch.equal(cache_a.conv_state, cache_b.conv_state)
+
+
+@pytest.mark.parametrize("cached", [False, True])
+@pytest.mark.parametrize("S", [1, 2, 9])
+def test_fused_front_and_back_match_the_operator_chain(monkeypatch, cached, S):
+    """gdn2_layer_front / gdn2_layer_back against the torch operator chain they replace (float32, so the
+    only differences are fast-math exponentials): every output, the new convolution cache, the gated norm."""
+    cfg = gdn2.GatedDeltaNet2Config(hidden_size=96, num_heads=6, num_kv_heads=2, head_dim_k=32, head_dim_v=48)
+    layer = gdn2.GatedDeltaNet2(cfg).eval().to(DEV)
+    gen = torch.Generator().manual_seed(11)
+    with torch.no_grad():
+        for prm in layer.parameters():
+            prm.copy_(torch.randn(prm.shape, generator=gen).to(DEV) * 0.3)
+    x = torch.randn(2, S, 96, generator=gen).to(DEV)
+    state = torch.randn(2, 2 * 2 * 32 + 6 * 48, 3, generator=gen).to(DEV) if cached else None
+    fused = layer._front(x, state, cached=cached)
+    assert fused[7] is not None                            # the fused path ran
+    monkeypatch.setattr(type(layer), "_use_fused", lambda self, x: False)
+    chain = layer._front(x, state, cached=cached)
+    assert chain[7] is None
+    for name, a, b in zip("q k v g b w conv".split(), fused[:7], chain[:7]):
+        assert a.shape == b.shape and a.dtype == b.dtype, name
+        assert orc.rel_max_err(a.float().cpu(), b.float().cpu()) < 2e-5, name
+    o = torch.randn(2, S, 6, 48, generator=gen).to(DEV)
+    want = layer._back(x, o)
+    monkeypatch.undo()
+    got = layer._back(x, o, fused[7])
+    assert orc.rel_max_err(got.cpu(), want.cpu()) < 2e-5
