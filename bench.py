@@ -403,8 +403,8 @@ def main():
         gen = torch.Generator(device=dev).manual_seed(0)
         layer = gdn2.GatedDeltaNet2(cfg).to(torch.bfloat16).eval().to(dev)
         with torch.no_grad():
-            for prm in layer.parameters():
-                if prm.dim() == 2:
+            for name, prm in layer.named_parameters():      # projections ~ N(0, 0.02); gate parameters keep their init
+                if name.endswith("proj.weight"):
                     prm.copy_(torch.randn(prm.shape, device=dev, generator=gen) * 0.02)
         x = torch.randn(2, 4096, 2048, device=dev, generator=gen).bfloat16()
         ms_pre = time_events(lambda: layer.prefill(x), 5, 3, torch.cuda.synchronize)

@@ -135,6 +135,116 @@ layer_front_kernel(gdn2_layer_front_args a) {
   }
 }
 
+// The common shape (DK = DV = 128, four taps, 16-bit storage): lane owns channels 4 lane .. 4 lane + 3 of a
+// head, so every access to the projection buffer, the weights and the outputs is one 8- or 16-byte access
+// and a warp covers a head's 256 bytes in one instruction.
+template <typename T>
+struct alignas(4 * sizeof(T)) Vec4 { T x[4]; };
+
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&o)[4]) {
+  const Vec4<T> v = *reinterpret_cast<const Vec4<T>*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = to_f32(v.x[i]);
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&o)[4]) {
+  Vec4<T> v;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v.x[i] = from_f32<T>(o[i]);
+  *reinterpret_cast<Vec4<T>*>(p) = v;
+}
+
+// convolution + SiLU of 4 adjacent channels: projection columns col.., convolved-channel index cch..
+template <typename T>
+__device__ __forceinline__ void conv4(const T* P, const T* cs, const T* cw, const T* cb, int64_t b, int t, int S, int NP,
+                                      int col, int cch, int CC, float (&y)[4]) {
+  constexpr int K = 4;
+  float wt[4][4];                                        // [channel][tap]
+#pragma unroll
+  for (int i = 0; i < 4; ++i) load4(cw + (size_t)(cch + i) * K, wt[i]);
+  if (cb) load4(cb + cch, y);
+  else { y[0] = y[1] = y[2] = y[3] = 0.f; }
+#pragma unroll
+  for (int j = 0; j < K; ++j) {
+    const int tt = t - (K - 1) + j;
+    float x[4];
+    if (tt >= 0) {
+      load4(P + ((size_t)b * S + tt) * NP + col, x);
+    } else if (cs) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[i] = to_f32(cs[((size_t)b * CC + cch + i) * (K - 1) + (K - 1 + tt)]);
+    } else {
+      x[0] = x[1] = x[2] = x[3] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) y[i] = fmaf(wt[i][j], x[i], y[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) y[i] = silu(y[i]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(32 * kWarps)
+layer_front_d128_kernel(gdn2_layer_front_args a) {
+  constexpr int DK = 128, DV = 128;
+  const int lane = threadIdx.x & 31;
+  const int64_t item = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  if (item >= a.B * a.S * a.HK) return;
+  const int hk = (int)(item % a.HK);
+  const int64_t bt = item / a.HK;
+  const int t = (int)(bt % a.S);
+  const int64_t b = bt / a.S;
+  const int S = (int)a.S, NP = (int)a.NP, H = (int)a.H, HK = (int)a.HK;
+  const int rep = H / HK;
+  const int Cqk = HK * DK, CC = 2 * Cqk + H * DV;
+  const T* P = static_cast<const T*>(a.proj);
+  const T* cs = static_cast<const T*>(a.conv_state);
+  const T* cw = static_cast<const T*>(a.conv_weight);
+  const T* cb = static_cast<const T*>(a.conv_bias);
+  const size_t prow = ((size_t)b * S + t) * NP;
+  const int c = 4 * lane;
+  const size_t tokh = ((size_t)b * S + t) * H;
+
+  for (int which = 0; which < 2; ++which) {
+    float y[4];
+    conv4(P, cs, cw, cb, b, t, S, NP, (which == 0 ? (int)a.off_q : (int)a.off_k) + hk * DK + c, which * Cqk + hk * DK + c, CC, y);
+    const float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
+    const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) y[i] *= inv;
+    T* dst = static_cast<T*>(which == 0 ? a.q : a.k);
+    for (int r = 0; r < rep; ++r) store4(dst + (tokh + hk * rep + r) * DK + c, y);
+  }
+  {
+    float pb[4], pf[4], db[4], bo[4], go[4];
+    load4(P + prow + a.off_b + hk * DK + c, pb);
+    load4(P + prow + a.off_f + hk * DK + c, pf);
+    load4(static_cast<const T*>(a.dt_bias) + hk * DK + c, db);
+    const float nega = -__expf(to_f32(static_cast<const T*>(a.A_log)[hk]));
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      bo[i] = to_f32(from_f32<T>(sigmoidf_(pb[i]))) * a.erase_scale;
+      go[i] = nega * softplusf_(pf[i] + db[i]);
+    }
+    for (int r = 0; r < rep; ++r) {
+      const size_t o = (tokh + hk * rep + r) * DK + c;
+      store4(static_cast<T*>(a.b) + o, bo);
+      *reinterpret_cast<float4*>(a.g + o) = make_float4(go[0], go[1], go[2], go[3]);
+    }
+  }
+  for (int r = 0; r < rep; ++r) {
+    const int h = hk * rep + r;
+    float y[4], pw[4];
+    conv4(P, cs, cw, cb, b, t, S, NP, (int)a.off_v + h * DV + c, 2 * Cqk + h * DV + c, CC, y);
+    load4(P + prow + a.off_w + h * DV + c, pw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pw[i] = sigmoidf_(pw[i]);
+    store4(static_cast<T*>(a.v) + (tokh + h) * DV + c, y);
+    store4(static_cast<T*>(a.w) + (tokh + h) * DV + c, pw);
+  }
+}
+
 // new_conv[b, cch, s] = pre-convolution value at time S - (K-1) + s (from P, the old cache, or zero)
 template <typename T>
 __global__ void layer_conv_tail_kernel(gdn2_layer_front_args a) {
@@ -182,7 +292,12 @@ layer_back_kernel(const T* __restrict__ o, const T* __restrict__ proj, const T* 
 template <typename T>
 int launch_front_typed(const gdn2_layer_front_args& a, cudaStream_t st) {
   const int64_t items = a.B * a.S * a.HK;
-  layer_front_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
+  const bool aligned = a.NP % 4 == 0 && a.off_q % 4 == 0 && a.off_k % 4 == 0 && a.off_v % 4 == 0 && a.off_b % 4 == 0 &&
+                       a.off_w % 4 == 0 && a.off_f % 4 == 0;
+  if (sizeof(T) == 2 && a.DK == 128 && a.DV == 128 && a.K == 4 && aligned)
+    layer_front_d128_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
+  else
+    layer_front_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
   GDN2_CUDA_TRY(cudaGetLastError());
   if (a.K > 1 && a.new_conv_state) {
     const int64_t total = a.B * (2 * a.HK * a.DK + a.H * a.DV) * (a.K - 1);
