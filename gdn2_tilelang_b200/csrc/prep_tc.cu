@@ -35,8 +35,6 @@
 //   X (72.5 KiB): MMA1 operands, then Tm + Ai + (w*v)^T;   Y (32.25 KiB): E^T, then the WQ staging.
 // Qg = scale*q*gamma is produced in step 1 but only needed in step 5; it waits in 32 spare TMEM
 // columns (packed bf16 pairs: the two channels of one token per word).
-#include <cstdlib>
-
 #include "common.cuh"
 #include "tc_utils.cuh"
 
@@ -568,10 +566,7 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
                    const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
                    cudaStream_t st) {
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
-  size_t smem = sizeof(PrepTcSmem) + 128;
-#ifdef GDN2_SCAN_TIMING
-  if (getenv("GDN2_EXP_ONE_BLOCK")) smem = 120 * 1024;    // experiment: one resident block per SM
-#endif
+  const size_t smem = sizeof(PrepTcSmem) + 128;
   dim3 grid(S / BS, B * H);
   using bf16 = __nv_bfloat16;
   auto launch = [&](auto kern) -> int {
