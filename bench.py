@@ -257,6 +257,7 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG", "WARN")      # keeps NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     B, S, H, DK, DV = (CFG[x] for x in ("B", "S", "H", "DK", "DV"))
     if args.profile_case:
