@@ -131,7 +131,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
                const __nv_bfloat16* __restrict__ b, const __nv_bfloat16* __restrict__ w, WsPtrs P, int S, int H,
-               int64_t in_bs, float scale, uint32_t* status) {
+               int64_t in_bs, float scale, int a_sm_count, uint32_t* status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   PrepTcSmem& s = *reinterpret_cast<PrepTcSmem*>(smem_raw);
   const int NC = S / BS;
@@ -314,6 +314,17 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     tc::mma_commit_warp(&s.bar_m1);
   }
   PTICK(3);
+  // The block that will most likely run next in this slot (two resident blocks per SM, dispatched in
+  // linear order) starts with a cold read of its g tile: pull those 256 lines towards L2 now.
+  {
+    const int64_t nxt = (int64_t)blockIdx.y * gridDim.x + blockIdx.x + 2 * (int64_t)a_sm_count;
+    if (nxt < (int64_t)gridDim.x * gridDim.y) {
+      const int nb_ = (int)(nxt / gridDim.x), nn_ = (int)(nxt % gridDim.x);
+      const size_t r0n = ((size_t)(nb_ / H) * in_bs + (size_t)nn_ * BS) * H + (nb_ % H);
+      const char* ptr = reinterpret_cast<const char*>(g + r0n * D + (size_t)(tid >> 2) * rstride) + (tid & 3) * 128;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
+    }
+  }
   // value side: raw loads issued while the tensor core works
   // z = w*v of this thread's two value channels waits in TMEM columns [192,256) of its own lane until the
   // MMA1 operands are dead and (w*v)^T can take their place in shared memory
@@ -573,7 +584,7 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
     GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, kThreads, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
                                        static_cast<const bf16*>(v), g, static_cast<const bf16*>(b),
-                                       static_cast<const bf16*>(w), P, S, H, in_bs, scale, device_status_word());
+                                       static_cast<const bf16*>(w), P, S, H, in_bs, scale, device_sm_count(), device_status_word());
     GDN2_CUDA_TRY(cudaGetLastError());
     return GDN2_OK;
   };
