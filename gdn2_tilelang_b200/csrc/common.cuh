@@ -31,9 +31,9 @@ template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return
 // the low 13 mantissa bits, i.e. truncates; rounding operands first removes that bias, which
 // otherwise shows up as a systematic ~1e-3 shrink of products of two tf32 operands.
 __device__ __forceinline__ float tf32_rn(float x) {
-  uint32_t u;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
-  return __uint_as_float(u);
+  // round to nearest, ties away from zero, on the bit pattern: add half a tf32 unit, drop the low 13 bits
+  // (a carry into the exponent is the correct rounding; infinities and NaNs do not occur on these paths)
+  return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xffffe000u);
 }
 
 // ---------------------------------------------------------------- workspace layout
