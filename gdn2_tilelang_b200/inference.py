@@ -92,9 +92,9 @@ def gdn2_prefill_from_host(q, k, v, g, b, w, state=None, scale=None, config: GDN
     """``gdn2_prefill`` for prompts whose tensors live in host memory (pinned, for the copies to be
     asynchronous). No counterpart in the reference, whose callers upload first and call ``gdn2_prefill``.
 
-    The batch is streamed one sequence at a time through double-buffered device inputs: the upload of
-    sequence i + 1 and the download of the outputs of sequence i - 1 run on their own CUDA streams while
-    sequence i is computed, so the call costs about as much as its host-to-device traffic alone instead
+    The batch is streamed one sequence (long sequences: a quarter of one) at a time through double-buffered
+    device inputs: the upload of unit i + 1 and the download of the outputs of unit i - 1 run on their own
+    CUDA streams while unit i is computed, so the call costs about as much as its host-to-device traffic alone instead
     of upload + kernels + download one after the other. Sequences are independent, so the results are
     those of one ``gdn2_prefill`` over the whole batch.
 
@@ -124,39 +124,48 @@ def gdn2_prefill_from_host(q, k, v, g, b, w, state=None, scale=None, config: GDN
     with torch.cuda.device(dev):
         main = torch.cuda.current_stream(dev)
         up, down = _transfer_streams(dev)
-        slots = [[torch.empty((1,) + tuple(t.shape[1:]), dtype=t.dtype, device=dev) for t in ins] for _ in range(2)]
+        # pipeline units: (sequence, token range), ranges cut at multiples of the chunk size so that the
+        # state chains from one unit of a sequence to the next; long sequences are cut so that the last
+        # unit's compute and download, which nothing overlaps, are short
+        BS = config.chunk_size
+        pieces = max(1, min(4, S // (64 * BS)))
+        step = -(-S // pieces)
+        step = -(-step // BS) * BS
+        bounds = [(lo, min(S, lo + step)) for lo in range(0, S, step)]
+        units = [(i, lo, hi) for i in range(B) for lo, hi in bounds]
+        U = len(units)
+        slots = [[torch.empty((1, step) + tuple(t.shape[2:]), dtype=t.dtype, device=dev) for t in ins] for _ in range(2)]
         state_out = torch.empty(B, H, DK, DV, dtype=config.state_dtype, device=dev)
         if state is not None:
             state_out.copy_(state, non_blocking=True)
-        uploaded = [torch.cuda.Event() for _ in range(B)]
-        consumed = [torch.cuda.Event() for _ in range(B)]      # sequence i's input slot may be overwritten
-        computed = [torch.cuda.Event() for _ in range(B)]
+        uploaded = [torch.cuda.Event() for _ in range(U)]
+        consumed = [torch.cuda.Event() for _ in range(U)]      # unit u's input slot may be overwritten
         outputs = []                                            # device outputs stay alive until the call ends
         up.wait_stream(main)                                    # the buffers above exist before anything lands in them
         down.wait_stream(main)
 
-        def upload(i):
+        def upload(u):
+            i, lo, hi = units[u]
             with torch.cuda.stream(up):
-                if i >= 2:
-                    up.wait_event(consumed[i - 2])
-                for d, h in zip(slots[i & 1], ins):
-                    d.copy_(h[i:i + 1], non_blocking=True)
-                uploaded[i].record(up)
+                if u >= 2:
+                    up.wait_event(consumed[u - 2])
+                for d, h in zip(slots[u & 1], ins):
+                    d[:, :hi - lo].copy_(h[i:i + 1, lo:hi], non_blocking=True)
+                uploaded[u].record(up)
 
         upload(0)
-        for i in range(B):
-            if i + 1 < B:
-                upload(i + 1)
-            main.wait_event(uploaded[i])
-            st_in = state_out[i:i + 1] if state is not None else None
-            o_i, st_i = gdn2_prefill(*slots[i & 1], st_in, scale, config)
-            outputs.append(o_i)
-            state_out[i:i + 1].copy_(st_i)
-            consumed[i].record(main)
-            computed[i].record(main)
+        for u, (i, lo, hi) in enumerate(units):
+            if u + 1 < U:
+                upload(u + 1)
+            main.wait_event(uploaded[u])
+            st_in = state_out[i:i + 1] if (state is not None or lo > 0) else None
+            o_u, st_u = gdn2_prefill(*(t[:, :hi - lo] for t in slots[u & 1]), st_in, scale, config)
+            outputs.append(o_u)
+            state_out[i:i + 1].copy_(st_u)
+            consumed[u].record(main)
             with torch.cuda.stream(down):
-                down.wait_event(computed[i])
-                out[i:i + 1].copy_(o_i, non_blocking=True)
+                down.wait_event(consumed[u])
+                out[i:i + 1, lo:hi].copy_(o_u, non_blocking=True)
         main.wait_stream(down)
         main.wait_stream(up)
     return out, state_out

@@ -255,6 +255,17 @@ def test_prefill_from_host_streams_sequences(K):
     K.check_device_status()
 
 
+def test_prefill_from_host_cuts_long_sequences(K):
+    """Sequences of 8192+ tokens travel in several units with the state chained between them."""
+    B, S, H, D = 2, 64 * 64 * 2 + 21, 2, 128
+    dev, _ = bf16_inputs(B, S, H, D, D, seed=16)
+    o_ref, s_ref = gdn2.gdn2_prefill(*dev)
+    o, s = gdn2.gdn2_prefill_from_host(*[t.cpu().pin_memory() for t in dev])
+    torch.cuda.synchronize()
+    assert torch.equal(o, o_ref.cpu()) and torch.equal(s, s_ref)
+    K.check_device_status()
+
+
 @pytest.mark.parametrize("D", [64, 128])
 def test_fp16_inputs_prefill_and_decode(K, D):
     """fp16 tensors (the third dtype the reference accepts) go through the SIMT family with fp32 records."""
