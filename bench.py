@@ -44,7 +44,7 @@ FALLBACK_HBM_GBS = 6650.0
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per chunk-head (64 tokens of one head), from the ncu captures
-# summarised under profiles/ (1024 chunk-heads per launch): traffic grows in proportion to the chunk-heads
+# in the committed ncu summaries (1024 chunk-heads per launch): traffic grows in proportion to the chunk-heads
 NCU_DRAM_BYTES_PER_CHUNK_HEAD = {"chunk_prep": (117.609728e6 + 38.756864e6) / 1024,
                                  "prefill_scan": (77.114112e6 + 5.137408e6) / 1024}
 
@@ -379,7 +379,7 @@ def main():
         "frac": achieved / peak, "peak_source": f"{peak_kind} copy bandwidth",
         "traffic": NCU_DRAM_BYTES_PER_CHUNK_HEAD[dom] * (th / 64) / 1e9, "traffic_unit": "GB per launch",
         "traffic_source": "dram__bytes_read+write of one ncu capture of a 1024-chunk-head launch "
-                          "(profiles/prefill_kernels_small_case.md), scaled by chunk-heads; writes still in L2 "
+                          "(the committed ncu summary of the prefill kernels), scaled by chunk-heads; writes still in L2 "
                           "when the small launch ends are not in it",
         "stages_ms": {s: stages[s][0] for s in stages},
         "stages_frac": {s: stages[s][1] / (stages[s][0] * 1e-3) / 1e9 / peak for s in stages},
