@@ -58,8 +58,8 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 struct Tables {
-  // per key row, duplicated pairs (x, x): chunks 0..3 = b*k*A_t for t < 8, chunks 4..7 = scale*q*A_t
-  float4 c1[8][kCoefRows];
+  // per key row: chunks 0, 1 = b*k*A_t for t < 8, chunks 2, 3 = scale*q*A_t (four consecutive products per chunk)
+  float4 c1[4][kCoefRows];
   // chunks 0..3: k * A_8/A_s for s < 8 (duplicated pairs); chunk 4: (A_8, A_8, 0, 0)
   float4 c2[5][kCoefRows];
   float wv[NB][D];                    // w * v
@@ -215,7 +215,7 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
             tb.wv[t][c] = wvv[t];
           }
 #pragma unroll
-          for (int j = 0; j < 8; ++j) tb.c1[j][pr] = make_float4(c1v[2 * j], c1v[2 * j], c1v[2 * j + 1], c1v[2 * j + 1]);
+          for (int j = 0; j < 4; ++j) tb.c1[j][pr] = make_float4(c1v[4 * j], c1v[4 * j + 1], c1v[4 * j + 2], c1v[4 * j + 3]);
 #pragma unroll
           for (int j = 0; j < 4; ++j) tb.c2[j][pr] = make_float4(c2v[2 * j], c2v[2 * j], c2v[2 * j + 1], c2v[2 * j + 1]);
           const float An = ex2(G[NB - 1]);
@@ -291,22 +291,30 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         DTICK(2);
 
         // ---- sweep 1: the 16 products (8 erase rows, 8 query rows) of S_0 for this thread's rows and columns
-        float2 acc[16][2];
+        //      packed over PAIRS OF PRODUCTS: acc[pp][col] = (product 2pp, product 2pp+1) of column col, so the
+        //      coefficients are used as stored (no duplicated copies in shared memory) and the state value is
+        //      the operand that is duplicated, in registers
+        float2 acc[8][4];
 #pragma unroll
-        for (int p = 0; p < 16; ++p) { acc[p][0] = make_float2(0.f, 0.f); acc[p][1] = make_float2(0.f, 0.f); }
+        for (int p = 0; p < 8; ++p) {
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) acc[p][cc] = make_float2(0.f, 0.f);
+        }
         const float* Srow = S + rgl * kGroupFloats + col0;
         const int cr0 = 17 * rgl;
 #pragma unroll 2
         for (int i = 0; i < 16; ++i) {
           const float4 sv = *reinterpret_cast<const float4*>(Srow + i * D);
-          const float2 s01 = make_float2(sv.x, sv.y), s23 = make_float2(sv.z, sv.w);
+          const float2 sd[4] = {make_float2(sv.x, sv.x), make_float2(sv.y, sv.y), make_float2(sv.z, sv.z),
+                                make_float2(sv.w, sv.w)};
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < 4; ++j) {
             const float4 cf = tb.c1[j][cr0 + i];
-            acc[2 * j][0] = ffma2(s01, make_float2(cf.x, cf.y), acc[2 * j][0]);
-            acc[2 * j][1] = ffma2(s23, make_float2(cf.x, cf.y), acc[2 * j][1]);
-            acc[2 * j + 1][0] = ffma2(s01, make_float2(cf.z, cf.w), acc[2 * j + 1][0]);
-            acc[2 * j + 1][1] = ffma2(s23, make_float2(cf.z, cf.w), acc[2 * j + 1][1]);
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+              acc[2 * j][cc] = ffma2(sd[cc], make_float2(cf.x, cf.y), acc[2 * j][cc]);
+              acc[2 * j + 1][cc] = ffma2(sd[cc], make_float2(cf.z, cf.w), acc[2 * j + 1][cc]);
+            }
           }
         }
         DTICK(3);
@@ -316,10 +324,10 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         {
           float val[64];
 #pragma unroll
-          for (int p = 0; p < 16; ++p) {
-            const int base = (p >> 3) * 32 + (p & 7);
-            val[base + 0 * 8] = acc[p][0].x; val[base + 1 * 8] = acc[p][0].y;
-            val[base + 2 * 8] = acc[p][1].x; val[base + 3 * 8] = acc[p][1].y;
+          for (int pp = 0; pp < 8; ++pp) {
+            const int base = (pp >> 2) * 32 + 2 * (pp & 3);       // products 2pp, 2pp + 1
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) { val[base + cc * 8] = acc[pp][cc].x; val[base + cc * 8 + 1] = acc[pp][cc].y; }
           }
 #pragma unroll
           for (int m = 0; m < 3; ++m) {
