@@ -19,8 +19,8 @@
 //   * eight sweep warps do the two sweeps in place: warp w owns value columns 16w .. 16w+15, lane
 //     (rgl = lane >> 2, cq = lane & 3) columns 16w + 4cq .. +3 of key rows 16 rgl .. 16 rgl + 15.
 // Hand-offs are mbarriers with bounded waits.
-// Per-row coefficients sit in shared memory as duplicated pairs so the packed f32x2 FMAs take them
-// as they are.
+// Per-row coefficients sit in shared memory once; the packed f32x2 FMAs pair them over products (sweep 1)
+// or tokens (sweep 2), so no duplicated copies are stored or fetched.
 #include "common.cuh"
 #include "tc_utils.cuh"
 
@@ -60,8 +60,9 @@ __device__ __forceinline__ float ex2(float x) {
 struct Tables {
   // per key row: chunks 0, 1 = b*k*A_t for t < 8, chunks 2, 3 = scale*q*A_t (four consecutive products per chunk)
   float4 c1[4][kCoefRows];
-  // chunks 0..3: k * A_8/A_s for s < 8 (duplicated pairs); chunk 4: (A_8, A_8, 0, 0)
-  float4 c2[5][kCoefRows];
+  // per key row: k * A_8/A_s for s = 0..3 (chunk 0) and s = 4..7 (chunk 1); A_8 itself
+  float4 c2[2][kCoefRows];
+  float gam[kCoefRows];
   float wv[NB][D];                    // w * v
   float akk[NB][NB];                  // strictly lower
   float aqk[NB][NB];                  // lower incl. diagonal, scale folded in
@@ -217,9 +218,9 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
 #pragma unroll
           for (int j = 0; j < 4; ++j) tb.c1[j][pr] = make_float4(c1v[4 * j], c1v[4 * j + 1], c1v[4 * j + 2], c1v[4 * j + 3]);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) tb.c2[j][pr] = make_float4(c2v[2 * j], c2v[2 * j], c2v[2 * j + 1], c2v[2 * j + 1]);
+          for (int j = 0; j < 2; ++j) tb.c2[j][pr] = make_float4(c2v[4 * j], c2v[4 * j + 1], c2v[4 * j + 2], c2v[4 * j + 3]);
           const float An = ex2(G[NB - 1]);
-          tb.c2[4][pr] = make_float4(An, An, 0.f, 0.f);
+          tb.gam[pr] = An;
         }
         // Slot (t, sx) holds the Akk[t, sx] term for sx < t and the Aqk[sx, t] term for sx >= t (the upper
         // triangle is free). Summing over the warp's 32 channels: each step halves what a lane keeps.
@@ -388,7 +389,8 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         }
         DTICK(5);
         // gather u of the thread's four columns from the lanes that share cq (rgl bits 0 and 1 = lane bits 2, 3)
-        float2 u01[8], u23[8];
+        //      and pair them over tokens: up[tp][c] = (u_{2tp}, u_{2tp+1}) of column col0 + c
+        float2 up[4][4];
 #pragma unroll
         for (int t = 0; t < NB; ++t) {
           const float o4 = __shfl_xor_sync(0xffffffffu, u[t], 4);      // column (rgl & 3) ^ 1
@@ -396,8 +398,12 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
           const float od = (rgl & 1) ? u[t] : o4;                      // odd column of my pair
           const float e2 = __shfl_xor_sync(0xffffffffu, e, 8);         // the other pair
           const float od2 = __shfl_xor_sync(0xffffffffu, od, 8);
-          if (rgl & 2) { u01[t] = make_float2(e2, od2); u23[t] = make_float2(e, od); }
-          else { u01[t] = make_float2(e, od); u23[t] = make_float2(e2, od2); }
+          const float uc[4] = {(rgl & 2) ? e2 : e, (rgl & 2) ? od2 : od, (rgl & 2) ? e : e2, (rgl & 2) ? od : od2};
+#pragma unroll
+          for (int cc = 0; cc < 4; ++cc) {
+            if (t & 1) up[t >> 1][cc].y = uc[cc];
+            else up[t >> 1][cc].x = uc[cc];
+          }
         }
         DTICK(6);
         // ---- sweep 2: S <- A_8 * S + sum_s (k_s A_8/A_s) u_s^T, in place
@@ -405,19 +411,20 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
           float* Sw = S + rgl * kGroupFloats + col0;
 #pragma unroll 4
           for (int i = 0; i < 16; ++i) {
+            // per column a dot product over the 8 tokens, packed over token pairs (coefficients as stored)
             const float4 sv = *reinterpret_cast<const float4*>(Sw + i * D);
-            const float4 ga = tb.c2[4][cr0 + i];
-            float2 n01 = fmul2(make_float2(ga.x, ga.y), make_float2(sv.x, sv.y));
-            float2 n23 = fmul2(make_float2(ga.x, ga.y), make_float2(sv.z, sv.w));
+            const float4 ka = tb.c2[0][cr0 + i], kb = tb.c2[1][cr0 + i];
+            const float ga = tb.gam[cr0 + i];
+            const float2 k01 = make_float2(ka.x, ka.y), k23 = make_float2(ka.z, ka.w);
+            const float2 k45 = make_float2(kb.x, kb.y), k67 = make_float2(kb.z, kb.w);
+            const float svv[4] = {sv.x, sv.y, sv.z, sv.w};
+            float nn[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float4 cf = tb.c2[j][cr0 + i];
-              n01 = ffma2(make_float2(cf.x, cf.y), u01[2 * j], n01);
-              n23 = ffma2(make_float2(cf.x, cf.y), u23[2 * j], n23);
-              n01 = ffma2(make_float2(cf.z, cf.w), u01[2 * j + 1], n01);
-              n23 = ffma2(make_float2(cf.z, cf.w), u23[2 * j + 1], n23);
+            for (int cc = 0; cc < 4; ++cc) {
+              const float2 d = ffma2(k01, up[0][cc], ffma2(k23, up[1][cc], ffma2(k45, up[2][cc], fmul2(k67, up[3][cc]))));
+              nn[cc] = fmaf(ga, svv[cc], d.x + d.y);
             }
-            *reinterpret_cast<float4*>(Sw + i * D) = make_float4(n01.x, n01.y, n23.x, n23.y);
+            *reinterpret_cast<float4*>(Sw + i * D) = make_float4(nn[0], nn[1], nn[2], nn[3]);
           }
         }
         mbar_arrive(&s.tab_empty[step & 1]);             // this step's tables may be overwritten
