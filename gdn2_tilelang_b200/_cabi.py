@@ -264,7 +264,7 @@ class NativeKernels:
                 state_ptr = states[i].data_ptr()
             if side is not None:
                 main.wait_stream(side)
-        self.launches += (4 if p == PATH_TCGEN05 else 2) * nseg
+        self.launches += (3 if p == PATH_TCGEN05 else 2) * nseg
         return out, final_state, hs
 
     def chunk_output(self, q, k, v, g, b, w, scale: float, chunk_states, path=None):

@@ -288,6 +288,7 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         ok = tc::mbar_wait(&s.tab_full[step & 1], (step >> 1) & 1, &s.abort_flag, status, kWaitTab);
         DTICK(1);
         if (ok && t0 == 0) ok = tc::mbar_wait(&s.tile_full[buf], (it >> 1) & 1, &s.abort_flag, status, kWaitTile);
+        ok = __all_sync(0xffffffffu, ok);                // the warp leaves together: what follows uses full-warp shuffles
         if (!ok) break;
         DTICK(2);
 

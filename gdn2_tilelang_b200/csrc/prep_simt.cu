@@ -171,11 +171,6 @@ prep_simt_flagged_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, c
   }
 }
 
-__global__ void collect_flagged_kernel(int* flags, int nch) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < nch && flags[i] != 0) flags[nch + atomicAdd(&flags[2 * nch], 1)] = i;
-}
-
 template <typename TIn, typename TW>
 int launch_typed(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
                  const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
@@ -187,9 +182,8 @@ int launch_typed(const void* q, const void* k, const void* v, const float* g, co
   if (only_flagged) {
     auto kern = prep_simt_flagged_kernel<TIn, TW>;
     GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    // the tensor-core kernel has appended the flagged chunks to the list behind the flags
     const int nch = (int)L.nch;
-    GDN2_CUDA_TRY(cudaMemsetAsync(P.flags + 2 * (size_t)nch, 0, sizeof(int), st));
-    collect_flagged_kernel<<<(nch + 255) / 256, 256, 0, st>>>(P.flags, nch);
     kern<<<nch < 296 ? nch : 296, 256, smem, st>>>(tq, tk, tv, g, tb, tw, L, P, S, H, in_bs, scale);
   } else {
     auto kern = prep_simt_kernel<TIn, TW>;

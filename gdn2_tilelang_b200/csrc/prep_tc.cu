@@ -199,7 +199,13 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   }
   PTICK(0);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
-  if (tid == 0) P.flags[ch] = any_bad ? 1 : 0;
+  if (tid == 0) {
+    P.flags[ch] = any_bad ? 1 : 0;
+    if (any_bad) {                    // append to the compacted list the exact kernel walks (count zeroed by the launcher)
+      const int64_t nch_all = (int64_t)gridDim.x * gridDim.y;
+      P.flags[nch_all + atomicAdd(&P.flags[2 * nch_all], 1)] = (int)ch;
+    }
+  }
   if (any_bad) return;              // the exact kernel redoes this chunk; nothing allocated yet
   {
     const float2 f0 = *reinterpret_cast<const float2*>(&s.pre[0][0][c0]), t0_ = *reinterpret_cast<const float2*>(&s.pre[0][1][c0]);
@@ -580,6 +586,7 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
   const size_t smem = sizeof(PrepTcSmem) + 128;
   dim3 grid(S / BS, B * H);
   using bf16 = __nv_bfloat16;
+  GDN2_CUDA_TRY(cudaMemsetAsync(P.flags + 2 * (size_t)L.nch, 0, sizeof(int), st));   // length of the flagged list
   auto launch = [&](auto kern) -> int {
     GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, kThreads, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
