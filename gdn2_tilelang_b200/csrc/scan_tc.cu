@@ -88,6 +88,12 @@ enum : uint32_t {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc::smem_u32(bar)) : "memory");
 }
+// one arrival per warp: every lane has fenced its tensor-memory traffic, the warp converges, lane 0 arrives
+// (256 single-thread arrivals on one shared-memory word cost the hand-off several hundred cycles)
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
 // barrier among the 128 output threads only (hardware barrier 2)
 __device__ __forceinline__ void output_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
@@ -128,7 +134,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       tc::mbar_init(&s.bar_wq[i], 1); tc::mbar_init(&s.bar_kgt[i], 1); tc::mbar_init(&s.bar_ut[i], 1);
     }
     tc::mbar_init(&s.bar_aqk, 1); tc::mbar_init(&s.bar_m1, 1); tc::mbar_init(&s.bar_m3, 1); tc::mbar_init(&s.bar_m2, 1);
-    tc::mbar_init(&s.bar_sb, kComputeThreads + kOutputThreads); tc::mbar_init(&s.bar_un, kComputeThreads);
+    tc::mbar_init(&s.bar_sb, (kComputeThreads + kOutputThreads) / 32); tc::mbar_init(&s.bar_un, kComputeThreads / 32);   // one arrival per warp
     s.abort_flag = 0;
     tc::mbar_init_fence();
   }
@@ -233,7 +239,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     const int dv = lq * 32 + lane;
     const int otid = tid - (kComputeThreads + 64);
     const uint32_t t_o = tc::tmem_addr(tm, lq * 32, kColO);
-    mbar_arrive(&s.bar_sb);                                // nothing to read out before chunk 0
+    warp_arrive(&s.bar_sb, lane);                          // nothing to read out before chunk 0
     for (int n = 0; n < NC; ++n) {
       float ov[64];
       tc::mbar_wait(&s.bar_m2, n & 1, &s.abort_flag, status, kWaitM2);
@@ -242,7 +248,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       tc::tmem_ld32(t_o + 32, *reinterpret_cast<float(*)[32]>(&ov[32]));
       tc::tmem_ld_wait();
       tc::tc_fence_before_sync();
-      if (n + 1 < NC) mbar_arrive(&s.bar_sb);              // the accumulator may be overwritten by the next MMA1
+      if (n + 1 < NC) warp_arrive(&s.bar_sb, lane);        // the accumulator may be overwritten by the next MMA1
       output_sync();                                       // the previous chunk's rows have left the staging buffer
 #pragma unroll
       for (int i = 0; i < 64; ++i) s.ostage[i * D + dv] = __float2bfloat16_rn(ov[i]);
@@ -284,7 +290,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       tc::tmem_st_wait();
     }
     tc::tc_fence_before_sync();
-    mbar_arrive(&s.bar_sb);
+    warp_arrive(&s.bar_sb, lane);
 
     TDECL;
     for (int n = 0; n < NC; ++n) {
@@ -320,7 +326,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         tc::tmem_st16(t_lane + kColUn16 + tokp / 2, p16);
         tc::tmem_st_wait();
         tc::tc_fence_before_sync();
-        mbar_arrive(&s.bar_un);
+        warp_arrive(&s.bar_un, lane);
         TICK(4);
       }
 
@@ -355,7 +361,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         if (more) {
           tc::tmem_st_wait();
           tc::tc_fence_before_sync();
-          mbar_arrive(&s.bar_sb);
+          warp_arrive(&s.bar_sb, lane);
         }
         TICK(8);
         float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
