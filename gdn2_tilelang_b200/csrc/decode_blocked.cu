@@ -84,6 +84,11 @@ constexpr int kAllThreads = kSweepThreads + kTableThreads + 32;   // + warp 12: 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc::smem_u32(bar)) : "memory");
 }
+// one arrival per warp: the lanes' writes are ordered before lane 0's arrival by the warp barrier
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void table_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 // the same barrier fused with an OR over one predicate per thread: every table thread gets the same answer
 __device__ __forceinline__ bool table_sync_or(bool pred) {
@@ -127,9 +132,9 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   if (tid == 0) {
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&s.tile_full[i], 1);
-      tc::mbar_init(&s.tile_done[i], kSweepThreads);
-      tc::mbar_init(&s.tab_full[i], kTableThreads);
-      tc::mbar_init(&s.tab_empty[i], kSweepThreads);
+      tc::mbar_init(&s.tile_done[i], kSweepThreads / 32);     // one arrival per warp
+      tc::mbar_init(&s.tab_full[i], kTableThreads / 32);
+      tc::mbar_init(&s.tab_empty[i], kSweepThreads / 32);
     }
     s.abort_flag = 0;
     tc::mbar_init_fence();
@@ -264,7 +269,7 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
           if (sx < t) tb.akk[t][sx] = sum;               // Akk[t, sx]
           else tb.aqk[sx][t] = sum;                      // slot (t, sx) with sx >= t holds Aqk[sx, t]
         }
-        mbar_arrive(&s.tab_full[step & 1]);
+        warp_arrive(&s.tab_full[step & 1], lane);
         DTICK(4);
       }
       if (s.abort_flag) break;
@@ -428,12 +433,12 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
             *reinterpret_cast<float4*>(Sw + i * D) = make_float4(nn[0], nn[1], nn[2], nn[3]);
           }
         }
-        mbar_arrive(&s.tab_empty[step & 1]);             // this step's tables may be overwritten
+        warp_arrive(&s.tab_empty[step & 1], lane);       // this step's tables may be overwritten
         DTICK(7);
       }
       if (!ok) break;
       tc::fence_async_smem();                            // the tile's new values are visible to the bulk store
-      mbar_arrive(&s.tile_done[buf]);
+      warp_arrive(&s.tile_done[buf], lane);
     }
     if (wid == 0) DFLUSH(16);
   }
