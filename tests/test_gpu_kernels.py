@@ -255,6 +255,25 @@ def test_prefill_from_host_streams_sequences(K):
     K.check_device_status()
 
 
+def test_prefill_on_a_side_stream_matches_default_stream(K):
+    """The calls launch on the caller's current stream (and, for long prompts, hand the scan of one sequence
+    segment to an internal stream): results on a user stream equal those on the default stream, and work
+    queued behind the call on that stream sees the finished outputs."""
+    B, S, H, D = 2, 64 * 40 + 9, 4, 128
+    dev, _ = bf16_inputs(B, S, H, D, D, seed=23)
+    o_ref, s_ref = gdn2.gdn2_prefill(*dev)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        o, st = gdn2.gdn2_prefill(*dev)
+        total = o.float().sum() + st.sum()                 # consumer queued right behind the call
+    side.synchronize()
+    assert torch.equal(o, o_ref) and torch.equal(st, s_ref)
+    assert torch.equal(total, o_ref.float().sum() + s_ref.sum())
+    K.check_device_status()
+
+
 def test_prefill_from_host_cuts_long_sequences(K):
     """Sequences of 8192+ tokens travel in several units with the state chained between them."""
     B, S, H, D = 2, 64 * 64 * 2 + 21, 2, 128
