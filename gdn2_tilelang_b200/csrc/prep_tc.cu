@@ -20,7 +20,7 @@
 //     Left of the diagonal both exponents are <= 0. ON the diagonal sub-block the key factor is
 //     >= 1 but bounded by the decay span of 16 tokens; the reference evaluates those blocks
 //     pairwise on CUDA cores (intra_diag_kernel) -- here they ride the same tensor-core product
-//     as long as every sub-block's span stays below 2^64. A chunk that decays faster is flagged in
+//     as long as every sub-block's span stays below 2^96. A chunk that decays faster is flagged in
 //     the workspace and redone exactly by the SIMT family's kernel.
 //  2. MMA1 (bf16, M = 128: rows 0..63 = b*k rows, 64..127 = q rows, all scaled by their own ref):
 //     four products A * B_i^T, B_i = key rows s < 16(i+1) scaled to ref_i, N = 16(i+1).
@@ -48,7 +48,7 @@ constexpr int kThreads = 256;
 constexpr int A_PAD = 129;        // rows per K chunk of a 128-row bf16 image, +1 pad row: kills bank conflicts
 constexpr int B_PAD = 161;        // 160 key rows (16 + 32 + 48 + 64) + 1 pad row
 constexpr int TM_STRIDE = 68;     // floats per Tm row (row-major, padded against bank conflicts)
-constexpr float kMaxSpanLog2 = 64.f;
+constexpr float kMaxSpanLog2 = 96.f;     // 2^96 keeps every scaled operand inside bf16 and fp32 range (|k|, |q| << 2^30)
 constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kZCol = 192;   // TMEM columns [192,256): w*v of the thread's value channel (fp32)
 constexpr uint32_t kQgCol = 160;  // TMEM columns [160,192): packed Qg of the thread's channel

@@ -306,6 +306,19 @@ def test_fp16_inputs_prefill_and_decode(K, D):
     assert orc.rel_fro_err(st.cpu(), s2) < 1e-4
 
 
+@pytest.mark.parametrize("decay_scale", [1.5, 2.5, 3.0, 3.5, 5.0])
+def test_decay_spans_around_the_tensor_core_limit(K, decay_scale):
+    """16-token decay spans from well inside the factorised range (2^40) through its limit (2^96) to chunks
+    that are flagged and redone exactly: all within the bf16 bounds against the recurrence."""
+    dev, host = bf16_inputs(2, 64 * 6, 3, 128, 128, seed=19, gate="softplus", decay_scale=decay_scale)
+    o_ref, s_ref = orc.recurrence(*host)
+    o, s = gdn2.gdn2_attention(*dev, output_final_state=True)
+    assert torch.isfinite(o).all() and torch.isfinite(s).all()
+    assert orc.max_abs_err(o.float().cpu(), o_ref) < O_ABS_BF16
+    assert orc.rel_fro_err(s.cpu(), s_ref) < 2e-3          # states this decayed are a few tokens of history only
+    K.check_device_status()
+
+
 def test_fast_decay_d128_bf16_takes_exact_path(K):
     dev, host = bf16_inputs(1, 128, 2, 128, 128, seed=17, gate="softplus", decay_scale=30.0)
     o_ref, s_ref = orc.recurrence(*host)
