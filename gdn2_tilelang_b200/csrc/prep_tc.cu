@@ -15,13 +15,14 @@
 // round-trips through HBM (G, Akk, Ai) never leave the SM:
 //
 //  1. G = log2(e) * cumsum(g) as a running sum. The overflow-safe factorisation of the reference
-//     (gdn2/forward.py:266-270): rows of sub-block i (16 tokens) are scaled by 2^(G_r - ref_i),
-//     ref_i = G at the sub-block's first row, and paired with key rows scaled by 2^(ref_i - G_s).
-//     Left of the diagonal both exponents are <= 0. ON the diagonal sub-block the key factor is
-//     >= 1 but bounded by the decay span of 16 tokens; the reference evaluates those blocks
-//     pairwise on CUDA cores (intra_diag_kernel) -- here they ride the same tensor-core product
-//     as long as every sub-block's span stays below 2^96. A chunk that decays faster is flagged in
-//     the workspace and redone exactly by the SIMT family's kernel.
+//     (gdn2/forward.py:266-270): rows of sub-block i (16 tokens) are scaled by 2^(G_r - ref_i) and paired
+//     with key rows scaled by 2^(ref_i - G_s). Here ref_i is G at the MIDDLE row of the sub-block. Against
+//     keys of earlier sub-blocks the key exponent is <= 0 and the row factor is bounded by the decay of half
+//     a sub-block; ON the diagonal sub-block both factors are bounded by half its span. The reference
+//     evaluates the diagonal blocks pairwise on CUDA cores (intra_diag_kernel) -- here they ride the same
+//     tensor-core product as long as each half of every sub-block decays by less than 2^96 (every product
+//     2^(G_r - G_s), r >= s, is then formed from two factors inside bf16 range). A chunk that decays faster
+//     is flagged in the workspace and redone exactly by the SIMT family's kernel.
 //  2. MMA1 (bf16, M = 128: rows 0..63 = b*k rows, 64..127 = q rows, all scaled by their own ref):
 //     four products A * B_i^T, B_i = key rows s < 16(i+1) scaled to ref_i, N = 16(i+1).
 //     Row block i of product i gives Tm (strictly lower) and Aqk (lower incl. diagonal, * scale).
@@ -76,7 +77,7 @@ struct PrepTcSmem {
     float et[16 * D * 4];                    // A of MMA2: E^T  [tok/4][128 dk][4]
     __nv_bfloat16 wq[16 * A_PAD * 8];        // staging of the WQ record: [dk/8][129][8]
   } y;
-  float pre[4][2][D];                        // per sub-block and channel: G at its first row and its total, both relative to its start
+  float pre[4][2][D];                        // per sub-block and channel: G at its reference row (row 8) and its total, both relative to its start
   uint64_t bar_m1, bar_m2;
   uint32_t tmem_base;
   int abort_flag;
@@ -185,10 +186,18 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     for (int t = 0; t < 16; ++t) gv[t] = __ldg(gp + t * pstride);                 // 16 independent loads in flight
     float2 run = make_float2(0.f, 0.f);
 #pragma unroll
-    for (int u = 0; u < 16; ++u) { run.x = fmaf(gv[u].x, kLog2e, run.x); run.y = fmaf(gv[u].y, kLog2e, run.y); }
+    float2 mid = make_float2(0.f, 0.f);                  // G at row 8 of the sub-block: its reference row
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      run.x = fmaf(gv[u].x, kLog2e, run.x); run.y = fmaf(gv[u].y, kLog2e, run.y);
+      if (u == 8) mid = run;
+    }
+    // The reference sits in the middle of the sub-block, so both the row factors 2^(G_r - ref) and the key
+    // factors 2^(ref - G_s) of its diagonal block stay within 2^(half span): the two half spans are checked.
     const float2 first = make_float2(gv[0].x * kLog2e, gv[0].y * kLog2e);
-    bad = !((first.x - run.x) <= kMaxSpanLog2) || !((first.y - run.y) <= kMaxSpanLog2);
-    *reinterpret_cast<float2*>(&s.pre[sbk][0][c0]) = first;
+    bad = !((first.x - mid.x) <= kMaxSpanLog2) || !((first.y - mid.y) <= kMaxSpanLog2) ||
+          !((mid.x - run.x) <= kMaxSpanLog2) || !((mid.y - run.y) <= kMaxSpanLog2);
+    *reinterpret_cast<float2*>(&s.pre[sbk][0][c0]) = mid;
     *reinterpret_cast<float2*>(&s.pre[sbk][1][c0]) = run;
   }
   if (tid == 0) {
@@ -257,8 +266,8 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         const int t = t0 + u;
         run.x = fmaf(r.g[u].x, kLog2e, run.x); run.y = fmaf(r.g[u].y, kLog2e, run.y);
         const float2 kf = bf16x2_bits_to_f32(r.k[u]), qf = bf16x2_bits_to_f32(r.q[u]);
-        const float2 a = ex2(run - ref);                      // <= 1
-        const float2 co = ex2(ref - run);                     // >= 1, bounded by the span check
+        const float2 a = ex2(run - ref);                      // both bounded by the half-span check
+        const float2 co = ex2(ref - run);
         const float2 nx = nx_c * co;                          // 2^(refn - run) (2^(g_last - run) for j = 3), <= 1
         const float2 e = bf16x2_bits_to_f32(r.b[u]) * kf;
         a_own32[t * 4] = pack_bf16x2_rn(e.x * a.x, e.y * a.y);

@@ -306,9 +306,9 @@ def test_fp16_inputs_prefill_and_decode(K, D):
     assert orc.rel_fro_err(st.cpu(), s2) < 1e-4
 
 
-@pytest.mark.parametrize("decay_scale", [1.5, 2.5, 3.0, 3.5, 5.0])
+@pytest.mark.parametrize("decay_scale", [1.5, 2.5, 3.5, 5.0, 6.5, 9.0])
 def test_decay_spans_around_the_tensor_core_limit(K, decay_scale):
-    """16-token decay spans from well inside the factorised range (2^40) through its limit (2^96) to chunks
+    """Sub-block decay from well inside the factorised range through its limit (2^96 per half sub-block) to chunks
     that are flagged and redone exactly: all within the bf16 bounds against the recurrence."""
     dev, host = bf16_inputs(2, 64 * 6, 3, 128, 128, seed=19, gate="softplus", decay_scale=decay_scale)
     o_ref, s_ref = orc.recurrence(*host)
