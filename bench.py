@@ -4,22 +4,29 @@
 
 Workload: the serving prefill of the benchmark definition -- B=4, S=16037 (250 chunks of 64 plus a
 37-token ragged tail), H=16, DK=DV=128, bf16 q/k/v/b/w, fp32 g, fp32 state, zero initial state --
-one step = one `gdn2_prefill` over the whole batch. With N > 1 ranks (torchrun, one per GPU) every
-rank runs the whole workload on its own sequences ("weak" scaling, no collective: sequences and heads
-are independent); the `head_sharded` object adds the fixed global problem with its 16 heads split
-over the ranks, the way a tensor-parallel layer calls the op.
-Inputs are seeded synthetic tensors of the stated shapes and distributions.
+one step = one `gdn2_prefill` over the whole batch. With N > 1 ranks (torchrun, one per GPU) the SAME
+global problem is split by heads, 16 / N per rank ("strong" scaling; sequences and heads are independent,
+so there is no collective on the data path) and `value` = global tokens / max-over-ranks time; the
+`replicas` object adds the other way to use N GPUs, every rank running the whole workload on its own
+sequences. Inputs are seeded synthetic tensors of the stated shapes and distributions.
 
 One JSON line on rank 0:
   value       prefill tokens/s with inputs resident in HBM (CUDA events, max over ranks)
   e2e         the same metric through the public API with pinned-host inputs: per step the H2D copy
               of all six inputs and the D2H read of o are inside the timed region
+  parity      (N = 1) the outputs of the timed GPU step against the CPU baseline's outputs on the same
+              bf16-rounded inputs: output max-abs error and final-state relative Frobenius error
   roofline    the dominant kernel's algorithmic HBM bytes per launch / its event-timed duration,
               against the measured copy bandwidth in MEASURED_PEAKS.json
   decode      state HBM GB/s of decode (n=1) and decode_multi (n=8) at B=256, H=16 (rank 0, N=1)
-  cpu_baseline  the CPU oracle timed on the host cores on a bounded sample of the same workload
+  layer       the full layer (hidden 2048, 16 heads, 8 kv heads): prefill of [2,4096,2048] and 128 one-token
+              steps; with N > 1 the head-parallel layer with its all-reduce after o_proj inside the timed
+              region, the all-reduce's own time for both message sizes, and a parity check against the
+              unsharded layer
+  cpu_baseline  the reference's CPU path (oracle/_ref when built, else the oracle port) timed on the host
+              cores on the whole workload, one sequence at a time
 
-`--impl reference` times the reference algorithm's CPU restatement (oracle/) on the host cores.
+`--impl reference` times that CPU path alone, the whole workload per step.
 """
 
 from __future__ import annotations
@@ -179,49 +186,87 @@ def time_events(fn, steps, warmup, stream_sync):
     return t0.elapsed_time(t1) / steps   # ms per step
 
 
-def cpu_baseline(threads):
-    """The oracle's prefill over the whole benchmark workload, one sequence (B = 1) at a time so that the
-    fp32 intermediates stay within a few GB: 4 x 16037 tokens, H=16, D=128, fp32 (about 10 s of CPU work)."""
+def config_dict(world):
+    """The workload description both arms print: identical for `--impl ours` and `--impl reference`."""
+    H = CFG["H"]
+    par = ("one GPU" if world == 1 else
+           f"heads split over {world} GPUs ({H // world} per GPU), one global problem, no collective")
+    return {"workload": WORKLOAD, "parallelism": par, "l2": "inputs (2.1 GB) exceed L2, no flush needed"}
+
+
+# ---- the CPU arm: the reference's own host path, or its restatement ---------------------------------------
+
+
+def cpu_prefill_fn():
+    """(prefill(q,k,v,g,b,w) -> (o, state), kind): the reference's own gdn2/reference.py when the build step
+    placed a copy under oracle/_ref (chunk_gdn2_torch on the whole chunks, the token recurrence on the ragged
+    tail: the host branch of the reference's gdn2_prefill), else the oracle restatement."""
+    from oracle.build_ref import load_ref
+
+    ref = load_ref()
+    if ref is not None:
+
+        def prefill(q, k, v, g, b, w):
+            S, DK = q.shape[1], q.shape[-1]
+            scale, n_full = DK**-0.5, S // 64 * 64
+            o1, state = ref.chunk_gdn2_torch(*(t[:, :n_full] for t in (q, k, v, g, b, w)), scale, None, True)
+            o2, state = ref.recurrent_gdn2(*(t[:, n_full:] for t in (q, k, v, g, b, w)), scale, state, True)
+            return torch.cat([o1, o2], 1), state
+
+        return prefill, "reference"
     from oracle import gdn2_oracle as orc
 
-    torch.set_num_threads(threads)
-    B, S = CFG["B"], CFG["S"]
-    warm = orc.make_inputs(1, 128, CFG["H"], CFG["DK"], CFG["DV"], seed=0)
-    orc.prefill(*warm)
-    dt = 0.0
+    return (lambda *ins: orc.prefill(*ins)), "port"
+
+
+def host_sequences(B, S, H, DK, DV):
+    """Per sequence i (seed i): bf16-rounded host inputs as fp32, the values both arms compute on."""
+    from oracle import gdn2_oracle as orc
+
+    seqs = []
     for i in range(B):
-        ins = orc.make_inputs(1, S, CFG["H"], CFG["DK"], CFG["DV"], seed=i)
+        q, k, v, g, b, w = orc.make_inputs(1, S, H, DK, DV, seed=i)
+        seqs.append(tuple(t.bfloat16().float() for t in (q, k, v)) + (g, b.bfloat16().float(), w.bfloat16().float()))
+    return seqs
+
+
+def cpu_workload_pass(prefill, seqs):
+    """One pass of the CPU path over the whole workload, one sequence (B = 1) at a time so that the fp32
+    intermediates stay within a few GB. Returns (seconds, [o_i], [state_i])."""
+    outs, states, dt = [], [], 0.0
+    for ins in seqs:
         t = time.perf_counter()
-        orc.prefill(*ins)
+        o, s = prefill(*ins)
         dt += time.perf_counter() - t
-        del ins
-    return B * S / dt, f"the whole workload, {B} passes of B=1 S={S} H=16 DK=DV=128 fp32 ({dt:.1f} s)"
+        outs.append(o)
+        states.append(s)
+    return dt, outs, states
 
 
 def run_reference(args, rank, world):
-    """CPU arm: the reference algorithm (oracle restatement of gdn2/reference.py) on the host cores."""
+    """CPU arm: the reference's host path on the box's cores, the whole workload per step."""
     if rank != 0:
         return
-    from oracle import gdn2_oracle as orc
-
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    S = 63 * 64 + 5
-    ins = orc.make_inputs(1, S, CFG["H"], CFG["DK"], CFG["DV"], seed=0)
+    B, S, H, DK, DV = (CFG[x] for x in ("B", "S", "H", "DK", "DV"))
+    prefill, kind = cpu_prefill_fn()
+    seqs = host_sequences(B, S, H, DK, DV)
     for _ in range(args.warmup):
-        orc.prefill(*ins)
-    t = time.perf_counter()
+        cpu_workload_pass(prefill, seqs[:1])                 # warm-up: one sequence is enough to page everything in
+    total = 0.0
     for _ in range(args.steps):
-        orc.prefill(*ins)
-    dt = (time.perf_counter() - t) / args.steps
-    val = S / dt
-    sample = f"each step: oracle prefill of B=1 S={S} H=16 DK=DV=128 fp32 (a bounded sample of the workload)"
+        total += cpu_workload_pass(prefill, seqs)[0]
+    dt = total / args.steps
+    val = B * S / dt
+    sample = (f"each step: the whole workload, {B} passes of B=1 S={S} H={H} DK=DV={DK} fp32 on bf16-rounded inputs; "
+              f"warm-up steps run one sequence")
     print(json.dumps({
         "impl": "reference", "metric": "gdn2_prefill_tokens_per_s", "value": val, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
-        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(world),
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -232,11 +277,13 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg")
+    ap.add_argument("--skip-cpu", action="store_true", help="omit the CPU baseline leg (and with it the parity object)")
     ap.add_argument("--skip-decode", action="store_true", help="omit the decode leg")
     ap.add_argument("--skip-layer", action="store_true", help="omit the layer leg (launch-list captures)")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the end-to-end leg (launch-list captures)")
-    ap.add_argument("--profile-case", choices=["prefill", "decode"],
+    ap.add_argument("--heads", type=int, default=None,
+                    help="single GPU only: run the problem of ONE rank of a head-sharded job (this many of the 16 heads)")
+    ap.add_argument("--profile-case", choices=["prefill", "prefill-sharded", "decode", "output"],
                     help="run a small case a profiler can capture (3 iterations, no JSON line) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -260,13 +307,24 @@ def main():
         os.environ.setdefault("NCCL_DEBUG", "WARN")      # keeps NCCL's version banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
     B, S, H, DK, DV = (CFG[x] for x in ("B", "S", "H", "DK", "DV"))
+    K = _cabi.kernels()
     if args.profile_case:
         # small enough for a multi-pass capture, larger than L2: prefill B=1 S=4096+37 (workspace 107 MB),
-        # decode B=128 (state 134 MB)
+        # the same with 2 heads and the full length (the scan cut into segments), decode B=128 (state 134 MB),
+        # chunk-parallel output B=1 S=4096 H=16 (chunk states 67 MB + workspace 76 MB)
         if args.profile_case == "prefill":
             ins = device_inputs(1, 4096 + 37, H, DK, DV, dev, seed=0)
             for _ in range(3):
                 gdn2.gdn2_prefill(*ins)
+        elif args.profile_case == "prefill-sharded":
+            ins = device_inputs(4, 16037, 2, DK, DV, dev, seed=0)
+            for _ in range(3):
+                gdn2.gdn2_prefill(*ins)
+        elif args.profile_case == "output":
+            ins = device_inputs(1, 4096, H, DK, DV, dev, seed=0)
+            _, _, hs = gdn2.chunk_gdn2_fwd(*ins, DK**-0.5, None, False, return_chunk_states=True)
+            for _ in range(3):
+                gdn2.chunk_gdn2_output(*ins, DK**-0.5, hs)
         else:
             state = torch.randn(128, H, DK, DV, device=dev) * 0.02
             for n in (1, 8):
@@ -274,21 +332,50 @@ def main():
                 for _ in range(3):
                     gdn2.gdn2_decode(*dq, state)
         torch.cuda.synchronize()
-        _cabi.kernels().check_device_status(dev)
+        K.check_device_status(dev)
         print(f"profile case {args.profile_case} done")
         return
-    # N > 1: data parallel. Every rank runs the whole workload on its own sequences (seeded by rank);
-    # the op has no cross-sequence or cross-head term, so there is no collective on the data path.
-    Hl = H
-    K = _cabi.kernels()
-    q, k, v, g, b, w = device_inputs(B, S, Hl, DK, DV, dev, seed=rank)
-    ins = (q, k, v, g, b, w)
 
     def barrier():
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
             torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- inputs. One GPU: host-generated, bf16-rounded, the very values the CPU baseline computes on (its
+    # outputs are kept for the parity object). N GPUs: the global problem generated identically on every
+    # device, this rank keeping its 16 / N heads.
+    cpu, cpu_ref = None, None
+    run_cpu = rank == 0 and world == 1 and not args.skip_cpu and args.heads is None
+    if world > 1 and H % world:
+        raise SystemExit(f"{H} heads do not split over {world} GPUs")
+    Hl = H // world if world > 1 else (args.heads or H)
+    if run_cpu:
+        threads = os.cpu_count() or 1
+        torch.set_num_threads(threads)
+        prefill_cpu, kind = cpu_prefill_fn()
+        seqs = host_sequences(B, S, H, DK, DV)
+        cpu_workload_pass(prefill_cpu, [tuple(t[:, :128] for t in seqs[0])])       # warm-up
+        dt, o_ref, s_ref = cpu_workload_pass(prefill_cpu, seqs)
+        cpu = {"value": B * S / dt, "unit": "tokens/s", "cores": threads, "kind": kind,
+               "sample": f"the whole workload, {B} passes of B=1 S={S} H={H} DK=DV={DK} fp32 on the bf16-rounded "
+                         f"inputs of the GPU arm ({dt:.1f} s)"}
+        cpu_ref = (torch.cat(o_ref, 0), torch.cat(s_ref, 0))
+        ins = tuple(torch.cat([sq[j] for sq in seqs], 0).to(torch.float32 if j == 3 else torch.bfloat16).to(dev)
+                    for j in range(6))
+        del seqs, o_ref, s_ref
+    else:
+        full = device_inputs(B, S, H, DK, DV, dev, seed=0)
+        h0 = rank * Hl if world > 1 else 0
+        ins = tuple(t[:, :, h0:h0 + Hl].contiguous() for t in full)
+        del full
+    q, k, v, g, b, w = ins
 
     def step():
         return gdn2.gdn2_prefill(*ins)
@@ -297,29 +384,22 @@ def main():
     barrier()
     launches0 = K.launches
     with ClockSampler(local) as clk:
-        ms = time_events(step, args.steps, args.warmup, barrier)
+        ms = max_over_ranks(time_events(step, args.steps, args.warmup, barrier))
     launches = (K.launches - launches0) // (args.steps + args.warmup) * args.steps
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    tokens = B * S * world
-    value = tokens / (ms * 1e-3)
+    launches_all = max_over_ranks(float(launches)) * world
+    tokens = B * S                                         # the global problem, whatever N
+    value = tokens / (ms * 1e-3) * (Hl * world / H)        # --heads: scaled to the share of the problem that ran
     K.check_device_status(dev)
 
-    # ---- the other way to use N GPUs: ONE copy of the workload with its heads split over the ranks
-    # (how a tensor-parallel layer calls the op); fixed global problem, still no collective
-    head_sharded = None
-    if world > 1 and H % world == 0:
-        hs_ins = device_inputs(B, S, H // world, DK, DV, dev, seed=1000 + rank)
-        barrier()
-        ms_hs = time_events(lambda: gdn2.gdn2_prefill(*hs_ins), args.steps, args.warmup, barrier)
-        t = torch.tensor([ms_hs], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_hs = float(t.item())
-        head_sharded = {"heads_per_gpu": H // world, "ms_per_step": ms_hs, "value": B * S / (ms_hs * 1e-3),
-                        "unit": "tokens/s", "scaling": "strong"}
-        del hs_ins
+    parity = None
+    if cpu_ref is not None:
+        o_gpu, s_gpu = step()
+        torch.cuda.synchronize()
+        o_cpu, s_cpu = cpu_ref
+        parity = {"o_max_abs": float((o_gpu.float().cpu() - o_cpu).abs().max()),
+                  "state_rel_fro": float((s_gpu.cpu() - s_cpu).norm() / s_cpu.norm()),
+                  "against": cpu["kind"], "bounds": {"o_max_abs": 2e-2, "state_rel_fro": 1e-3}}
+        del o_gpu, s_gpu, cpu_ref
 
     # ---- end to end: pinned host inputs, H2D + kernels + D2H of o per step
     host = [x.cpu().pin_memory() for x in ins]
@@ -331,15 +411,12 @@ def main():
     barrier()
     e2e_steps = max(2, min(args.steps, 5))
     ms_e2e = float("nan") if args.skip_e2e else time_events(e2e_step, e2e_steps, 1, barrier)
-    t = torch.tensor([ms_e2e], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_e2e = float(t.item())
+    ms_e2e = max_over_ranks(ms_e2e)
     h2d = sum(x.numel() * x.element_size() for x in host) * world
     d2h = o_host.numel() * o_host.element_size() * world
     del host, o_host
 
-    # ---- per-kernel timing of the two chunkwise stages (same stream, CUDA events)
+    # ---- per-kernel timing of the two chunkwise stages (same stream, CUDA events) on this rank's problem
     n_full = S // 64 * 64
     code = _cabi.dtype_code(q.dtype)
     path = K.resolved_path(DK, DV, q.dtype)
@@ -362,6 +439,7 @@ def main():
 
     ms_prep = time_events(prep, args.steps, 3, barrier)
     ms_scan = time_events(scan, args.steps, 3, barrier)
+    scan_segments = K.scan_segments(B, n_full, Hl, DK, DV, q.dtype, path)
     th = B * n_full * Hl                                   # token-heads per launch on this rank
     ws_per_th = (2 * DK * 2 + 64 * 2 + DK * 2 + DV * 2) + DK * 4 / 64.0   # WQ + AQK + KG^T + U^T (fp16) + gamma_last
     in_per_th = 3 * DK * 2 + 2 * DV * 2 + DK * 4                          # q,k,b + v,w (bf16) + g (fp32)
@@ -369,7 +447,7 @@ def main():
         "chunk_prep": (ms_prep, th * (in_per_th + ws_per_th)),
         "prefill_scan": (ms_scan, th * (ws_per_th + DV * 2) + B * Hl * DK * DV * 4),
     }
-    dom = max(stages, key=lambda s: stages[s][0])
+    dom = max(stages, key=lambda s_: stages[s_][0])
     peak, peak_kind = measured_peaks()
     dom_ms, dom_bytes = stages[dom]
     achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
@@ -381,11 +459,22 @@ def main():
         "traffic_source": "dram__bytes_read+write of one ncu capture of a 1024-chunk-head launch "
                           "(the committed ncu summary of the prefill kernels), scaled by chunk-heads; writes still in L2 "
                           "when the small launch ends are not in it",
-        "stages_ms": {s: stages[s][0] for s in stages},
-        "stages_frac": {s: stages[s][1] / (stages[s][0] * 1e-3) / 1e9 / peak for s in stages},
+        "stages_ms": {s_: stages[s_][0] for s_ in stages},
+        "stages_frac": {s_: stages[s_][1] / (stages[s_][0] * 1e-3) / 1e9 / peak for s_ in stages},
+        "stage_sum_frac": sum(stages[s_][1] for s_ in stages) / 1e9 / peak / (sum(stages[s_][0] for s_ in stages) * 1e-3),
         "whole_op_frac": whole_op_bytes / (ms * 1e-3) / 1e9 / peak,       # per GPU, of its own HBM
+        "scan_segments": scan_segments,
     }
     del ws, o, fin
+
+    # ---- the other way to use N GPUs: every rank runs the whole workload on its own sequences
+    replicas = None
+    if world > 1:
+        rep_ins = device_inputs(B, S, H, DK, DV, dev, seed=1000 + rank)
+        barrier()
+        ms_rep = max_over_ranks(time_events(lambda: gdn2.gdn2_prefill(*rep_ins), max(3, args.steps // 2), 3, barrier))
+        replicas = {"ms_per_step": ms_rep, "value": B * S * world / (ms_rep * 1e-3), "unit": "tokens/s", "scaling": "weak"}
+        del rep_ins
 
     # ---- decode leg (benchmark definition: B=256, H=16, state ~ N(0, 0.02))
     decode = None
@@ -401,63 +490,92 @@ def main():
                                "total_gbs": (2 * Bd * H * DK * DV * 4 + Bd * n * H * 2048) / (ms_d * 1e-3) / 1e9}
         del state
 
-    # ---- the layer around the op (hidden 2048, 16 heads, 8 kv heads, D = 128, bf16): prefill of
-    # [2, 4096, hidden], then 128 one-token steps, eager and replayed from a CUDA graph
-    layer_leg = None
-    if rank == 0 and world == 1 and not args.skip_layer:
-        cfg = gdn2.GatedDeltaNet2Config(hidden_size=2048, num_heads=16, num_kv_heads=8)
-        gen = torch.Generator(device=dev).manual_seed(0)
-        layer = gdn2.GatedDeltaNet2(cfg).to(torch.bfloat16).eval().to(dev)
-        with torch.no_grad():
-            for name, prm in layer.named_parameters():      # projections ~ N(0, 0.02); gate parameters keep their init
-                if name.endswith("proj.weight"):
-                    prm.copy_(torch.randn(prm.shape, device=dev, generator=gen) * 0.02)
-        x = torch.randn(2, 4096, 2048, device=dev, generator=gen).bfloat16()
-        ms_pre = time_events(lambda: layer.prefill(x), 5, 3, torch.cuda.synchronize)
-        _, cache = layer.prefill(x)
-        xt = torch.randn(2, 2048, device=dev, generator=gen).bfloat16()
+    layer_leg = None if args.skip_layer else layer_bench(gdn2, dist, dev, rank, world, barrier, max_over_ranks)
 
-        def eager_steps():
-            for _ in range(128):
-                layer.step(xt, cache)
+    if rank == 0:
+        cfg = config_dict(world)
+        if args.heads is not None:
+            cfg["parallelism"] = f"ONE rank's share of a head-sharded job: {Hl} of {H} heads on one GPU"
+        print(json.dumps({
+            "metric": "gdn2_prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": cfg, "heads_per_gpu": Hl, "prefill_path": {1: "simt", 2: "tcgen05", 3: "tcgen05"}[path],
+            "clocks": clk.result,
+            "e2e": {"value": tokens * (Hl * world / H) / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches_all), "parity": parity,
+            "roofline": roofline, "decode": decode, "layer": layer_leg, "cpu_baseline": cpu,
+            "replicas": replicas,
+        }))
+    if world > 1:
+        dist.destroy_process_group()
 
-        ms_eager = time_events(eager_steps, 3, 1, torch.cuda.synchronize)
+
+def layer_bench(gdn2, dist, dev, rank, world, barrier, max_over_ranks):
+    """The layer around the op (hidden 2048, 16 heads, 8 kv heads, D = 128, bf16 weights ~ N(0, 0.02)): prefill of
+    x [2, 4096, 2048], then 128 one-token steps. One GPU: eager and replayed from a CUDA graph. N GPUs: the
+    head-parallel layer, its one all-reduce after o_proj inside the timed region; the all-reduce alone is timed
+    for both message sizes, and every rank's output is compared with the unsharded layer run on the same GPU."""
+    cfg = gdn2.GatedDeltaNet2Config(hidden_size=2048, num_heads=16, num_kv_heads=8)
+    gen = torch.Generator(device=dev).manual_seed(0)
+    full = gdn2.GatedDeltaNet2(cfg).to(torch.bfloat16).eval().to(dev)
+    with torch.no_grad():
+        for name, prm in full.named_parameters():      # projections ~ N(0, 0.02); gate parameters keep their init
+            if name.endswith("proj.weight"):
+                prm.copy_(torch.randn(prm.shape, device=dev, generator=gen) * 0.02)
+    x = torch.randn(2, 4096, 2048, device=dev, generator=gen).bfloat16()
+    xt = torch.randn(2, 2048, device=dev, generator=gen).bfloat16()
+    sync = barrier
+    leg = {"config": "hidden 2048, H=16, HK=8, DK=DV=128, bf16, x [2,4096,2048], then 128 one-token steps"}
+    if world == 1:
+        layer = full
+    else:
+        if cfg.num_kv_heads % world:
+            return {"skipped": f"{cfg.num_kv_heads} kv heads do not split over {world} GPUs"}
+        layer = gdn2.TensorParallelGatedDeltaNet2(cfg).to(torch.bfloat16).eval()
+        layer.load_full_state_dict({k_: v_.cpu() for k_, v_ in full.state_dict().items()})   # same seed on every rank
+        layer.to(dev)
+        # parity of the sharded layer with the unsharded one (prefill + 4 steps), on every rank
+        ref_out, ref_cache = full.prefill(x)
+        got_out, got_cache = layer.prefill(x)
+        errs = [float((got_out.float() - ref_out.float()).abs().max() / ref_out.float().abs().max())]
+        for _ in range(4):
+            r_, ref_cache = full.step(xt, ref_cache)
+            g_, got_cache = layer.step(xt, got_cache)
+            errs.append(float((g_.float() - r_.float()).abs().max() / r_.float().abs().max()))
+        hl = cfg.num_heads // world
+        s_ref = ref_cache.recurrent_state[:, rank * hl:(rank + 1) * hl]
+        s_err = float((got_cache.recurrent_state - s_ref).norm() / s_ref.norm())
+        leg["tp_parity"] = {"out_rel_max": max_over_ranks(max(errs)), "state_rel_fro": max_over_ranks(s_err),
+                            "bounds": {"out_rel_max": 2e-2, "state_rel_fro": 1e-3}}
+        del ref_out, got_out, ref_cache, got_cache
+    ms_pre = max_over_ranks(time_events(lambda: layer.prefill(x), 5, 3, sync))
+    _, cache = layer.prefill(x)
+
+    def eager_steps():
+        for _ in range(128):
+            layer.step(xt, cache)
+
+    ms_eager = max_over_ranks(time_events(eager_steps, 3, 1, sync))
+    leg.update(prefill_ms=ms_pre, prefill_tokens_per_s=2 * 4096 / (ms_pre * 1e-3), step_us_eager=ms_eager * 1e3 / 128)
+    if world == 1:
         step = gdn2.GraphedStep(layer, cache)
 
         def graphed_steps():
             for _ in range(128):
                 step(xt)
 
-        ms_graph = time_events(graphed_steps, 3, 1, torch.cuda.synchronize)
-        layer_leg = {"config": "hidden 2048, H=16, HK=8, DK=DV=128, bf16, x [2,4096,2048]",
-                     "prefill_ms": ms_pre, "prefill_tokens_per_s": 2 * 4096 / (ms_pre * 1e-3),
-                     "step_us_eager": ms_eager * 1e3 / 128, "step_us_cuda_graph": ms_graph * 1e3 / 128}
-        del layer, x, cache, step
-
-    cpu = None
-    if rank == 0 and world == 1 and not args.skip_cpu:
-        threads = os.cpu_count() or 1
-        val, sample = cpu_baseline(threads)
-        cpu = {"value": val, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
-
-    if rank == 0:
-        print(json.dumps({
-            "metric": "gdn2_prefill_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "heads_per_gpu": Hl,
-                       "parallelism": f"data-parallel x{world}: the whole workload per GPU on its own sequences, no collective",
-                       "l2": "inputs (2.1 GB) exceed L2, no flush needed", "prefill_path":
-                       {1: "simt", 2: "tcgen05"}[path]},
-            "clocks": clk.result,
-            "e2e": {"value": tokens / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": launches * world,
-            "roofline": roofline, "decode": decode, "layer": layer_leg, "cpu_baseline": cpu,
-            "head_sharded": head_sharded,
-        }))
-    if world > 1:
-        dist.destroy_process_group()
+        leg["step_us_cuda_graph"] = time_events(graphed_steps, 3, 1, sync) * 1e3 / 128
+    else:
+        big = torch.zeros(2, 4096, 2048, device=dev, dtype=torch.bfloat16)       # 32 MiB: the prefill message
+        small = torch.zeros(2, 2048, device=dev, dtype=torch.bfloat16)           # 8 KiB: the step message
+        ms_big = max_over_ranks(time_events(lambda: dist.all_reduce(big), 10, 3, sync))
+        ms_small = max_over_ranks(time_events(lambda: dist.all_reduce(small), 200, 20, sync))
+        leg["all_reduce"] = {"prefill_32MiB_ms": ms_big, "prefill_share": ms_big / ms_pre,
+                             "step_8KiB_us": ms_small * 1e3, "step_share": ms_small * 1e3 / (ms_eager * 1e3 / 128),
+                             "backend": "nccl", "n_ranks": world}
+    return leg
 
 
 if __name__ == "__main__":

@@ -21,8 +21,8 @@ _PKG = pathlib.Path(__file__).resolve().parent
 _LIB_PATH = _PKG / "libgdn2_b200.so"
 
 GDN2_F32, GDN2_BF16, GDN2_F16 = 0, 1, 2
-PATH_AUTO, PATH_SIMT, PATH_TCGEN05 = 0, 1, 2
-_PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "tcgen05": PATH_TCGEN05}
+PATH_AUTO, PATH_SIMT, PATH_TCGEN05, PATH_TCGEN05_SERIAL = 0, 1, 2, 3
+_PATHS = {"auto": PATH_AUTO, "simt": PATH_SIMT, "tcgen05": PATH_TCGEN05, "tcgen05_serial": PATH_TCGEN05_SERIAL}
 CHUNK = 64
 
 _DTYPES = {torch.float32: GDN2_F32, torch.bfloat16: GDN2_BF16, torch.float16: GDN2_F16}
@@ -36,11 +36,14 @@ SIGNATURES = {
     "gdn2_last_cuda_error": (_int, []),
     "gdn2_decode": (_int, [_vp] * 8 + [_i64] * 7 + [_f32, _int, _vp]),
     "gdn2_prefill_workspace_bytes": (_sz, [_i64] * 5 + [_int, _int]),
+    "gdn2_prefill_scan_segments": (_int, [_i64] * 5 + [_int, _int]),
+    "gdn2_prefill_workspace_layout": (_int, [_i64] * 5 + [_int, _int, ctypes.POINTER(ctypes.c_int64)]),
     "gdn2_chunk_prep": (_int, [_vp] * 7 + [_sz] + [_i64] * 6 + [_f32, _int, _int, _vp]),
     "gdn2_prefill_scan": (_int, [_vp, _sz, _vp, _vp, _vp, _vp] + [_i64] * 6 + [_int, _int, _vp]),
     "gdn2_chunk_output": (_int, [_vp, _sz, _vp, _vp] + [_i64] * 6 + [_int, _int, _vp]),
     "gdn2_check_device_status": (_int, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
     "gdn2_selftest_mma": (_int, [_vp, _vp, _vp, _vp]),
+    "gdn2_selftest_wait": (_int, [_i64, _vp, _vp]),
     "gdn2_prefill_static": (_int, [_vp] * 9 + [_i64] * 7 + [_f32, _int, _vp]),
     "gdn2_layer_front": (_int, [_vp, _int, _vp]),
     "gdn2_layer_back": (_int, [_vp] * 4 + [_i64] * 5 + [_f32, _int, _vp]),
@@ -144,12 +147,20 @@ class NativeKernels:
             p = PATH_TCGEN05 if (DK == 128 and DV == 128 and dtype == torch.bfloat16) else PATH_SIMT
         return p
 
-    def _segments(self, n_chunks: int, path: int) -> int:
-        """How many sequence segments the chunkwise prefill is cut into (1 = no overlap of the two stages)."""
-        if path != PATH_TCGEN05:
+    def scan_segments(self, B, S, H, DK, DV, dtype, path) -> int:
+        """Sequence segments the scan kernel itself cuts this problem into (1 = one block per (batch, head))."""
+        return self.lib.gdn2_prefill_scan_segments(B, S, H, DK, DV, dtype_code(dtype), path)
+
+    def _segments(self, B, S, H, DK, DV, dtype, path: int) -> int:
+        """How many sequence segments the host cuts the chunkwise prefill into so that the chunk-local stage
+        of one segment overlaps the scan of the previous one (1 = no cut). Only worth it while the scan runs
+        one block per (batch, head) and leaves SMs idle; a scan that cuts the sequence itself fills the GPU."""
+        if path not in (PATH_TCGEN05, PATH_TCGEN05_SERIAL):
+            return 1
+        if self.scan_segments(B, S, H, DK, DV, dtype, path) > 1:
             return 1
         want = int(os.environ.get("GDN2_B200_PREFILL_SEGMENTS", "2"))
-        return max(1, min(want, n_chunks // 16))
+        return max(1, min(want, (S // CHUNK) // 16))
 
     def _side_stream(self, dev):
         key = (dev.type, dev.index)
@@ -215,7 +226,6 @@ class NativeKernels:
         if nbytes == 0:
             raise GDN2KernelError(
                 f"no kernel for DK={DK}, DV={DV}, dtype={q.dtype} (SIMT family: DK<=128, DK%8==0, DV%4==0)")
-        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
         if out is None:
             out = torch.empty(B, S, H, DV, dtype=v.dtype, device=dev)
             out_batch_stride = S
@@ -225,7 +235,7 @@ class NativeKernels:
             if initial_state.dtype != torch.float32 or not initial_state.is_contiguous():
                 initial_state = initial_state.to(torch.float32).contiguous()
         NC = S // CHUNK
-        nseg = 1 if want_chunk_states else self._segments(NC, p)
+        nseg = 1 if want_chunk_states else self._segments(B, S, H, DK, DV, q.dtype, p)
         esz = out.element_size()
         with torch.cuda.device(dev):
             main = torch.cuda.current_stream(dev)
@@ -239,14 +249,14 @@ class NativeKernels:
                 side = self._side_stream(dev)
                 side.wait_stream(main)
             state_ptr = None if initial_state is None else initial_state.data_ptr()
+            scratch = []   # every segment's workspace stays alive until the side stream has been joined
+            launched = 0
             for i in range(nseg):
                 c0, c1 = bounds[i], bounds[i + 1]
                 t0, S_i = c0 * CHUNK, (c1 - c0) * CHUNK
-                if nseg == 1:
-                    ws_i, nb_i = ws, nbytes
-                else:
-                    nb_i = self.lib.gdn2_prefill_workspace_bytes(B, S_i, H, DK, DV, code, p)
-                    ws_i = torch.empty(nb_i, dtype=torch.uint8, device=dev)
+                nb_i = nbytes if nseg == 1 else self.lib.gdn2_prefill_workspace_bytes(B, S_i, H, DK, DV, code, p)
+                ws_i = torch.empty(nb_i, dtype=torch.uint8, device=dev)
+                scratch.append(ws_i)
                 ptrs = [x.data_ptr() + t0 * H * x.shape[-1] * x.element_size() for x in (q, k, v, g, b, w)]
                 rc = self.lib.gdn2_chunk_prep(*ptrs, ws_i.data_ptr(), nb_i, B, S_i, H, DK, DV, in_bs, float(scale),
                                               code, p, main.cuda_stream)
@@ -262,9 +272,12 @@ class NativeKernels:
                                                 B, S_i, H, DK, DV, out_batch_stride, code, p, scan_stream.cuda_stream)
                 _check(self.lib, rc, "gdn2_prefill_scan")
                 state_ptr = states[i].data_ptr()
+                cut = 1 if want_chunk_states else self.scan_segments(B, S_i, H, DK, DV, q.dtype, p)
+                launched += (2 if p != PATH_SIMT else 1) + (3 if cut > 1 else 1)
             if side is not None:
-                main.wait_stream(side)
-        self.launches += (3 if p == PATH_TCGEN05 else 2) * nseg
+                main.wait_stream(side)             # from here on the caller's stream is ordered after every scan
+            del scratch                            # ... so only now may the allocator hand these blocks out again
+        self.launches += launched
         return out, final_state, hs
 
     def chunk_output(self, q, k, v, g, b, w, scale: float, chunk_states, path=None):
@@ -287,7 +300,7 @@ class NativeKernels:
             rc = self.lib.gdn2_chunk_output(ws.data_ptr(), nbytes, chunk_states.data_ptr(), out.data_ptr(),
                                             B, S, H, DK, DV, S, code, p, st)
             _check(self.lib, rc, "gdn2_chunk_output")
-        self.launches += 3 if p == PATH_TCGEN05 else 2
+        self.launches += 3 if p != PATH_SIMT else 2
         return out
 
     # -- diagnostics -------------------------------------------------------------------------
@@ -339,6 +352,49 @@ class NativeKernels:
         _check(self.lib, rc, "gdn2_layer_back")
         self.launches += 1
         return out
+
+    def maybe_check_device_status(self, device):
+        """With ``GDN2_B200_CHECK_STATUS=1`` every public call ends with a synchronising status check, so a
+        kernel that gave up on a bounded wait raises at the call that launched it (debugging aid; off by default
+        because it serialises the host with the device)."""
+        if os.environ.get("GDN2_B200_CHECK_STATUS", "0") not in ("", "0"):
+            self.check_device_status(device)
+
+    def workspace_layout(self, B, S, H, DK, DV, dtype, path=None) -> dict:
+        """Byte offsets of the record arrays inside the prefill workspace (``gdn2_prefill_workspace_layout``)."""
+        p = self.resolved_path(DK, DV, dtype, path)
+        out = (ctypes.c_int64 * 8)()
+        _check(self.lib, self.lib.gdn2_prefill_workspace_layout(B, S, H, DK, DV, dtype_code(dtype), p, out),
+               "gdn2_prefill_workspace_layout")
+        return dict(zip(("wq", "aqk", "kgt", "ut", "gl", "flags", "seg", "total"), list(out)))
+
+    def chunk_prep(self, q, k, v, g, b, w, scale: float, path=None):
+        """The chunk-local stage alone. Returns ``(workspace uint8 tensor, resolved path)``."""
+        _require_cuda(q)
+        B, S, H, DK = q.shape
+        DV = v.shape[-1]
+        code = dtype_code(q.dtype)
+        p = self.resolved_path(DK, DV, q.dtype, path)
+        q, k, v, g, b, w = (t.contiguous() for t in (q, k, v, g, b, w))
+        nbytes = self.lib.gdn2_prefill_workspace_bytes(B, S, H, DK, DV, code, p)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+        with torch.cuda.device(q.device):
+            rc = self.lib.gdn2_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
+                                          w.data_ptr(), ws.data_ptr(), nbytes, B, S, H, DK, DV, S, float(scale),
+                                          code, p, self._stream(q))
+        _check(self.lib, rc, "gdn2_chunk_prep")
+        self.launches += 2 if p != PATH_SIMT else 1
+        return ws, p
+
+    def selftest_wait(self, limit_cycles: int, device=None) -> int:
+        """Launch the block whose bounded wait nothing satisfies; returns how many threads gave up."""
+        device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        counter = torch.zeros(1, dtype=torch.int32, device=device)
+        with torch.cuda.device(device):
+            rc = self.lib.gdn2_selftest_wait(limit_cycles, counter.data_ptr(),
+                                             torch.cuda.current_stream(device).cuda_stream)
+        _check(self.lib, rc, "gdn2_selftest_wait")
+        return int(counter.item())
 
     def selftest_mma(self, a: torch.Tensor, bt: torch.Tensor) -> torch.Tensor:
         _require_cuda(a, bt)

@@ -78,40 +78,26 @@ class GDN2Cache:
 
 
 class _ShortConv(nn.Module):
-    """Causal depthwise conv1d + SiLU over ``[B, S, C]`` with a ``kernel_size-1`` column cache."""
+    """Parameter holder of the causal depthwise conv1d (+ SiLU) over ``[B, S, C]``: ``conv.weight [C, 1, K]``,
+    ``conv.bias [C]``, the names and shapes of the reference module. The convolution itself runs inside
+    ``gdn2_layer_front`` together with everything else element-wise."""
 
     def __init__(self, channels: int, kernel_size: int = 4, activation: bool = True):
         super().__init__()
+        if not activation:
+            raise ValueError("the fused kernel always applies SiLU after the convolution, as the layer does")
         self.channels, self.kernel_size, self.activation = channels, kernel_size, activation
         self.conv = nn.Conv1d(channels, channels, kernel_size, groups=channels, padding=kernel_size - 1)
 
-    def forward(self, x):
-        y = self.conv(x.transpose(1, 2))[..., : x.shape[1]].transpose(1, 2)
-        return F.silu(y) if self.activation else y
-
-    def decode(self, x, state):
-        """``x [B, n, C]`` continuing from ``state [B, C, kernel_size-1]``; returns ``(y, new_state)``."""
-        buf = torch.cat([state.to(x.dtype), x.transpose(1, 2)], dim=-1)
-        y = F.conv1d(buf, self.conv.weight, self.conv.bias, groups=self.channels).transpose(1, 2)
-        return (F.silu(y) if self.activation else y), buf[..., -(self.kernel_size - 1):]
-
-    def step(self, x, state):
-        y, state = self.decode(x.unsqueeze(1), state)
-        return y[:, 0], state
-
 
 class _GatedRMSNorm(nn.Module):
-    """Per-head RMSNorm multiplied by a SiLU gate, computed in float32."""
+    """Parameter holder of the per-head RMSNorm multiplied by a SiLU gate (``weight [DV]``, ``eps``); evaluated
+    in float32 by ``gdn2_layer_back``."""
 
     def __init__(self, dim: int, eps: float = 1e-5):
         super().__init__()
         self.eps = eps
         self.weight = nn.Parameter(torch.ones(dim))
-
-    def forward(self, x, gate):
-        x = x.float()
-        x = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps)
-        return (x * self.weight.float() * F.silu(gate.float())).to(gate.dtype)
 
 
 class GatedDeltaNet2(nn.Module):
@@ -156,13 +142,6 @@ class GatedDeltaNet2(nn.Module):
         self.erase_scale = config.erase_gate_scale
 
     # ------------------------------------------------------------------ pieces
-    def _gates(self, x, lead):
-        f = self.f_proj(x).view(*lead, self.num_kv_heads, self.head_dim_k)
-        return -self.A_log.float().exp().unsqueeze(-1) * F.softplus(f.float() + self.dt_bias.float())
-
-    def _expand(self, x):
-        return x if self.head_repeat == 1 else x.repeat_interleave(self.head_repeat, dim=-2)
-
     def _fused_tables(self):
         """Concatenated projection weight ``[NP, hidden]`` (q | k | v | b | w | f | o_gate), its column
         offsets, and the convolution weight ``[CC, K]`` / bias ``[CC]`` (q | k | v); rebuilt when a
@@ -183,61 +162,39 @@ class GatedDeltaNet2(nn.Module):
             self._fused_key, self._fused = key, (w_cat, offs, cw, cb)
         return self._fused
 
-    def _use_fused(self, x) -> bool:
-        return (x.is_cuda and self.head_dim_k <= 256 and self.head_dim_v <= 256
-                and self.q_proj.weight.dtype == x.dtype and self.q_proj.bias is None)
+    def _check_supported(self, x):
+        """The element-wise stages run in the fused kernels only; configurations they do not cover raise."""
+        if self.head_dim_k > 256 or self.head_dim_v > 256:
+            raise ValueError("the fused layer kernels support head dimensions up to 256")
+        if self.q_proj.weight.dtype != x.dtype:
+            raise TypeError(f"input dtype {x.dtype} differs from the layer's parameter dtype {self.q_proj.weight.dtype}")
+        if any(m.bias is not None for m in (self.q_proj, self.k_proj, self.v_proj, self.b_proj, self.w_proj,
+                                            self.f_proj, self.o_gate_proj)):
+            raise ValueError("projection biases are not supported (the reference layer has none)")
 
     def _front(self, x, conv_state, cached: bool):
-        """Everything before the attention kernels. Returns ``(q, k, v, g, b, w, new_conv_state, proj)``;
-        ``proj`` is the fused projection buffer (its o_gate columns feed ``_back``) or ``None``."""
-        B, S, _ = x.shape
+        """Everything before the attention kernels: ONE GEMM for the seven input projections, then one kernel
+        for everything element-wise. Returns ``(q, k, v, g, b, w, new_conv_state, proj)``; the o_gate columns
+        of the projection buffer ``proj`` feed ``_back``."""
+        self._check_supported(x)
         H, HK, DK, DV = self.num_heads, self.num_kv_heads, self.head_dim_k, self.head_dim_v
-        if self._use_fused(x):
-            # one GEMM for the seven input projections, then one kernel for everything element-wise
-            w_cat, offs, cw, cb = self._fused_tables()
-            proj = F.linear(x, w_cat)
-            K = self.cfg.conv_size if self.q_conv is not None else 0
-            state = None
-            if cached and conv_state is not None:
-                state = conv_state if conv_state.dtype == x.dtype else conv_state.to(x.dtype)
-                state = state.contiguous()
-            q, k, v, g, b, w, new_conv = _cabi.kernels().layer_front(
-                proj, offs[:6], state, cw, cb, self.A_log.detach().to(x.dtype), self.dt_bias.detach().to(x.dtype).contiguous(),
-                H, HK, DK, DV, K, float(self.erase_scale), want_conv_state=True)
-            return q, k, v, g, b, w, new_conv, proj
-        q, k, v = self.q_proj(x), self.k_proj(x), self.v_proj(x)
-        new_conv = None
-        if self.q_conv is not None:
-            d = HK * DK
-            if cached:
-                q, cq = self.q_conv.decode(q, conv_state[:, :d])
-                k, ck = self.k_conv.decode(k, conv_state[:, d:2 * d])
-                v, cv = self.v_conv.decode(v, conv_state[:, 2 * d:])
-                new_conv = torch.cat([cq, ck, cv], dim=1)
-            else:
-                width = self.cfg.conv_size - 1
-                tail = torch.cat([q, k, v], dim=-1).transpose(1, 2)
-                new_conv = F.pad(tail, (max(0, width - S), 0))[..., -width:]
-                q, k, v = self.q_conv(q), self.k_conv(k), self.v_conv(v)
-        q = F.normalize(q.view(B, S, HK, DK), p=2, dim=-1)
-        k = F.normalize(k.view(B, S, HK, DK), p=2, dim=-1)
-        v = v.view(B, S, H, DV)
-        g = self._gates(x, (B, S))
-        b = torch.sigmoid(self.b_proj(x).view(B, S, HK, DK)) * self.erase_scale
-        w = torch.sigmoid(self.w_proj(x).view(B, S, H, DV))
-        q, k, b, g = (self._expand(t) for t in (q, k, b, g))
-        return q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), b.contiguous(), w.contiguous(), new_conv, None
+        w_cat, offs, cw, cb = self._fused_tables()
+        proj = F.linear(x, w_cat)
+        K = self.cfg.conv_size if self.q_conv is not None else 0
+        state = None
+        if cached and conv_state is not None:
+            state = conv_state if conv_state.dtype == x.dtype else conv_state.to(x.dtype)
+            state = state.contiguous()
+        q, k, v, g, b, w, new_conv = _cabi.kernels().layer_front(
+            proj, offs[:6], state, cw, cb, self.A_log.detach().to(x.dtype), self.dt_bias.detach().to(x.dtype).contiguous(),
+            H, HK, DK, DV, K, float(self.erase_scale), want_conv_state=True)
+        return q, k, v, g, b, w, new_conv, proj
 
-    def _back(self, x, o, proj=None):
-        B, S, _ = x.shape
-        if proj is not None:
-            off_gate = self._fused_tables()[1][6]
-            normed = _cabi.kernels().layer_back(o.contiguous(), proj, self.o_norm.weight.detach().to(o.dtype),
-                                                off_gate, float(self.o_norm.eps))
-            return self._reduce(self.o_proj(normed))
-        gate = self.o_gate_proj(x).view(B, S, self.num_heads, self.head_dim_v)
-        o = self.o_norm(o, gate).reshape(B, S, self.num_heads * self.head_dim_v)
-        return self._reduce(self.o_proj(o))
+    def _back(self, x, o, proj):
+        off_gate = self._fused_tables()[1][6]
+        normed = _cabi.kernels().layer_back(o.contiguous(), proj, self.o_norm.weight.detach().to(o.dtype),
+                                            off_gate, float(self.o_norm.eps))
+        return self._reduce(self.o_proj(normed))
 
     def _reduce(self, y):
         """Hook for the head-parallel variant (sum over ranks); identity on one device."""

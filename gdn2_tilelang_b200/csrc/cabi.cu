@@ -40,11 +40,14 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 bool valid_dtype(int dtype) { return dtype == GDN2_F32 || dtype == GDN2_BF16 || dtype == GDN2_F16; }
 
-// Resolve AUTO and check that the chosen family supports the shape. Returns a gdn2_status.
-int resolve_path(int64_t DK, int64_t DV, int dtype, int path, int* resolved) {
+// Resolve AUTO and check that the chosen family supports the shape. Returns a gdn2_status; *resolved is
+// GDN2_PATH_SIMT or GDN2_PATH_TCGEN05, *segments whether the scan may cut the sequence.
+int resolve_path(int64_t DK, int64_t DV, int dtype, int path, int* resolved, bool* segments) {
   const bool tc_ok = (DK == 128 && DV == 128 && dtype == GDN2_BF16);
   const bool simt_ok = (DK >= 8 && DK <= 128 && DK % 8 == 0 && DV >= 4 && DV % 4 == 0);
   if (path == GDN2_PATH_AUTO) path = tc_ok ? GDN2_PATH_TCGEN05 : GDN2_PATH_SIMT;
+  *segments = path == GDN2_PATH_TCGEN05;
+  if (path == GDN2_PATH_TCGEN05_SERIAL) path = GDN2_PATH_TCGEN05;
   if (path == GDN2_PATH_TCGEN05 && !tc_ok) return GDN2_ERR_UNSUPPORTED;
   if (path == GDN2_PATH_SIMT && !simt_ok) return GDN2_ERR_UNSUPPORTED;
   if (path != GDN2_PATH_SIMT && path != GDN2_PATH_TCGEN05) return GDN2_ERR_UNSUPPORTED;
@@ -52,10 +55,16 @@ int resolve_path(int64_t DK, int64_t DV, int dtype, int path, int* resolved) {
   return GDN2_OK;
 }
 
+// The workspace layout of a validated problem.
+WsLayout layout_for(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int family, bool segments) {
+  return make_ws_layout(B, S, H, (int)DK, (int)DV, family == GDN2_PATH_TCGEN05 ? 2 : 4, segments);
+}
+
 int check_prefill_shape(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype) {
   if (!valid_dtype(dtype)) return GDN2_ERR_BAD_DTYPE;
   if (B <= 0 || S <= 0 || H <= 0 || DK <= 0 || DV <= 0 || S % kChunk != 0) return GDN2_ERR_BAD_SHAPE;
-  if (B * H > 2147483647LL / 4 || S > (1LL << 30)) return GDN2_ERR_BAD_SHAPE;
+  // the chunk-local kernels put (batch, head) on gridDim.y
+  if (B * H > 65535 || S > (1LL << 30)) return GDN2_ERR_BAD_SHAPE;
   return GDN2_OK;
 }
 
@@ -72,7 +81,7 @@ const char* gdn2_status_string(int status) {
   switch (status) {
     case GDN2_OK: return "ok";
     case GDN2_ERR_NULL_POINTER: return "a required pointer is NULL";
-    case GDN2_ERR_BAD_SHAPE: return "bad shape (sizes must be positive, S a multiple of 64)";
+    case GDN2_ERR_BAD_SHAPE: return "bad shape (sizes must be positive, S a multiple of 64, B*H <= 65535 for the chunkwise calls)";
     case GDN2_ERR_BAD_DTYPE: return "unknown element type";
     case GDN2_ERR_MISALIGNED: return "a pointer is not 16-byte aligned";
     case GDN2_ERR_WORKSPACE: return "workspace too small";
@@ -103,8 +112,32 @@ int gdn2_decode(const void* q, const void* k, const void* v, const float* g, con
 size_t gdn2_prefill_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path) {
   if (check_prefill_shape(B, S, H, DK, DV, dtype) != GDN2_OK) return 0;
   int p;
-  if (resolve_path(DK, DV, dtype, path, &p) != GDN2_OK) return 0;
-  return make_ws_layout(B, S, H, (int)DK, (int)DV, p == GDN2_PATH_TCGEN05 ? 2 : 4).total;
+  bool seg;
+  if (resolve_path(DK, DV, dtype, path, &p, &seg) != GDN2_OK) return 0;
+  return layout_for(B, S, H, DK, DV, p, seg).total;
+}
+
+int gdn2_prefill_workspace_layout(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path,
+                                  int64_t* out8) {
+  if (!out8) return GDN2_ERR_NULL_POINTER;
+  int rc = check_prefill_shape(B, S, H, DK, DV, dtype);
+  if (rc != GDN2_OK) return rc;
+  int p;
+  bool seg;
+  rc = resolve_path(DK, DV, dtype, path, &p, &seg);
+  if (rc != GDN2_OK) return rc;
+  const WsLayout L = layout_for(B, S, H, DK, DV, p, seg);
+  const size_t v[8] = {L.off_wq, L.off_aqk, L.off_kgt, L.off_ut, L.off_gl, L.off_flags, L.off_seg, L.total};
+  for (int i = 0; i < 8; ++i) out8[i] = (int64_t)v[i];
+  return GDN2_OK;
+}
+
+int gdn2_prefill_scan_segments(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path) {
+  if (check_prefill_shape(B, S, H, DK, DV, dtype) != GDN2_OK) return 0;
+  int p;
+  bool seg;
+  if (resolve_path(DK, DV, dtype, path, &p, &seg) != GDN2_OK) return 0;
+  return layout_for(B, S, H, DK, DV, p, seg).nseg;
 }
 
 int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
@@ -115,12 +148,13 @@ int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g,
   if (rc != GDN2_OK) return rc;
   if (in_batch_stride < S) return GDN2_ERR_BAD_SHAPE;
   int p;
-  rc = resolve_path(DK, DV, dtype, path, &p);
+  bool seg;
+  rc = resolve_path(DK, DV, dtype, path, &p, &seg);
   if (rc != GDN2_OK) return rc;
   if (!aligned16(workspace) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(g) ||
       !aligned16(b) || !aligned16(w))
     return GDN2_ERR_MISALIGNED;
-  const WsLayout L = make_ws_layout(B, S, H, (int)DK, (int)DV, p == GDN2_PATH_TCGEN05 ? 2 : 4);
+  const WsLayout L = layout_for(B, S, H, DK, DV, p, seg);
   if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
   const WsPtrs P = ws_pointers(workspace, L);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -141,10 +175,11 @@ int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float
   if (rc != GDN2_OK) return rc;
   if (o_batch_stride < S) return GDN2_ERR_BAD_SHAPE;
   int p;
-  rc = resolve_path(DK, DV, dtype, path, &p);
+  bool seg;
+  rc = resolve_path(DK, DV, dtype, path, &p, &seg);
   if (rc != GDN2_OK) return rc;
   if (!aligned16(workspace)) return GDN2_ERR_MISALIGNED;
-  const WsLayout L = make_ws_layout(B, S, H, (int)DK, (int)DV, p == GDN2_PATH_TCGEN05 ? 2 : 4);
+  const WsLayout L = layout_for(B, S, H, DK, DV, p, seg);
   if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
   const WsPtrs P = ws_pointers(const_cast<void*>(workspace), L);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -163,12 +198,16 @@ int gdn2_chunk_output(const void* workspace, size_t workspace_bytes, const float
   if (rc != GDN2_OK) return rc;
   if (o_batch_stride < S) return GDN2_ERR_BAD_SHAPE;
   int p;
-  rc = resolve_path(DK, DV, dtype, path, &p);
+  bool seg;
+  rc = resolve_path(DK, DV, dtype, path, &p, &seg);
   if (rc != GDN2_OK) return rc;
   if (!aligned16(workspace)) return GDN2_ERR_MISALIGNED;
-  const WsLayout L = make_ws_layout(B, S, H, (int)DK, (int)DV, p == GDN2_PATH_TCGEN05 ? 2 : 4);
+  const WsLayout L = layout_for(B, S, H, DK, DV, p, seg);
   if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
   const WsPtrs P = ws_pointers(const_cast<void*>(workspace), L);
+  if (p == GDN2_PATH_TCGEN05)
+    return launch_output_tc(L, P, chunk_states, o, (int)B, (int)S, (int)H, o_batch_stride,
+                            static_cast<cudaStream_t>(stream));
   return launch_output_simt(L, P, chunk_states, o, (int)B, (int)S, (int)H, o_batch_stride, dtype,
                             static_cast<cudaStream_t>(stream));
 }
@@ -183,6 +222,11 @@ int gdn2_check_device_status(void* stream, uint32_t* detail) {
   if (host != 0) GDN2_CUDA_TRY(cudaMemsetAsync(dw, 0, sizeof(host), st));
   if (detail) *detail = host;
   return host == 0 ? GDN2_OK : GDN2_ERR_DEVICE_WAIT;
+}
+
+int gdn2_selftest_wait(int64_t limit_cycles, int* gave_up, void* stream) {
+  if (limit_cycles <= 0 || limit_cycles > 2000000000LL) return GDN2_ERR_BAD_SHAPE;   // about a second at most
+  return launch_selftest_wait(limit_cycles, gave_up, static_cast<cudaStream_t>(stream));
 }
 
 int gdn2_selftest_mma(const float* a, const float* bt, float* out, void* stream) {

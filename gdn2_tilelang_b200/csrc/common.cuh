@@ -58,18 +58,34 @@ __device__ __forceinline__ float tf32_rn(float x) {
 
 struct WsLayout {
   int64_t nch;        // number of chunk-heads
+  int64_t BH;         // (batch, head) pairs
   int DK, DV;
   int esz;            // bytes per TW element (2 or 4); TV has the same size
+  int nseg;           // sequence segments of the tensor-core scan (1 = one block per head walks the whole sequence)
   size_t wq_bytes, aqk_bytes, kgt_bytes, ut_bytes, gl_bytes;   // per chunk-head
-  size_t off_wq, off_aqk, off_kgt, off_ut, off_gl, off_flags, total;
+  size_t off_wq, off_aqk, off_kgt, off_ut, off_gl, off_flags, off_seg, total;
 };
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-__host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK, int DV, int esz) {
+// Segments the tensor-core scan cuts a sequence of NC chunks into when a GPU holds BH (batch, head)
+// pairs. The first pass runs 2 * nseg - 1 blocks per pair, one per SM, and all of them have to be
+// resident at once for the cut to shorten the chain, so it is only made while they fit on 144 SMs;
+// a segment is at least 8 chunks. 1 = no cut.
+__host__ __device__ inline int scan_segments(int64_t BH, int64_t NC) {
+  int64_t n = (144 / BH + 1) / 2;
+  if (n > NC / 8) n = NC / 8;
+  if (n > 16) n = 16;
+  return n < 2 ? 1 : (int)n;
+}
+
+__host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK, int DV, int esz,
+                                        bool allow_segments = false) {
   WsLayout L;
   L.nch = B * H * (S / kChunk);
+  L.BH = B * H;
   L.DK = DK; L.DV = DV; L.esz = esz;
+  L.nseg = (allow_segments && esz == 2) ? scan_segments(B * H, S / kChunk) : 1;
   L.wq_bytes = (size_t)2 * kChunk * DK * esz;
   L.aqk_bytes = (size_t)kChunk * kChunk * esz;
   L.kgt_bytes = (size_t)DK * kChunk * esz;
@@ -82,6 +98,11 @@ __host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK,
   L.off_ut = off;   off = align_up(off + L.ut_bytes * L.nch, 1024);
   L.off_gl = off;   off = align_up(off + L.gl_bytes * L.nch, 1024);
   L.off_flags = off; off = align_up(off + sizeof(int) * (2 * L.nch + 4), 1024);   // flags, compacted list, count
+  // per (batch, head) and segment: transition T_j, local final state C_j, true entering state (fp32 [DK, DV]
+  // each), then one int per (batch, head, segment): the chunks the correction pass has to redo
+  L.off_seg = off;
+  if (L.nseg > 1)
+    off = align_up(off + (size_t)B * H * L.nseg * ((size_t)3 * DK * DV * 4 + sizeof(int)), 1024);
   L.total = off;
   return L;
 }
@@ -93,12 +114,21 @@ template <int E> __host__ __device__ __forceinline__ int kc_index(int row, int k
 
 struct WsPtrs {
   char* wq; char* aqk; char* kgt; char* ut; float* gl; int* flags;
+  float* seg_t; float* seg_c; float* seg_in; int* seg_stop;   // segment records of the cut scan (nseg > 1)
 };
 
 __host__ inline WsPtrs ws_pointers(void* base, const WsLayout& L) {
   char* p = static_cast<char*>(base);
-  return WsPtrs{p + L.off_wq, p + L.off_aqk, p + L.off_kgt, p + L.off_ut, reinterpret_cast<float*>(p + L.off_gl),
-                reinterpret_cast<int*>(p + L.off_flags)};
+  WsPtrs P{p + L.off_wq, p + L.off_aqk, p + L.off_kgt, p + L.off_ut, reinterpret_cast<float*>(p + L.off_gl),
+           reinterpret_cast<int*>(p + L.off_flags), nullptr, nullptr, nullptr, nullptr};
+  if (L.nseg > 1) {
+    const size_t mats = (size_t)L.BH * L.nseg * L.DK * L.DV;      // floats per record kind
+    P.seg_t = reinterpret_cast<float*>(p + L.off_seg);
+    P.seg_c = P.seg_t + mats;
+    P.seg_in = P.seg_c + mats;
+    P.seg_stop = reinterpret_cast<int*>(P.seg_in + mats);
+  }
+  return P;
 }
 
 // Per-family element types of the workspace: TW for WQ, TV (+ scales) for AQK/KGT/UT
@@ -152,6 +182,9 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
                    cudaStream_t st);
 int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o, float* sT, float* hs,
                    int B, int S, int H, int64_t o_bs, cudaStream_t st);
+int launch_output_tc(const WsLayout& L, const WsPtrs& P, const float* hs, void* o, int B, int S, int H, int64_t o_bs,
+                     cudaStream_t st);
+int launch_selftest_wait(long long limit_cycles, int* gave_up, cudaStream_t st);
 int launch_selftest_mma(const float* a, const float* bt, float* out, cudaStream_t st);
 
 }  // namespace gdn2

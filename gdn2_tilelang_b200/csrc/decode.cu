@@ -145,10 +145,10 @@ decode_generic_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
                       const float* __restrict__ g, const T* __restrict__ b, const T* __restrict__ w,
                       float* __restrict__ state, T* __restrict__ o, int n, int H, int DK, int DV, int64_t in_bs,
                       int64_t o_bs, float scale) {
-  const int bh = blockIdx.y;
+  const int bh = blockIdx.x;                 // (batch, head) on x: no 65535 limit
   const int ib = bh / H, ih = bh % H;
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
-  const int dv = blockIdx.x * 32 + lane;
+  const int dv = blockIdx.y * 32 + lane;
   const bool col_ok = dv < DV;
   const int rpw = (DK + 3) / 4;
   const int r0 = wid * rpw;
@@ -221,7 +221,7 @@ int launch_typed(const void* q, const void* k, const void* v, const float* g, co
   } else if (DK == 128 && DV == 128) {
     decode_d128_kernel<T><<<B * H, 128, 0, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, in_bs, o_bs, scale);
   } else {
-    dim3 grid((DV + 31) / 32, B * H);
+    dim3 grid(B * H, (DV + 31) / 32);
     const size_t sm = (size_t)4 * DK * sizeof(float);
     if (DK <= 64)
       decode_generic_kernel<T, 16><<<grid, 128, sm, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, DK, DV, in_bs, o_bs, scale);

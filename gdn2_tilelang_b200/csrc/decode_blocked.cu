@@ -106,17 +106,6 @@ __device__ __forceinline__ bool table_sync_or(bool pred) {
   return r != 0;
 }
 
-#ifdef GDN2_SCAN_TIMING
-__device__ unsigned long long g_dec_timing[32];
-#define DTICK(i) do { if (blockIdx.x == 0 && lane == 0) { long long now_ = clock64(); dacc[i] += now_ - dprev; dprev = now_; } } while (0)
-#define DDECL long long dacc[12] = {0}; long long dprev = clock64()
-#define DFLUSH(off) do { if (blockIdx.x == 0 && lane == 0) for (int i_ = 0; i_ < 12; ++i_) g_dec_timing[off + i_] = dacc[i_]; } while (0)
-#else
-#define DTICK(i) do {} while (0)
-#define DDECL do {} while (0)
-#define DFLUSH(off) do {} while (0)
-#endif
-
 enum : uint32_t { kWaitTile = 0x10000u, kWaitTab = 0x20000u, kWaitEmpty = 0x40000u, kWaitDone = 0x80000u };
 
 template <typename T>
@@ -175,13 +164,11 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     const int c = tid - kSweepThreads;
     const int pw_ = wid - 8;                             // 32-channel group
     int step = 0;
-    DDECL;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
       const int ib = tile / H, ih = tile % H;
       for (int t0 = 0; t0 < n; t0 += NB, ++step) {
         const int nb = min(NB, n - t0);
         Tables& tb = s.tab[step & 1];
-        DTICK(0);
         // all 48 loads of the step are issued before any is used (padding tokens re-read the last real one)
         float graw[NB];
         T kraw[NB], braw[NB], qraw[NB], wraw[NB], vraw[NB];
@@ -204,11 +191,9 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
           G[t] = run;                                    // log2 of A_t
         }
         // the sweep warps have finished with this table buffer (two steps ago)
-        DTICK(1);
         const bool okw = tc::mbar_wait(&s.tab_empty[step & 1], ((step >> 1) & 1) ^ 1, &s.abort_flag, status, kWaitEmpty);
         // uniform over the table warps; it also orders this step after the reads of the previous step's partial sums
         if (table_sync_or(!okw)) break;
-        DTICK(2);
         {
           const int pr = crow(c);
           float c1v[16], c2v[8];
@@ -261,7 +246,6 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
           for (int m = 0; m < 5; ++m) idx += ((lane >> (4 - m)) & 1) * (16 >> m);
           s.part[pw_][32 * hb + idx] = term[0];
         }
-        DTICK(3);
         table_sync();
         if (c < 64) {
           const float sum = s.part[0][c] + s.part[1][c] + s.part[2][c] + s.part[3][c];
@@ -270,17 +254,14 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
           else tb.aqk[sx][t] = sum;                      // slot (t, sx) with sx >= t holds Aqk[sx, t]
         }
         warp_arrive(&s.tab_full[step & 1], lane);
-        DTICK(4);
       }
       if (s.abort_flag) break;
     }
-    if (wid == 8) DFLUSH(0);
   } else {
     // =============================== sweep warps ================================================
     const int rgl = lane >> 2, cq = lane & 3;
     const int col0 = 16 * wid + 4 * cq;
     int it = 0, step = 0;
-    DDECL;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
       const int buf = it & 1;
       const int ib = tile / H, ih = tile % H;
@@ -289,13 +270,10 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
       for (int t0 = 0; t0 < n; t0 += NB, ++step) {
         const int nb = min(NB, n - t0);
         const Tables& tb = s.tab[step & 1];
-        DTICK(0);
         ok = tc::mbar_wait(&s.tab_full[step & 1], (step >> 1) & 1, &s.abort_flag, status, kWaitTab);
-        DTICK(1);
         if (ok && t0 == 0) ok = tc::mbar_wait(&s.tile_full[buf], (it >> 1) & 1, &s.abort_flag, status, kWaitTile);
         ok = __all_sync(0xffffffffu, ok);                // the warp leaves together: what follows uses full-warp shuffles
         if (!ok) break;
-        DTICK(2);
 
         // ---- sweep 1: the 16 products (8 erase rows, 8 query rows) of S_0 for this thread's rows and columns
         //      packed over PAIRS OF PRODUCTS: acc[pp][col] = (product 2pp, product 2pp+1) of column col, so the
@@ -324,7 +302,6 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
             }
           }
         }
-        DTICK(3);
         // reduce over the 8 row groups. Index = half*32 + column*8 + t (half 0: erase products, 1: query
         // products); lane (rgl) ends with the 8 values of half rgl >> 2, column rgl & 3.
         float pv[8];
@@ -351,7 +328,6 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
 #pragma unroll
           for (int t = 0; t < 8; ++t) pv[t] = val[t];
         }
-        DTICK(4);
         // ---- forward substitution for u on the lanes that hold the erase products; the lanes that hold
         //      the query products of the same column take u from them and form the outputs
         const bool has_q = (rgl & 4) != 0;
@@ -393,7 +369,6 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
             if (t < nb) o[(((size_t)ib * o_bs + (t0 + t)) * H + ih) * D + mycol] = from_f32<T>(ov);
           }
         }
-        DTICK(5);
         // gather u of the thread's four columns from the lanes that share cq (rgl bits 0 and 1 = lane bits 2, 3)
         //      and pair them over tokens: up[tp][c] = (u_{2tp}, u_{2tp+1}) of column col0 + c
         float2 up[4][4];
@@ -411,7 +386,6 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
             else up[t >> 1][cc].x = uc[cc];
           }
         }
-        DTICK(6);
         // ---- sweep 2: S <- A_8 * S + sum_s (k_s A_8/A_s) u_s^T, in place
         {
           float* Sw = S + rgl * kGroupFloats + col0;
@@ -434,13 +408,11 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
           }
         }
         warp_arrive(&s.tab_empty[step & 1], lane);       // this step's tables may be overwritten
-        DTICK(7);
       }
       if (!ok) break;
       tc::fence_async_smem();                            // the tile's new values are visible to the bulk store
       warp_arrive(&s.tile_done[buf], lane);
     }
-    if (wid == 0) DFLUSH(16);
   }
 }
 
@@ -459,12 +431,6 @@ int launch_decode_blocked(const T* q, const T* k, const T* v, const float* g, co
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }
-
-#ifdef GDN2_SCAN_TIMING
-extern "C" int gdn2_debug_decode_timing(unsigned long long* out32) {
-  return cudaMemcpyFromSymbol(out32, g_dec_timing, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -6;
-}
-#endif
 
 template int launch_decode_blocked<float>(const float*, const float*, const float*, const float*, const float*,
                                           const float*, float*, float*, int, int, int, int64_t, int64_t, float,

@@ -54,13 +54,6 @@ constexpr uint32_t kTmemCols = 256;
 constexpr uint32_t kZCol = 192;   // TMEM columns [192,256): w*v of the thread's value channel (fp32)
 constexpr uint32_t kQgCol = 160;  // TMEM columns [160,192): packed Qg of the thread's channel
 
-#ifdef GDN2_SCAN_TIMING
-__device__ unsigned long long g_prep_timing[16];
-#define PTICK(i) do { if (blockIdx.x == 100 && blockIdx.y == 32 && tid == 0) { long long now_ = clock64(); g_prep_timing[i] = now_ - tprev; tprev = now_; } } while (0)
-#else
-#define PTICK(i) do {} while (0)
-#endif
-
 struct PrepTcSmem {
   union {
     struct {
@@ -152,9 +145,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const size_t pstride = rstride / 2;                                   // channel pairs between tokens
   const size_t soff = (size_t)(16 * sbk) * rstride;                     // first token of this thread's sub-block
   const float2* gp = reinterpret_cast<const float2*>(g + row0 * D + soff) + cp;
-#ifdef GDN2_SCAN_TIMING
-  long long tprev = clock64();
-#endif
 
   // Pull the whole input tile of this chunk-head towards L2 before anything depends on it: 64 rows x
   // (5 x 256 B + 512 B) = 896 128-byte lines, 3.5 per thread.
@@ -185,7 +175,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
 #pragma unroll
     for (int t = 0; t < 16; ++t) gv[t] = __ldg(gp + t * pstride);                 // 16 independent loads in flight
     float2 run = make_float2(0.f, 0.f);
-#pragma unroll
     float2 mid = make_float2(0.f, 0.f);                  // G at row 8 of the sub-block: its reference row
 #pragma unroll
     for (int u = 0; u < 16; ++u) {
@@ -206,7 +195,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     s.abort_flag = 0;
     tc::mbar_init_fence();
   }
-  PTICK(0);
   const int any_bad = __syncthreads_or(bad ? 1 : 0);
   if (tid == 0) {
     P.flags[ch] = any_bad ? 1 : 0;
@@ -232,7 +220,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::tc_fence_after_sync();
   const uint32_t tm = s.tmem_base;
 
-  PTICK(1);
   // ---- 1b. gated operands of the channel pair for this thread's 16 tokens, in four groups of 4; the next
   //          group's 16 loads are issued (raw, unconverted) before the current one is processed. Two
   //          channels per thread: every 16-bit operand leaves as a packed pair (one convert, one store).
@@ -250,7 +237,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     const float2 ref = pick4(j, ref0, ref1, ref2, ref3);
     const float2 refn = pick4(j, ref1, ref2, ref3, zero2);      // ref of the next sub-block (unused for j = 3)
     const float2 gam_ref = ex2(ref);
-    const float2 nx_c = ex2(((j < 3) ? refn : g_last) - ref);  // 2^(refn - run) = nx_c * 2^(ref - run)
+    const float2 nx_ref = (j < 3) ? refn : g_last;             // keys of this sub-block, seen from the next one
     const float2 kg_c = (j < 3) ? ex2(g_last - refn) : make_float2(1.f, 1.f);
     const float2 cc_a = ex2(pick4(j, ref2, ref3, zero2, zero2) - refn);   // B_{j+2} relative to B_{j+1}
     const float2 cc_b = ex2(ref3 - refn);                      // B_{j+3} relative to B_{j+1} (j = 0 only)
@@ -268,7 +255,11 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         const float2 kf = bf16x2_bits_to_f32(r.k[u]), qf = bf16x2_bits_to_f32(r.q[u]);
         const float2 a = ex2(run - ref);                      // both bounded by the half-span check
         const float2 co = ex2(ref - run);
-        const float2 nx = nx_c * co;                          // 2^(refn - run) (2^(g_last - run) for j = 3), <= 1
+        // 2^(refn - run) (2^(g_last - run) for j = 3), <= 1. Formed from its own exponent: the step from this
+        // sub-block's reference to the next one's is not covered by the span check, so a product of
+        // 2^(refn - ref) (which may flush to zero) and 2^(ref - run) (up to 2^96) would lose keys whose true
+        // factor is still a normal number.
+        const float2 nx = ex2(nx_ref - run);
         const float2 e = bf16x2_bits_to_f32(r.b[u]) * kf;
         a_own32[t * 4] = pack_bf16x2_rn(e.x * a.x, e.y * a.y);
         a_own32[(BS + t) * 4] = pack_bf16x2_rn(qf.x * a.x, qf.y * a.y);
@@ -316,7 +307,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::tc_fence_before_sync();
   __syncthreads();
 
-  PTICK(2);
   // ---- 2. MMA1: D_i[128 x 16(i+1)] at TMEM columns 0, 16, 48, 96
   //         The four products are independent: warps 0..3 issue one each (converged, one elected
   //         lane) and commit it, so no warp falls far behind the others before the value-side loads.
@@ -328,7 +318,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
                             tc::smem_u32(s.x.ops.bfam) + off * 16, B_PAD, D, tc::instr_desc(1, 128, 16 * (i + 1)));
     tc::mma_commit_warp(&s.bar_m1);
   }
-  PTICK(3);
   // The block that will most likely run next in this slot (two resident blocks per SM, dispatched in
   // linear order) starts with a cold read of its g tile: pull those 256 lines towards L2 now.
   {
@@ -359,12 +348,10 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     tc::tmem_st16(tc::tmem_addr(tm, lq * 32, kZCol + 32 * (sbk >> 1) + 16), zy);
     tc::tmem_st_wait();
   }
-  PTICK(4);
   // one warp polls the MMA barrier; the rest sleep at the block barrier instead of spending issue slots
   if (wid == 0) tc::mbar_wait(&s.bar_m1, 0, &s.abort_flag, status, 0x1000u);
   __syncthreads();
   tc::tc_fence_after_sync();
-  PTICK(5);
 
   // ---- 2b. read back: lane = row (0..63 Tm, 64..127 Aqk); a warp spans sub-blocks i0 and i0+1, and
   //          the two threads of a row split the four 16-column groups.
@@ -422,7 +409,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::tc_fence_before_sync();
   __syncthreads();
 
-  PTICK(6);
   // ---- 3. (I + Tm)^-1 by 16x16 blocks. With D_i = (I + T_ii)^-1 and N_ik = D_i T_ik (i > k):
   //          X_ii = D_i,   X_ij = - sum_{k=j}^{i-1} N_ik X_kj   (i > j),   zero above the diagonal.
   //      The diagonal blocks are substituted column by column in registers (one thread per column);
@@ -520,7 +506,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::tc_fence_before_sync();
   __syncthreads();
 
-  PTICK(7);
   // ---- 4. MMA2 (tf32): W^T at TMEM columns 0..63, U^T at 64..127
   if (wid < 2 && !s.abort_flag) {  // warp 0: W^T, warp 1: U^T
     tc::tc_fence_after_sync();
@@ -532,7 +517,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   if (wid == 0) tc::mbar_wait(&s.bar_m2, 0, &s.abort_flag, status, 0x2000u);
   __syncthreads();
   tc::tc_fence_after_sync();
-  PTICK(8);
 
   // ---- 5. W and Qg rows into the WQ staging image (E^T is dead now), U^T straight to global; each
   //         thread handles the 32 tokens of its half
@@ -568,7 +552,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   }
   tc::tc_fence_before_sync();
   __syncthreads();
-  PTICK(9);
   if (wid == 0) tc::tmem_dealloc(tm, kTmemCols);
   // WQ record: 16 K chunks x 128 rows x 16 bytes; every thread copies 8 pieces with 128-bit accesses
   // (16 consecutive threads cover 256 contiguous bytes) and the block ends without waiting on them
@@ -583,7 +566,6 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
           *reinterpret_cast<const uint4*>(stage + (kc * A_PAD + row) * 16);
     }
   }
-  PTICK(10);
 }
 
 }  // namespace
@@ -612,11 +594,5 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
     default: return launch(prep_tc_kernel<0>);
   }
 }
-
-#ifdef GDN2_SCAN_TIMING
-extern "C" int gdn2_debug_prep_timing(unsigned long long* out16) {
-  return cudaMemcpyFromSymbol(out16, g_prep_timing, sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : -6;
-}
-#endif
 
 }  // namespace gdn2

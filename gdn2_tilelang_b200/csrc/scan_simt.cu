@@ -193,10 +193,7 @@ int launch_output_typed(const WsLayout& L, const WsPtrs& P, const float* hs, voi
 
 int launch_scan_simt(const WsLayout& L, const WsPtrs& P, const float* s0, void* o, float* sT, float* hs,
                      int B, int S, int H, int64_t o_bs, int dtype, cudaStream_t st) {
-  if (L.esz == 2) {
-    if (dtype != GDN2_BF16) return GDN2_ERR_UNSUPPORTED;
-    return launch_scan_typed<__nv_bfloat16, __nv_bfloat16>(L, P, s0, o, sT, hs, B, S, H, o_bs, st);
-  }
+  if (L.esz != 4) return GDN2_ERR_UNSUPPORTED;   // 16-bit records belong to the tensor-core family's kernels
   switch (dtype) {
     case GDN2_F32: return launch_scan_typed<float, float>(L, P, s0, o, sT, hs, B, S, H, o_bs, st);
     case GDN2_BF16: return launch_scan_typed<__nv_bfloat16, float>(L, P, s0, o, sT, hs, B, S, H, o_bs, st);
@@ -207,10 +204,7 @@ int launch_scan_simt(const WsLayout& L, const WsPtrs& P, const float* s0, void* 
 
 int launch_output_simt(const WsLayout& L, const WsPtrs& P, const float* hs, void* o, int B, int S, int H,
                        int64_t o_bs, int dtype, cudaStream_t st) {
-  if (L.esz == 2) {
-    if (dtype != GDN2_BF16) return GDN2_ERR_UNSUPPORTED;
-    return launch_output_typed<__nv_bfloat16, __nv_bfloat16>(L, P, hs, o, B, S, H, o_bs, st);
-  }
+  if (L.esz != 4) return GDN2_ERR_UNSUPPORTED;
   switch (dtype) {
     case GDN2_F32: return launch_output_typed<float, float>(L, P, hs, o, B, S, H, o_bs, st);
     case GDN2_BF16: return launch_output_typed<__nv_bfloat16, float>(L, P, hs, o, B, S, H, o_bs, st);

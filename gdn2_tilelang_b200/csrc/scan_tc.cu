@@ -1,38 +1,52 @@
 // Sequential state scan fused with the output, tensor-core (tcgen05 / TMEM / TMA) family, for
-// DK = DV = 128, bf16 outputs, fp32 state. One block per (batch, head), sequential over chunks; the
-// state never leaves the SM between chunks.
+// DK = DV = 128, bf16 outputs, fp32 state. One block walks a run of consecutive chunks of one
+// (batch, head); the state never leaves the SM between chunks.
 //
 // The algebra of the reference's prefill_scan_kernel (gdn2/inference.py:446-475 of the reference
 // project) is evaluated TRANSPOSED so that every product has the 128 value channels as the MMA M
 // dimension (= TMEM lane = thread), tokens or key channels as N:
 //
-//   MMA1w  WS[dv, tok]  = S^T[dv,dk] * W[tok,dk]^T            (W S)^T          bf16
-//   MMA1q  O [dv, tok]  = S^T[dv,dk] * Qg[tok,dk]^T           (Qg S)^T         bf16
+//   MMA1   [WS | O][dv, tok] = S^T[dv,dk] * [W ; Qg][tok,dk]^T  (W S)^T and (Qg S)^T, one N = 128 product, bf16
 //   regs   Un^T[dv,tok] = U^T - WS
 //   MMA3   P [dv,dk]    = Un^T[dv,tok] * KG^T[dk,tok]^T       (KG^T Un)^T      fp16 (scaled, see common.cuh)
 //   MMA2   O [dv, r]   += Un^T[dv,s] * Aqk[r,s]^T             (tril(Aqk) Un)^T fp16 (same scaled Un^T image)
 //   regs   S^T         <- gamma_C[dk] * S^T + P   (the fp32 state lives in registers, 64 values per thread)
 //
-// Only MMA1w, the Un pass, MMA3 and the state pass are on the recurrence's critical path; the
+// Only MMA1, the Un pass, MMA3 and the state pass are on the recurrence's critical path; the
 // kernel is organised around that:
-//   * warp 8 (one thread) issues every MMA, MMA3 before MMA2 so the state update never queues behind
-//     the output product; warp 9 (one thread) issues every bulk copy.
+//   * warp 8 issues every MMA (converged, one elected lane), MMA3 before MMA2 so the state update never
+//     queues behind the output product; one thread of warp 9 issues every bulk copy.
 //   * warps 10-13 read each finished O accumulator into registers, release it, and write the rows
 //     out through a shared staging tile with 128-bit coalesced stores, off the critical path.
 //   * warps 0-7 (256 threads; two warps share each 32-lane quarter of TMEM and split its columns)
-//     do the register passes. The output pass of chunk n (TMEM -> bf16 -> shared staging ->
-//     128-bit coalesced global stores) runs after the state hand-off, while MMA1w of chunk n+1
-//     executes; the O accumulator is double buffered in TMEM for that.
+//     do the register passes and hand each result over the moment the next product can use it.
 //   * operands arrive as whole workspace records with one bulk copy each; WQ, KG^T and U^T are
 //     double buffered so that a copy is always issued a full chunk ahead of its use.
-//   * hand-offs are mbarriers (arrive / wait), every wait is bounded (tc_utils.cuh).
-//
+//   * hand-offs are mbarriers (arrive / wait), every wait is bounded (tc_utils.cuh); there is no
+//     block-level barrier inside the chunk loop.
 //   * the A operands (S^T in bf16, Un^T in fp16) never touch shared memory: the register
-//     passes store them as packed 16-bit pairs into tensor memory and the MMAs read them from there,
-//     which halves the shared-memory traffic the tensor core competes for.
+//     passes store them as packed 16-bit pairs into tensor memory and the MMAs read them from there.
 //
-// TMEM columns: [0,128) the update product P; [128,192) WS; [192,256) and [256,320) the two O accumulators;
+// TMEM columns: [0,128) the update product P; [128,192) WS; [192,256) the O accumulator;
 // [320,384) S^T bf16 pairs; [384,416) Un^T/256 fp16 pairs.
+//
+// Sequence-parallel form. One block per (batch, head) leaves most of the GPU idle when a GPU holds few
+// (batch, head) pairs (a head-sharded layer), and its chunk-to-chunk chain then sets the time. The
+// recurrence is affine in the state, S_out = T S_in + C per run of chunks, with T a [DK, DK] matrix that
+// does not depend on the values: running the very same chunk loop from S = I with U = 0 yields T. So the
+// sequence is cut into `nseg` segments and evaluated in three launches:
+//   pass 1  one "local" block per segment (from the true initial state for segment 0, from zero for the
+//           others: outputs, C_j) and one "transition" block per segment j >= 1 (from the identity, no U,
+//           no outputs: T_j); the transition block also records after how many chunks every entry of its
+//           running T fell below 2^-27 for good (`stop_j`): from there on the local outputs are already
+//           the true ones;
+//   pass 2  scan_combine_kernel chains S_in(j+1) = T_j S_in(j) + C_j in fp32 (T_j is skipped where it
+//           vanished) and writes every segment's true entering state and the final state;
+//   pass 3  one block per segment j >= 1 redoes chunks [0, stop_j) from the true entering state and
+//           overwrites their outputs.
+// Nothing waits on another block inside a launch. With slowly decaying gates stop_j is the segment
+// length and the cost is two chains of NC / nseg chunks; with the usual gates it is one such chain plus
+// a few chunks.
 #include <cuda_fp16.h>
 
 #include "common.cuh"
@@ -67,18 +81,22 @@ struct ScanTcSmem {
   uint64_t bar_sb, bar_un;                              // compute threads -> issuer (256 arrivals)
   uint32_t tmem_base;
   int abort_flag;
+  int last_big[kComputeThreads / 32];                   // transition blocks: per warp, last chunk after which an entry was still >= kVanish
 };
 
-#ifdef GDN2_SCAN_TIMING
-__device__ unsigned long long g_scan_timing[32];
-#define TICK(i) do { if (blockIdx.x == 0) { long long now_ = clock64(); tacc[i] += now_ - tprev; tprev = now_; } } while (0)
-#define TDECL long long tacc[16] = {0}; long long tprev = clock64()
-#define TFLUSH(off) do { if (blockIdx.x == 0) for (int i_ = 0; i_ < 16; ++i_) g_scan_timing[off + i_] = tacc[i_]; } while (0)
-#else
-#define TICK(i) do {} while (0)
-#define TDECL do {} while (0)
-#define TFLUSH(off) do {} while (0)
-#endif
+// A transition matrix entry below this is treated as vanished: 128 of them times the entering state stay
+// below 1e-6 of that state, three orders under the fp32-state tolerance and far under bf16 output resolution.
+constexpr float kVanish = 7.450580596923828e-09f;   // 2^-27
+
+// What a block of the cut scan does (ScanPlan::pass). kWhole: one block per (batch, head) over the whole
+// sequence. kFirst: blockIdx = slot * BH + bh; slots [0, nseg) are local blocks of segment `slot`, slots
+// [nseg, 2 nseg - 1) transition blocks of segment slot - nseg + 1. kRedo: blockIdx = (seg - 1) * BH + bh.
+// kOutput: the chunk-parallel output from stored chunk states (no recurrence): blockIdx = seg * BH + bh, every
+// block walks the chunks of its segment and takes the state entering each chunk from `hs` instead of carrying it.
+enum ScanPass : int { kWhole = 0, kFirst = 1, kRedo = 3, kOutput = 4 };
+struct ScanPlan {
+  int pass, nseg;
+};
 
 enum : uint32_t {
   kWaitWq = 0x10, kWaitUt = 0x20, kWaitAqk = 0x40, kWaitKgt = 0x80, kWaitM1 = 0x100, kWaitM2 = 0x200,
@@ -114,14 +132,56 @@ __device__ __forceinline__ void unpack8_f16(const uint4& p, float* x) {
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
-scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16* __restrict__ o,
+scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0, __nv_bfloat16* __restrict__ o,
                float* __restrict__ sT, float* __restrict__ hs, int S, int H, int64_t o_bs, uint32_t* status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   ScanTcSmem& s = *reinterpret_cast<ScanTcSmem*>(smem_raw);
-  const int NC = S / BS;
-  const int bh = blockIdx.x, ib = bh / H, ih = bh % H;
+  const int NC_all = S / BS;
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
-  const int64_t ch0 = (int64_t)bh * NC;
+
+  // ---- this block's job: which (batch, head), which run of chunks, where the state comes from and goes to
+  const int BH = (int)L.BH;
+  int bh = blockIdx.x, seg = 0;
+  bool transition = false;                  // identity start, no U, no outputs: yields the segment's transition matrix
+  if (plan.pass != kWhole) {
+    const int slot = blockIdx.x / BH;
+    bh = blockIdx.x % BH;
+    if (plan.pass == kFirst) {
+      transition = slot >= plan.nseg;
+      seg = transition ? slot - plan.nseg + 1 : slot;
+    } else if (plan.pass == kRedo) {
+      seg = slot + 1;
+    } else {
+      seg = slot;
+    }
+  }
+  const bool output_only = plan.pass == kOutput;
+  const int ib = bh / H, ih = bh % H;
+  const int c_first = plan.pass == kWhole ? 0 : (int)((int64_t)NC_all * seg / plan.nseg);
+  const int c_end = plan.pass == kWhole ? NC_all : (int)((int64_t)NC_all * (seg + 1) / plan.nseg);
+  int NC = c_end - c_first;                 // chunks this block walks
+  if (plan.pass == kRedo) {
+    const int redo = P.seg_stop[bh * plan.nseg + seg];
+    NC = redo < NC ? redo : NC;
+  }
+  if (plan.pass == kFirst || plan.pass == kRedo) hs = nullptr;
+  // where the state comes from (nullptr = zero, or the identity for a transition block) and where it goes;
+  // evaluated where they are used so that they do not occupy registers across the chunk loop
+  auto state_source = [&]() -> const float* {
+    const size_t seg_rec = ((size_t)bh * plan.nseg + seg) * D * D;
+    if (plan.pass == kRedo) return P.seg_in + seg_rec;
+    if (plan.pass == kFirst && seg != 0) return nullptr;
+    if (output_only) return hs + (((size_t)ib * NC_all + c_first) * H + ih) * D * D;
+    return s0 ? s0 + (size_t)bh * D * D : nullptr;
+  };
+  auto state_sink = [&]() -> float* {
+    const size_t seg_rec = ((size_t)bh * plan.nseg + seg) * D * D;
+    if (plan.pass == kRedo || output_only) return nullptr;
+    if (plan.pass == kFirst) return (transition ? P.seg_t : P.seg_c) + seg_rec;
+    return sT ? sT + (size_t)bh * D * D : nullptr;
+  };
+  const bool write_o = !transition;
+  const int64_t ch0 = (int64_t)bh * NC_all + c_first;
 
   const char* g_wq = P.wq + (size_t)ch0 * kWqBytes;
   const char* g_aqk = P.aqk + (size_t)ch0 * kAqkBytes;
@@ -152,11 +212,13 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         tc::bulk_g2s(s.wq[n & 1], g_wq + (size_t)n * kWqBytes, kWqBytes, &s.bar_wq[n & 1]);
       };
       auto load_kgt = [&](int n) {
+        if (output_only) return;                           // no state update: KG^T and gamma are not needed
         tc::mbar_expect_tx(&s.bar_kgt[n & 1], kKgtBytes + D * 4);
         tc::bulk_g2s(s.kgt[n & 1], g_kgt + (size_t)n * kKgtBytes, kKgtBytes, &s.bar_kgt[n & 1]);
         tc::bulk_g2s(s.gl[n & 3], g_gl + (size_t)n * D, D * 4, &s.bar_kgt[n & 1]);
       };
       auto load_ut = [&](int n) {
+        if (transition) return;                            // U = 0: nothing to bring in, nobody waits for it
         tc::mbar_expect_tx(&s.bar_ut[n & 1], kUtBytes);
         tc::bulk_g2s(s.ut[n & 1], g_ut + (size_t)n * kUtBytes, kUtBytes, &s.bar_ut[n & 1]);
       };
@@ -192,46 +254,32 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
       auto wait_all = [&](uint64_t* bar, uint32_t parity, uint32_t code) {
         return __all_sync(0xffffffffu, tc::mbar_wait(bar, parity, &s.abort_flag, status, code)) != 0;
       };
-      TDECL;
       for (int n = 0; n < NC; ++n) {
         const int b = n & 1;
         const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
-        TICK(0);
         // S^T (bf16) of chunk n is in place and the O accumulator has been read out
         bool ok = wait_all(&s.bar_wq[b], ph2, kWaitWq);
-        TICK(1);
         ok = ok && wait_all(&s.bar_sb, ph, kWaitSb);
-        TICK(2);
         if (ok) {
           tc::tc_fence_after_sync();
           // one N = 128 product: columns [128,192) = (W S)^T, [192,256) = (Qg S)^T
           tc::mma_f16_ts_ktile_warp(tc::tmem_addr(tm, 0, kColWs), a_sb, tc::smem_u32(s.wq[b]), 2 * BS, D, idesc_n128, false);
           tc::mma_commit_warp(&s.bar_m1);
         }
-        TICK(3);
-#ifdef GDN2_SCAN_TIMING
-        wait_all(&s.bar_m1, ph, kWaitM1);
-        TICK(9);
-#endif
-        ok = wait_all(&s.bar_kgt[b], ph2, kWaitKgt);
-        TICK(4);
+        ok = output_only || wait_all(&s.bar_kgt[b], ph2, kWaitKgt);
         ok = ok && wait_all(&s.bar_un, ph, kWaitUn);
-        TICK(5);
-        if (ok) {
+        if (ok && !output_only) {
           tc::tc_fence_after_sync();
           tc::mma_f16_ts_ktile_warp(tc::tmem_addr(tm, 0, 0), a_un16, tc::smem_u32(s.kgt[b]), D, BS, idesc_f16, false);
           tc::mma_commit_warp(&s.bar_m3);
         }
-        TICK(6);
         ok = ok && wait_all(&s.bar_aqk, ph, kWaitAqk);
-        TICK(7);
         if (ok) {
+          tc::tc_fence_after_sync();
           tc::mma_f16_ts_ktile_warp(tc::tmem_addr(tm, 0, kColO), a_un16, a_aqk, BS, BS, idesc_f16_n64, true);
           tc::mma_commit_warp(&s.bar_m2);
         }
-        TICK(8);
       }
-      if (lane == 0) TFLUSH(0);
     }
   } else if (wid >= 10) {
     // =============================== output warps: O^T -> bf16 rows in global memory =============
@@ -253,9 +301,9 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
 #pragma unroll
       for (int i = 0; i < 64; ++i) s.ostage[i * D + dv] = __float2bfloat16_rn(ov[i]);
       output_sync();
-      if (!s.abort_flag) {
+      if (write_o && !s.abort_flag) {
         // 64 rows x 256 bytes = 1024 16-byte pieces, 8 per thread, 128-bit coalesced stores
-        __nv_bfloat16* obase = o + (((size_t)ib * o_bs + (size_t)n * BS) * H + ih) * D;
+        __nv_bfloat16* obase = o + (((size_t)ib * o_bs + (size_t)(c_first + n) * BS) * H + ih) * D;
 #pragma unroll
         for (int x = 0; x < 8; ++x) {
           const int piece = otid + x * kOutputThreads;
@@ -275,10 +323,13 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
 
     // The fp32 state: S[i] = S^T[dv][dkp + i]. It never leaves these registers between chunks.
     float S[64];
+    int last_big = -1;                                     // transition blocks: see ScanTcSmem::last_big
     {
-      float* h0 = hs ? hs + (((size_t)ib * NC + 0) * H + ih) * D * D : nullptr;
+      float* h0 = (hs && !output_only) ? hs + (((size_t)ib * NC_all + c_first) * H + ih) * D * D : nullptr;
+      const float* init = state_source();
 #pragma unroll
-      for (int i = 0; i < 64; ++i) S[i] = s0 ? s0[((size_t)bh * D + dkp + i) * D + dv] : 0.f;
+      for (int i = 0; i < 64; ++i)
+        S[i] = init ? init[(size_t)(dkp + i) * D + dv] : (transition && dkp + i == dv) ? 1.f : 0.f;
       if (h0) {
 #pragma unroll
         for (int i = 0; i < 64; ++i) h0[(size_t)(dkp + i) * D + dv] = S[i];
@@ -291,24 +342,32 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
     }
     tc::tc_fence_before_sync();
     warp_arrive(&s.bar_sb, lane);
-
-    TDECL;
     for (int n = 0; n < NC; ++n) {
-      TICK(0);
       const int b = n & 1;
       const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
       const bool more = n + 1 < NC;
 
+      if (output_only && more) {
+        // the state entering the next chunk comes from memory; its bf16 copy of this chunk is already in tensor
+        // memory, so the registers are free and the loads fly while this chunk's products run
+        const float* hn = hs + (((size_t)ib * NC_all + (c_first + n + 1)) * H + ih) * D * D;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) S[i] = __ldg(hn + (size_t)(dkp + i) * D + dv);
+      }
+
       // ---- Un^T / 256 = U^T / 256 - (W S)^T / 256 for this thread's 32 tokens, as the fp16 operand of
       // both the state update and the output product
-      tc::mbar_wait(&s.bar_ut[b], ph2, &s.abort_flag, status, kWaitUt);
-      TICK(2);
       uint4 uraw[4];
+      if (!transition) {
+        tc::mbar_wait(&s.bar_ut[b], ph2, &s.abort_flag, status, kWaitUt);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) uraw[j] = *reinterpret_cast<const uint4*>(&s.ut[b][((tokp / 8 + j) * D + dv) * 8]);
+        for (int j = 0; j < 4; ++j) uraw[j] = *reinterpret_cast<const uint4*>(&s.ut[b][((tokp / 8 + j) * D + dv) * 8]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) uraw[j] = make_uint4(0u, 0u, 0u, 0u);
+      }
       tc::mbar_wait(&s.bar_m1, ph, &s.abort_flag, status, kWaitM1);
       tc::tc_fence_after_sync();
-      TICK(3);
       {
         float ws[32];
         tc::tmem_ld32(t_lane + kColWs + tokp, ws);
@@ -327,15 +386,27 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
         tc::tmem_st_wait();
         tc::tc_fence_before_sync();
         warp_arrive(&s.bar_un, lane);
-        TICK(4);
+      }
+
+      if (output_only) {
+        // MMA1 of this chunk has completed (waited above): its S^T operand may be replaced
+        if (more) {
+          float pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pk[i] = pack_bf16x2(S[2 * i], S[2 * i + 1]);
+          tc::tmem_st32(t_lane + kColSb + dkp / 2, pk);
+          tc::tmem_st_wait();
+          tc::tc_fence_before_sync();
+          warp_arrive(&s.bar_sb, lane);
+        }
+        if (s.abort_flag) break;
+        continue;
       }
 
       // ---- new state S <- gamma_C * S + P, its bf16 operand copy for the next chunk, optional snapshot
       tc::mbar_wait(&s.bar_kgt[b], ph2, &s.abort_flag, status, kWaitKgt);   // gamma arrived with KG^T
-      TICK(5);
       tc::mbar_wait(&s.bar_m3, ph, &s.abort_flag, status, kWaitM3);
       tc::tc_fence_after_sync();
-      TICK(7);
       {
         const float* gln = s.gl[n & 3];
 #pragma unroll
@@ -363,27 +434,103 @@ scan_tc_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, __nv_bfloat16
           tc::tc_fence_before_sync();
           warp_arrive(&s.bar_sb, lane);
         }
-        TICK(8);
-        float* hn = (hs && more) ? hs + (((size_t)ib * NC + (n + 1)) * H + ih) * D * D : nullptr;
-        float* fin = (!more && sT) ? sT + (size_t)bh * D * D : nullptr;
+        float* hn = (hs && more) ? hs + (((size_t)ib * NC_all + (c_first + n + 1)) * H + ih) * D * D : nullptr;
         if (hn) {
 #pragma unroll
           for (int i = 0; i < 64; ++i) hn[(size_t)(dkp + i) * D + dv] = S[i];
         }
-        if (fin) {
+        if (!more) {
+          float* fin = state_sink();
+          if (fin) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) fin[(size_t)(dkp + i) * D + dv] = S[i];
+            for (int i = 0; i < 64; ++i) fin[(size_t)(dkp + i) * D + dv] = S[i];
+          }
+        }
+        if (transition) {
+          // has the running transition matrix vanished? (positive floats order like their bit patterns)
+          float m = 0.f;
+#pragma unroll
+          for (int i = 0; i < 64; ++i) m = fmaxf(m, fabsf(S[i]));
+          if (__reduce_max_sync(0xffffffffu, __float_as_uint(m)) >= __float_as_uint(kVanish)) last_big = n;
         }
       }
-      TICK(9);
       if (s.abort_flag) break;                             // per thread: no block-level barrier in this loop
     }
-    if (tid == 0) TFLUSH(16);
+    if (lane == 0) s.last_big[wid] = last_big;
   }
 
   tc::tc_fence_before_sync();
   __syncthreads();
   if (wid == 0) tc::tmem_dealloc(tm, 512);
+  if (transition && tid == 0) {
+    // Chunks the correction pass must redo: through the last chunk whose ENTERING state still carried a
+    // visible share of the segment's entering state, i.e. one past the last chunk after which the transition
+    // matrix was still visible; chunk 0 always (it starts from the true state).
+    int last = -1;
+    for (int i = 0; i < kComputeThreads / 32; ++i) last = s.last_big[i] > last ? s.last_big[i] : last;
+    const int redo = last + 2;
+    P.seg_stop[bh * plan.nseg + seg] = redo < NC ? redo : NC;
+  }
+}
+
+// Pass 2 of the cut scan: chains the segments' affine maps in fp32. Block (bh, column slice of 16 value
+// channels): S = C_0 (segment 0 ran from the true initial state); for j = 1 .. nseg-1: the state entering
+// segment j is S; S <- T_j S + C_j (T_j skipped where the transition block saw it vanish). The value
+// columns evolve independently, so the slices need no exchange.
+constexpr int kCombineCols = 16;
+constexpr int kTPad = D + 1;
+__global__ void __launch_bounds__(256)
+scan_combine_kernel(WsPtrs P, int nseg, int NC_all, float* __restrict__ sT) {
+  extern __shared__ __align__(16) float csm[];
+  float* Ts = csm;                         // [128][129] transition matrix of the current segment
+  float* Ss = csm + D * kTPad;             // [128][16] current state slice
+  const int bh = blockIdx.x, col0 = blockIdx.y * kCombineCols;
+  const int tid = threadIdx.x, r = tid & (D - 1), cg = tid >> 7;      // row, 8-column group
+  const size_t rec0 = (size_t)bh * nseg * D * D;
+  float acc[8];
+  {
+    const float* c0p = P.seg_c + rec0 + (size_t)r * D + col0 + 8 * cg;
+    const float4 a = *reinterpret_cast<const float4*>(c0p), b = *reinterpret_cast<const float4*>(c0p + 4);
+    acc[0] = a.x; acc[1] = a.y; acc[2] = a.z; acc[3] = a.w; acc[4] = b.x; acc[5] = b.y; acc[6] = b.z; acc[7] = b.w;
+  }
+  for (int j = 1; j < nseg; ++j) {
+    const size_t rec = rec0 + (size_t)j * D * D;
+    float* inp = P.seg_in + rec + (size_t)r * D + col0 + 8 * cg;
+    *reinterpret_cast<float4*>(inp) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(inp + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    const int len = (int)((int64_t)NC_all * (j + 1) / nseg) - (int)((int64_t)NC_all * j / nseg);
+    const bool vanished = P.seg_stop[bh * nseg + j] < len;             // uniform over the block
+    const float* cp = P.seg_c + rec + (size_t)r * D + col0 + 8 * cg;
+    const float4 ca = *reinterpret_cast<const float4*>(cp), cb = *reinterpret_cast<const float4*>(cp + 4);
+    if (vanished) {
+      acc[0] = ca.x; acc[1] = ca.y; acc[2] = ca.z; acc[3] = ca.w; acc[4] = cb.x; acc[5] = cb.y; acc[6] = cb.z; acc[7] = cb.w;
+      continue;
+    }
+    __syncthreads();                       // the previous segment's Ts / Ss have been read
+#pragma unroll
+    for (int i = 0; i < 8; ++i) Ss[r * kCombineCols + 8 * cg + i] = acc[i];
+    const float* tp = P.seg_t + rec;
+    for (int idx = tid; idx < D * D / 4; idx += 256) {                 // coalesced 128-bit reads, padded rows
+      const float4 t4 = *reinterpret_cast<const float4*>(tp + (size_t)idx * 4);
+      float* d = Ts + (idx >> 5) * kTPad + (idx & 31) * 4;
+      d[0] = t4.x; d[1] = t4.y; d[2] = t4.z; d[3] = t4.w;
+    }
+    __syncthreads();
+    acc[0] = ca.x; acc[1] = ca.y; acc[2] = ca.z; acc[3] = ca.w; acc[4] = cb.x; acc[5] = cb.y; acc[6] = cb.z; acc[7] = cb.w;
+#pragma unroll 4
+    for (int kk = 0; kk < D; ++kk) {
+      const float t = Ts[r * kTPad + kk];
+      const float4 sa = *reinterpret_cast<const float4*>(&Ss[kk * kCombineCols + 8 * cg]);
+      const float4 sb = *reinterpret_cast<const float4*>(&Ss[kk * kCombineCols + 8 * cg + 4]);
+      acc[0] = fmaf(t, sa.x, acc[0]); acc[1] = fmaf(t, sa.y, acc[1]); acc[2] = fmaf(t, sa.z, acc[2]); acc[3] = fmaf(t, sa.w, acc[3]);
+      acc[4] = fmaf(t, sb.x, acc[4]); acc[5] = fmaf(t, sb.y, acc[5]); acc[6] = fmaf(t, sb.z, acc[6]); acc[7] = fmaf(t, sb.w, acc[7]);
+    }
+  }
+  if (sT) {
+    float* fp = sT + ((size_t)bh * D + r) * D + col0 + 8 * cg;
+    *reinterpret_cast<float4*>(fp) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4*>(fp + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
 }
 
 }  // namespace
@@ -393,16 +540,45 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
   const size_t smem = sizeof(ScanTcSmem) + 128;
   GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  scan_tc_kernel<<<B * H, kThreads, smem, st>>>(L, P, s0, static_cast<__nv_bfloat16*>(o), sT, hs, S, H, o_bs,
-                                                device_status_word());
+  __nv_bfloat16* ob = static_cast<__nv_bfloat16*>(o);
+  uint32_t* status = device_status_word();
+  const int BH = B * H;
+  // chunk states are a by-product of the one-block-per-head walk only
+  const int nseg = hs ? 1 : L.nseg;
+  if (nseg <= 1) {
+    scan_tc_kernel<<<BH, kThreads, smem, st>>>(L, P, ScanPlan{kWhole, 1}, s0, ob, sT, hs, S, H, o_bs, status);
+    GDN2_CUDA_TRY(cudaGetLastError());
+    return GDN2_OK;
+  }
+  scan_tc_kernel<<<BH * (2 * nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kFirst, nseg}, s0, ob, nullptr, nullptr,
+                                                             S, H, o_bs, status);
+  GDN2_CUDA_TRY(cudaGetLastError());
+  const size_t csmem = (size_t)(D * kTPad + D * kCombineCols) * sizeof(float);
+  GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
+  scan_combine_kernel<<<dim3(BH, D / kCombineCols), 256, csmem, st>>>(P, nseg, S / BS, sT);
+  GDN2_CUDA_TRY(cudaGetLastError());
+  scan_tc_kernel<<<BH * (nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kRedo, nseg}, nullptr, ob, nullptr, nullptr,
+                                                         S, H, o_bs, status);
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }
 
-#ifdef GDN2_SCAN_TIMING
-extern "C" int gdn2_debug_scan_timing(unsigned long long* out32) {
-  return cudaMemcpyFromSymbol(out32, g_scan_timing, sizeof(unsigned long long) * 32) == cudaSuccess ? 0 : -6;
+// Chunk-parallel output from stored chunk states on the tensor-core family: the scan kernel's chunk body without
+// the state update, every block walking a run of chunks of one (batch, head) with the records prefetched a chunk ahead.
+int launch_output_tc(const WsLayout& L, const WsPtrs& P, const float* hs, void* o, int B, int S, int H, int64_t o_bs,
+                     cudaStream_t st) {
+  if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
+  const size_t smem = sizeof(ScanTcSmem) + 128;
+  GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int BH = B * H, NC = S / BS;
+  // enough runs to give every SM a few blocks, none shorter than 4 chunks
+  int runs = (4 * device_sm_count() + BH - 1) / BH;
+  if (runs > NC / 4) runs = NC / 4;
+  if (runs < 1) runs = 1;
+  scan_tc_kernel<<<BH * runs, kThreads, smem, st>>>(L, P, ScanPlan{kOutput, runs}, nullptr, static_cast<__nv_bfloat16*>(o),
+                                                   nullptr, const_cast<float*>(hs), S, H, o_bs, device_status_word());
+  GDN2_CUDA_TRY(cudaGetLastError());
+  return GDN2_OK;
 }
-#endif
 
 }  // namespace gdn2

@@ -124,7 +124,30 @@ selftest_kernel(const float* __restrict__ a, const float* __restrict__ bt, float
   if (wid == 0) tc::tmem_dealloc(tm, 512);
 }
 
+// A wait that nothing satisfies: the barrier expects one arrival and nobody arrives. The bounded wait gives up
+// after `limit_cycles`, records `kWaitSelftest` in the status word, and the block returns normally.
+constexpr uint32_t kWaitSelftest = 0x80000000u;
+__global__ void __launch_bounds__(64)
+selftest_wait_kernel(long long limit_cycles, uint32_t* status, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&bar, 1);
+    abort_flag = 0;
+    tc::mbar_init_fence();
+  }
+  __syncthreads();
+  const bool ok = tc::mbar_wait_limit(&bar, 0, &abort_flag, status, kWaitSelftest, limit_cycles);
+  if (!ok && gave_up) atomicAdd(gave_up, 1);
+}
+
 }  // namespace
+
+int launch_selftest_wait(long long limit_cycles, int* gave_up, cudaStream_t st) {
+  selftest_wait_kernel<<<1, 64, 0, st>>>(limit_cycles, device_status_word(), gave_up);
+  GDN2_CUDA_TRY(cudaGetLastError());
+  return GDN2_OK;
+}
 
 int launch_selftest_mma(const float* a, const float* bt, float* out, cudaStream_t st) {
   const size_t smem = sizeof(SelfSmem) + 1024;

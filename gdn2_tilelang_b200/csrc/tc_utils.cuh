@@ -49,20 +49,24 @@ constexpr long long kWaitCycles = 400LL * 1000 * 1000;
 // Bounded wait. `abort_flag` is a shared-memory word shared by the whole block: once any wait has
 // run out every later wait returns false at once, so a broken pipeline drains in bounded time.
 // On the first failure `code` is OR-ed into the device status word.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          uint32_t* status_word, uint32_t code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                uint32_t* status_word, uint32_t code, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;   // the common case costs one probe and no shared-memory load
   if (*abort_flag) return false;
   const long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > kWaitCycles) {
+    if (clock64() - t0 > limit_cycles) {
       *abort_flag = 1;
       atomicOr(status_word, code);
       return false;
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t* status_word, uint32_t code) {
+  return mbar_wait_limit(bar, parity, abort_flag, status_word, code, kWaitCycles);
 }
 
 // ------------------------------------------------------------------ proxy / tcgen05 fences

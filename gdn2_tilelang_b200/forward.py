@@ -46,6 +46,7 @@ def chunk_gdn2_fwd(q, k, v, g, b, w, scale, initial_state=None, output_final_sta
         elif n_full == 0:
             state = state.to(torch.float32).clone()   # never write into the caller's initial state
         K.decode(*(t[:, n_full:] for t in (q, k, v, g, b, w)), state, scale, out=o[:, n_full:])
+    K.maybe_check_device_status(q.device)
     final = state if output_final_state else None
     return (o, final, hs) if return_chunk_states else (o, final)
 

@@ -46,7 +46,10 @@ def gdn2_decode(q, k, v, g, b, w, state, scale=None):
     scale = DK**-0.5 if scale is None else scale
     if state.shape != (B, H, DK, DV):
         raise ValueError(f"state must have shape {(B, H, DK, DV)}, got {tuple(state.shape)}")
-    return _cabi.kernels().decode(q, k, v, g.float(), b, w, state, scale)
+    K = _cabi.kernels()
+    o = K.decode(q, k, v, g.float(), b, w, state, scale)
+    K.maybe_check_device_status(q.device)
+    return o
 
 
 def gdn2_decode_step(q, k, v, g, b, w, state, scale=None):
@@ -83,6 +86,7 @@ def gdn2_prefill(q, k, v, g, b, w, state=None, scale=None, config: GDN2Config = 
                                       out=o, out_batch_stride=S)
     if S > n_full:
         K.decode(*(t[:, n_full:] for t in (q, k, v, g, b, w)), state, scale, out=o[:, n_full:])
+    K.maybe_check_device_status(q.device)
     return o, state
 
 

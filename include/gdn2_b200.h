@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define GDN2_B200_ABI_VERSION 1
+#define GDN2_B200_ABI_VERSION 2
 
 /* element type of q, k, v, b, w and o */
 enum gdn2_dtype { GDN2_F32 = 0, GDN2_BF16 = 1, GDN2_F16 = 2 };
@@ -49,8 +49,12 @@ enum gdn2_status {
 
 /* Which kernel family runs the chunkwise prefill. AUTO picks the tcgen05 family when the shape
  * allows it (DK = DV = 128, bf16) and the SIMT family otherwise. The explicit values exist so the
- * two families can be cross-checked against each other; both are hand-written CUDA for sm_100a. */
-enum gdn2_prefill_path { GDN2_PATH_AUTO = 0, GDN2_PATH_SIMT = 1, GDN2_PATH_TCGEN05 = 2 };
+ * two families can be cross-checked against each other; both are hand-written CUDA for sm_100a.
+ * TCGEN05_SERIAL is the tcgen05 family with the scan forced to walk each (batch, head) in one
+ * block; TCGEN05 (and AUTO) cut the sequence into segments scanned in parallel when a GPU holds so
+ * few (batch, head) pairs that most SMs would idle (see gdn2_prefill_scan). Pass the SAME path to
+ * gdn2_prefill_workspace_bytes, gdn2_chunk_prep and gdn2_prefill_scan of one problem. */
+enum gdn2_prefill_path { GDN2_PATH_AUTO = 0, GDN2_PATH_SIMT = 1, GDN2_PATH_TCGEN05 = 2, GDN2_PATH_TCGEN05_SERIAL = 3 };
 
 /* ABI version of the loaded library (== GDN2_B200_ABI_VERSION it was built with). */
 int gdn2_abi_version(void);
@@ -79,6 +83,29 @@ int gdn2_decode(const void* q, const void* k, const void* v, const float* g, con
 size_t gdn2_prefill_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path);
 
 /*
+ * Byte offsets of the record arrays inside the workspace, for tools and tests that inspect the
+ * intermediates: out8 = { WQ, AQK, KG^T, U^T, gamma_last, flags, segment records, total bytes }.
+ * Records are indexed by chunk-head ch = (b*H + h)*(S/64) + n. Tensor-core family (DK = DV = 128, bf16):
+ *   WQ    32 KiB  bf16 [dk/8][128 rows][8]: rows 0..63 = W of token r, rows 64..127 = scale*q*gamma of token r-64
+ *   AQK    8 KiB  fp16 [s/8][64 r][8]:  256 * Aqk[r, s], lower triangular including the diagonal
+ *   KG^T  16 KiB  fp16 [t/8][128 dk][8]: 256 * k[t, dk] * gamma_last[dk] / gamma[t, dk]
+ *   U^T   16 KiB  fp16 [t/8][128 dv][8]: U[t, dv] / 256
+ *   gamma_last 512 B fp32 [dk]
+ * SIMT family: the same images with 4-byte elements ([x/4][rows][4]) and no scaling.
+ * No counterpart in the reference, whose intermediates are separate tensors (gdn2/forward.py:756-829).
+ */
+int gdn2_prefill_workspace_layout(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path,
+                                  int64_t* out8);
+
+/*
+ * Number of sequence segments gdn2_prefill_scan cuts this problem into (1 = one block per (batch, head)
+ * walks the whole sequence; 0 for an unsupported combination). A caller that overlaps the two stages of
+ * its own sequence segments on two streams uses this to see that the scan already fills the GPU.
+ * No counterpart in the reference.
+ */
+int gdn2_prefill_scan_segments(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path);
+
+/*
  * Chunk-local stage of the chunkwise forward (chunk = 64 tokens): cumulative log2 decay, the
  * intra-chunk matrices Aqk / Akk, the (I + Akk)^-1 solve and the WY factors W, U, KG, plus the
  * decayed queries, written into `workspace` in the operand layout the scan consumes.
@@ -97,6 +124,13 @@ int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g,
  *   chunk_states   [B,S/64,H,DK,DV] fp32 or NULL; when given, the state entering every chunk is stored
  * Replaces prefill_scan_kernel (gdn2/inference.py:356-479) and, with chunk_states, the
  * state_kernel + output_kernel pair of the training-style forward (gdn2/forward.py:538-727).
+ *
+ * Few (batch, head) pairs (B*H <= 36, sequences of 16 chunks or more, tcgen05 family, no chunk_states):
+ * the sequence is cut into segments. Every segment is scanned from a zero state while a second block
+ * accumulates the segment's state-transition matrix; a small kernel chains the segments' affine maps
+ * and a last launch redoes, from the true entering state, the leading chunks of each segment that the
+ * entering state still reaches. The result equals the one-block walk up to the rounding of the state
+ * hand-over (below 1e-6 of the state); the form used is reported by gdn2_prefill_scan_segments.
  */
 int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
                       float* final_state, float* chunk_states, int64_t B, int64_t S, int64_t H, int64_t DK,
@@ -129,6 +163,15 @@ int gdn2_check_device_status(void* stream, uint32_t* detail);
 int gdn2_selftest_mma(const float* a, const float* bt, float* out, void* stream);
 
 /*
+ * Self-test of the failure path: one small block waits, with a limit of `limit_cycles` SM clock cycles
+ * (1 .. 2e9), on a barrier that nothing ever satisfies. The wait gives up, the block returns normally, the
+ * device stays usable, and the next gdn2_check_device_status reports GDN2_ERR_DEVICE_WAIT with bit 31
+ * of the detail word set. `gave_up` (device pointer to an int, may be NULL) is incremented once per
+ * thread whose wait ran out (64 threads). No counterpart in the reference.
+ */
+int gdn2_selftest_wait(int64_t limit_cycles, int* gave_up, void* stream);
+
+/*
  * Whole-chunk prefill that allocates nothing and asks the caller for no workspace: the chunk-local
  * stage and the fused scan of gdn2_chunk_prep + gdn2_prefill_scan, exchanging their intermediates
  * through a fixed scratch array built into the library. It has no counterpart in the reference.
@@ -147,7 +190,12 @@ int gdn2_selftest_mma(const float* a, const float* bt, float* out, void* stream)
  * array until the process exits.
  *
  * The first call on each device resolves the array's device address (cudaGetSymbolAddress) with
- * that device current; make that first call outside any stream capture. All calls on a device
+ * that device current; make that first call outside any stream capture. That first call is also the
+ * moment the CUDA driver brings the library's device image -- and with it the 32 MiB array -- into
+ * device memory (module loading is lazy by default), so it is a warm-up that DOES take device memory:
+ * make it at start-up, before the rest of HBM is handed to a pool (a tiny problem is enough); if it
+ * comes later and no memory is left it returns GDN2_ERR_CUDA. Every later call on that device
+ * allocates nothing. All calls on a device
  * share the one array, which keeps whatever the previous call left in it: each call rewrites every
  * record it later reads, so nothing needs clearing, but two calls that overlap on the GPU (different
  * streams, or concurrent host threads) race on it -- serialise them.

@@ -49,3 +49,15 @@ def golden_checksum(*tensors):
 def golden_state(B, H, DK, DV, seed, std):
     gen = torch.Generator(device="cpu").manual_seed(1000 + seed)
     return torch.randn(B, H, DK, DV, generator=gen) * std
+
+
+def note(test, **values):
+    """Append measured error figures to the file named by ``GDN2_TEST_NOTES`` (one JSON object per line), so a
+    run leaves a record of how far inside its tolerances every comparison landed. No-op without the variable."""
+    import json
+    import os
+
+    path = os.environ.get("GDN2_TEST_NOTES")
+    if path:
+        with open(path, "a") as f:
+            f.write(json.dumps({"test": test, **{k: (float(v) if hasattr(v, "__float__") else v) for k, v in values.items()}}) + "\n")

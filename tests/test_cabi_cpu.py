@@ -86,3 +86,45 @@ def test_dtype_codes():
     assert _cabi.dtype_code(torch.float32) == 0 and _cabi.dtype_code(torch.bfloat16) == 1
     with pytest.raises(TypeError):
         _cabi.dtype_code(torch.float64)
+
+
+def test_batch_times_heads_limit_is_a_clear_status(lib):
+    """The chunk-local kernels put (batch, head) on gridDim.y: more than 65535 pairs is refused as a bad shape
+    before anything is enqueued, not reported as a failed launch."""
+    one = ctypes.c_void_p(16)
+    assert lib.gdn2_prefill_workspace_bytes(4095, 64, 16, 128, 128, _cabi.GDN2_BF16, 0) > 0       # 65520 pairs
+    assert lib.gdn2_prefill_workspace_bytes(4096, 64, 16, 128, 128, _cabi.GDN2_BF16, 0) == 0      # 65536 pairs
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 1 << 40, 4097, 64, 16, 128, 128, 64, 1.0, 1, 0, None) == -2
+    assert lib.gdn2_prefill_scan(one, 1 << 40, None, one, None, None, 4097, 64, 16, 128, 128, 64, 1, 0, None) == -2
+
+
+def test_scan_segments_rule(lib):
+    """How the tensor-core scan cuts a sequence: only with few (batch, head) pairs and long sequences, never for
+    the SIMT family or the explicitly serial path; the workspace grows by the segment records and nothing else."""
+    f = lib.gdn2_prefill_scan_segments
+    bf = _cabi.GDN2_BF16
+    assert f(4, 16000, 16, 128, 128, bf, _cabi.PATH_AUTO) == 1       # 64 pairs: one block per pair fills the chain
+    assert f(4, 16000, 8, 128, 128, bf, _cabi.PATH_AUTO) == 2        # 32 pairs
+    assert f(4, 16000, 4, 128, 128, bf, _cabi.PATH_AUTO) == 5        # 16 pairs: 9 blocks each = 144
+    assert f(4, 16000, 2, 128, 128, bf, _cabi.PATH_AUTO) == 9        # 8 pairs: 17 blocks each = 136
+    assert f(1, 16000, 1, 128, 128, bf, _cabi.PATH_AUTO) == 16       # capped
+    assert f(4, 64 * 15, 2, 128, 128, bf, _cabi.PATH_AUTO) == 1      # shorter than two 8-chunk segments
+    assert f(4, 64 * 24, 2, 128, 128, bf, _cabi.PATH_AUTO) == 3
+    assert f(4, 16000, 2, 128, 128, bf, _cabi.PATH_TCGEN05_SERIAL) == 1
+    assert f(4, 16000, 2, 64, 64, bf, _cabi.PATH_AUTO) == 1          # SIMT family
+    assert f(4, 100, 2, 128, 128, bf, _cabi.PATH_AUTO) == 0          # invalid shape
+    w = lib.gdn2_prefill_workspace_bytes
+    cut, serial = w(4, 16000, 2, 128, 128, bf, _cabi.PATH_TCGEN05), w(4, 16000, 2, 128, 128, bf, _cabi.PATH_TCGEN05_SERIAL)
+    want = 8 * 9 * (3 * 128 * 128 * 4 + 4)
+    assert want <= cut - serial <= want + 1024
+    out = (ctypes.c_int64 * 8)()
+    assert lib.gdn2_prefill_workspace_layout(4, 16000, 2, 128, 128, bf, _cabi.PATH_TCGEN05, out) == 0
+    offs = list(out)
+    assert offs == sorted(offs) and offs[0] == 0 and offs[7] == cut and offs[6] == serial
+    assert lib.gdn2_prefill_workspace_layout(4, 100, 2, 128, 128, bf, 0, out) == -2
+    assert lib.gdn2_prefill_workspace_layout(4, 128, 2, 128, 128, bf, 0, None) == -1
+
+
+def test_wait_selftest_rejects_unbounded_limits(lib):
+    assert lib.gdn2_selftest_wait(0, None, None) == -2
+    assert lib.gdn2_selftest_wait(3_000_000_000, None, None) == -2

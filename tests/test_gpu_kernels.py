@@ -12,7 +12,7 @@ import torch
 import gdn2_tilelang_b200 as gdn2
 from gdn2_tilelang_b200 import _cabi
 from oracle import gdn2_oracle as orc
-from tests.conftest import golden_state, load_golden
+from tests.conftest import golden_state, load_golden, note
 from tests.golden.make_golden import CORE_CASES, DECODE_CASES, PREFILL_CASES
 
 pytestmark = pytest.mark.gpu
@@ -357,3 +357,210 @@ def test_zero_gates_only_decay_large(K):
                                initial_state=s0.to(DEV), output_final_state=True)
     want = s0 * host[3].sum(dim=1).exp().unsqueeze(-1)
     assert orc.rel_fro_err(s.cpu(), want) < STATE_FRO
+
+
+# ---- chunk-local intermediates against the stored intermediates of the reference ------------------------
+
+
+def test_workspace_records_match_reference_intermediates(K):
+    """The records the chunk-local stage hands to the scan, de-scaled, against (a) the oracle's factors on the
+    same bf16-rounded inputs and (b) the reference's own forward_intermediates stored in the golden file (those
+    come from unrounded fp32 inputs, so the bf16 input rounding is allowed on top)."""
+    from tests.ws_records import decode_tc_workspace
+
+    B, S, H, D = 1, 128, 2, 128
+    gold = load_golden("d128_s128_h2")
+    q, k, v, g, b, w = orc.make_inputs(B, S, H, D, D, seed=0)
+    host = tuple(t.bfloat16().float() for t in (q, k, v)) + (g, b.bfloat16().float(), w.bfloat16().float())
+    dev = tuple(t.bfloat16().to(DEV) for t in (q, k, v)) + (g.to(DEV), b.bfloat16().to(DEV), w.bfloat16().to(DEV))
+    ws, p = K.chunk_prep(*dev, D**-0.5, path="tcgen05")
+    K.check_device_status()
+    rec = decode_tc_workspace(ws, K.workspace_layout(B, S, H, D, D, torch.bfloat16, p), B, S, H)
+    assert int(rec["flags"].sum()) == 0
+    f = orc.chunk_factors(*host)
+    # relative to the largest entry of each matrix: bf16 records carry 8 bits, fp16 ones 11
+    tight = {"Aqk": 2e-3, "W": 6e-3, "Qg": 6e-3, "U": 3e-3, "KG": 2e-3, "gamma_last": 1e-5}
+    for name, tol in tight.items():
+        assert orc.rel_max_err(rec[name], f[name]) < tol, name
+    for mine, theirs in (("Aqk", "Aqk"), ("W", "W"), ("U", "U"), ("KG", "Ktail")):
+        assert orc.rel_max_err(rec[mine], gold[f"f_{theirs}"]) < 2e-2, mine
+
+
+def test_burst_decay_across_sub_block_references(K):
+    """Two decay steps of about 2^-90 placed right after the reference row of one 16-token sub-block and right
+    before the reference row of the next, no decay elsewhere: every half sub-block stays inside the factorised
+    range, but consecutive reference rows are about 2^-180 apart. Keys between the two steps still pair with
+    the rows before the second step through factors that are normal numbers; they must not vanish."""
+    B, S, H, D = 1, 128, 2, 128
+    q, k, v, g, b, w = orc.make_inputs(B, S, H, D, D, seed=29)
+    big = -90.0 * 0.6931471805599453
+    for per_head in (False, True):
+        g2 = torch.zeros_like(g)
+        g2[:, 16 + 9] = big              # sub-block 1: rows 0..8 at G = 0, rows 9..15 at -90 (log2)
+        g2[:, 32 + 8] = big              # sub-block 2: rows 0..7 at -90, rows 8.. at -180
+        g2[:, 64 + 32 + 9] = big         # the same pattern in the second chunk, one sub-block later
+        g2[:, 64 + 48 + 8] = big
+        if not per_head:                 # per-channel variant: only half of the channels burst
+            g2[..., ::2] = 0.0
+        host = tuple(t.bfloat16().float() for t in (q, k, v)) + (g2, b.bfloat16().float(), w.bfloat16().float())
+        dev = tuple(t.bfloat16().to(DEV) for t in (q, k, v)) + (g2.to(DEV), b.bfloat16().to(DEV), w.bfloat16().to(DEV))
+        o_ref, s_ref = orc.recurrence(*host)
+        res = _run_paths(K, dev, None)
+        for p, (o, s, _) in res.items():
+            assert torch.isfinite(o).all(), p
+            assert orc.max_abs_err(o, o_ref) < O_ABS_BF16, (p, per_head)
+            assert orc.rel_fro_err(s, s_ref) < STATE_FRO, (p, per_head)
+        from tests.ws_records import decode_tc_workspace
+        ws, p = K.chunk_prep(*dev, D**-0.5, path="tcgen05")
+        rec = decode_tc_workspace(ws, K.workspace_layout(B, S, H, D, D, torch.bfloat16, p), B, S, H)
+        assert int(rec["flags"].sum()) == 0          # the tensor-core path itself handled these chunks
+        f = orc.chunk_factors(*host)
+        assert orc.rel_max_err(rec["Aqk"], f["Aqk"]) < 2e-3, per_head
+
+
+# ---- chunk-parallel output on the tensor-core family -------------------------------------------------------
+
+
+def test_chunk_output_tcgen05_vs_oracle(K):
+    """gdn2_chunk_output on the 16-bit workspace (tcgen05 products) from stored chunk states: against the
+    oracle's outputs, and from the ORACLE's chunk states, so the check does not lean on this library's scan."""
+    B, S, H, D = 2, 64 * 24, 3, 128
+    dev, host = bf16_inputs(B, S, H, D, D, seed=37)
+    s0 = golden_state(B, H, D, D, 37, 0.1)
+    o_ref, _, h_ref = orc.chunkwise(*host, None, s0, return_chunk_states=True)
+    o = K.chunk_output(*dev, D**-0.5, h_ref.to(DEV), path="tcgen05")
+    K.check_device_status()
+    assert o.dtype == torch.bfloat16
+    assert orc.max_abs_err(o.float().cpu(), o_ref) < O_ABS_BF16
+    o_simt = K.chunk_output(*dev, D**-0.5, h_ref.to(DEV), path="simt")
+    assert orc.max_abs_err(o_simt.float().cpu(), o_ref) < O_ABS_BF16
+
+
+# ---- the scan cut into sequence segments ------------------------------------------------------------------
+
+
+@pytest.mark.parametrize("B,H,NC,decay", [(1, 2, 40, "bench"), (2, 4, 72, "bench"), (1, 1, 130, "bench"),
+                                          (1, 2, 40, "slow"), (2, 2, 64, "none"), (4, 2, 250, "bench")])
+def test_scan_cut_into_segments_matches_one_block_walk_and_oracle(K, B, H, NC, decay):
+    """Few (batch, head) pairs: the scan cuts the sequence (transition matrices + correction pass). Against the
+    one-block-per-head walk of the same workspace and against the oracle, for gates that let the carried state
+    vanish within a few chunks ("bench"), that keep it alive across whole segments ("slow": the correction pass
+    redoes everything) and for no decay at all."""
+    S, D = 64 * NC, 128
+    q, k, v, g, b, w = orc.make_inputs(B, S, H, D, D, seed=41 + NC)
+    if decay == "slow":
+        g = g / 64.0
+    elif decay == "none":
+        g = torch.zeros_like(g)
+    host = tuple(t.bfloat16().float() for t in (q, k, v)) + (g, b.bfloat16().float(), w.bfloat16().float())
+    dev = tuple(t.bfloat16().to(DEV) for t in (q, k, v)) + (g.to(DEV), b.bfloat16().to(DEV), w.bfloat16().to(DEV))
+    s0 = golden_state(B, H, D, D, 41, 0.1)
+    assert K.scan_segments(B, S, H, D, D, torch.bfloat16, _cabi.PATH_TCGEN05) > 1
+    assert K.scan_segments(B, S, H, D, D, torch.bfloat16, _cabi.PATH_TCGEN05_SERIAL) == 1
+    o_cut, s_cut, _ = K.chunk_forward(*dev, D**-0.5, s0.to(DEV), path="tcgen05")
+    o_one, s_one, _ = K.chunk_forward(*dev, D**-0.5, s0.to(DEV), path="tcgen05_serial")
+    K.check_device_status()
+    o_ref, s_ref = orc.chunkwise(*host, None, s0)
+    e = dict(o_cut=orc.max_abs_err(o_cut.float().cpu(), o_ref), s_cut=orc.rel_fro_err(s_cut.cpu(), s_ref),
+             o_one=orc.max_abs_err(o_one.float().cpu(), o_ref), s_one=orc.rel_fro_err(s_one.cpu(), s_ref),
+             o_cut_vs_one=orc.max_abs_err(o_cut.float(), o_one.float()),
+             o_cut_vs_one_mean=float((o_cut.float() - o_one.float()).abs().mean()),
+             s_cut_vs_one=orc.rel_fro_err(s_cut, s_one))
+    note("scan_cut", B=B, H=H, NC=NC, decay=decay, **e)
+    # without decay nothing forgets the bf16 rounding of the state operand: both forms drift alike
+    s_tol = STATE_FRO if decay == "bench" else 4e-3
+    assert e["o_cut"] < O_ABS_BF16 and e["o_one"] < O_ABS_BF16
+    assert e["s_cut"] < s_tol and e["s_one"] < s_tol
+    # the two forms differ only by the rounding of the state hand-over between segments: at most one bf16
+    # step on single outputs, nothing on average
+    assert e["o_cut_vs_one"] < O_ABS_BF16 and e["o_cut_vs_one_mean"] < 5e-4
+    assert e["s_cut_vs_one"] < s_tol
+
+
+def test_host_cut_prefill_three_segments_equals_one(K, monkeypatch):
+    """The host-side cut (chunk-local stage of one segment overlapping the scan of the previous one on a side
+    stream) with three segments: bit-equal to the uncut evaluation, repeatedly, with allocations in between."""
+    B, S, H, D = 4, 64 * 64, 10, 128          # 40 (batch, head) pairs: the scan itself stays one block per pair
+    dev, _ = bf16_inputs(B, S, H, D, D, seed=43)
+    assert K.scan_segments(B, S, H, D, D, torch.bfloat16, _cabi.PATH_TCGEN05) == 1
+    monkeypatch.setenv("GDN2_B200_PREFILL_SEGMENTS", "1")
+    o1, s1 = gdn2.gdn2_prefill(*dev)
+    monkeypatch.setenv("GDN2_B200_PREFILL_SEGMENTS", "3")
+    for _ in range(3):
+        o3, s3 = gdn2.gdn2_prefill(*dev)
+        junk = torch.full((1 << 22,), 7.0, device=DEV)      # reuses freed blocks of the caching allocator
+        assert torch.equal(o3, o1) and torch.equal(s3, s1)
+        del junk
+    K.check_device_status()
+
+
+# ---- failure path and out-of-bounds guards ---------------------------------------------------------------
+
+
+def test_bounded_wait_runs_out_and_reports(K):
+    """A wait that nothing satisfies gives up after its limit, the kernel returns, the status word says so once,
+    and the device keeps working."""
+    K.check_device_status()                                   # clean before
+    gave_up = K.selftest_wait(200_000)                        # about 0.1 ms
+    assert gave_up == 64
+    with pytest.raises(_cabi.GDN2KernelError, match="bounded wait"):
+        K.check_device_status()
+    K.check_device_status()                                   # the word was cleared by the failed check
+    dev, host = bf16_inputs(1, 128, 2, 128, 128, seed=47)
+    o, _ = gdn2.gdn2_prefill(*dev)
+    o_ref, _ = orc.prefill(*host)
+    assert orc.max_abs_err(o.float().cpu(), o_ref) < O_ABS_BF16
+    K.check_device_status()
+
+
+def _guarded(shape, dtype, guard=4096):
+    """A tensor of `shape` carved out of a larger buffer with `guard` bytes of 0xA5 on both sides."""
+    n = 1
+    for x in shape:
+        n *= x
+    esz = torch.empty((), dtype=dtype).element_size()
+    buf = torch.full((2 * guard + n * esz,), 0xA5, dtype=torch.uint8, device=DEV)
+    view = buf[guard: guard + n * esz].view(dtype).reshape(shape)
+    return buf, view, guard
+
+
+def _guards_intact(buf, guard):
+    return bool((buf[:guard] == 0xA5).all()) and bool((buf[-guard:] == 0xA5).all())
+
+
+@pytest.mark.parametrize("H,NC", [(3, 5), (2, 40)])
+def test_kernels_stay_inside_their_buffers(K, H, NC):
+    """Guard bytes around the workspace, the outputs and the states of every kernel family stay untouched
+    (stand-in for a memory checker): chunk-local stage, scan (one block per head and cut), chunk output, decode."""
+    B, D = 2, 128
+    S = 64 * NC
+    dev, _ = bf16_inputs(B, S, H, D, D, seed=53)
+    code = _cabi.GDN2_BF16
+    st = torch.cuda.current_stream().cuda_stream
+    for path in (_cabi.PATH_TCGEN05, _cabi.PATH_TCGEN05_SERIAL, _cabi.PATH_SIMT):
+        nbytes = K.lib.gdn2_prefill_workspace_bytes(B, S, H, D, D, code, path)
+        wbuf, ws, gd = _guarded((nbytes,), torch.uint8)
+        obuf, o, _ = _guarded((B, S, H, D), torch.bfloat16)
+        sbuf, sT, _ = _guarded((B, H, D, D), torch.float32)
+        hbuf, hs, _ = _guarded((B, NC, H, D, D), torch.float32)
+        ptrs = [t.data_ptr() for t in dev]
+        assert K.lib.gdn2_chunk_prep(*ptrs, ws.data_ptr(), nbytes, B, S, H, D, D, S, D**-0.5, code, path, st) == 0
+        assert K.lib.gdn2_prefill_scan(ws.data_ptr(), nbytes, None, o.data_ptr(), sT.data_ptr(), None,
+                                       B, S, H, D, D, S, code, path, st) == 0
+        assert K.lib.gdn2_prefill_scan(ws.data_ptr(), nbytes, None, o.data_ptr(), sT.data_ptr(), hs.data_ptr(),
+                                       B, S, H, D, D, S, code, path, st) == 0
+        assert K.lib.gdn2_chunk_output(ws.data_ptr(), nbytes, hs.data_ptr(), o.data_ptr(), B, S, H, D, D, S,
+                                       code, path, st) == 0
+        torch.cuda.synchronize()
+        for name, buf in (("workspace", wbuf), ("o", obuf), ("state", sbuf), ("chunk states", hbuf)):
+            assert _guards_intact(buf, gd), (path, name)
+    for n in (1, 8, 13):
+        sbuf, state, gd = _guarded((B, H, D, D), torch.float32)
+        state.zero_()
+        obuf, o, _ = _guarded((B, n, H, D), torch.bfloat16)
+        ptrs = [t[:, :n].contiguous() for t in dev]
+        assert K.lib.gdn2_decode(*(t.data_ptr() for t in ptrs), state.data_ptr(), o.data_ptr(), B, n, H, D, D, n, n,
+                                 D**-0.5, code, st) == 0
+        torch.cuda.synchronize()
+        assert _guards_intact(sbuf, gd) and _guards_intact(obuf, gd), n
+    K.check_device_status()

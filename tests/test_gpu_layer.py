@@ -73,9 +73,12 @@ def test_graphed_step_equals_eager_steps():
 
 @pytest.mark.parametrize("cached", [False, True])
 @pytest.mark.parametrize("S", [1, 2, 9])
-def test_fused_front_and_back_match_the_operator_chain(monkeypatch, cached, S):
-    """gdn2_layer_front / gdn2_layer_back against the torch operator chain they replace (float32, so the
-    only differences are fast-math exponentials): every output, the new convolution cache, the gated norm."""
+def test_fused_front_and_back_match_the_operator_chain(cached, S):
+    """gdn2_layer_front / gdn2_layer_back against the torch operator chain of the reference layer, evaluated on
+    the host on the same projection buffer (float32, so the only differences are fast-math exponentials): every
+    output, the new convolution cache, the gated norm."""
+    from tests.fake_kernels import layer_back_chain, layer_front_chain
+
     cfg = gdn2.GatedDeltaNet2Config(hidden_size=96, num_heads=6, num_kv_heads=2, head_dim_k=32, head_dim_v=48)
     layer = gdn2.GatedDeltaNet2(cfg).eval().to(DEV)
     gen = torch.Generator().manual_seed(11)
@@ -85,15 +88,16 @@ def test_fused_front_and_back_match_the_operator_chain(monkeypatch, cached, S):
     x = torch.randn(2, S, 96, generator=gen).to(DEV)
     state = torch.randn(2, 2 * 2 * 32 + 6 * 48, 3, generator=gen).to(DEV) if cached else None
     fused = layer._front(x, state, cached=cached)
-    assert fused[7] is not None                            # the fused path ran
-    monkeypatch.setattr(type(layer), "_use_fused", lambda self, x: False)
-    chain = layer._front(x, state, cached=cached)
-    assert chain[7] is None
-    for name, a, b in zip("q k v g b w conv".split(), fused[:7], chain[:7]):
+    proj = fused[7].cpu()
+    _, offs, cw, cb = layer._fused_tables()
+    chain = layer_front_chain(proj, offs[:6], None if state is None else state.cpu(), cw.cpu(), cb.cpu(),
+                              layer.A_log.detach().cpu(), layer.dt_bias.detach().cpu(), 6, 2, 32, 48, cfg.conv_size,
+                              float(layer.erase_scale))
+    for name, a, b in zip("q k v g b w conv".split(), fused[:7], chain):
         assert a.shape == b.shape and a.dtype == b.dtype, name
-        assert orc.rel_max_err(a.float().cpu(), b.float().cpu()) < 2e-5, name
-    o = torch.randn(2, S, 6, 48, generator=gen).to(DEV)
-    want = layer._back(x, o)
-    monkeypatch.undo()
-    got = layer._back(x, o, fused[7])
-    assert orc.rel_max_err(got.cpu(), want.cpu()) < 2e-5
+        assert orc.rel_max_err(a.float().cpu(), b.float()) < 2e-5, name
+    o = torch.randn(2, S, 6, 48, generator=gen)
+    want = layer_back_chain(o, proj, layer.o_norm.weight.detach().cpu(), offs[6], layer.o_norm.eps)
+    got = gdn2._cabi.kernels().layer_back(o.to(DEV), fused[7], layer.o_norm.weight.detach(), offs[6],
+                                           float(layer.o_norm.eps))
+    assert orc.rel_max_err(got.cpu(), want) < 2e-5

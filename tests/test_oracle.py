@@ -178,3 +178,21 @@ def test_segmented_prefill_equals_one_pass():
         outs.append(o)
     assert orc.rel_max_err(torch.cat(outs, 1), o_all) < 2e-5
     assert orc.rel_max_err(state, s_all) < 2e-5
+
+
+def test_oracle_matches_the_vendored_reference_when_built():
+    """``oracle/_ref`` (the reference's own gdn2/reference.py, placed there by oracle/build_ref.py) against the
+    restatement, on a ragged prefill: whole chunks through the chunkwise form, the tail through the recurrence."""
+    from oracle.build_ref import load_ref
+
+    ref = load_ref()
+    if ref is None:
+        pytest.skip("oracle/_ref has not been built (no reference checkout on this machine)")
+    q, k, v, g, b, w = orc.make_inputs(2, 64 * 3 + 11, 3, 32, 24, seed=7)
+    s0 = golden_state(2, 3, 32, 24, 7, 0.3)
+    o, s = orc.prefill(q, k, v, g, b, w, s0.clone())
+    n_full, scale = 64 * 3, 32**-0.5
+    o1, st = ref.chunk_gdn2_torch(*(t[:, :n_full] for t in (q, k, v, g, b, w)), scale, s0.clone(), True)
+    o2, st = ref.recurrent_gdn2(*(t[:, n_full:] for t in (q, k, v, g, b, w)), scale, st, True)
+    _close(o, torch.cat([o1, o2], 1), 5e-6)
+    _close(s, st, 5e-6)

@@ -82,3 +82,30 @@ def test_static_scratch_rejects_oversized_problems():
     rc = lib.gdn2_prefill_static(p, p, p, p, p, p, None, p, None, 1, 100, 1, 128, 128, 100, 100,
                                  1.0, _cabi.GDN2_BF16, None)
     assert rc == -2                        # S not a multiple of 64 is a shape error, not a size error
+
+
+def test_static_scratch_limit_is_exact():
+    """The largest problem that fits the built-in scratch runs (and equals the two-call form); one chunk more is
+    refused with GDN2_ERR_STATIC_LIMIT. One (batch, head) pair, so the scan of the fitting problem is also the
+    form that cuts the sequence into segments, whose records live in the same scratch."""
+    lib = _cabi.load_library()
+    dev = torch.device("cuda", 0)
+    code, D = _cabi.GDN2_BF16, 128
+    limit = 32 * 1024 * 1024
+    nc = max(n for n in range(1, 600) if lib.gdn2_prefill_workspace_bytes(1, 64 * n, 1, D, D, code, _cabi.PATH_AUTO) <= limit)
+    assert lib.gdn2_prefill_workspace_bytes(1, 64 * (nc + 1), 1, D, D, code, _cabi.PATH_AUTO) > limit
+    with torch.cuda.device(dev):
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        q, k, v, g, b, w = orc.make_inputs(1, 64 * (nc + 1), 1, D, D, seed=33)
+        full = tuple(t.bfloat16().to(dev) for t in (q, k, v)) + (g.to(dev), b.bfloat16().to(dev), w.bfloat16().to(dev))
+        s0 = torch.zeros(1, 1, D, D, device=dev)
+        S = 64 * nc
+        fits = tuple(t[:, :S].contiguous() for t in full)
+        o_ref, fin_ref = _two_call_form(lib, fits, s0, 1, S, 1, D, code, stream)
+        o, fin = _static_form(lib, fits, s0, 1, S, 1, D, code, stream)
+        torch.cuda.synchronize(dev)
+        assert torch.equal(o, o_ref) and torch.equal(fin, fin_ref)
+        o_big = torch.empty(1, S + 64, 1, D, dtype=torch.bfloat16, device=dev)
+        rc = lib.gdn2_prefill_static(*(t.data_ptr() for t in full), None, o_big.data_ptr(), None, 1, S + 64, 1, D, D,
+                                     S + 64, S + 64, D**-0.5, code, stream)
+        assert rc == -9
