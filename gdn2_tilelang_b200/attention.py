@@ -57,15 +57,50 @@ def gdn2_attention(q, k, v, g, b, w, scale=None, initial_state=None, output_fina
 
     ``q, k, b, g``: ``[B, S, H, DK]``; ``v, w``: ``[B, S, H, DV]``; ``g`` is the natural-log decay
     (``<= 0``). Returns ``(o [B, S, H, DV] in the input dtype, final_state float32 | None)``.
-    ``cu_seqlens`` is not implemented and raises, as in the reference.
+
+    ``cu_seqlens`` (``[N + 1]`` increasing token offsets starting at 0, the packing convention of the reference's
+    signature, gdn2/attention.py:142-145, where it still raises): the tensors hold ``N`` sequences packed along
+    the token axis of ONE batch entry (``B == 1``); sequence ``i`` is tokens ``cu_seqlens[i]:cu_seqlens[i+1]``
+    and starts from ``initial_state[i]`` (``[N, H, DK, DV]``) or zero. ``final_state`` is then ``[N, H, DK, DV]``.
+    Every sequence runs through the same kernels as an unpacked call on its slice: no padding, no copies.
     """
     scale = q.shape[-1] ** -0.5 if scale is None else scale
     needs_grad = torch.is_grad_enabled() and any(
         t is not None and t.requires_grad for t in (q, k, v, g, b, w, initial_state))
     resolve_backend(config.backend, q.device.type == "cuda", needs_grad)
     if cu_seqlens is not None:
-        raise NotImplementedError("packed variable-length batches are not implemented yet; pad the batch instead")
+        return _packed_attention(q, k, v, g, b, w, scale, initial_state, output_final_state, config, cu_seqlens)
     return chunk_gdn2_fwd(q, k, v, g, b, w, scale, initial_state, output_final_state, config)
+
+
+@torch.no_grad()
+def _packed_attention(q, k, v, g, b, w, scale, initial_state, output_final_state, config, cu_seqlens):
+    """Variable-length batch packed into one row: one chunkwise (+ tail) evaluation per sequence, all queued on
+    the current stream, results written straight into the packed output."""
+    offs = [int(x) for x in (cu_seqlens.tolist() if torch.is_tensor(cu_seqlens) else cu_seqlens)]
+    B, T, H, DK = q.shape
+    DV = v.shape[-1]
+    N = len(offs) - 1
+    if B != 1:
+        raise ValueError("with cu_seqlens the sequences are packed into one batch entry: expected B == 1")
+    if N < 1 or offs[0] != 0 or offs[-1] != T or any(hi < lo for lo, hi in zip(offs, offs[1:])):
+        raise ValueError(f"cu_seqlens must rise from 0 to the packed length {T}, got {offs}")
+    if initial_state is not None and tuple(initial_state.shape) != (N, H, DK, DV):
+        raise ValueError(f"initial_state must have shape {(N, H, DK, DV)} for {N} packed sequences")
+    o = torch.empty(1, T, H, DV, dtype=v.dtype, device=q.device)
+    finals = torch.zeros(N, H, DK, DV, dtype=torch.float32, device=q.device) if output_final_state else None
+    g = g.float()
+    for i, (lo, hi) in enumerate(zip(offs, offs[1:])):
+        if hi == lo:
+            if finals is not None and initial_state is not None:
+                finals[i].copy_(initial_state[i])
+            continue
+        s0 = None if initial_state is None else initial_state[i:i + 1]
+        _, s_i = chunk_gdn2_fwd(*(t[:, lo:hi] for t in (q, k, v, g, b, w)), scale, s0, output_final_state, config,
+                                out=o[:, lo:hi])
+        if finals is not None:
+            finals[i:i + 1].copy_(s_i)
+    return o, finals
 
 
 @dataclass
@@ -203,7 +238,15 @@ class GatedDeltaNet2(nn.Module):
     # ------------------------------------------------------------------ public API
     @torch.no_grad()
     def forward(self, hidden_states, cache: GDN2Cache | None = None, use_cache: bool = False, cu_seqlens=None):
-        """Full-sequence forward. Returns ``(output [B, S, hidden], GDN2Cache | None)``."""
+        """Full-sequence forward. Returns ``(output [B, S, hidden], GDN2Cache | None)``.
+
+        ``cu_seqlens`` raises here, as in the reference (gdn2/attention.py:299-357): the short convolution
+        would have to restart at every packed boundary, which the fused pre-processing kernel does not do;
+        the functional op ``gdn2_attention`` does take packed batches."""
+        if cu_seqlens is not None:
+            raise NotImplementedError("packed variable-length batches through the layer need a convolution that "
+                                      "restarts at sequence boundaries; call gdn2_attention with cu_seqlens on "
+                                      "pre-processed tensors, or pad the batch")
         q, k, v, g, b, w, conv, proj = self._front(hidden_states, None, cached=False)
         o, final_state = gdn2_attention(
             q, k, v, g, b, w, scale=self.scale,

@@ -21,11 +21,12 @@ __all__ = ["chunk_gdn2_fwd", "chunk_gdn2_output"]
 
 @torch.no_grad()
 def chunk_gdn2_fwd(q, k, v, g, b, w, scale, initial_state=None, output_final_state=False,
-                   config: GDN2Config = DEFAULT_KERNEL_CONFIG, return_chunk_states=False):
+                   config: GDN2Config = DEFAULT_KERNEL_CONFIG, return_chunk_states=False, out=None):
     """Returns ``(o, final_state | None)`` or, with ``return_chunk_states``, ``(o, final_state | None, h)``.
 
     ``o`` is ``[B, S, H, DV]`` in the input dtype, ``final_state`` ``[B, H, DK, DV]`` float32,
-    ``h`` ``[B, S // 64, H, DK, DV]`` float32 (whole chunks only).
+    ``h`` ``[B, S // 64, H, DK, DV]`` float32 (whole chunks only). ``out`` (optional) is a ``[B, S, H, DV]``
+    tensor or view with dense ``[S, H, DV]`` blocks that receives ``o`` (a slice of a packed batch, for instance).
     """
     config.validate()
     B, S, H, DK, DV = _check_inputs(q, k, v, g, b, w)
@@ -33,13 +34,20 @@ def chunk_gdn2_fwd(q, k, v, g, b, w, scale, initial_state=None, output_final_sta
     n_full = (S // BS) * BS
     K = _cabi.kernels()
     g = g.float()
-    o = torch.empty(B, S, H, DV, dtype=v.dtype, device=q.device)
+    if out is None:
+        o = torch.empty(B, S, H, DV, dtype=v.dtype, device=q.device)
+    else:
+        if tuple(out.shape) != (B, S, H, DV) or out.dtype != v.dtype or out.stride(3) != 1 or out.stride(2) != DV \
+                or out.stride(1) != H * DV or (B > 1 and out.stride(0) % (H * DV)):
+            raise ValueError("`out` must be [B, S, H, DV] in v's dtype with dense [S, H, DV] blocks")
+        o = out
+    o_bs = S if (out is None or B == 1) else out.stride(0) // (H * DV)
     state, hs = initial_state, None
     if state is not None and state.shape != (B, H, DK, DV):
         raise ValueError(f"initial_state must have shape {(B, H, DK, DV)}, got {tuple(state.shape)}")
     if n_full:
         _, state, hs = K.chunk_forward(*(t[:, :n_full] for t in (q, k, v, g, b, w)), scale, state,
-                                       want_chunk_states=return_chunk_states, out=o, out_batch_stride=S)
+                                       want_chunk_states=return_chunk_states, out=o, out_batch_stride=o_bs)
     if S > n_full:
         if state is None:
             state = torch.zeros(B, H, DK, DV, dtype=torch.float32, device=q.device)

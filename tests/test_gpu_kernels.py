@@ -564,3 +564,24 @@ def test_kernels_stay_inside_their_buffers(K, H, NC):
         torch.cuda.synchronize()
         assert _guards_intact(sbuf, gd) and _guards_intact(obuf, gd), n
     K.check_device_status()
+
+
+def test_packed_variable_length_batch_on_device(K):
+    """cu_seqlens on the device kernels (D = 128 bf16, the tensor-core family): every packed sequence against the
+    oracle on its slice, and the packed call against the same sequences evaluated one call each."""
+    offs = [0, 64 * 9 + 5, 64 * 9 + 5, 64 * 30, 64 * 30 + 17, 64 * 41 + 3]
+    H, D = 3, 128
+    dev, host = bf16_inputs(1, offs[-1], H, D, D, seed=61)
+    s0 = golden_state(5, H, D, D, 61, 0.1)
+    o, s = gdn2.gdn2_attention(*dev, initial_state=s0.to(DEV), output_final_state=True, cu_seqlens=offs)
+    K.check_device_status()
+    for i, (lo, hi) in enumerate(zip(offs, offs[1:])):
+        if hi == lo:
+            assert torch.equal(s[i].cpu(), s0[i])
+            continue
+        o_ref, s_ref = orc.prefill(*(t[:, lo:hi] for t in host), s0[i:i + 1])
+        assert orc.max_abs_err(o[:, lo:hi].float().cpu(), o_ref) < O_ABS_BF16, i
+        assert orc.rel_fro_err(s[i:i + 1].cpu(), s_ref) < STATE_FRO, i
+        o_one, s_one = gdn2.gdn2_attention(*(t[:, lo:hi].contiguous() for t in dev), initial_state=s0[i:i + 1].to(DEV),
+                                           output_final_state=True)
+        assert torch.equal(o[:, lo:hi], o_one) and torch.equal(s[i:i + 1], s_one)

@@ -137,12 +137,33 @@ def test_error_behaviour():
         _cabi.NativeKernels().decode(q, k, v, g, b, w, torch.zeros(1, 1, 32, 32), 1.0)
 
 
-def test_cu_seqlens_raises(fake, monkeypatch):
+def test_packed_variable_length_batch(fake, monkeypatch):
+    """cu_seqlens: sequences packed along the token axis of one batch entry, each evaluated on its own slice
+    (whole chunks, ragged tail, a sequence shorter than a chunk, an empty one), states per sequence."""
     import gdn2_tilelang_b200.attention as att
     monkeypatch.setattr(att, "resolve_backend", lambda *a, **kw: "cuda")
-    q, k, v, g, b, w = orc.make_inputs(1, 64, 1, 32, 32)
-    with pytest.raises(NotImplementedError):
-        gdn2.gdn2_attention(q, k, v, g, b, w, cu_seqlens=torch.tensor([0, 64]))
+    offs = [0, 130, 130, 194, 201, 330]
+    q, k, v, g, b, w = orc.make_inputs(1, offs[-1], 2, 32, 24, seed=9)
+    s0 = golden_state(5, 2, 32, 24, 9, 0.3)
+    o, s = gdn2.gdn2_attention(q, k, v, g, b, w, initial_state=s0, output_final_state=True,
+                               cu_seqlens=torch.tensor(offs))
+    assert o.shape == (1, offs[-1], 2, 24) and s.shape == (5, 2, 32, 24)
+    for i, (lo, hi) in enumerate(zip(offs, offs[1:])):
+        if hi == lo:
+            assert torch.equal(s[i], s0[i])
+            continue
+        o_ref, s_ref = orc.recurrence(*(t[:, lo:hi] for t in (q, k, v, g, b, w)), None, s0[i:i + 1])
+        assert orc.rel_max_err(o[:, lo:hi], o_ref) < 2e-5
+        assert orc.rel_max_err(s[i:i + 1], s_ref) < 2e-5
+    o2, s2 = gdn2.gdn2_attention(q, k, v, g, b, w, cu_seqlens=offs)          # a plain list, no states
+    assert s2 is None and o2.shape == o.shape
+    with pytest.raises(ValueError, match="B == 1"):
+        gdn2.gdn2_attention(*(t.repeat(2, 1, 1, 1) for t in (q, k, v, g, b, w)), cu_seqlens=offs)
+    with pytest.raises(ValueError, match="rise from 0"):
+        gdn2.gdn2_attention(q, k, v, g, b, w, cu_seqlens=[0, 100])
+    layer = gdn2.GatedDeltaNet2(gdn2.GatedDeltaNet2Config(**LAYER)).eval()
+    with pytest.raises(NotImplementedError, match="convolution"):
+        layer(torch.zeros(1, 8, LAYER["hidden_size"]), cu_seqlens=[0, 8])
 
 
 # ---- the layer --------------------------------------------------------------------------------
