@@ -305,7 +305,9 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         os.environ.setdefault("NCCL_DEBUG", "WARN")      # keeps NCCL's version banner off stdout: one JSON line only
-        dist.init_process_group("nccl", device_id=dev)
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # exchange buffers use plain peer stores only
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     B, S, H, DK, DV = (CFG[x] for x in ("B", "S", "H", "DK", "DV"))
     K = _cabi.kernels()
     if args.profile_case:
@@ -575,6 +577,34 @@ def layer_bench(gdn2, dist, dev, rank, world, barrier, max_over_ranks):
         leg["all_reduce"] = {"prefill_32MiB_ms": ms_big, "prefill_share": ms_big / ms_pre,
                              "step_8KiB_us": ms_small * 1e3, "step_share": ms_small * 1e3 / (ms_eager * 1e3 / 128),
                              "backend": "nccl", "n_ranks": world}
+        # o_proj + sum over ranks as ONE kernel (peer stores over NVLink), eager and replayed from a CUDA graph.
+        # The set-up is collective; whether it worked is agreed on by all ranks before anyone goes on.
+        ok, msg = 1.0, ""
+        try:
+            layer.enable_fused_reduce()
+        except Exception as e:
+            ok, msg = 0.0, f"{type(e).__name__}: {e}"[:300]
+        if -max_over_ranks(-ok) < 1.0:
+            layer.fused_reduce = None
+            leg["fused_reduce"] = {"error": msg or "the set-up failed on another rank"}
+            return leg
+        keep, layer.fused_reduce = layer.fused_reduce, None
+        _, cache_n = layer.prefill(x)
+        y_nccl, _ = layer.step(xt, cache_n)
+        layer.fused_reduce = keep
+        _, cache_f = layer.prefill(x)
+        y_fused, _ = layer.step(xt, cache_f)
+        err = float((y_fused.float() - y_nccl.float()).abs().max() / y_nccl.float().abs().max())
+        ms_fused = max_over_ranks(time_events(eager_steps, 3, 1, sync))
+        step = gdn2.GraphedStep(layer, cache)
+
+        def graphed_steps():
+            for _ in range(128):
+                step(xt)
+
+        ms_graph = max_over_ranks(time_events(graphed_steps, 3, 1, sync))
+        leg["fused_reduce"] = {"step_us_eager": ms_fused * 1e3 / 128, "step_us_cuda_graph": ms_graph * 1e3 / 128,
+                               "vs_nccl_rel_max": max_over_ranks(err)}
     return leg
 
 

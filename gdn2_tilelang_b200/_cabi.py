@@ -46,6 +46,8 @@ SIGNATURES = {
     "gdn2_selftest_wait": (_int, [_i64, _vp, _vp]),
     "gdn2_prefill_static": (_int, [_vp] * 9 + [_i64] * 7 + [_f32, _int, _vp]),
     "gdn2_layer_front": (_int, [_vp, _int, _vp]),
+    "gdn2_oproj_reduce_buffer_bytes": (_sz, [_i64, _i64, ctypes.POINTER(_sz)]),
+    "gdn2_oproj_reduce": (_int, [_vp, _int, _vp]),
     "gdn2_layer_back": (_int, [_vp] * 4 + [_i64] * 5 + [_f32, _int, _vp]),
 }
 
@@ -58,6 +60,13 @@ class LayerFrontArgs(ctypes.Structure):
                 + [(n, _i64) for n in ("B", "S", "H", "HK", "DK", "DV", "K", "NP",
                                        "off_q", "off_k", "off_v", "off_b", "off_w", "off_f")]
                 + [("erase_scale", _f32)])
+
+class OProjReduceArgs(ctypes.Structure):
+    """``gdn2_oproj_reduce_args`` of include/gdn2_b200.h."""
+
+    _fields_ = ([(n, _vp) for n in ("x", "weight", "out", "peer_slots", "peer_flags", "epochs")]
+                + [(n, _i64) for n in ("rows", "K", "hidden")] + [("rank", _int), ("world", _int), ("wait_cycles", _i64)])
+
 
 _lock = threading.Lock()
 _lib = None
@@ -385,6 +394,21 @@ class NativeKernels:
         _check(self.lib, rc, "gdn2_chunk_prep")
         self.launches += 2 if p != PATH_SIMT else 1
         return ws, p
+
+    def oproj_reduce(self, x, weight, out, peer_slots, peer_flags, epochs, rank, world, wait_cycles=0):
+        """``gdn2_oproj_reduce``: ``x [rows, K]``, ``weight [hidden, K]`` -> ``out [rows, hidden]`` summed over ranks.
+        ``peer_slots`` / ``peer_flags``: int64 device tensors holding the peer-mapped buffer addresses."""
+        _require_cuda(x, weight, out)
+        rows, K = x.shape
+        a = OProjReduceArgs(x.data_ptr(), weight.data_ptr(), out.data_ptr(),
+                            None if peer_slots is None else peer_slots.data_ptr(),
+                            None if peer_flags is None else peer_flags.data_ptr(), epochs.data_ptr(),
+                            rows, K, weight.shape[0], rank, world, wait_cycles)
+        with torch.cuda.device(x.device):
+            rc = self.lib.gdn2_oproj_reduce(ctypes.byref(a), dtype_code(x.dtype), self._stream(x))
+        _check(self.lib, rc, "gdn2_oproj_reduce")
+        self.launches += 1
+        return out
 
     def selftest_wait(self, limit_cycles: int, device=None) -> int:
         """Launch the block whose bounded wait nothing satisfies; returns how many threads gave up."""

@@ -229,11 +229,11 @@ class GatedDeltaNet2(nn.Module):
         off_gate = self._fused_tables()[1][6]
         normed = _cabi.kernels().layer_back(o.contiguous(), proj, self.o_norm.weight.detach().to(o.dtype),
                                             off_gate, float(self.o_norm.eps))
-        return self._reduce(self.o_proj(normed))
+        return self._project_out(normed)
 
-    def _reduce(self, y):
-        """Hook for the head-parallel variant (sum over ranks); identity on one device."""
-        return y
+    def _project_out(self, normed):
+        """``o_proj``; the head-parallel variant overrides it to add the sum over ranks."""
+        return self.o_proj(normed)
 
     # ------------------------------------------------------------------ public API
     @torch.no_grad()

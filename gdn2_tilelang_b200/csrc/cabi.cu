@@ -224,6 +224,27 @@ int gdn2_check_device_status(void* stream, uint32_t* detail) {
   return host == 0 ? GDN2_OK : GDN2_ERR_DEVICE_WAIT;
 }
 
+size_t gdn2_oproj_reduce_buffer_bytes(int64_t world, int64_t hidden, size_t* flags_offset) {
+  if (world < 1 || world > 64 || hidden < 32 || hidden % 32 != 0 || hidden > (1 << 20)) return 0;
+  const size_t slots = align_up((size_t)2 * world * 8 * hidden * sizeof(float), 256);
+  if (flags_offset) *flags_offset = slots;
+  return slots + align_up((size_t)2 * world * (hidden / 32) * sizeof(uint32_t), 256);
+}
+
+int gdn2_oproj_reduce(const gdn2_oproj_reduce_args* a, int dtype, void* stream) {
+  if (!a || !a->x || !a->weight || !a->out || !a->epochs) return GDN2_ERR_NULL_POINTER;
+  if (!valid_dtype(dtype)) return GDN2_ERR_BAD_DTYPE;
+  const int64_t e16 = dtype == GDN2_F32 ? 4 : 8, esz = dtype == GDN2_F32 ? 4 : 2;
+  if (a->rows < 1 || a->rows > 8 || a->K < e16 || a->K % e16 != 0 || a->hidden < 32 || a->hidden % 32 != 0 ||
+      a->hidden > (1 << 20) || a->rows * a->K * esz > 64 * 1024)
+    return GDN2_ERR_BAD_SHAPE;
+  if (a->world < 1 || a->world > 64 || a->rank < 0 || a->rank >= a->world) return GDN2_ERR_BAD_SHAPE;
+  if (a->world > 1 && (!a->peer_slots || !a->peer_flags)) return GDN2_ERR_NULL_POINTER;
+  if (a->wait_cycles < 0 || a->wait_cycles > 2000000000LL) return GDN2_ERR_BAD_SHAPE;
+  if (!aligned16(a->x) || !aligned16(a->weight) || !aligned16(a->out)) return GDN2_ERR_MISALIGNED;
+  return launch_oproj_reduce(*a, dtype, static_cast<cudaStream_t>(stream));
+}
+
 int gdn2_selftest_wait(int64_t limit_cycles, int* gave_up, void* stream) {
   if (limit_cycles <= 0 || limit_cycles > 2000000000LL) return GDN2_ERR_BAD_SHAPE;   // about a second at most
   return launch_selftest_wait(limit_cycles, gave_up, static_cast<cudaStream_t>(stream));

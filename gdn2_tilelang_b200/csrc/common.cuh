@@ -62,21 +62,30 @@ struct WsLayout {
   int DK, DV;
   int esz;            // bytes per TW element (2 or 4); TV has the same size
   int nseg;           // sequence segments of the tensor-core scan (1 = one block per head walks the whole sequence)
+  int nseg_guarded;   // 1 = that cut launches more blocks than SMs and is taken back on the device when the decay is slow
   size_t wq_bytes, aqk_bytes, kgt_bytes, ut_bytes, gl_bytes;   // per chunk-head
   size_t off_wq, off_aqk, off_kgt, off_ut, off_gl, off_flags, off_seg, total;
 };
 
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-// Segments the tensor-core scan cuts a sequence of NC chunks into when a GPU holds BH (batch, head)
-// pairs. The first pass runs 2 * nseg - 1 blocks per pair, one per SM, and all of them have to be
-// resident at once for the cut to shorten the chain, so it is only made while they fit on 144 SMs;
-// a segment is at least 8 chunks. 1 = no cut.
-__host__ __device__ inline int scan_segments(int64_t BH, int64_t NC) {
-  int64_t n = (144 / BH + 1) / 2;
-  if (n > NC / 8) n = NC / 8;
-  if (n > 16) n = 16;
-  return n < 2 ? 1 : (int)n;
+// Segments the tensor-core scan cuts a sequence of NC chunks into when a GPU holds BH (batch, head) pairs.
+// The first pass runs nseg "local" blocks and nseg - 1 "transition" blocks per pair, one per SM. While all of
+// them fit on 144 SMs at once the cut can only shorten the chain. With more pairs (transition blocks and local
+// blocks together exceed the SMs, but the local blocks alone fit) the cut still pays when the transition
+// blocks end after a few chunks, which they do when the decay makes the carried state vanish quickly; that cut
+// is "guarded": a decay check on the device takes it back for slowly decaying inputs. A segment is at least 8
+// chunks; 1 = no cut.
+__host__ __device__ inline int scan_segments(int64_t BH, int64_t NC, int* guarded) {
+  int64_t fit = (144 / BH + 1) / 2, over = 144 / BH, cap = NC / 8 < 16 ? NC / 8 : 16;
+  if (fit > cap) fit = cap;
+  if (over > cap) over = cap;
+  *guarded = 0;
+  if (fit <= 2 && over > fit && over >= 2 && NC / over >= 24) {   // guarded segments keep room for the decay check
+    *guarded = 1;
+    return (int)over;
+  }
+  return fit < 2 ? 1 : (int)fit;
 }
 
 __host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK, int DV, int esz,
@@ -85,7 +94,8 @@ __host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK,
   L.nch = B * H * (S / kChunk);
   L.BH = B * H;
   L.DK = DK; L.DV = DV; L.esz = esz;
-  L.nseg = (allow_segments && esz == 2) ? scan_segments(B * H, S / kChunk) : 1;
+  L.nseg_guarded = 0;
+  L.nseg = (allow_segments && esz == 2) ? scan_segments(B * H, S / kChunk, &L.nseg_guarded) : 1;
   L.wq_bytes = (size_t)2 * kChunk * DK * esz;
   L.aqk_bytes = (size_t)kChunk * kChunk * esz;
   L.kgt_bytes = (size_t)DK * kChunk * esz;
@@ -99,10 +109,10 @@ __host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK,
   L.off_gl = off;   off = align_up(off + L.gl_bytes * L.nch, 1024);
   L.off_flags = off; off = align_up(off + sizeof(int) * (2 * L.nch + 4), 1024);   // flags, compacted list, count
   // per (batch, head) and segment: transition T_j, local final state C_j, true entering state (fp32 [DK, DV]
-  // each), then one int per (batch, head, segment): the chunks the correction pass has to redo
+  // each), then one int per (batch, head, segment): the chunks the correction pass has to redo; one mode word
   L.off_seg = off;
   if (L.nseg > 1)
-    off = align_up(off + (size_t)B * H * L.nseg * ((size_t)3 * DK * DV * 4 + sizeof(int)), 1024);
+    off = align_up(off + (size_t)B * H * L.nseg * ((size_t)3 * DK * DV * 4 + sizeof(int)) + sizeof(int), 1024);
   L.total = off;
   return L;
 }
@@ -114,19 +124,20 @@ template <int E> __host__ __device__ __forceinline__ int kc_index(int row, int k
 
 struct WsPtrs {
   char* wq; char* aqk; char* kgt; char* ut; float* gl; int* flags;
-  float* seg_t; float* seg_c; float* seg_in; int* seg_stop;   // segment records of the cut scan (nseg > 1)
+  float* seg_t; float* seg_c; float* seg_in; int* seg_stop; int* seg_mode;   // segment records of the cut scan (nseg > 1)
 };
 
 __host__ inline WsPtrs ws_pointers(void* base, const WsLayout& L) {
   char* p = static_cast<char*>(base);
   WsPtrs P{p + L.off_wq, p + L.off_aqk, p + L.off_kgt, p + L.off_ut, reinterpret_cast<float*>(p + L.off_gl),
-           reinterpret_cast<int*>(p + L.off_flags), nullptr, nullptr, nullptr, nullptr};
+           reinterpret_cast<int*>(p + L.off_flags), nullptr, nullptr, nullptr, nullptr, nullptr};
   if (L.nseg > 1) {
     const size_t mats = (size_t)L.BH * L.nseg * L.DK * L.DV;      // floats per record kind
     P.seg_t = reinterpret_cast<float*>(p + L.off_seg);
     P.seg_c = P.seg_t + mats;
     P.seg_in = P.seg_c + mats;
     P.seg_stop = reinterpret_cast<int*>(P.seg_in + mats);
+    P.seg_mode = P.seg_stop + (size_t)L.BH * L.nseg;
   }
   return P;
 }
@@ -184,6 +195,7 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
                    int B, int S, int H, int64_t o_bs, cudaStream_t st);
 int launch_output_tc(const WsLayout& L, const WsPtrs& P, const float* hs, void* o, int B, int S, int H, int64_t o_bs,
                      cudaStream_t st);
+int launch_oproj_reduce(const gdn2_oproj_reduce_args& a, int dtype, cudaStream_t st);
 int launch_selftest_wait(long long limit_cycles, int* gave_up, cudaStream_t st);
 int launch_selftest_mma(const float* a, const float* bt, float* out, cudaStream_t st);
 

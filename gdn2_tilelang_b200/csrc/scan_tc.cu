@@ -81,7 +81,8 @@ struct ScanTcSmem {
   uint64_t bar_sb, bar_un;                              // compute threads -> issuer (256 arrivals)
   uint32_t tmem_base;
   int abort_flag;
-  int last_big[kComputeThreads / 32];                   // transition blocks: per warp, last chunk after which an entry was still >= kVanish
+  int last_big[kComputeThreads / 32];                   // transition blocks: last chunk after which an entry was still >= kVanish
+  int nc_limit;                                         // chunks this block walks; a transition block lowers it once its matrix vanished
 };
 
 // A transition matrix entry below this is treated as vanished: 128 of them times the entering state stay
@@ -89,13 +90,17 @@ struct ScanTcSmem {
 constexpr float kVanish = 7.450580596923828e-09f;   // 2^-27
 
 // What a block of the cut scan does (ScanPlan::pass). kWhole: one block per (batch, head) over the whole
-// sequence. kFirst: blockIdx = slot * BH + bh; slots [0, nseg) are local blocks of segment `slot`, slots
-// [nseg, 2 nseg - 1) transition blocks of segment slot - nseg + 1. kRedo: blockIdx = (seg - 1) * BH + bh.
+// sequence. kFirst: blockIdx = slot * BH + bh; slots [0, nseg - 1) are transition blocks of segment slot + 1
+// (first, because they are short once their matrix has vanished and free their SMs for the rest), slots
+// [nseg - 1, 2 nseg - 1) local blocks of segment slot - nseg + 1. kRedo: blockIdx = (seg - 1) * BH + bh.
+// `guarded`: the launch holds more blocks than SMs and only pays off when the transition blocks end early, so
+// the blocks first look at the mode word the decay check left in the workspace: if it says "slow", the local
+// block of segment 0 walks the whole sequence alone, exactly as kWhole, and every other block returns at once.
 // kOutput: the chunk-parallel output from stored chunk states (no recurrence): blockIdx = seg * BH + bh, every
 // block walks the chunks of its segment and takes the state entering each chunk from `hs` instead of carrying it.
 enum ScanPass : int { kWhole = 0, kFirst = 1, kRedo = 3, kOutput = 4 };
 struct ScanPlan {
-  int pass, nseg;
+  int pass, nseg, guarded;
 };
 
 enum : uint32_t {
@@ -114,6 +119,21 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
 }
 // barrier among the 128 output threads only (hardware barrier 2)
 __device__ __forceinline__ void output_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+// barrier among the 256 compute threads (hardware barrier 3) fused with an AND over one predicate per thread
+__device__ __forceinline__ bool compute_all(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.u32 p, %1, 0;\n\t"
+      "barrier.cta.red.and.pred q, 3, 256, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t"
+      "}"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
 
 __device__ __forceinline__ float pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
@@ -147,8 +167,8 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
     const int slot = blockIdx.x / BH;
     bh = blockIdx.x % BH;
     if (plan.pass == kFirst) {
-      transition = slot >= plan.nseg;
-      seg = transition ? slot - plan.nseg + 1 : slot;
+      transition = slot < plan.nseg - 1;
+      seg = transition ? slot + 1 : slot - (plan.nseg - 1);
     } else if (plan.pass == kRedo) {
       seg = slot + 1;
     } else {
@@ -156,6 +176,10 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
     }
   }
   const bool output_only = plan.pass == kOutput;
+  if (plan.guarded && *P.seg_mode != 0) {                  // slow decay: no cut after all (uniform over the launch)
+    if (plan.pass != kFirst || transition || seg != 0) return;
+    plan.pass = kWhole;
+  }
   const int ib = bh / H, ih = bh % H;
   const int c_first = plan.pass == kWhole ? 0 : (int)((int64_t)NC_all * seg / plan.nseg);
   const int c_end = plan.pass == kWhole ? NC_all : (int)((int64_t)NC_all * (seg + 1) / plan.nseg);
@@ -194,8 +218,11 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
       tc::mbar_init(&s.bar_wq[i], 1); tc::mbar_init(&s.bar_kgt[i], 1); tc::mbar_init(&s.bar_ut[i], 1);
     }
     tc::mbar_init(&s.bar_aqk, 1); tc::mbar_init(&s.bar_m1, 1); tc::mbar_init(&s.bar_m3, 1); tc::mbar_init(&s.bar_m2, 1);
-    tc::mbar_init(&s.bar_sb, (kComputeThreads + kOutputThreads) / 32); tc::mbar_init(&s.bar_un, kComputeThreads / 32);   // one arrival per warp
+    // one arrival per warp; a transition block has no outputs, its output warps take no part
+    tc::mbar_init(&s.bar_sb, (kComputeThreads + (transition ? 0 : kOutputThreads)) / 32);
+    tc::mbar_init(&s.bar_un, kComputeThreads / 32);
     s.abort_flag = 0;
+    s.nc_limit = NC;
     tc::mbar_init_fence();
   }
   if (wid == 0) tc::tmem_alloc(&s.tmem_base, 512);
@@ -226,19 +253,34 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
         tc::mbar_expect_tx(&s.bar_aqk, kAqkBytes);
         tc::bulk_g2s(s.aqk, g_aqk + (size_t)n * kAqkBytes, kAqkBytes, &s.bar_aqk);
       };
+      const volatile int* limit = &s.nc_limit;
+      int ahead = 0, ut_ahead = 0, aqk_ahead = 0;            // highest chunk whose WQ + KG^T, U^T and Aqk copies were issued
       load_wq(0); load_ut(0); load_kgt(0); load_aqk(0);
-      if (NC > 1) { load_wq(1); load_ut(1); load_kgt(1); }
-      for (int n = 0; n < NC; ++n) {
+      if (NC > 1) { load_wq(1); load_ut(1); load_kgt(1); ahead = ut_ahead = 1; }
+      int n = 0;
+      for (; n < NC; ++n) {
+        if (n >= *limit) break;                              // a transition block whose matrix has vanished stops early
         const uint32_t ph = n & 1;
         // the Un pass of chunk n has consumed its U^T buffer
         bool ok = tc::mbar_wait(&s.bar_un, ph, &s.abort_flag, status, kWaitUn);
-        if (ok && n + 2 < NC) load_ut(n + 2);
+        if (ok && n + 2 < *limit) { load_ut(n + 2); ut_ahead = n + 2; }
         // every product of chunk n has completed: refill the operand buffers it read
         ok = ok && tc::mbar_wait(&s.bar_m2, ph, &s.abort_flag, status, kWaitM2);
         if (ok) {
-          if (n + 1 < NC) load_aqk(n + 1);
-          if (n + 2 < NC) { load_wq(n + 2); load_kgt(n + 2); }
+          if (n + 1 < *limit) { load_aqk(n + 1); aqk_ahead = n + 1; }
+          if (n + 2 < *limit) { load_wq(n + 2); load_kgt(n + 2); ahead = n + 2; }
         }
+      }
+      // Copies issued for chunks that no one will consume any more (the limit dropped after they were issued)
+      // must land before the block gives its shared memory back.
+      if (!s.abort_flag) {
+        for (int c = n; c <= ahead; ++c) {
+          tc::mbar_wait(&s.bar_wq[c & 1], (c >> 1) & 1, &s.abort_flag, status, kWaitWq);
+          if (!output_only) tc::mbar_wait(&s.bar_kgt[c & 1], (c >> 1) & 1, &s.abort_flag, status, kWaitKgt);
+        }
+        if (!transition)
+          for (int c = n; c <= ut_ahead; ++c) tc::mbar_wait(&s.bar_ut[c & 1], (c >> 1) & 1, &s.abort_flag, status, kWaitUt);
+        if (aqk_ahead >= n && n < NC) tc::mbar_wait(&s.bar_aqk, aqk_ahead & 1, &s.abort_flag, status, kWaitAqk);
       }
     }
   } else if (wid == 8) {
@@ -255,6 +297,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
         return __all_sync(0xffffffffu, tc::mbar_wait(bar, parity, &s.abort_flag, status, code)) != 0;
       };
       for (int n = 0; n < NC; ++n) {
+        if (n >= *(volatile int*)&s.nc_limit) break;         // uniform: every lane reads the same word
         const int b = n & 1;
         const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
         // S^T (bf16) of chunk n is in place and the O accumulator has been read out
@@ -287,8 +330,8 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
     const int dv = lq * 32 + lane;
     const int otid = tid - (kComputeThreads + 64);
     const uint32_t t_o = tc::tmem_addr(tm, lq * 32, kColO);
-    warp_arrive(&s.bar_sb, lane);                          // nothing to read out before chunk 0
-    for (int n = 0; n < NC; ++n) {
+    if (!transition) warp_arrive(&s.bar_sb, lane);         // nothing to read out before chunk 0
+    for (int n = 0; n < (transition ? 0 : NC); ++n) {
       float ov[64];
       tc::mbar_wait(&s.bar_m2, n & 1, &s.abort_flag, status, kWaitM2);
       tc::tc_fence_after_sync();
@@ -343,6 +386,7 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
     tc::tc_fence_before_sync();
     warp_arrive(&s.bar_sb, lane);
     for (int n = 0; n < NC; ++n) {
+      if (n >= *(volatile int*)&s.nc_limit) break;
       const int b = n & 1;
       const uint32_t ph = n & 1, ph2 = (n >> 1) & 1;
       const bool more = n + 1 < NC;
@@ -447,11 +491,15 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
           }
         }
         if (transition) {
-          // has the running transition matrix vanished? (positive floats order like their bit patterns)
+          // Has the running transition matrix vanished? All 256 compute threads agree through one barrier with
+          // an AND reduction. If it has, chunks n + 1 and n + 2 are still walked (other warps of the block are
+          // already working on them) and every role stops before chunk n + 3: they all pass a hand-off of chunk
+          // n + 2 that is ordered after this store before they look at the limit again.
           float m = 0.f;
 #pragma unroll
           for (int i = 0; i < 64; ++i) m = fmaxf(m, fabsf(S[i]));
-          if (__reduce_max_sync(0xffffffffu, __float_as_uint(m)) >= __float_as_uint(kVanish)) last_big = n;
+          if (!compute_all(m < kVanish)) last_big = n;
+          else if (tid == 0 && n + 3 < s.nc_limit) s.nc_limit = n + 3;
         }
       }
       if (s.abort_flag) break;                             // per thread: no block-level barrier in this loop
@@ -468,9 +516,32 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
     // matrix was still visible; chunk 0 always (it starts from the true state).
     int last = -1;
     for (int i = 0; i < kComputeThreads / 32; ++i) last = s.last_big[i] > last ? s.last_big[i] : last;
-    const int redo = last + 2;
+    const int redo = last + 2;                               // < NC whenever the block stopped early: then no matrix was stored
     P.seg_stop[bh * plan.nseg + seg] = redo < NC ? redo : NC;
   }
+}
+
+// Decay check before a guarded launch (more blocks than SMs, see ScanPlan): one warp per (batch, head, segment
+// j >= 1) multiplies gamma_last of the segment's first kCheckChunks chunks per channel. If the slowest channel
+// has not decayed below kVanish by then, the carried state will not vanish quickly either, the transition
+// blocks would walk most of their segments, and the launch is better off not cutting: the mode word is set.
+// A heuristic for speed only: whatever it says, the results are those of the recurrence.
+constexpr int kCheckChunks = 12;
+__global__ void __launch_bounds__(256)
+scan_mode_kernel(WsPtrs P, int BH, int nseg, int NC_all) {
+  const int item = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (item >= BH * (nseg - 1)) return;
+  const int bh = item / (nseg - 1), seg = 1 + item % (nseg - 1);
+  const int c0 = (int)((int64_t)NC_all * seg / nseg), c1 = (int)((int64_t)NC_all * (seg + 1) / nseg);
+  const int n = c1 - c0 < kCheckChunks ? c1 - c0 : kCheckChunks;
+  float4 prod = make_float4(1.f, 1.f, 1.f, 1.f);
+  for (int c = 0; c < n; ++c) {
+    const float4 gv = *reinterpret_cast<const float4*>(P.gl + ((size_t)bh * NC_all + c0 + c) * D + 4 * lane);
+    prod.x *= gv.x; prod.y *= gv.y; prod.z *= gv.z; prod.w *= gv.w;
+  }
+  float m = fmaxf(fmaxf(prod.x, prod.y), fmaxf(prod.z, prod.w));
+  m = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(m)));
+  if (lane == 0 && (m >= kVanish || n < kCheckChunks)) atomicOr(P.seg_mode, 1);
 }
 
 // Pass 2 of the cut scan: chains the segments' affine maps in fp32. Block (bh, column slice of 16 value
@@ -480,8 +551,9 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
 constexpr int kCombineCols = 16;
 constexpr int kTPad = D + 1;
 __global__ void __launch_bounds__(256)
-scan_combine_kernel(WsPtrs P, int nseg, int NC_all, float* __restrict__ sT) {
+scan_combine_kernel(WsPtrs P, int nseg, int NC_all, int guarded, float* __restrict__ sT) {
   extern __shared__ __align__(16) float csm[];
+  if (guarded && *P.seg_mode != 0) return;                 // the first pass walked the whole sequences itself
   float* Ts = csm;                         // [128][129] transition matrix of the current segment
   float* Ss = csm + D * kTPad;             // [128][16] current state slice
   const int bh = blockIdx.x, col0 = blockIdx.y * kCombineCols;
@@ -542,22 +614,28 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
   GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   __nv_bfloat16* ob = static_cast<__nv_bfloat16*>(o);
   uint32_t* status = device_status_word();
-  const int BH = B * H;
+  const int BH = B * H, NC = S / BS;
   // chunk states are a by-product of the one-block-per-head walk only
   const int nseg = hs ? 1 : L.nseg;
   if (nseg <= 1) {
-    scan_tc_kernel<<<BH, kThreads, smem, st>>>(L, P, ScanPlan{kWhole, 1}, s0, ob, sT, hs, S, H, o_bs, status);
+    scan_tc_kernel<<<BH, kThreads, smem, st>>>(L, P, ScanPlan{kWhole, 1, 0}, s0, ob, sT, hs, S, H, o_bs, status);
     GDN2_CUDA_TRY(cudaGetLastError());
     return GDN2_OK;
   }
-  scan_tc_kernel<<<BH * (2 * nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kFirst, nseg}, s0, ob, nullptr, nullptr,
+  const int guarded = L.nseg_guarded ? 1 : 0;
+  if (guarded) {
+    GDN2_CUDA_TRY(cudaMemsetAsync(P.seg_mode, 0, sizeof(int), st));
+    scan_mode_kernel<<<(BH * (nseg - 1) + 7) / 8, 256, 0, st>>>(P, BH, nseg, NC);
+    GDN2_CUDA_TRY(cudaGetLastError());
+  }
+  scan_tc_kernel<<<BH * (2 * nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kFirst, nseg, guarded}, s0, ob, sT, nullptr,
                                                              S, H, o_bs, status);
   GDN2_CUDA_TRY(cudaGetLastError());
   const size_t csmem = (size_t)(D * kTPad + D * kCombineCols) * sizeof(float);
   GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
-  scan_combine_kernel<<<dim3(BH, D / kCombineCols), 256, csmem, st>>>(P, nseg, S / BS, sT);
+  scan_combine_kernel<<<dim3(BH, D / kCombineCols), 256, csmem, st>>>(P, nseg, NC, guarded, sT);
   GDN2_CUDA_TRY(cudaGetLastError());
-  scan_tc_kernel<<<BH * (nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kRedo, nseg}, nullptr, ob, nullptr, nullptr,
+  scan_tc_kernel<<<BH * (nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kRedo, nseg, guarded}, nullptr, ob, nullptr, nullptr,
                                                          S, H, o_bs, status);
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
@@ -575,7 +653,7 @@ int launch_output_tc(const WsLayout& L, const WsPtrs& P, const float* hs, void* 
   int runs = (4 * device_sm_count() + BH - 1) / BH;
   if (runs > NC / 4) runs = NC / 4;
   if (runs < 1) runs = 1;
-  scan_tc_kernel<<<BH * runs, kThreads, smem, st>>>(L, P, ScanPlan{kOutput, runs}, nullptr, static_cast<__nv_bfloat16*>(o),
+  scan_tc_kernel<<<BH * runs, kThreads, smem, st>>>(L, P, ScanPlan{kOutput, runs, 0}, nullptr, static_cast<__nv_bfloat16*>(o),
                                                    nullptr, const_cast<float*>(hs), S, H, o_bs, device_status_word());
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;

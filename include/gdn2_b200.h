@@ -242,6 +242,40 @@ int gdn2_layer_front(const gdn2_layer_front_args* args, int dtype, void* stream)
 int gdn2_layer_back(const void* o, const void* proj, const void* norm_weight, void* out, int64_t BS, int64_t H,
                     int64_t DV, int64_t NP, int64_t off_gate, float eps, int dtype, void* stream);
 
+/*
+ * Output projection of a head-parallel layer fused with its all-reduce, for decode-sized inputs (1..8 token
+ * rows): out [rows, hidden] = sum over the `world` ranks of x_r [rows, K] * weight_r [hidden, K]^T, the same
+ * bits on every rank. One launch per rank and call; all ranks must make the same sequence of calls.
+ *
+ * The ranks exchange their fp32 partial sums through an exchange buffer that every rank allocates with
+ * gdn2_oproj_reduce_buffer_bytes() bytes, zeroes ONCE before the first call, and maps into its peers' address
+ * spaces (CUDA IPC, cuMem handles or a symmetric-memory allocator; ordinary peer loads and stores over NVLink,
+ * no multicast). peer_slots[r] is rank r's buffer as seen from THIS rank (its own buffer at index `rank`),
+ * peer_flags[r] the same buffer plus the flags offset the size query reports; both arrays live in device memory.
+ * `epochs` is a local device array of hidden / 32 uint32, zeroed once. A rank that waits longer than
+ * `wait_cycles` SM clock cycles (0 = about 0.1 s) for a peer's partial gives up: the call still completes,
+ * gdn2_check_device_status then reports GDN2_ERR_DEVICE_WAIT (detail bit 30) and `out` is not to be used.
+ * world == 1 degenerates to the plain product (peer arrays may be NULL).
+ * Limits: hidden a multiple of 32; K a multiple of 8 (4 for fp32); rows * K elements at most 64 KiB.
+ * Replaces F.linear(o_proj) followed by an all-reduce in the sharded form of gdn2/attention.py:354-356;
+ * the reference itself has no multi-GPU code.
+ */
+typedef struct gdn2_oproj_reduce_args {
+  const void* x;                 /* [rows, K] */
+  const void* weight;            /* [hidden, K], this rank's columns of o_proj.weight */
+  void* out;                     /* [rows, hidden] */
+  void* const* peer_slots;       /* device array [world] */
+  uint32_t* const* peer_flags;   /* device array [world] */
+  uint32_t* epochs;              /* device array [hidden / 32], local */
+  int64_t rows, K, hidden;
+  int rank, world;
+  int64_t wait_cycles;
+} gdn2_oproj_reduce_args;
+
+/* Bytes of one rank's exchange buffer; *flags_offset (may be NULL) receives the byte offset of its flag array. */
+size_t gdn2_oproj_reduce_buffer_bytes(int64_t world, int64_t hidden, size_t* flags_offset);
+int gdn2_oproj_reduce(const gdn2_oproj_reduce_args* args, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,7 +46,7 @@ def test_status_strings(lib):
 
 def test_workspace_query(lib):
     f = lib.gdn2_prefill_workspace_bytes
-    big = f(4, 16000, 16, 128, 128, _cabi.GDN2_BF16, _cabi.PATH_AUTO)
+    big = f(4, 16000, 16, 128, 128, _cabi.GDN2_BF16, _cabi.PATH_TCGEN05_SERIAL)   # without the cut scan's segment records
     # per chunk-head: WQ 32 KiB + AQK 8 KiB + KG^T 16 KiB + U^T 16 KiB (fp16) + gamma_last 512 B (+ flag and list entry)
     per = 32768 + 8192 + 16384 + 16384 + 512 + 8
     nch = 4 * 16 * 250
@@ -103,11 +103,13 @@ def test_scan_segments_rule(lib):
     the SIMT family or the explicitly serial path; the workspace grows by the segment records and nothing else."""
     f = lib.gdn2_prefill_scan_segments
     bf = _cabi.GDN2_BF16
-    assert f(4, 16000, 16, 128, 128, bf, _cabi.PATH_AUTO) == 1       # 64 pairs: one block per pair fills the chain
-    assert f(4, 16000, 8, 128, 128, bf, _cabi.PATH_AUTO) == 2        # 32 pairs
-    assert f(4, 16000, 4, 128, 128, bf, _cabi.PATH_AUTO) == 5        # 16 pairs: 9 blocks each = 144
+    assert f(4, 16000, 16, 128, 128, bf, _cabi.PATH_AUTO) == 2       # 64 pairs: 128 local blocks fit, the cut is guarded
+    assert f(4, 16000, 8, 128, 128, bf, _cabi.PATH_AUTO) == 4        # 32 pairs: guarded as well
+    assert f(5, 16000, 16, 128, 128, bf, _cabi.PATH_AUTO) == 1       # 80 pairs: two local blocks each would not fit
+    assert f(4, 16000, 4, 128, 128, bf, _cabi.PATH_AUTO) == 5        # 16 pairs: 9 blocks each = 144, everything resident
     assert f(4, 16000, 2, 128, 128, bf, _cabi.PATH_AUTO) == 9        # 8 pairs: 17 blocks each = 136
     assert f(1, 16000, 1, 128, 128, bf, _cabi.PATH_AUTO) == 16       # capped
+    assert f(2, 4096, 16, 128, 128, bf, _cabi.PATH_AUTO) == 2        # 32 pairs, 64 chunks: too short for a guarded cut in 4
     assert f(4, 64 * 15, 2, 128, 128, bf, _cabi.PATH_AUTO) == 1      # shorter than two 8-chunk segments
     assert f(4, 64 * 24, 2, 128, 128, bf, _cabi.PATH_AUTO) == 3
     assert f(4, 16000, 2, 128, 128, bf, _cabi.PATH_TCGEN05_SERIAL) == 1

@@ -101,3 +101,61 @@ def test_fused_front_and_back_match_the_operator_chain(cached, S):
     got = gdn2._cabi.kernels().layer_back(o.to(DEV), fused[7], layer.o_norm.weight.detach(), offs[6],
                                            float(layer.o_norm.eps))
     assert orc.rel_max_err(got.cpu(), want) < 2e-5
+
+
+def _exchange_buffers(K, world, hidden):
+    import ctypes
+
+    off = ctypes.c_size_t(0)
+    nbytes = K.lib.gdn2_oproj_reduce_buffer_bytes(world, hidden, ctypes.byref(off))
+    bufs = [torch.zeros(nbytes // 4, dtype=torch.float32, device=DEV) for _ in range(world)]
+    slots = torch.tensor([b_.data_ptr() for b_ in bufs], dtype=torch.int64, device=DEV)
+    flags = torch.tensor([b_.data_ptr() + off.value for b_ in bufs], dtype=torch.int64, device=DEV)
+    epochs = [torch.zeros(hidden // 32, dtype=torch.int32, device=DEV) for _ in range(world)]
+    return bufs, slots, flags, epochs
+
+
+@pytest.mark.parametrize("dtype,rows,Kdim", [(torch.bfloat16, 2, 256), (torch.bfloat16, 8, 1024), (torch.float32, 3, 96),
+                                             (torch.float16, 1, 2048)])
+def test_fused_output_projection_single_rank(dtype, rows, Kdim):
+    """gdn2_oproj_reduce with one rank is the plain product x W^T (fp32 accumulation, one rounding)."""
+    K = gdn2._cabi.kernels()
+    hidden = 2048
+    gen = torch.Generator().manual_seed(71)
+    x = torch.randn(rows, Kdim, generator=gen).to(dtype).to(DEV)
+    wt = (torch.randn(hidden, Kdim, generator=gen) * 0.05).to(dtype).to(DEV)
+    out = torch.empty(rows, hidden, dtype=dtype, device=DEV)
+    epochs = torch.zeros(hidden // 32, dtype=torch.int32, device=DEV)
+    for call in (1, 2):
+        K.oproj_reduce(x, wt, out, None, None, epochs, 0, 1)
+        want = (x.double() @ wt.double().T).float()
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        assert orc.rel_max_err(out.float().cpu(), want.cpu()) < tol
+        assert int(epochs[0]) == call and int(epochs[-1]) == call
+    K.check_device_status()
+
+
+def test_fused_output_projection_two_ranks_emulated_on_one_gpu():
+    """Two ranks' exchange buffers on ONE GPU, the ranks' kernels launched one after the other: rank 1 goes first,
+    writes its partial sums and flags into both buffers, waits (200 k cycles) for rank 0's flags that nothing has
+    set yet, gives up and reports it; rank 0 then finds rank 1's partials in place and produces the sum. Twice,
+    so both parities of the double-buffered slots and the epoch counters are exercised. (Kernels that wait on
+    one another must not share a GPU, so the concurrent form runs only in the multi-GPU test.)"""
+    K = gdn2._cabi.kernels()
+    K.check_device_status()
+    hidden, rows, Kdim, world = 512, 2, 256, 2
+    bufs, slots, flags, epochs = _exchange_buffers(K, world, hidden)
+    gen = torch.Generator().manual_seed(73)
+    w = [(torch.randn(hidden, Kdim, generator=gen) * 0.05).bfloat16().to(DEV) for _ in range(world)]
+    for step in range(4):
+        x = [torch.randn(rows, Kdim, generator=gen).bfloat16().to(DEV) for _ in range(world)]
+        out1 = torch.empty(rows, hidden, dtype=torch.bfloat16, device=DEV)
+        K.oproj_reduce(x[1], w[1], out1, slots, flags, epochs[1], 1, world, wait_cycles=200_000)
+        with pytest.raises(gdn2._cabi.GDN2KernelError, match="bounded wait"):
+            K.check_device_status()
+        out0 = torch.empty(rows, hidden, dtype=torch.bfloat16, device=DEV)
+        K.oproj_reduce(x[0], w[0], out0, slots, flags, epochs[0], 0, world, wait_cycles=200_000)
+        K.check_device_status()                               # rank 0 found everything in place
+        want = (x[0].double() @ w[0].double().T + x[1].double() @ w[1].double().T).float()
+        assert orc.rel_max_err(out0.float().cpu(), want.cpu()) < 1e-2, step
+        assert int(epochs[0][0]) == step + 1 and int(epochs[1][3]) == step + 1

@@ -24,7 +24,8 @@ def _free_port():
 
 
 def _worker(rank, world, port, ret):
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -55,7 +56,23 @@ def _worker(rank, world, port, ret):
         hl = CFG["num_heads"] // world
         s_ref = cache_f.recurrent_state[:, rank * hl:(rank + 1) * hl]
         s_err = ((cache_tp.recurrent_state - s_ref).norm() / s_ref.norm()).item()
-        ret[rank] = (err, s_err, tuple(cache_tp.recurrent_state.shape))
+        # the fused o_proj + sum kernel (peer stores over NVLink) instead of o_proj + all-reduce, eager and
+        # replayed from a CUDA graph: the same sums in another order, so equal up to bf16 rounding
+        tp.enable_fused_reduce()
+        pre_f, cache_e = tp.prefill(x[:, :150])
+        steps_e = torch.stack([tp.step(x[:, t], cache_e)[0] for t in range(150, 170)], 1)
+        _, cache_g = tp.prefill(x[:, :150])
+        graphed = gdn2.GraphedStep(tp, cache_g)
+        steps_g = torch.stack([graphed(x[:, t]).clone() for t in range(150, 170)], 1)
+        _, cache_r = full.prefill(x[:, :150])
+        steps_r = torch.stack([full.step(x[:, t], cache_r)[0] for t in range(150, 170)], 1)
+        torch.cuda.synchronize()
+        from gdn2_tilelang_b200 import _cabi
+        _cabi.kernels().check_device_status(dev)
+        scale_ = steps_r.float().abs().max()
+        f_err = ((steps_e.float() - steps_r.float()).abs().max() / scale_).item()
+        g_equal = bool(torch.equal(steps_g, steps_e))
+        ret[rank] = (err, s_err, tuple(cache_tp.recurrent_state.shape), f_err, g_equal)
     finally:
         dist.destroy_process_group()
 
@@ -66,7 +83,9 @@ def test_head_parallel_layer_matches_single_gpu_layer():
     ret = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
     for rank in range(world):
-        err, s_err, shape = ret[rank]
+        err, s_err, shape, f_err, g_equal = ret[rank]
         assert err < 2e-2, (rank, err)          # bf16 partial sums are added in a different order
         assert s_err < 1e-3, (rank, s_err)      # identical kernels on a head slice
         assert shape == (2, 2, 128, 128)
+        assert f_err < 2e-2, (rank, f_err)      # fused o_proj + sum against the unsharded layer
+        assert g_equal, rank                    # the graph replays the same kernels on the same values
