@@ -422,7 +422,7 @@ def main():
     n_full = S // 64 * 64
     code = _cabi.dtype_code(q.dtype)
     path = K.resolved_path(DK, DV, q.dtype)
-    nbytes = K.lib.gdn2_prefill_workspace_bytes(B, n_full, Hl, DK, DV, code, path)
+    nbytes = K.lib.gdn2_prefill_workspace_bytes(B, n_full, Hl, Hl, DK, DV, code, path)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     o = torch.empty(B, S, Hl, DV, dtype=torch.bfloat16, device=dev)
     fin = torch.empty(B, Hl, DK, DV, dtype=torch.float32, device=dev)
@@ -430,13 +430,13 @@ def main():
 
     def prep():
         rc = K.lib.gdn2_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
-                                   w.data_ptr(), ws.data_ptr(), nbytes, B, n_full, Hl, DK, DV, S, DK**-0.5,
+                                   w.data_ptr(), ws.data_ptr(), nbytes, B, n_full, Hl, Hl, DK, DV, S, DK**-0.5,
                                    code, path, st)
         assert rc == 0, rc
 
     def scan():
         rc = K.lib.gdn2_prefill_scan(ws.data_ptr(), nbytes, None, o.data_ptr(), fin.data_ptr(), None,
-                                     B, n_full, Hl, DK, DV, S, code, path, st)
+                                     B, n_full, Hl, Hl, DK, DV, S, code, path, st)
         assert rc == 0, rc
 
     ms_prep = time_events(prep, args.steps, 3, barrier)

@@ -34,13 +34,13 @@ SIGNATURES = {
     "gdn2_abi_version": (_int, []),
     "gdn2_status_string": (ctypes.c_char_p, [_int]),
     "gdn2_last_cuda_error": (_int, []),
-    "gdn2_decode": (_int, [_vp] * 8 + [_i64] * 7 + [_f32, _int, _vp]),
-    "gdn2_prefill_workspace_bytes": (_sz, [_i64] * 5 + [_int, _int]),
+    "gdn2_decode": (_int, [_vp] * 8 + [_i64] * 8 + [_f32, _int, _vp]),
+    "gdn2_prefill_workspace_bytes": (_sz, [_i64] * 6 + [_int, _int]),
     "gdn2_prefill_scan_segments": (_int, [_i64] * 5 + [_int, _int]),
-    "gdn2_prefill_workspace_layout": (_int, [_i64] * 5 + [_int, _int, ctypes.POINTER(ctypes.c_int64)]),
-    "gdn2_chunk_prep": (_int, [_vp] * 7 + [_sz] + [_i64] * 6 + [_f32, _int, _int, _vp]),
-    "gdn2_prefill_scan": (_int, [_vp, _sz, _vp, _vp, _vp, _vp] + [_i64] * 6 + [_int, _int, _vp]),
-    "gdn2_chunk_output": (_int, [_vp, _sz, _vp, _vp] + [_i64] * 6 + [_int, _int, _vp]),
+    "gdn2_prefill_workspace_layout": (_int, [_i64] * 6 + [_int, _int, ctypes.POINTER(ctypes.c_int64)]),
+    "gdn2_chunk_prep": (_int, [_vp] * 7 + [_sz] + [_i64] * 7 + [_f32, _int, _int, _vp]),
+    "gdn2_prefill_scan": (_int, [_vp, _sz, _vp, _vp, _vp, _vp] + [_i64] * 7 + [_int, _int, _vp]),
+    "gdn2_chunk_output": (_int, [_vp, _sz, _vp, _vp] + [_i64] * 7 + [_int, _int, _vp]),
     "gdn2_check_device_status": (_int, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
     "gdn2_selftest_mma": (_int, [_vp, _vp, _vp, _vp]),
     "gdn2_selftest_wait": (_int, [_i64, _vp, _vp]),
@@ -185,8 +185,8 @@ class NativeKernels:
         ``out`` may be a ``[B,n,H,DV]`` view into a longer preallocated sequence tensor.
         """
         _require_cuda(q, k, v, g, b, w, state)
-        B, n, H, DK = q.shape
-        DV = v.shape[-1]
+        B, n, HK, DK = q.shape
+        H, DV = v.shape[2], v.shape[-1]
         code = dtype_code(q.dtype)
         if state.dtype != torch.float32 or not state.is_contiguous():
             raise ValueError("the recurrent state must be a contiguous float32 tensor")
@@ -204,7 +204,7 @@ class NativeKernels:
                 raise ValueError("`out` must be a [B,n,H,DV] view with dense [n,H,DV] blocks in v's dtype")
         with torch.cuda.device(q.device):
             rc = self.lib.gdn2_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
-                                      w.data_ptr(), state.data_ptr(), o.data_ptr(), B, n, H, DK, DV, in_bs, o_bs,
+                                      w.data_ptr(), state.data_ptr(), o.data_ptr(), B, n, H, HK, DK, DV, in_bs, o_bs,
                                       float(scale), code, self._stream(q))
         _check(self.lib, rc, "gdn2_decode")
         self.launches += 1
@@ -219,8 +219,8 @@ class NativeKernels:
         per batch entry receive the result (``out_batch_stride`` = its token stride).
         """
         _require_cuda(q, k, v, g, b, w, initial_state)
-        B, S, H, DK = q.shape
-        DV = v.shape[-1]
+        B, S, HK, DK = q.shape
+        H, DV = v.shape[2], v.shape[-1]
         if S % CHUNK:
             raise ValueError(f"sequence length {S} must be a multiple of {CHUNK}")
         code = dtype_code(q.dtype)
@@ -231,7 +231,7 @@ class NativeKernels:
         in_bs = views[0][1]
         q, k, v, g, b, w = (t for t, _ in views)
         dev = q.device
-        nbytes = self.lib.gdn2_prefill_workspace_bytes(B, S, H, DK, DV, code, p)
+        nbytes = self.lib.gdn2_prefill_workspace_bytes(B, S, H, HK, DK, DV, code, p)
         if nbytes == 0:
             raise GDN2KernelError(
                 f"no kernel for DK={DK}, DV={DV}, dtype={q.dtype} (SIMT family: DK<=128, DK%8==0, DV%4==0)")
@@ -263,11 +263,11 @@ class NativeKernels:
             for i in range(nseg):
                 c0, c1 = bounds[i], bounds[i + 1]
                 t0, S_i = c0 * CHUNK, (c1 - c0) * CHUNK
-                nb_i = nbytes if nseg == 1 else self.lib.gdn2_prefill_workspace_bytes(B, S_i, H, DK, DV, code, p)
+                nb_i = nbytes if nseg == 1 else self.lib.gdn2_prefill_workspace_bytes(B, S_i, H, HK, DK, DV, code, p)
                 ws_i = torch.empty(nb_i, dtype=torch.uint8, device=dev)
                 scratch.append(ws_i)
-                ptrs = [x.data_ptr() + t0 * H * x.shape[-1] * x.element_size() for x in (q, k, v, g, b, w)]
-                rc = self.lib.gdn2_chunk_prep(*ptrs, ws_i.data_ptr(), nb_i, B, S_i, H, DK, DV, in_bs, float(scale),
+                ptrs = [x.data_ptr() + t0 * x.shape[2] * x.shape[-1] * x.element_size() for x in (q, k, v, g, b, w)]
+                rc = self.lib.gdn2_chunk_prep(*ptrs, ws_i.data_ptr(), nb_i, B, S_i, H, HK, DK, DV, in_bs, float(scale),
                                               code, p, main.cuda_stream)
                 _check(self.lib, rc, "gdn2_chunk_prep")
                 scan_stream = main
@@ -278,7 +278,7 @@ class NativeKernels:
                     scan_stream = side
                 rc = self.lib.gdn2_prefill_scan(ws_i.data_ptr(), nb_i, state_ptr, out.data_ptr() + t0 * H * DV * esz,
                                                 states[i].data_ptr(), None if hs is None else hs.data_ptr(),
-                                                B, S_i, H, DK, DV, out_batch_stride, code, p, scan_stream.cuda_stream)
+                                                B, S_i, H, HK, DK, DV, out_batch_stride, code, p, scan_stream.cuda_stream)
                 _check(self.lib, rc, "gdn2_prefill_scan")
                 state_ptr = states[i].data_ptr()
                 cut = 1 if want_chunk_states else self.scan_segments(B, S_i, H, DK, DV, q.dtype, p)
@@ -292,22 +292,22 @@ class NativeKernels:
     def chunk_output(self, q, k, v, g, b, w, scale: float, chunk_states, path=None):
         """Chunk-parallel output from stored chunk states (re-runs the chunk-local stage)."""
         _require_cuda(q, chunk_states)
-        B, S, H, DK = q.shape
-        DV = v.shape[-1]
+        B, S, HK, DK = q.shape
+        H, DV = v.shape[2], v.shape[-1]
         code = dtype_code(q.dtype)
         p = self.resolved_path(DK, DV, q.dtype, path)
         q, k, v, g, b, w = (t.contiguous() for t in (q, k, v, g, b, w))
-        nbytes = self.lib.gdn2_prefill_workspace_bytes(B, S, H, DK, DV, code, p)
+        nbytes = self.lib.gdn2_prefill_workspace_bytes(B, S, H, HK, DK, DV, code, p)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
         out = torch.empty(B, S, H, DV, dtype=v.dtype, device=q.device)
         st = self._stream(q)
         with torch.cuda.device(q.device):
             rc = self.lib.gdn2_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
-                                          w.data_ptr(), ws.data_ptr(), nbytes, B, S, H, DK, DV, S, float(scale),
+                                          w.data_ptr(), ws.data_ptr(), nbytes, B, S, H, HK, DK, DV, S, float(scale),
                                           code, p, st)
             _check(self.lib, rc, "gdn2_chunk_prep")
             rc = self.lib.gdn2_chunk_output(ws.data_ptr(), nbytes, chunk_states.data_ptr(), out.data_ptr(),
-                                            B, S, H, DK, DV, S, code, p, st)
+                                            B, S, H, HK, DK, DV, S, code, p, st)
             _check(self.lib, rc, "gdn2_chunk_output")
         self.launches += 3 if p != PATH_SIMT else 2
         return out
@@ -369,27 +369,27 @@ class NativeKernels:
         if os.environ.get("GDN2_B200_CHECK_STATUS", "0") not in ("", "0"):
             self.check_device_status(device)
 
-    def workspace_layout(self, B, S, H, DK, DV, dtype, path=None) -> dict:
+    def workspace_layout(self, B, S, H, DK, DV, dtype, path=None, HK=None) -> dict:
         """Byte offsets of the record arrays inside the prefill workspace (``gdn2_prefill_workspace_layout``)."""
         p = self.resolved_path(DK, DV, dtype, path)
         out = (ctypes.c_int64 * 8)()
-        _check(self.lib, self.lib.gdn2_prefill_workspace_layout(B, S, H, DK, DV, dtype_code(dtype), p, out),
+        _check(self.lib, self.lib.gdn2_prefill_workspace_layout(B, S, H, HK or H, DK, DV, dtype_code(dtype), p, out),
                "gdn2_prefill_workspace_layout")
         return dict(zip(("wq", "aqk", "kgt", "ut", "gl", "flags", "seg", "total"), list(out)))
 
     def chunk_prep(self, q, k, v, g, b, w, scale: float, path=None):
         """The chunk-local stage alone. Returns ``(workspace uint8 tensor, resolved path)``."""
         _require_cuda(q)
-        B, S, H, DK = q.shape
-        DV = v.shape[-1]
+        B, S, HK, DK = q.shape
+        H, DV = v.shape[2], v.shape[-1]
         code = dtype_code(q.dtype)
         p = self.resolved_path(DK, DV, q.dtype, path)
         q, k, v, g, b, w = (t.contiguous() for t in (q, k, v, g, b, w))
-        nbytes = self.lib.gdn2_prefill_workspace_bytes(B, S, H, DK, DV, code, p)
+        nbytes = self.lib.gdn2_prefill_workspace_bytes(B, S, H, HK, DK, DV, code, p)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
         with torch.cuda.device(q.device):
             rc = self.lib.gdn2_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
-                                          w.data_ptr(), ws.data_ptr(), nbytes, B, S, H, DK, DV, S, float(scale),
+                                          w.data_ptr(), ws.data_ptr(), nbytes, B, S, H, HK, DK, DV, S, float(scale),
                                           code, p, self._stream(q))
         _check(self.lib, rc, "gdn2_chunk_prep")
         self.launches += 2 if p != PATH_SIMT else 1

@@ -78,8 +78,8 @@ def _packed_attention(q, k, v, g, b, w, scale, initial_state, output_final_state
     """Variable-length batch packed into one row: one chunkwise (+ tail) evaluation per sequence, all queued on
     the current stream, results written straight into the packed output."""
     offs = [int(x) for x in (cu_seqlens.tolist() if torch.is_tensor(cu_seqlens) else cu_seqlens)]
-    B, T, H, DK = q.shape
-    DV = v.shape[-1]
+    B, T, _, DK = q.shape
+    H, DV = v.shape[2], v.shape[-1]
     N = len(offs) - 1
     if B != 1:
         raise ValueError("with cu_seqlens the sequences are packed into one batch entry: expected B == 1")

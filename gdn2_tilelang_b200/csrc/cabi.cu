@@ -56,13 +56,14 @@ int resolve_path(int64_t DK, int64_t DV, int dtype, int path, int* resolved, boo
 }
 
 // The workspace layout of a validated problem.
-WsLayout layout_for(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int family, bool segments) {
-  return make_ws_layout(B, S, H, (int)DK, (int)DV, family == GDN2_PATH_TCGEN05 ? 2 : 4, segments);
+WsLayout layout_for(int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV, int family, bool segments) {
+  return make_ws_layout(B, S, H, HK, (int)DK, (int)DV, family == GDN2_PATH_TCGEN05 ? 2 : 4, segments);
 }
 
-int check_prefill_shape(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype) {
+int check_prefill_shape(int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV, int dtype) {
   if (!valid_dtype(dtype)) return GDN2_ERR_BAD_DTYPE;
   if (B <= 0 || S <= 0 || H <= 0 || DK <= 0 || DV <= 0 || S % kChunk != 0) return GDN2_ERR_BAD_SHAPE;
+  if (HK <= 0 || H % HK != 0) return GDN2_ERR_BAD_SHAPE;            // value heads share key heads in equal groups
   // the chunk-local kernels put (batch, head) on gridDim.y
   if (B * H > 65535 || S > (1LL << 30)) return GDN2_ERR_BAD_SHAPE;
   return GDN2_OK;
@@ -97,54 +98,57 @@ const char* gdn2_status_string(int status) {
 int gdn2_last_cuda_error(void) { return g_last_cuda_error; }
 
 int gdn2_decode(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                float* state, void* o, int64_t B, int64_t n, int64_t H, int64_t DK, int64_t DV,
+                float* state, void* o, int64_t B, int64_t n, int64_t H, int64_t HK, int64_t DK, int64_t DV,
                 int64_t in_batch_stride, int64_t o_batch_stride, float scale, int dtype, void* stream) {
   if (!q || !k || !v || !g || !b || !w || !state || !o) return GDN2_ERR_NULL_POINTER;
   if (!valid_dtype(dtype)) return GDN2_ERR_BAD_DTYPE;
   if (B <= 0 || n <= 0 || H <= 0 || DK <= 0 || DV <= 0 || DK > 256) return GDN2_ERR_BAD_SHAPE;
+  if (HK <= 0 || H % HK != 0) return GDN2_ERR_BAD_SHAPE;
   if (B * H > 2147483647LL / 4 || n > (1 << 24)) return GDN2_ERR_BAD_SHAPE;
   if (in_batch_stride < n || o_batch_stride < n) return GDN2_ERR_BAD_SHAPE;
   if (DK == 128 && DV == 128 && !aligned16(state)) return GDN2_ERR_MISALIGNED;
-  return launch_decode(q, k, v, g, b, w, state, o, (int)B, (int)n, (int)H, (int)DK, (int)DV, in_batch_stride,
+  return launch_decode(q, k, v, g, b, w, state, o, (int)B, (int)n, (int)H, (int)HK, (int)DK, (int)DV, in_batch_stride,
                        o_batch_stride, scale, dtype, static_cast<cudaStream_t>(stream));
 }
 
-size_t gdn2_prefill_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path) {
-  if (check_prefill_shape(B, S, H, DK, DV, dtype) != GDN2_OK) return 0;
+size_t gdn2_prefill_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV, int dtype,
+                                    int path) {
+  if (check_prefill_shape(B, S, H, HK, DK, DV, dtype) != GDN2_OK) return 0;
   int p;
   bool seg;
   if (resolve_path(DK, DV, dtype, path, &p, &seg) != GDN2_OK) return 0;
-  return layout_for(B, S, H, DK, DV, p, seg).total;
+  return layout_for(B, S, H, HK, DK, DV, p, seg).total;
 }
 
-int gdn2_prefill_workspace_layout(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path,
-                                  int64_t* out8) {
+int gdn2_prefill_workspace_layout(int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV, int dtype,
+                                  int path, int64_t* out8) {
   if (!out8) return GDN2_ERR_NULL_POINTER;
-  int rc = check_prefill_shape(B, S, H, DK, DV, dtype);
+  int rc = check_prefill_shape(B, S, H, HK, DK, DV, dtype);
   if (rc != GDN2_OK) return rc;
   int p;
   bool seg;
   rc = resolve_path(DK, DV, dtype, path, &p, &seg);
   if (rc != GDN2_OK) return rc;
-  const WsLayout L = layout_for(B, S, H, DK, DV, p, seg);
+  const WsLayout L = layout_for(B, S, H, HK, DK, DV, p, seg);
   const size_t v[8] = {L.off_wq, L.off_aqk, L.off_kgt, L.off_ut, L.off_gl, L.off_flags, L.off_seg, L.total};
   for (int i = 0; i < 8; ++i) out8[i] = (int64_t)v[i];
   return GDN2_OK;
 }
 
 int gdn2_prefill_scan_segments(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path) {
-  if (check_prefill_shape(B, S, H, DK, DV, dtype) != GDN2_OK) return 0;
+  const int64_t HK = H;                                    // the cut depends on the (batch, value head) pairs only
+  if (check_prefill_shape(B, S, H, HK, DK, DV, dtype) != GDN2_OK) return 0;
   int p;
   bool seg;
   if (resolve_path(DK, DV, dtype, path, &p, &seg) != GDN2_OK) return 0;
-  return layout_for(B, S, H, DK, DV, p, seg).nseg;
+  return layout_for(B, S, H, HK, DK, DV, p, seg).nseg;
 }
 
 int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                    void* workspace, size_t workspace_bytes, int64_t B, int64_t S, int64_t H, int64_t DK,
+                    void* workspace, size_t workspace_bytes, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
                     int64_t DV, int64_t in_batch_stride, float scale, int dtype, int path, void* stream) {
   if (!q || !k || !v || !g || !b || !w || !workspace) return GDN2_ERR_NULL_POINTER;
-  int rc = check_prefill_shape(B, S, H, DK, DV, dtype);
+  int rc = check_prefill_shape(B, S, H, HK, DK, DV, dtype);
   if (rc != GDN2_OK) return rc;
   if (in_batch_stride < S) return GDN2_ERR_BAD_SHAPE;
   int p;
@@ -154,24 +158,24 @@ int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g,
   if (!aligned16(workspace) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(g) ||
       !aligned16(b) || !aligned16(w))
     return GDN2_ERR_MISALIGNED;
-  const WsLayout L = layout_for(B, S, H, DK, DV, p, seg);
+  const WsLayout L = layout_for(B, S, H, HK, DK, DV, p, seg);
   if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
   const WsPtrs P = ws_pointers(workspace, L);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (p == GDN2_PATH_TCGEN05) {
-    rc = launch_prep_tc(q, k, v, g, b, w, L, P, (int)B, (int)S, (int)H, in_batch_stride, scale, st);
+    rc = launch_prep_tc(q, k, v, g, b, w, L, P, (int)B, (int)S, (int)H, (int)HK, in_batch_stride, scale, st);
     if (rc != GDN2_OK) return rc;
     // chunks whose decay is too fast for the factorised diagonal blocks are redone exactly
-    return launch_prep_simt(q, k, v, g, b, w, L, P, (int)B, (int)S, (int)H, in_batch_stride, scale, dtype, true, st);
+    return launch_prep_simt(q, k, v, g, b, w, L, P, (int)B, (int)S, (int)H, (int)HK, in_batch_stride, scale, dtype, true, st);
   }
-  return launch_prep_simt(q, k, v, g, b, w, L, P, (int)B, (int)S, (int)H, in_batch_stride, scale, dtype, false, st);
+  return launch_prep_simt(q, k, v, g, b, w, L, P, (int)B, (int)S, (int)H, (int)HK, in_batch_stride, scale, dtype, false, st);
 }
 
 int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
-                      float* final_state, float* chunk_states, int64_t B, int64_t S, int64_t H, int64_t DK,
+                      float* final_state, float* chunk_states, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
                       int64_t DV, int64_t o_batch_stride, int dtype, int path, void* stream) {
   if (!workspace || !o) return GDN2_ERR_NULL_POINTER;
-  int rc = check_prefill_shape(B, S, H, DK, DV, dtype);
+  int rc = check_prefill_shape(B, S, H, HK, DK, DV, dtype);
   if (rc != GDN2_OK) return rc;
   if (o_batch_stride < S) return GDN2_ERR_BAD_SHAPE;
   int p;
@@ -179,7 +183,7 @@ int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float
   rc = resolve_path(DK, DV, dtype, path, &p, &seg);
   if (rc != GDN2_OK) return rc;
   if (!aligned16(workspace)) return GDN2_ERR_MISALIGNED;
-  const WsLayout L = layout_for(B, S, H, DK, DV, p, seg);
+  const WsLayout L = layout_for(B, S, H, HK, DK, DV, p, seg);
   if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
   const WsPtrs P = ws_pointers(const_cast<void*>(workspace), L);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -191,10 +195,10 @@ int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float
 }
 
 int gdn2_chunk_output(const void* workspace, size_t workspace_bytes, const float* chunk_states, void* o,
-                      int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int64_t o_batch_stride, int dtype,
-                      int path, void* stream) {
+                      int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV, int64_t o_batch_stride,
+                      int dtype, int path, void* stream) {
   if (!workspace || !o || !chunk_states) return GDN2_ERR_NULL_POINTER;
-  int rc = check_prefill_shape(B, S, H, DK, DV, dtype);
+  int rc = check_prefill_shape(B, S, H, HK, DK, DV, dtype);
   if (rc != GDN2_OK) return rc;
   if (o_batch_stride < S) return GDN2_ERR_BAD_SHAPE;
   int p;
@@ -202,7 +206,7 @@ int gdn2_chunk_output(const void* workspace, size_t workspace_bytes, const float
   rc = resolve_path(DK, DV, dtype, path, &p, &seg);
   if (rc != GDN2_OK) return rc;
   if (!aligned16(workspace)) return GDN2_ERR_MISALIGNED;
-  const WsLayout L = layout_for(B, S, H, DK, DV, p, seg);
+  const WsLayout L = layout_for(B, S, H, HK, DK, DV, p, seg);
   if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
   const WsPtrs P = ws_pointers(const_cast<void*>(workspace), L);
   if (p == GDN2_PATH_TCGEN05)

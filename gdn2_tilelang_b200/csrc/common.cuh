@@ -38,7 +38,9 @@ __device__ __forceinline__ float tf32_rn(float x) {
 
 // ---------------------------------------------------------------- workspace layout
 //
-// One record set per chunk-head, index ch = (b*H + h)*NC + n. All matrices are stored as
+// One record set per chunk-head. The records that depend on q, k, b, g only (WQ, AQK, KGT, GL) exist once per
+// KEY head, index (b*HK + hk)*NC + n; UT exists per VALUE head, index (b*H + h)*NC + n, and value head h reads the
+// records of key head h / (H/HK) (grouped-query heads share them; with HK = H the two indices coincide). All matrices are stored as
 // "K-chunked" operand images: a matrix with R rows and a reduction axis of K elements is an
 // array [K/E][R][E] where E elements fill 16 bytes (E = 8 for bf16, 4 for fp32). This is the
 // no-swizzle, K-major shared-memory layout tcgen05.mma reads (8 rows x 16 bytes core matrices,
@@ -57,8 +59,10 @@ __device__ __forceinline__ float tf32_rn(float x) {
 // everything above 0.016 stays a normal number, and the product (Un/256) * (256 KG) is exact.
 
 struct WsLayout {
-  int64_t nch;        // number of chunk-heads
-  int64_t BH;         // (batch, head) pairs
+  int64_t nch;        // number of key chunk-heads, B * HK * S/64: records WQ, AQK, KG^T, gamma_last, flags
+  int64_t nch_v;      // number of value chunk-heads, B * H * S/64: records U^T
+  int64_t BH;         // (batch, value head) pairs
+  int rep;            // value heads per key head, H / HK (grouped-query heads; 1 = every head has its own q, k, b, g)
   int DK, DV;
   int esz;            // bytes per TW element (2 or 4); TV has the same size
   int nseg;           // sequence segments of the tensor-core scan (1 = one block per head walks the whole sequence)
@@ -88,11 +92,13 @@ __host__ __device__ inline int scan_segments(int64_t BH, int64_t NC, int* guarde
   return fit < 2 ? 1 : (int)fit;
 }
 
-__host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK, int DV, int esz,
+__host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int64_t HK, int DK, int DV, int esz,
                                         bool allow_segments = false) {
   WsLayout L;
-  L.nch = B * H * (S / kChunk);
+  L.nch = B * HK * (S / kChunk);
+  L.nch_v = B * H * (S / kChunk);
   L.BH = B * H;
+  L.rep = (int)(H / HK);
   L.DK = DK; L.DV = DV; L.esz = esz;
   L.nseg_guarded = 0;
   L.nseg = (allow_segments && esz == 2) ? scan_segments(B * H, S / kChunk, &L.nseg_guarded) : 1;
@@ -105,7 +111,7 @@ __host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int DK,
   L.off_wq = off;   off = align_up(off + L.wq_bytes * L.nch, 1024);
   L.off_aqk = off;  off = align_up(off + L.aqk_bytes * L.nch, 1024);
   L.off_kgt = off;  off = align_up(off + L.kgt_bytes * L.nch, 1024);
-  L.off_ut = off;   off = align_up(off + L.ut_bytes * L.nch, 1024);
+  L.off_ut = off;   off = align_up(off + L.ut_bytes * L.nch_v, 1024);
   L.off_gl = off;   off = align_up(off + L.gl_bytes * L.nch, 1024);
   L.off_flags = off; off = align_up(off + sizeof(int) * (2 * L.nch + 4), 1024);   // flags, compacted list, count
   // per (batch, head) and segment: transition T_j, local final state C_j, true entering state (fp32 [DK, DV]
@@ -178,18 +184,19 @@ int device_sm_count();            // streaming multiprocessors of the current de
 
 // ---------------------------------------------------------------- launchers (one per .cu file)
 
+// H = value heads, HK = key heads (H % HK == 0): q, k, b, g are [.., HK, DK], v, w, o [.., H, DV]
 int launch_decode(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                  float* state, void* o, int B, int n, int H, int DK, int DV, int64_t in_bs, int64_t o_bs,
+                  float* state, void* o, int B, int n, int H, int HK, int DK, int DV, int64_t in_bs, int64_t o_bs,
                   float scale, int dtype, cudaStream_t st);
 int launch_prep_simt(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                     const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
+                     const WsLayout& L, const WsPtrs& P, int B, int S, int H, int HK, int64_t in_bs, float scale,
                      int dtype, bool only_flagged, cudaStream_t st);
 int launch_scan_simt(const WsLayout& L, const WsPtrs& P, const float* s0, void* o, float* sT, float* hs,
                      int B, int S, int H, int64_t o_bs, int dtype, cudaStream_t st);
 int launch_output_simt(const WsLayout& L, const WsPtrs& P, const float* hs, void* o, int B, int S, int H,
                        int64_t o_bs, int dtype, cudaStream_t st);
 int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                   const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
+                   const WsLayout& L, const WsPtrs& P, int B, int S, int H, int HK, int64_t in_bs, float scale,
                    cudaStream_t st);
 int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o, float* sT, float* hs,
                    int B, int S, int H, int64_t o_bs, cudaStream_t st);

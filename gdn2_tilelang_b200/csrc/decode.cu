@@ -24,7 +24,7 @@ namespace gdn2 {
 // decode_blocked.cu: blocks of up to 8 tokens without a per-token dependent sweep (DK = DV = 128)
 template <typename T>
 int launch_decode_blocked(const T* q, const T* k, const T* v, const float* g, const T* b, const T* w, float* state,
-                          T* o, int B, int n, int H, int64_t in_bs, int64_t o_bs, float scale, cudaStream_t st);
+                          T* o, int B, int n, int H, int HK, int64_t in_bs, int64_t o_bs, float scale, cudaStream_t st);
 
 namespace {
 
@@ -55,10 +55,12 @@ template <typename T>
 __global__ void __launch_bounds__(128, 3)
 decode_d128_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                    const float* __restrict__ g, const T* __restrict__ b, const T* __restrict__ w,
-                   float* __restrict__ state, T* __restrict__ o, int n, int H, int64_t in_bs, int64_t o_bs, float scale) {
+                   float* __restrict__ state, T* __restrict__ o, int n, int H, int HK, int64_t in_bs, int64_t o_bs,
+                   float scale) {
   constexpr int D = 128;
   const int bh = blockIdx.x;
   const int ib = bh / H, ih = bh % H;
+  const int ihk = ih / (H / HK);                         // the key head this value head reads q, k, b, g from
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
   const int rg = lane >> 3, cq = lane & 7;               // 32-row group, 4-column group inside the warp's 32 columns
   const int col0 = 32 * wid + 4 * cq;
@@ -79,10 +81,11 @@ decode_d128_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __
     __syncthreads();                                     // the previous batch's vectors are no longer read
     for (int j = 0; j < nt; ++j) {
       const size_t tok = ((size_t)ib * in_bs + (t0 + j)) * H + ih;
-      const float a = exp2f(g[tok * D + tid] * kLog2e);
-      const float kk = to_f32(k[tok * D + tid]);
-      const float abk = a * to_f32(b[tok * D + tid]) * kk;
-      const float qs = to_f32(q[tok * D + tid]) * scale;
+      const size_t tokk = ((size_t)ib * in_bs + (t0 + j)) * HK + ihk;
+      const float a = exp2f(g[tokk * D + tid] * kLog2e);
+      const float kk = to_f32(k[tokk * D + tid]);
+      const float abk = a * to_f32(b[tokk * D + tid]) * kk;
+      const float qs = to_f32(q[tokk * D + tid]) * scale;
       s_p1[j][prow(tid)] = make_float4(abk, abk, qs * a, qs * a);
       s_p2[j][prow(tid)] = make_float4(kk, kk, a, a);
       s_wv[j][tid] = to_f32(w[tok * D + tid]) * to_f32(v[tok * D + tid]);
@@ -143,10 +146,11 @@ template <typename T, int MAXR>
 __global__ void __launch_bounds__(128)
 decode_generic_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                       const float* __restrict__ g, const T* __restrict__ b, const T* __restrict__ w,
-                      float* __restrict__ state, T* __restrict__ o, int n, int H, int DK, int DV, int64_t in_bs,
+                      float* __restrict__ state, T* __restrict__ o, int n, int H, int HK, int DK, int DV, int64_t in_bs,
                       int64_t o_bs, float scale) {
   const int bh = blockIdx.x;                 // (batch, head) on x: no 65535 limit
   const int ib = bh / H, ih = bh % H;
+  const int ihk = ih / (H / HK);             // the key head this value head reads q, k, b, g from
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
   const int dv = blockIdx.y * 32 + lane;
   const bool col_ok = dv < DV;
@@ -168,14 +172,15 @@ decode_generic_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
   }
   for (int t = 0; t < n; ++t) {
     const size_t tok = ((size_t)ib * in_bs + t) * H + ih;
+    const size_t tokk = ((size_t)ib * in_bs + t) * HK + ihk;
     const size_t otok = ((size_t)ib * o_bs + t) * H + ih;
     __syncthreads();
     for (int c = tid; c < DK; c += 128) {
-      const float a = exp2f(g[tok * DK + c] * kLog2e);
-      const float kk = to_f32(k[tok * DK + c]);
+      const float a = exp2f(g[tokk * DK + c] * kLog2e);
+      const float kk = to_f32(k[tokk * DK + c]);
       s_a[c] = a; s_k[c] = kk;
-      s_abk[c] = a * to_f32(b[tok * DK + c]) * kk;
-      s_q[c] = to_f32(q[tok * DK + c]) * scale;
+      s_abk[c] = a * to_f32(b[tokk * DK + c]) * kk;
+      s_q[c] = to_f32(q[tokk * DK + c]) * scale;
     }
     const float wv = col_ok ? to_f32(w[tok * DV + dv]) * to_f32(v[tok * DV + dv]) : 0.f;
     __syncthreads();
@@ -211,24 +216,24 @@ decode_generic_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
 
 template <typename T>
 int launch_typed(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                 float* state, void* o, int B, int n, int H, int DK, int DV, int64_t in_bs, int64_t o_bs, float scale,
+                 float* state, void* o, int B, int n, int H, int HK, int DK, int DV, int64_t in_bs, int64_t o_bs, float scale,
                  cudaStream_t st) {
   const T* tq = static_cast<const T*>(q); const T* tk = static_cast<const T*>(k);
   const T* tv = static_cast<const T*>(v); const T* tb = static_cast<const T*>(b);
   const T* tw = static_cast<const T*>(w); T* to = static_cast<T*>(o);
   if (DK == 128 && DV == 128 && n >= kBlockedMinTokens) {
-    return launch_decode_blocked<T>(tq, tk, tv, g, tb, tw, state, to, B, n, H, in_bs, o_bs, scale, st);
+    return launch_decode_blocked<T>(tq, tk, tv, g, tb, tw, state, to, B, n, H, HK, in_bs, o_bs, scale, st);
   } else if (DK == 128 && DV == 128) {
-    decode_d128_kernel<T><<<B * H, 128, 0, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, in_bs, o_bs, scale);
+    decode_d128_kernel<T><<<B * H, 128, 0, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, HK, in_bs, o_bs, scale);
   } else {
     dim3 grid(B * H, (DV + 31) / 32);
     const size_t sm = (size_t)4 * DK * sizeof(float);
     if (DK <= 64)
-      decode_generic_kernel<T, 16><<<grid, 128, sm, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, DK, DV, in_bs, o_bs, scale);
+      decode_generic_kernel<T, 16><<<grid, 128, sm, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, HK, DK, DV, in_bs, o_bs, scale);
     else if (DK <= 128)
-      decode_generic_kernel<T, 32><<<grid, 128, sm, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, DK, DV, in_bs, o_bs, scale);
+      decode_generic_kernel<T, 32><<<grid, 128, sm, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, HK, DK, DV, in_bs, o_bs, scale);
     else
-      decode_generic_kernel<T, 64><<<grid, 128, sm, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, DK, DV, in_bs, o_bs, scale);
+      decode_generic_kernel<T, 64><<<grid, 128, sm, st>>>(tq, tk, tv, g, tb, tw, state, to, n, H, HK, DK, DV, in_bs, o_bs, scale);
   }
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
@@ -237,12 +242,12 @@ int launch_typed(const void* q, const void* k, const void* v, const float* g, co
 }  // namespace
 
 int launch_decode(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                  float* state, void* o, int B, int n, int H, int DK, int DV, int64_t in_bs, int64_t o_bs,
+                  float* state, void* o, int B, int n, int H, int HK, int DK, int DV, int64_t in_bs, int64_t o_bs,
                   float scale, int dtype, cudaStream_t st) {
   switch (dtype) {
-    case GDN2_F32: return launch_typed<float>(q, k, v, g, b, w, state, o, B, n, H, DK, DV, in_bs, o_bs, scale, st);
-    case GDN2_BF16: return launch_typed<__nv_bfloat16>(q, k, v, g, b, w, state, o, B, n, H, DK, DV, in_bs, o_bs, scale, st);
-    case GDN2_F16: return launch_typed<__half>(q, k, v, g, b, w, state, o, B, n, H, DK, DV, in_bs, o_bs, scale, st);
+    case GDN2_F32: return launch_typed<float>(q, k, v, g, b, w, state, o, B, n, H, HK, DK, DV, in_bs, o_bs, scale, st);
+    case GDN2_BF16: return launch_typed<__nv_bfloat16>(q, k, v, g, b, w, state, o, B, n, H, HK, DK, DV, in_bs, o_bs, scale, st);
+    case GDN2_F16: return launch_typed<__half>(q, k, v, g, b, w, state, o, B, n, H, HK, DK, DV, in_bs, o_bs, scale, st);
     default: return GDN2_ERR_BAD_DTYPE;
   }
 }

@@ -112,7 +112,7 @@ template <typename T>
 __global__ void __launch_bounds__(kAllThreads, 1)
 decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __restrict__ v,
                       const float* __restrict__ g, const T* __restrict__ b, const T* __restrict__ w,
-                      float* __restrict__ state, T* __restrict__ o, int ntiles, int n, int H, int64_t in_bs,
+                      float* __restrict__ state, T* __restrict__ o, int ntiles, int n, int H, int HK, int64_t in_bs,
                       int64_t o_bs, float scale, uint32_t* status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   BlockedSmem& s = *reinterpret_cast<BlockedSmem*>(smem_raw);
@@ -166,6 +166,7 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     int step = 0;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
       const int ib = tile / H, ih = tile % H;
+      const int ihk = ih / (H / HK);                     // the key head this value head reads q, k, b, g from
       for (int t0 = 0; t0 < n; t0 += NB, ++step) {
         const int nb = min(NB, n - t0);
         Tables& tb = s.tab[step & 1];
@@ -176,7 +177,8 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         for (int t = 0; t < NB; ++t) {
           const int tt = t < nb ? t : nb - 1;
           const size_t tok = (((size_t)ib * in_bs + (t0 + tt)) * H + ih) * D + c;
-          graw[t] = g[tok]; kraw[t] = k[tok]; braw[t] = b[tok]; qraw[t] = q[tok]; wraw[t] = w[tok]; vraw[t] = v[tok];
+          const size_t tokk = (((size_t)ib * in_bs + (t0 + tt)) * HK + ihk) * D + c;
+          graw[t] = g[tokk]; kraw[t] = k[tokk]; braw[t] = b[tokk]; qraw[t] = q[tokk]; wraw[t] = w[tok]; vraw[t] = v[tok];
         }
         float G[NB], kk[NB], bk[NB], qs[NB], wvv[NB];
         float run = 0.f;
@@ -420,26 +422,26 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
 
 template <typename T>
 int launch_decode_blocked(const T* q, const T* k, const T* v, const float* g, const T* b, const T* w, float* state,
-                          T* o, int B, int n, int H, int64_t in_bs, int64_t o_bs, float scale, cudaStream_t st) {
+                          T* o, int B, int n, int H, int HK, int64_t in_bs, int64_t o_bs, float scale, cudaStream_t st) {
   const size_t smem = sizeof(BlockedSmem) + 128;
   GDN2_CUDA_TRY(cudaFuncSetAttribute(decode_blocked_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int ntiles = B * H;
   const int sms = device_sm_count();
   const int grid = ntiles < sms ? ntiles : sms;
-  decode_blocked_kernel<T><<<grid, kAllThreads, smem, st>>>(q, k, v, g, b, w, state, o, ntiles, n, H, in_bs, o_bs, scale,
+  decode_blocked_kernel<T><<<grid, kAllThreads, smem, st>>>(q, k, v, g, b, w, state, o, ntiles, n, H, HK, in_bs, o_bs, scale,
                                                          device_status_word());
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
 }
 
 template int launch_decode_blocked<float>(const float*, const float*, const float*, const float*, const float*,
-                                          const float*, float*, float*, int, int, int, int64_t, int64_t, float,
+                                          const float*, float*, float*, int, int, int, int, int64_t, int64_t, float,
                                           cudaStream_t);
 template int launch_decode_blocked<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*,
                                                   const float*, const __nv_bfloat16*, const __nv_bfloat16*, float*,
-                                                  __nv_bfloat16*, int, int, int, int64_t, int64_t, float, cudaStream_t);
+                                                  __nv_bfloat16*, int, int, int, int, int64_t, int64_t, float, cudaStream_t);
 template int launch_decode_blocked<__half>(const __half*, const __half*, const __half*, const float*, const __half*,
-                                           const __half*, float*, __half*, int, int, int, int64_t, int64_t, float,
+                                           const __half*, float*, __half*, int, int, int, int, int64_t, int64_t, float,
                                            cudaStream_t);
 
 }  // namespace gdn2

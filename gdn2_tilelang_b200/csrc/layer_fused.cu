@@ -4,7 +4,7 @@
 //          kernel inputs -- causal depthwise convolution + SiLU on q, k, v (with the cached last
 //          conv_size-1 columns when decoding), L2 normalisation of q and k per head, the decay
 //          g = -exp(A_log) * softplus(f + dt_bias), the gates b = erase_scale * sigmoid(.), w = sigmoid(.),
-//          and the grouped-query expansion (a kv head written to its head_repeat value heads);
+//          -- q, k, b, g once per key head: the attention kernels index key heads, no repeated copies;
 //   tail:  the new convolution cache (the last conv_size-1 pre-convolution columns of q | k | v);
 //   back:  per-head RMSNorm of the attention output times SiLU(o_gate).
 //
@@ -88,12 +88,11 @@ layer_front_kernel(gdn2_layer_front_args a) {
     for (int i = 0; i < 8; ++i) {
       const int c = lane + 32 * i;
       if (c < DK) {
-        const T o = from_f32<T>(vals[i] * inv);
-        for (int r = 0; r < rep; ++r) dst[(((size_t)b * S + t) * H + hk * rep + r) * DK + c] = o;
+        dst[(((size_t)b * S + t) * HK + hk) * DK + c] = from_f32<T>(vals[i] * inv);
       }
     }
   }
-  // ---- erase gate b and decay g for the kv head, written to its value heads
+  // ---- erase gate b and decay g of the key head
   {
     const T* A_log = static_cast<const T*>(a.A_log);
     const T* dtb = static_cast<const T*>(a.dt_bias);
@@ -102,11 +101,9 @@ layer_front_kernel(gdn2_layer_front_args a) {
     for (int c = lane; c < DK; c += 32) {
       const T bo = from_f32<T>(to_f32(from_f32<T>(sigmoidf_(to_f32(P[prow + a.off_b + hk * DK + c])))) * a.erase_scale);
       const float go = nega * softplusf_(to_f32(P[prow + a.off_f + hk * DK + c]) + to_f32(dtb[hk * DK + c]));
-      for (int r = 0; r < rep; ++r) {
-        const size_t o = (((size_t)b * S + t) * H + hk * rep + r) * DK + c;
-        bd[o] = bo;
-        a.g[o] = go;
-      }
+      const size_t o = (((size_t)b * S + t) * HK + hk) * DK + c;
+      bd[o] = bo;
+      a.g[o] = go;
     }
   }
   // ---- v (convolution + SiLU) and the write gate w for the value heads of this kv head

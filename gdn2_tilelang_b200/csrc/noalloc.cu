@@ -49,11 +49,11 @@ extern "C" int gdn2_prefill_static(const void* q, const void* k, const void* v, 
                                    int64_t in_batch_stride, int64_t o_batch_stride, float scale, int dtype,
                                    void* stream) {
   if (!q || !k || !v || !g || !b || !w || !o) return GDN2_ERR_NULL_POINTER;
-  const size_t need = gdn2_prefill_workspace_bytes(B, S, H, DK, DV, dtype, GDN2_PATH_AUTO);
+  const size_t need = gdn2_prefill_workspace_bytes(B, S, H, H, DK, DV, dtype, GDN2_PATH_AUTO);
   if (need == 0) {
     // Not a size problem: let the regular entry point's validation name the reason (bad shape,
     // bad dtype, unsupported head dims). With a zero-byte workspace it cannot launch anything.
-    const int why = gdn2_chunk_prep(q, k, v, g, b, w, const_cast<void*>(q), 0, B, S, H, DK, DV, in_batch_stride,
+    const int why = gdn2_chunk_prep(q, k, v, g, b, w, const_cast<void*>(q), 0, B, S, H, H, DK, DV, in_batch_stride,
                                     scale, dtype, GDN2_PATH_AUTO, stream);
     return (why == GDN2_OK || why == GDN2_ERR_WORKSPACE) ? GDN2_ERR_UNSUPPORTED : why;
   }
@@ -63,9 +63,9 @@ extern "C" int gdn2_prefill_static(const void* q, const void* k, const void* v, 
   if (rc != GDN2_OK) return rc;
   // Every record of the scratch that the scan reads is rewritten by the chunk-local stage of the
   // same call, so nothing has to be cleared between calls.
-  rc = gdn2_chunk_prep(q, k, v, g, b, w, scratch, GDN2_STATIC_SCRATCH_BYTES, B, S, H, DK, DV, in_batch_stride,
+  rc = gdn2_chunk_prep(q, k, v, g, b, w, scratch, GDN2_STATIC_SCRATCH_BYTES, B, S, H, H, DK, DV, in_batch_stride,
                        scale, dtype, GDN2_PATH_AUTO, stream);
   if (rc != GDN2_OK) return rc;
-  return gdn2_prefill_scan(scratch, GDN2_STATIC_SCRATCH_BYTES, initial_state, o, final_state, nullptr, B, S, H,
+  return gdn2_prefill_scan(scratch, GDN2_STATIC_SCRATCH_BYTES, initial_state, o, final_state, nullptr, B, S, H, H,
                            DK, DV, o_batch_stride, dtype, GDN2_PATH_AUTO, stream);
 }

@@ -20,21 +20,22 @@ namespace gdn2 {
 namespace {
 
 
-// The whole chunk-local stage for chunk n of (batch*head) bh, by one 256-thread block.
+// The whole chunk-local stage for chunk n of (batch, KEY head) bk, by one 256-thread block: everything that depends
+// on q, k, b, g once, then U = Ai (w*v) for each of the H / HK value heads that share the key head.
 template <typename TIn, typename TW>
 __device__ __forceinline__ void prep_simt_chunk(const TIn* __restrict__ q, const TIn* __restrict__ k,
                                                 const TIn* __restrict__ v, const float* __restrict__ g,
                                                 const TIn* __restrict__ b, const TIn* __restrict__ w,
-                                                const WsLayout& L, const WsPtrs& P, int S, int H, int64_t in_bs,
-                                                float scale, int n, int bh) {
+                                                const WsLayout& L, const WsPtrs& P, int S, int H, int HK, int64_t in_bs,
+                                                float scale, int n, int bk) {
   constexpr int BS = kChunk;
   using WT = WsTraits<TW>;
   using TV = typename WT::TV;
   constexpr int E = WT::E;
   const int DK = L.DK, DV = L.DV;
   const int NC = S / BS;
-  const int ib = bh / H, ih = bh % H;
-  const int64_t ch = (int64_t)bh * NC + n;
+  const int ib = bk / HK, ihk = bk % HK;
+  const int64_t ch = (int64_t)bk * NC + n;
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
 
   extern __shared__ float sm[];
@@ -46,10 +47,10 @@ __device__ __forceinline__ void prep_simt_chunk(const TIn* __restrict__ q, const
   float* Aq = Tm + BS * BS;          // [BS][BS] lower incl. diagonal (scaled)
   float* Ai = Aq + BS * BS;          // [BS][BS] (I + Tm)^-1
 
-  const size_t tok0 = ((size_t)ib * in_bs + (size_t)n * BS) * H + ih;   // token index of row 0 (stride H per row)
+  const size_t tok0 = ((size_t)ib * in_bs + (size_t)n * BS) * HK + ihk;   // token index of row 0 (stride HK per row)
   for (int idx = tid; idx < BS * DK; idx += 256) {
     const int t = idx / DK, c = idx % DK;
-    const size_t gi = (tok0 + (size_t)t * H) * DK + c;
+    const size_t gi = (tok0 + (size_t)t * HK) * DK + c;
     const float kk = to_f32(k[gi]);
     ks[idx] = kk;
     qs[idx] = to_f32(q[gi]);
@@ -103,7 +104,6 @@ __device__ __forceinline__ void prep_simt_chunk(const TIn* __restrict__ q, const
   TW* wq = reinterpret_cast<TW*>(P.wq + (size_t)ch * L.wq_bytes);
   TV* aqk = reinterpret_cast<TV*>(P.aqk + (size_t)ch * L.aqk_bytes);
   TV* kgt = reinterpret_cast<TV*>(P.kgt + (size_t)ch * L.kgt_bytes);
-  TV* ut = reinterpret_cast<TV*>(P.ut + (size_t)ch * L.ut_bytes);
   float* gl = P.gl + (size_t)ch * DK;
   for (int idx = tid; idx < BS * BS; idx += 256) {
     const int r = idx / BS, s = idx % BS;
@@ -127,21 +127,27 @@ __device__ __forceinline__ void prep_simt_chunk(const TIn* __restrict__ q, const
     for (int s = 0; s <= r; ++s) acc = fmaf(Ai[r * BS + s], es[s * DK + c], acc);
     wq[kc_index<E>(r, c, 2 * BS)] = from_f32<TW>(acc);
   }
-  // U = Ai (w*v), value columns in tiles of DK
-  for (int c0 = 0; c0 < DV; c0 += DK) {
-    const int cw = min(DK, DV - c0);
-    __syncthreads();
-    for (int idx = tid; idx < BS * cw; idx += 256) {
-      const int t = idx / cw, c = idx % cw;
-      const size_t gi = (tok0 + (size_t)t * H) * DV + c0 + c;
-      qs[t * DK + c] = to_f32(w[gi]) * to_f32(v[gi]);
-    }
-    __syncthreads();
-    for (int idx = tid; idx < BS * cw; idx += 256) {
-      const int r = idx / cw, c = idx % cw;
-      float acc = 0.f;
-      for (int s = 0; s <= r; ++s) acc = fmaf(Ai[r * BS + s], qs[s * DK + c], acc);
-      ut[kc_index<E>(c0 + c, r, DV)] = WT::u_store(acc);
+  // U = Ai (w*v) for every value head of this key head, value columns in tiles of DK
+  const int rep = H / HK;
+  for (int hr = 0; hr < rep; ++hr) {
+    const int ih = ihk * rep + hr;
+    const size_t tok0v = ((size_t)ib * in_bs + (size_t)n * BS) * H + ih;
+    TV* ut = reinterpret_cast<TV*>(P.ut + (size_t)(((int64_t)ib * H + ih) * NC + n) * L.ut_bytes);
+    for (int c0 = 0; c0 < DV; c0 += DK) {
+      const int cw = min(DK, DV - c0);
+      __syncthreads();
+      for (int idx = tid; idx < BS * cw; idx += 256) {
+        const int t = idx / cw, c = idx % cw;
+        const size_t gi = (tok0v + (size_t)t * H) * DV + c0 + c;
+        qs[t * DK + c] = to_f32(w[gi]) * to_f32(v[gi]);
+      }
+      __syncthreads();
+      for (int idx = tid; idx < BS * cw; idx += 256) {
+        const int r = idx / cw, c = idx % cw;
+        float acc = 0.f;
+        for (int s = 0; s <= r; ++s) acc = fmaf(Ai[r * BS + s], qs[s * DK + c], acc);
+        ut[kc_index<E>(c0 + c, r, DV)] = WT::u_store(acc);
+      }
     }
   }
 }
@@ -150,8 +156,8 @@ template <typename TIn, typename TW>
 __global__ void __launch_bounds__(256)
 prep_simt_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn* __restrict__ v,
                  const float* __restrict__ g, const TIn* __restrict__ b, const TIn* __restrict__ w,
-                 WsLayout L, WsPtrs P, int S, int H, int64_t in_bs, float scale) {
-  prep_simt_chunk<TIn, TW>(q, k, v, g, b, w, L, P, S, H, in_bs, scale, blockIdx.x, blockIdx.y);
+                 WsLayout L, WsPtrs P, int S, int H, int HK, int64_t in_bs, float scale) {
+  prep_simt_chunk<TIn, TW>(q, k, v, g, b, w, L, P, S, H, HK, in_bs, scale, blockIdx.x, blockIdx.y);
 }
 
 // Exact redo of the chunks the tensor-core kernel flagged: a fixed small grid walks the compacted list
@@ -160,20 +166,20 @@ template <typename TIn, typename TW>
 __global__ void __launch_bounds__(256)
 prep_simt_flagged_kernel(const TIn* __restrict__ q, const TIn* __restrict__ k, const TIn* __restrict__ v,
                          const float* __restrict__ g, const TIn* __restrict__ b, const TIn* __restrict__ w,
-                         WsLayout L, WsPtrs P, int S, int H, int64_t in_bs, float scale) {
+                         WsLayout L, WsPtrs P, int S, int H, int HK, int64_t in_bs, float scale) {
   const int NC = S / kChunk;
   const int* list = P.flags + L.nch;
   const int count = P.flags[2 * L.nch];
   for (int li = blockIdx.x; li < count; li += gridDim.x) {
     const int ch = list[li];
-    prep_simt_chunk<TIn, TW>(q, k, v, g, b, w, L, P, S, H, in_bs, scale, ch % NC, ch / NC);
+    prep_simt_chunk<TIn, TW>(q, k, v, g, b, w, L, P, S, H, HK, in_bs, scale, ch % NC, ch / NC);
     __syncthreads();                                   // shared memory is reused by the next chunk
   }
 }
 
 template <typename TIn, typename TW>
 int launch_typed(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                 const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
+                 const WsLayout& L, const WsPtrs& P, int B, int S, int H, int HK, int64_t in_bs, float scale,
                  bool only_flagged, cudaStream_t st) {
   const size_t smem = ((size_t)4 * kChunk * L.DK + 3 * kChunk * kChunk) * sizeof(float);
   const TIn* tq = static_cast<const TIn*>(q); const TIn* tk = static_cast<const TIn*>(k);
@@ -184,12 +190,12 @@ int launch_typed(const void* q, const void* k, const void* v, const float* g, co
     GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     // the tensor-core kernel has appended the flagged chunks to the list behind the flags
     const int nch = (int)L.nch;
-    kern<<<nch < 296 ? nch : 296, 256, smem, st>>>(tq, tk, tv, g, tb, tw, L, P, S, H, in_bs, scale);
+    kern<<<nch < 296 ? nch : 296, 256, smem, st>>>(tq, tk, tv, g, tb, tw, L, P, S, H, HK, in_bs, scale);
   } else {
     auto kern = prep_simt_kernel<TIn, TW>;
     GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid(S / kChunk, B * H);
-    kern<<<grid, 256, smem, st>>>(tq, tk, tv, g, tb, tw, L, P, S, H, in_bs, scale);
+    dim3 grid(S / kChunk, B * HK);
+    kern<<<grid, 256, smem, st>>>(tq, tk, tv, g, tb, tw, L, P, S, H, HK, in_bs, scale);
   }
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
@@ -198,18 +204,18 @@ int launch_typed(const void* q, const void* k, const void* v, const float* g, co
 }  // namespace
 
 int launch_prep_simt(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                     const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
+                     const WsLayout& L, const WsPtrs& P, int B, int S, int H, int HK, int64_t in_bs, float scale,
                      int dtype, bool only_flagged, cudaStream_t st) {
   if (L.esz == 4) {
     switch (dtype) {
-      case GDN2_F32: return launch_typed<float, float>(q, k, v, g, b, w, L, P, B, S, H, in_bs, scale, only_flagged, st);
-      case GDN2_BF16: return launch_typed<__nv_bfloat16, float>(q, k, v, g, b, w, L, P, B, S, H, in_bs, scale, only_flagged, st);
-      case GDN2_F16: return launch_typed<__half, float>(q, k, v, g, b, w, L, P, B, S, H, in_bs, scale, only_flagged, st);
+      case GDN2_F32: return launch_typed<float, float>(q, k, v, g, b, w, L, P, B, S, H, HK, in_bs, scale, only_flagged, st);
+      case GDN2_BF16: return launch_typed<__nv_bfloat16, float>(q, k, v, g, b, w, L, P, B, S, H, HK, in_bs, scale, only_flagged, st);
+      case GDN2_F16: return launch_typed<__half, float>(q, k, v, g, b, w, L, P, B, S, H, HK, in_bs, scale, only_flagged, st);
       default: return GDN2_ERR_BAD_DTYPE;
     }
   }
   if (dtype != GDN2_BF16) return GDN2_ERR_UNSUPPORTED;
-  return launch_typed<__nv_bfloat16, __nv_bfloat16>(q, k, v, g, b, w, L, P, B, S, H, in_bs, scale, only_flagged, st);
+  return launch_typed<__nv_bfloat16, __nv_bfloat16>(q, k, v, g, b, w, L, P, B, S, H, HK, in_bs, scale, only_flagged, st);
 }
 
 }  // namespace gdn2

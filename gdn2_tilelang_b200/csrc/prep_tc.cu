@@ -71,7 +71,7 @@ struct PrepTcSmem {
     __nv_bfloat16 wq[16 * A_PAD * 8];        // staging of the WQ record: [dk/8][129][8]
   } y;
   float pre[4][2][D];                        // per sub-block and channel: G at its reference row (row 8) and its total, both relative to its start
-  uint64_t bar_m1, bar_m2;
+  uint64_t bar_m1, bar_m2, bar_m2v;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -118,19 +118,25 @@ __device__ __forceinline__ float2 pick4(int j, float2 a0, float2 a1, float2 a2, 
   return j == 0 ? a0 : j == 1 ? a1 : j == 2 ? a2 : a3;
 }
 
-// HT > 0: the number of heads is a compile-time constant, so every token offset of the strided channel
-// loads folds into the load instruction's immediate; HT = 0 takes it from the argument.
-template <int HT>
+// One block per (chunk, batch, KEY head). Everything that depends on q, k, b, g is computed once; U^T = (w*v)^T Ai^T
+// is then formed for each of the `rep` value heads that share the key head (grouped-query heads; rep = 1 when every
+// head has its own q, k, b, g).
+// HT > 0: the number of key heads is a compile-time constant (and RT > 0 the value heads per key head), so every
+// token offset of the strided channel loads folds into the load instruction's immediate; 0 takes them from the
+// arguments.
+template <int HT, int RT>
 __global__ void __launch_bounds__(kThreads, 2)
 prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
                const __nv_bfloat16* __restrict__ v, const float* __restrict__ g,
                const __nv_bfloat16* __restrict__ b, const __nv_bfloat16* __restrict__ w, WsPtrs P, int S, int H,
-               int64_t in_bs, float scale, int a_sm_count, uint32_t* status) {
+               int HK_arg, int64_t in_bs, float scale, int a_sm_count, uint32_t* status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   PrepTcSmem& s = *reinterpret_cast<PrepTcSmem*>(smem_raw);
   const int NC = S / BS;
-  const int n = blockIdx.x, bh = blockIdx.y;
-  const int ib = bh / H, ih = bh % H;
+  const int HK = HT > 0 ? HT : HK_arg;                                  // key heads
+  const int rep = RT > 0 ? RT : H / HK;                                 // value heads per key head
+  const int n = blockIdx.x, bh = blockIdx.y;                            // bh: (batch, key head)
+  const int ib = bh / HK, ih = bh % HK;
   const int64_t ch = (int64_t)bh * NC + n;
   const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
   const int c = tid & (D - 1);                                          // lane-true mapping: channel / row = TMEM lane
@@ -140,14 +146,19 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   const int cp = tid & 63;                                              // channels 2 cp, 2 cp + 1
   const int sbk = tid >> 6;
   const int c0 = 2 * cp;
-  const size_t row0 = ((size_t)ib * in_bs + (size_t)n * BS) * H + ih;   // token row of t = 0
-  const size_t rstride = HT > 0 ? (size_t)HT * D : (size_t)H * D;       // elements between tokens
+  const size_t row0 = ((size_t)ib * in_bs + (size_t)n * BS) * HK + ih;  // q, k, b, g: token row of t = 0
+  const size_t rstride = (size_t)HK * D;                                // ... and elements between tokens
   const size_t pstride = rstride / 2;                                   // channel pairs between tokens
   const size_t soff = (size_t)(16 * sbk) * rstride;                     // first token of this thread's sub-block
+  // v, w: the same for the first value head of this key head (the others follow at +D elements each)
+  const size_t vrow0 = ((size_t)ib * in_bs + (size_t)n * BS) * HK * rep + (size_t)ih * rep;
+  const size_t vstride = rstride * rep, vpstride = vstride / 2;
+  const size_t vsoff = (size_t)(16 * sbk) * vstride;
   const float2* gp = reinterpret_cast<const float2*>(g + row0 * D + soff) + cp;
 
   // Pull the whole input tile of this chunk-head towards L2 before anything depends on it: 64 rows x
-  // (5 x 256 B + 512 B) = 896 128-byte lines, 3.5 per thread.
+  // (5 x 256 B + 512 B) = 896 128-byte lines, 3.5 per thread (v and w of the first value head; the other value
+  // heads' lines are adjacent in memory and are fetched when their turn comes).
   {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -160,7 +171,8 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
         const void* tb = ten == 0 ? (const void*)g : ten == 1 ? (const void*)k : ten == 2 ? (const void*)q
                        : ten == 3 ? (const void*)b : ten == 4 ? (const void*)v : (const void*)w;
         const size_t es = ten == 0 ? 4 : 2;
-        const char* ptr = static_cast<const char*>(tb) + (row0 * D + (size_t)rowi * rstride) * es + seg * 128;
+        const size_t r0 = ten >= 4 ? vrow0 : row0, rs = ten >= 4 ? vstride : rstride;
+        const char* ptr = static_cast<const char*>(tb) + (r0 * D + (size_t)rowi * rs) * es + seg * 128;
         asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
       }
     }
@@ -192,6 +204,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   if (tid == 0) {
     tc::mbar_init(&s.bar_m1, 4);     // one commit per issuing warp
     tc::mbar_init(&s.bar_m2, 2);
+    tc::mbar_init(&s.bar_m2v, 1);    // U^T of the further value heads: one product, one commit each
     s.abort_flag = 0;
     tc::mbar_init_fence();
   }
@@ -324,7 +337,7 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     const int64_t nxt = (int64_t)blockIdx.y * gridDim.x + blockIdx.x + 2 * (int64_t)a_sm_count;
     if (nxt < (int64_t)gridDim.x * gridDim.y) {
       const int nb_ = (int)(nxt / gridDim.x), nn_ = (int)(nxt % gridDim.x);
-      const size_t r0n = ((size_t)(nb_ / H) * in_bs + (size_t)nn_ * BS) * H + (nb_ % H);
+      const size_t r0n = ((size_t)(nb_ / HK) * in_bs + (size_t)nn_ * BS) * HK + (nb_ % HK);
       const char* ptr = reinterpret_cast<const char*>(g + r0n * D + (size_t)(tid >> 2) * rstride) + (tid & 3) * 128;
       asm volatile("prefetch.global.L2 [%0];" ::"l"(ptr));
     }
@@ -333,11 +346,11 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   // z = w*v of this thread's two value channels waits in TMEM columns [192,256) of its own lane until the
   // MMA1 operands are dead and (w*v)^T can take their place in shared memory
   {
-    const uint32_t* vp = reinterpret_cast<const uint32_t*>(v + row0 * D + soff) + cp;
-    const uint32_t* wp = reinterpret_cast<const uint32_t*>(w + row0 * D + soff) + cp;
+    const uint32_t* vp = reinterpret_cast<const uint32_t*>(v + vrow0 * D + vsoff) + cp;
+    const uint32_t* wp = reinterpret_cast<const uint32_t*>(w + vrow0 * D + vsoff) + cp;
     uint32_t vr[16], wr[16];                              // raw bf16 pairs: all 32 loads in flight, then converted
 #pragma unroll
-    for (int u = 0; u < 16; ++u) { vr[u] = __ldg(vp + u * pstride); wr[u] = __ldg(wp + u * pstride); }
+    for (int u = 0; u < 16; ++u) { vr[u] = __ldg(vp + u * vpstride); wr[u] = __ldg(wp + u * vpstride); }
     float zx[16], zy[16];
 #pragma unroll
     for (int u = 0; u < 16; ++u) {
@@ -522,7 +535,8 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   //         thread handles the 32 tokens of its half
   {
     const int ca = (c >> 3) * A_PAD * 8 + (c & 7);
-    char* ut_g = P.ut + (size_t)ch * (D * BS * 2) + c * 16;       // fp16 image [tok/8][128 dv][8]
+    // U^T of the first value head: fp16 image [tok/8][128 dv][8] of value chunk-head (b, ih * rep, n)
+    char* ut_g = P.ut + (size_t)(((int64_t)ib * HK * rep + (int64_t)ih * rep) * NC + n) * (D * BS * 2) + c * 16;
     float val[32];
     tc::tmem_ld32(tc::tmem_addr(tm, lq * 32, 32 * hf), val);
     tc::tmem_ld_wait();
@@ -552,9 +566,8 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   }
   tc::tc_fence_before_sync();
   __syncthreads();
-  if (wid == 0) tc::tmem_dealloc(tm, kTmemCols);
   // WQ record: 16 K chunks x 128 rows x 16 bytes; every thread copies 8 pieces with 128-bit accesses
-  // (16 consecutive threads cover 256 contiguous bytes) and the block ends without waiting on them
+  // (16 consecutive threads cover 256 contiguous bytes) and nothing waits on them
   if (!s.abort_flag) {
     char* g_wq = P.wq + (size_t)ch * (2 * BS * D * 2);
     const char* stage = reinterpret_cast<const char*>(s.y.wq);
@@ -566,33 +579,105 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
           *reinterpret_cast<const uint4*>(stage + (kc * A_PAD + row) * 16);
     }
   }
+
+  // ---- 6. the further value heads of this key head: (w*v)^T straight into its shared-memory image (the previous
+  //         head's product has completed, so the image and the U^T columns of tensor memory are free), one tf32
+  //         product against the same Ai^T, U^T out. Ai^T, the only other operand, stays where it is.
+#pragma unroll 1
+  for (int hr = 1; hr < rep; ++hr) {
+    {
+      const uint32_t* vp = reinterpret_cast<const uint32_t*>(v + (vrow0 + hr) * D + vsoff) + cp;
+      const uint32_t* wp = reinterpret_cast<const uint32_t*>(w + (vrow0 + hr) * D + vsoff) + cp;
+      uint32_t vr[16], wr[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) { vr[u] = __ldg(vp + u * vpstride); wr[u] = __ldg(wp + u * vpstride); }
+#pragma unroll
+      for (int t4 = 0; t4 < 4; ++t4) {
+        float zx[4], zy[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float2 vf = bf16x2_bits_to_f32(vr[4 * t4 + u]), wf = bf16x2_bits_to_f32(wr[4 * t4 + u]);
+          zx[u] = tf32_rn(vf.x * wf.x); zy[u] = tf32_rn(vf.y * wf.y);
+        }
+        const int tq = 4 * sbk + t4;
+        *reinterpret_cast<float4*>(&s.x.sol.zt[(tq * D + c0) * 4]) = make_float4(zx[0], zx[1], zx[2], zx[3]);
+        *reinterpret_cast<float4*>(&s.x.sol.zt[(tq * D + c0 + 1) * 4]) = make_float4(zy[0], zy[1], zy[2], zy[3]);
+      }
+    }
+    tc::fence_async_smem();
+    tc::tc_fence_before_sync();
+    __syncthreads();
+    if (wid == 1 && !s.abort_flag) {
+      tc::tc_fence_after_sync();
+      constexpr uint32_t idesc = tc::instr_desc(2, 128, BS);
+      tc::mma_tf32_ktile_warp(tc::tmem_addr(tm, 0, 64), tc::smem_u32(s.x.sol.zt), D, tc::smem_u32(s.x.sol.ai), BS, BS, idesc);
+      tc::mma_commit_warp(&s.bar_m2v);
+    }
+    if (wid == 0) tc::mbar_wait(&s.bar_m2v, (hr - 1) & 1, &s.abort_flag, status, 0x2000u);
+    __syncthreads();
+    tc::tc_fence_after_sync();
+    {
+      char* ut_g = P.ut + (size_t)(((int64_t)ib * HK * rep + (int64_t)ih * rep + hr) * NC + n) * (D * BS * 2) + c * 16;
+      float val[32];
+      tc::tmem_ld32(tc::tmem_addr(tm, lq * 32, 64 + 32 * hf), val);
+      tc::tmem_ld_wait();
+#pragma unroll
+      for (int i8 = 0; i8 < 4; ++i8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          __half2 h = __floats2half2_rn(val[8 * i8 + 2 * x] * (1.f / kValScale),
+                                        val[8 * i8 + 2 * x + 1] * (1.f / kValScale));
+          pk[x] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(ut_g + (size_t)(hf * 4 + i8) * D * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+    }
+    tc::tc_fence_before_sync();
+    __syncthreads();
+  }
+  if (wid == 0) tc::tmem_dealloc(tm, kTmemCols);
 }
 
 }  // namespace
 
 int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                   const WsLayout& L, const WsPtrs& P, int B, int S, int H, int64_t in_bs, float scale,
+                   const WsLayout& L, const WsPtrs& P, int B, int S, int H, int HK, int64_t in_bs, float scale,
                    cudaStream_t st) {
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
   const size_t smem = sizeof(PrepTcSmem) + 128;
-  dim3 grid(S / BS, B * H);
+  dim3 grid(S / BS, B * HK);
   using bf16 = __nv_bfloat16;
   GDN2_CUDA_TRY(cudaMemsetAsync(P.flags + 2 * (size_t)L.nch, 0, sizeof(int), st));   // length of the flagged list
   auto launch = [&](auto kern) -> int {
     GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kern<<<grid, kThreads, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
                                        static_cast<const bf16*>(v), g, static_cast<const bf16*>(b),
-                                       static_cast<const bf16*>(w), P, S, H, in_bs, scale, device_sm_count(), device_status_word());
+                                       static_cast<const bf16*>(w), P, S, H, HK, in_bs, scale, device_sm_count(),
+                                       device_status_word());
     GDN2_CUDA_TRY(cudaGetLastError());
     return GDN2_OK;
   };
-  switch (H) {                                  // common head counts, whole and sharded
-    case 16: return launch(prep_tc_kernel<16>);
-    case 8: return launch(prep_tc_kernel<8>);
-    case 4: return launch(prep_tc_kernel<4>);
-    case 2: return launch(prep_tc_kernel<2>);
-    default: return launch(prep_tc_kernel<0>);
+  const int rep = H / HK;
+  if (rep == 1) {
+    switch (HK) {                               // common head counts, whole and sharded
+      case 16: return launch(prep_tc_kernel<16, 1>);
+      case 8: return launch(prep_tc_kernel<8, 1>);
+      case 4: return launch(prep_tc_kernel<4, 1>);
+      case 2: return launch(prep_tc_kernel<2, 1>);
+      default: return launch(prep_tc_kernel<0, 1>);
+    }
   }
+  if (rep == 2) {                               // two value heads per key head, whole and sharded
+    switch (HK) {
+      case 8: return launch(prep_tc_kernel<8, 2>);
+      case 4: return launch(prep_tc_kernel<4, 2>);
+      case 2: return launch(prep_tc_kernel<2, 2>);
+      case 1: return launch(prep_tc_kernel<1, 2>);
+      default: break;
+    }
+  }
+  return launch(prep_tc_kernel<0, 0>);
 }
 
 }  // namespace gdn2

@@ -36,7 +36,7 @@ struct ScanSmem {
 };
 
 template <typename TW>
-__device__ __forceinline__ void load_chunk_operands(const WsLayout& L, const WsPtrs& P, int64_t ch, int lo,
+__device__ __forceinline__ void load_chunk_operands(const WsLayout& L, const WsPtrs& P, int64_t ch, int64_t chv, int lo,
                                                     ScanSmem& s, bool want_kg) {
   using WT = WsTraits<TW>;
   using TV = typename WT::TV;
@@ -45,7 +45,7 @@ __device__ __forceinline__ void load_chunk_operands(const WsLayout& L, const WsP
   const TW* wq = reinterpret_cast<const TW*>(P.wq + (size_t)ch * L.wq_bytes);
   const TV* aqk = reinterpret_cast<const TV*>(P.aqk + (size_t)ch * L.aqk_bytes);
   const TV* kgt = reinterpret_cast<const TV*>(P.kgt + (size_t)ch * L.kgt_bytes);
-  const TV* ut = reinterpret_cast<const TV*>(P.ut + (size_t)ch * L.ut_bytes);
+  const TV* ut = reinterpret_cast<const TV*>(P.ut + (size_t)chv * L.ut_bytes);   // per value head; the rest per key head
   for (int idx = tid; idx < kChunk * DK; idx += 256) {
     const int t = idx / DK, c = idx % DK;
     s.Ws[idx] = to_f32(wq[kc_index<E>(t, c, 2 * kChunk)]);
@@ -112,10 +112,11 @@ scan_simt_kernel(WsLayout L, WsPtrs P, const float* __restrict__ s0, TOut* __res
     const int c = idx / NV, d = lo + idx % NV;
     s.St[idx] = (s0 != nullptr && d < DV) ? s0[((size_t)bh * DK + c) * DV + d] : 0.f;
   }
+  const int64_t bk = (int64_t)ib * (H / L.rep) + ih / L.rep;       // (batch, key head) whose records this value head reads
   for (int n = 0; n < NC; ++n) {
-    const int64_t ch = (int64_t)bh * NC + n;
+    const int64_t ch = bk * NC + n;
     __syncthreads();
-    load_chunk_operands<TW>(L, P, ch, lo, s, true);
+    load_chunk_operands<TW>(L, P, ch, (int64_t)bh * NC + n, lo, s, true);
     if (hs != nullptr) {
       float* hp = hs + (((size_t)ib * NC + n) * H + ih) * DK * DV;
       for (int idx = tid; idx < DK * NV; idx += 256) {
@@ -153,13 +154,13 @@ output_simt_kernel(WsLayout L, WsPtrs P, const float* __restrict__ hs, TOut* __r
   const int tid = threadIdx.x;
   extern __shared__ float sm[];
   ScanSmem s(sm, DK);
-  const int64_t ch = (int64_t)bh * NC + n;
+  const int64_t ch = ((int64_t)ib * (H / L.rep) + ih / L.rep) * NC + n;
   const float* hp = hs + (((size_t)ib * NC + n) * H + ih) * DK * DV;
   for (int idx = tid; idx < DK * NV; idx += 256) {
     const int c = idx / NV, d = lo + idx % NV;
     s.St[idx] = d < DV ? hp[(size_t)c * DV + d] : 0.f;
   }
-  load_chunk_operands<TW>(L, P, ch, lo, s, false);
+  load_chunk_operands<TW>(L, P, ch, (int64_t)bh * NC + n, lo, s, false);
   __syncthreads();
   TOut* o_rows = o + (((size_t)ib * o_bs + (size_t)n * kChunk) * H + ih) * DV;
   un_and_output<TOut>(s, DK, DV, lo, o_rows, (size_t)H * DV);

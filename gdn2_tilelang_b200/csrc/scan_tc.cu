@@ -205,12 +205,14 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
     return sT ? sT + (size_t)bh * D * D : nullptr;
   };
   const bool write_o = !transition;
-  const int64_t ch0 = (int64_t)bh * NC_all + c_first;
+  // records that depend on q, k, b, g only exist once per KEY head; U^T per value head
+  const int64_t ch0 = ((int64_t)ib * (H / L.rep) + ih / L.rep) * NC_all + c_first;
+  const int64_t chv0 = (int64_t)bh * NC_all + c_first;
 
   const char* g_wq = P.wq + (size_t)ch0 * kWqBytes;
   const char* g_aqk = P.aqk + (size_t)ch0 * kAqkBytes;
   const char* g_kgt = P.kgt + (size_t)ch0 * kKgtBytes;
-  const char* g_ut = P.ut + (size_t)ch0 * kUtBytes;
+  const char* g_ut = P.ut + (size_t)chv0 * kUtBytes;
   const float* g_gl = P.gl + (size_t)ch0 * D;
 
   if (tid == 0) {
@@ -528,10 +530,10 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
 // A heuristic for speed only: whatever it says, the results are those of the recurrence.
 constexpr int kCheckChunks = 12;
 __global__ void __launch_bounds__(256)
-scan_mode_kernel(WsPtrs P, int BH, int nseg, int NC_all) {
+scan_mode_kernel(WsPtrs P, int BK, int nseg, int NC_all) {
   const int item = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (item >= BH * (nseg - 1)) return;
-  const int bh = item / (nseg - 1), seg = 1 + item % (nseg - 1);
+  if (item >= BK * (nseg - 1)) return;
+  const int bh = item / (nseg - 1), seg = 1 + item % (nseg - 1);   // (batch, KEY head): gamma is a key-side record
   const int c0 = (int)((int64_t)NC_all * seg / nseg), c1 = (int)((int64_t)NC_all * (seg + 1) / nseg);
   const int n = c1 - c0 < kCheckChunks ? c1 - c0 : kCheckChunks;
   float4 prod = make_float4(1.f, 1.f, 1.f, 1.f);
@@ -625,7 +627,8 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
   const int guarded = L.nseg_guarded ? 1 : 0;
   if (guarded) {
     GDN2_CUDA_TRY(cudaMemsetAsync(P.seg_mode, 0, sizeof(int), st));
-    scan_mode_kernel<<<(BH * (nseg - 1) + 7) / 8, 256, 0, st>>>(P, BH, nseg, NC);
+    const int BK = BH / L.rep;
+    scan_mode_kernel<<<(BK * (nseg - 1) + 7) / 8, 256, 0, st>>>(P, BK, nseg, NC);
     GDN2_CUDA_TRY(cudaGetLastError());
   }
   scan_tc_kernel<<<BH * (2 * nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kFirst, nseg, guarded}, s0, ob, sT, nullptr,

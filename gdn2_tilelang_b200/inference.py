@@ -23,14 +23,19 @@ __all__ = ["gdn2_prefill", "gdn2_prefill_from_host", "gdn2_decode", "gdn2_decode
 
 
 def _check_inputs(q, k, v, g, b, w):
-    if q.dim() != 4:
-        raise ValueError(f"expected [B, S, H, D] tensors, got shape {tuple(q.shape)}")
-    B, S, H, DK = q.shape
-    DV = v.shape[-1]
+    """Shapes and dtypes. ``q, k, b, g`` may carry fewer heads than ``v, w`` (``HK`` key heads, ``H`` a multiple
+    of it): value head ``h`` then reads key head ``h // (H // HK)``, which is what the reference's layer gets by
+    ``repeat_interleave`` (gdn2/attention.py:295-297) before calling the op; here nothing is repeated."""
+    if q.dim() != 4 or v.dim() != 4:
+        raise ValueError(f"expected [B, S, H, D] tensors, got shapes {tuple(q.shape)} and {tuple(v.shape)}")
+    B, S, HK, DK = q.shape
+    H, DV = v.shape[2], v.shape[-1]
     if k.shape != q.shape or b.shape != q.shape or g.shape != q.shape:
-        raise ValueError("q, k, b and g must share the shape [B, S, H, DK]")
+        raise ValueError("q, k, b and g must share the shape [B, S, HK, DK]")
     if v.shape != (B, S, H, DV) or w.shape != v.shape:
         raise ValueError("v and w must share the shape [B, S, H, DV]")
+    if HK < 1 or H % HK:
+        raise ValueError(f"the {H} value heads must be a multiple of the {HK} key heads")
     _cabi.dtype_code(q.dtype)
     if not (k.dtype == v.dtype == b.dtype == w.dtype == q.dtype):
         raise TypeError("q, k, v, b and w must share one dtype")

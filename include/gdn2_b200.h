@@ -5,13 +5,17 @@
  * (a cudaStream_t passed as void*, NULL = the legacy default stream), allocates nothing and
  * returns 0 or a negative gdn2_status. No C++ or framework types cross this boundary.
  *
- * Tensor conventions (identical to the reference project's Python API):
- *   q, k, b : [B, S, H, DK]   v, w : [B, S, H, DV]   element type `dtype`
- *   g       : [B, S, H, DK]   fp32 natural-log decay, <= 0
+ * Tensor conventions (those of the reference project's Python API):
+ *   q, k, b : [B, S, HK, DK]  v, w : [B, S, H, DV]   element type `dtype`
+ *   g       : [B, S, HK, DK]  fp32 natural-log decay, <= 0
  *   state   : [B, H, DK, DV]  fp32, contiguous
  *   o       : [B, S, H, DV]   element type `dtype`
- * The [S, H, D] block of one batch entry is contiguous; consecutive batch entries are
- * `in_batch_stride` (inputs) / `o_batch_stride` (o) TOKENS apart, counted in rows of H*D elements
+ * H counts the value heads, HK the key heads, H a multiple of HK: value head h reads q, k, b, g of key head
+ * h / (H / HK) (grouped-query heads). HK = H is the reference's layout, where its layer has already repeated
+ * every key head H / HK times (gdn2/attention.py:295-297, 342); with HK < H the kernels index the key heads
+ * instead and nothing is repeated in memory.
+ * The [S, heads, D] block of one batch entry is contiguous; consecutive batch entries are
+ * `in_batch_stride` (inputs) / `o_batch_stride` (o) TOKENS apart, counted in rows of heads*D elements
  * (pass S for a contiguous tensor). This lets a caller hand over a slice of a longer sequence --
  * the whole chunks to the chunkwise path, the ragged tail to gdn2_decode -- without copying it.
  *
@@ -29,7 +33,7 @@
 extern "C" {
 #endif
 
-#define GDN2_B200_ABI_VERSION 2
+#define GDN2_B200_ABI_VERSION 3
 
 /* element type of q, k, v, b, w and o */
 enum gdn2_dtype { GDN2_F32 = 0, GDN2_BF16 = 1, GDN2_F16 = 2 };
@@ -67,25 +71,27 @@ int gdn2_last_cuda_error(void);
 
 /*
  * n-token recurrent decode; `state` is read once, updated in place and written once.
- *   q,k,b [B,n,H,DK]  v,w [B,n,H,DV]  g [B,n,H,DK] fp32  state [B,H,DK,DV] fp32  o [B,n,H,DV]
+ *   q,k,b [B,n,HK,DK]  v,w [B,n,H,DV]  g [B,n,HK,DK] fp32  state [B,H,DK,DV] fp32  o [B,n,H,DV]
  * n = 1 is the single-token step. Supported: DK <= 256, any DV >= 1, n >= 1.
  * Replaces decode_step_kernel / decode_multi_kernel and the device branch of gdn2_decode and
  * gdn2_decode_step (gdn2/inference.py:61-153, 199-303, 306-353, 156-196).
  */
 int gdn2_decode(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                float* state, void* o, int64_t B, int64_t n, int64_t H, int64_t DK, int64_t DV,
+                float* state, void* o, int64_t B, int64_t n, int64_t H, int64_t HK, int64_t DK, int64_t DV,
                 int64_t in_batch_stride, int64_t o_batch_stride, float scale, int dtype, void* stream);
 
 /*
  * Bytes of scratch the chunkwise prefill needs for a [B,S,H,DK,DV] problem (S a multiple of 64).
  * Returns 0 for an unsupported combination. `path` is a gdn2_prefill_path.
  */
-size_t gdn2_prefill_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path);
+size_t gdn2_prefill_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV, int dtype,
+                                    int path);
 
 /*
  * Byte offsets of the record arrays inside the workspace, for tools and tests that inspect the
  * intermediates: out8 = { WQ, AQK, KG^T, U^T, gamma_last, flags, segment records, total bytes }.
- * Records are indexed by chunk-head ch = (b*H + h)*(S/64) + n. Tensor-core family (DK = DV = 128, bf16):
+ * WQ, AQK, KG^T, gamma_last and the flags are indexed by KEY chunk-head (b*HK + hk)*(S/64) + n, U^T by value
+ * chunk-head (b*H + h)*(S/64) + n. Tensor-core family (DK = DV = 128, bf16):
  *   WQ    32 KiB  bf16 [dk/8][128 rows][8]: rows 0..63 = W of token r, rows 64..127 = scale*q*gamma of token r-64
  *   AQK    8 KiB  fp16 [s/8][64 r][8]:  256 * Aqk[r, s], lower triangular including the diagonal
  *   KG^T  16 KiB  fp16 [t/8][128 dk][8]: 256 * k[t, dk] * gamma_last[dk] / gamma[t, dk]
@@ -94,8 +100,8 @@ size_t gdn2_prefill_workspace_bytes(int64_t B, int64_t S, int64_t H, int64_t DK,
  * SIMT family: the same images with 4-byte elements ([x/4][rows][4]) and no scaling.
  * No counterpart in the reference, whose intermediates are separate tensors (gdn2/forward.py:756-829).
  */
-int gdn2_prefill_workspace_layout(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path,
-                                  int64_t* out8);
+int gdn2_prefill_workspace_layout(int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV, int dtype,
+                                  int path, int64_t* out8);
 
 /*
  * Number of sequence segments gdn2_prefill_scan cuts this problem into (1 = one block per (batch, head)
@@ -113,7 +119,7 @@ int gdn2_prefill_scan_segments(int64_t B, int64_t S, int64_t H, int64_t DK, int6
  * driver wy_stages (gdn2/forward.py:65-535, 756-829).
  */
 int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
-                    void* workspace, size_t workspace_bytes, int64_t B, int64_t S, int64_t H, int64_t DK,
+                    void* workspace, size_t workspace_bytes, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
                     int64_t DV, int64_t in_batch_stride, float scale, int dtype, int path, void* stream);
 
 /*
@@ -133,7 +139,7 @@ int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g,
  * hand-over (below 1e-6 of the state); the form used is reported by gdn2_prefill_scan_segments.
  */
 int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
-                      float* final_state, float* chunk_states, int64_t B, int64_t S, int64_t H, int64_t DK,
+                      float* final_state, float* chunk_states, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
                       int64_t DV, int64_t o_batch_stride, int dtype, int path, void* stream);
 
 /*
@@ -143,8 +149,8 @@ int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float
  * Replaces output_kernel (gdn2/forward.py:644-727).
  */
 int gdn2_chunk_output(const void* workspace, size_t workspace_bytes, const float* chunk_states, void* o,
-                      int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int64_t o_batch_stride, int dtype,
-                      int path, void* stream);
+                      int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV, int64_t o_batch_stride,
+                      int dtype, int path, void* stream);
 
 /*
  * Kernels with bounded waits record a non-zero word when a wait runs out. This copies the word
@@ -213,11 +219,12 @@ int gdn2_prefill_static(const void* q, const void* k, const void* v, const float
  * projections (q, k, b, f: HK*DK columns each; v, w, o_gate: H*DV columns each).
  *
  * gdn2_layer_front writes the six kernel inputs in the layout of gdn2_prefill / gdn2_decode:
- *   q, k, b [B, S, H, DK] and v, w [B, S, H, DV] in `dtype`, g [B, S, H, DK] fp32, with
+ *   q, k, b [B, S, HK, DK] and v, w [B, S, H, DV] in `dtype`, g [B, S, HK, DK] fp32 (one copy per key head: the
+ *   attention kernels index key heads, gdn2/attention.py:295-297's repeat_interleave is not materialised), with
  *   q, k = l2norm(silu(conv(proj_q,k)))  v = silu(conv(proj_v))  (depthwise causal convolution of K taps:
  *   conv_weight [2*HK*DK + H*DV, K], conv_bias [same] or NULL, channels ordered q | k | v; K = 0 skips it),
  *   b = erase_scale * sigmoid(proj_b)  w = sigmoid(proj_w)  g = -exp(A_log[hk]) * softplus(proj_f + dt_bias[hk]),
- *   every kv head hk written to its H/HK value heads. conv_state [B, 2*HK*DK + H*DV, K-1] (or NULL = zeros)
+ *   conv_state [B, 2*HK*DK + H*DV, K-1] (or NULL = zeros)
  *   supplies the columns before the first token; new_conv_state (or NULL) receives the last K-1
  *   pre-convolution columns. A_log [HK] and dt_bias [HK, DK] are in `dtype`.
  * gdn2_layer_back writes out [B*S, H*DV] = rmsnorm_per_head(o) * norm_weight[DV] * silu(proj_o_gate).

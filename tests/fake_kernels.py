@@ -10,6 +10,14 @@ import torch
 from oracle import gdn2_oracle as orc
 
 
+def _expanded(q, k, v, g, b, w):
+    """Key heads repeated to the value heads (the oracle, like the reference op, takes equal head counts)."""
+    rep = v.shape[2] // q.shape[2]
+    if rep > 1:
+        q, k, g, b = (t.repeat_interleave(rep, dim=2) for t in (q, k, g, b))
+    return q, k, v, g, b, w
+
+
 class OracleKernels:
     def __init__(self):
         self.calls = []
@@ -17,6 +25,7 @@ class OracleKernels:
 
     def decode(self, q, k, v, g, b, w, state, scale, out=None):
         self.calls.append(("decode", q.shape[1]))
+        q, k, v, g, b, w = _expanded(q, k, v, g, b, w)
         o = orc.decode(q, k, v, g, b, w, state, scale)
         if out is not None:
             out.copy_(o)
@@ -27,6 +36,7 @@ class OracleKernels:
                       path=None, out=None, out_batch_stride=None):
         self.calls.append(("chunk_forward", q.shape[1]))
         assert q.shape[1] % 64 == 0
+        q, k, v, g, b, w = _expanded(q, k, v, g, b, w)
         res = orc.chunkwise(q, k, v, g, b, w, scale, initial_state, return_chunk_states=want_chunk_states)
         o, s = res[0].to(v.dtype), res[1]
         if out is not None:
@@ -35,6 +45,7 @@ class OracleKernels:
         return o, s, (res[2] if want_chunk_states else None)
 
     def chunk_output(self, q, k, v, g, b, w, scale, chunk_states, path=None):
+        q, k, v, g, b, w = _expanded(q, k, v, g, b, w)
         f = orc.chunk_factors(q, k, v, g, b, w, scale)
         B, S, H, DK = q.shape
         h = chunk_states.permute(0, 2, 1, 3, 4).float()
@@ -78,9 +89,6 @@ def layer_front_chain(proj, offsets, conv_state, conv_weight, conv_bias, A_log, 
     g = -A_log.float().exp().unsqueeze(-1) * F.softplus(f.float() + dt_bias.float())
     b = torch.sigmoid(proj[..., ob:ob + dqk].reshape(B, S, HK, DK)) * erase_scale
     w = torch.sigmoid(proj[..., ow:ow + dv].reshape(B, S, H, DV))
-    rep = H // HK
-    if rep > 1:
-        q, k, b, g = (t.repeat_interleave(rep, dim=-2) for t in (q, k, b, g))
     return q.contiguous(), k.contiguous(), v.contiguous(), g.contiguous(), b.contiguous(), w.contiguous(), new_conv
 
 

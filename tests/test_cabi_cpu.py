@@ -46,37 +46,37 @@ def test_status_strings(lib):
 
 def test_workspace_query(lib):
     f = lib.gdn2_prefill_workspace_bytes
-    big = f(4, 16000, 16, 128, 128, _cabi.GDN2_BF16, _cabi.PATH_TCGEN05_SERIAL)   # without the cut scan's segment records
+    big = f(4, 16000, 16, 16, 128, 128, _cabi.GDN2_BF16, _cabi.PATH_TCGEN05_SERIAL)   # without the cut scan's segment records
     # per chunk-head: WQ 32 KiB + AQK 8 KiB + KG^T 16 KiB + U^T 16 KiB (fp16) + gamma_last 512 B (+ flag and list entry)
     per = 32768 + 8192 + 16384 + 16384 + 512 + 8
     nch = 4 * 16 * 250
     assert per * nch <= big <= per * nch + 8 * 1024
-    assert f(1, 100, 1, 128, 128, _cabi.GDN2_BF16, 0) == 0          # S not a multiple of 64
-    assert f(1, 64, 1, 36, 32, _cabi.GDN2_F32, 0) == 0              # DK not a multiple of 8
-    assert f(1, 64, 1, 256, 32, _cabi.GDN2_F32, 0) == 0             # DK too large for the chunkwise kernels
-    assert f(1, 64, 1, 64, 64, _cabi.GDN2_BF16, _cabi.PATH_TCGEN05) == 0   # tcgen05 family is D=128 only
-    assert f(1, 64, 1, 64, 64, _cabi.GDN2_BF16, _cabi.PATH_SIMT) > 0
-    assert f(1, 64, 1, 32, 24, 7, 0) == 0                           # bad dtype
+    assert f(1, 100, 1, 1, 128, 128, _cabi.GDN2_BF16, 0) == 0          # S not a multiple of 64
+    assert f(1, 64, 1, 1, 36, 32, _cabi.GDN2_F32, 0) == 0              # DK not a multiple of 8
+    assert f(1, 64, 1, 1, 256, 32, _cabi.GDN2_F32, 0) == 0             # DK too large for the chunkwise kernels
+    assert f(1, 64, 1, 1, 64, 64, _cabi.GDN2_BF16, _cabi.PATH_TCGEN05) == 0   # tcgen05 family is D=128 only
+    assert f(1, 64, 1, 1, 64, 64, _cabi.GDN2_BF16, _cabi.PATH_SIMT) > 0
+    assert f(1, 64, 1, 1, 32, 24, 7, 0) == 0                           # bad dtype
 
 
 def test_argument_validation_returns_status_without_device_work(lib):
     null = None
     one = ctypes.c_void_p(16)   # never dereferenced: validation fails first
-    assert lib.gdn2_decode(null, one, one, one, one, one, one, one, 1, 1, 1, 32, 32, 1, 1, 1.0, 0, None) == -1
-    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 1, 1, 1, 32, 32, 1, 1, 1.0, 9, None) == -3
-    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 0, 1, 1, 32, 32, 1, 1, 1.0, 0, None) == -2
-    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 1, 1, 1, 512, 32, 1, 1, 1.0, 0, None) == -2
-    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 1, 4, 1, 32, 32, 2, 4, 1.0, 0, None) == -2
+    assert lib.gdn2_decode(null, one, one, one, one, one, one, one, 1, 1, 1, 1, 32, 32, 1, 1, 1.0, 0, None) == -1
+    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 1, 1, 1, 1, 32, 32, 1, 1, 1.0, 9, None) == -3
+    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 0, 1, 1, 1, 32, 32, 1, 1, 1.0, 0, None) == -2
+    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 1, 1, 1, 1, 512, 32, 1, 1, 1.0, 0, None) == -2
+    assert lib.gdn2_decode(one, one, one, one, one, one, one, one, 1, 4, 1, 1, 32, 32, 2, 4, 1.0, 0, None) == -2
     misaligned = ctypes.c_void_p(24)
-    assert lib.gdn2_decode(one, one, one, one, one, one, misaligned, one, 1, 1, 1, 128, 128, 1, 1, 1.0, 0, None) == -4
-    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, null, 0, 1, 64, 1, 32, 32, 64, 1.0, 0, 0, None) == -1
-    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 0, 1, 65, 1, 32, 32, 65, 1.0, 0, 0, None) == -2
-    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 0, 1, 64, 1, 32, 32, 64, 1.0, 0, 2, None) == -8
-    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, misaligned, 1 << 30, 1, 64, 1, 32, 32, 64, 1.0, 0, 0, None) == -4
-    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 16, 1, 64, 1, 32, 32, 64, 1.0, 0, 0, None) == -5
-    assert lib.gdn2_prefill_scan(one, 16, null, one, null, null, 1, 64, 1, 32, 32, 64, 0, 0, None) == -5
-    assert lib.gdn2_prefill_scan(one, 1 << 30, null, null, null, null, 1, 64, 1, 32, 32, 64, 0, 0, None) == -1
-    assert lib.gdn2_chunk_output(one, 1 << 30, null, one, 1, 64, 1, 32, 32, 64, 0, 0, None) == -1
+    assert lib.gdn2_decode(one, one, one, one, one, one, misaligned, one, 1, 1, 1, 1, 128, 128, 1, 1, 1.0, 0, None) == -4
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, null, 0, 1, 64, 1, 1, 32, 32, 64, 1.0, 0, 0, None) == -1
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 0, 1, 65, 1, 1, 32, 32, 65, 1.0, 0, 0, None) == -2
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 0, 1, 64, 1, 1, 32, 32, 64, 1.0, 0, 2, None) == -8
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, misaligned, 1 << 30, 1, 64, 1, 1, 32, 32, 64, 1.0, 0, 0, None) == -4
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 16, 1, 64, 1, 1, 32, 32, 64, 1.0, 0, 0, None) == -5
+    assert lib.gdn2_prefill_scan(one, 16, null, one, null, null, 1, 64, 1, 1, 32, 32, 64, 0, 0, None) == -5
+    assert lib.gdn2_prefill_scan(one, 1 << 30, null, null, null, null, 1, 64, 1, 1, 32, 32, 64, 0, 0, None) == -1
+    assert lib.gdn2_chunk_output(one, 1 << 30, null, one, 1, 64, 1, 1, 32, 32, 64, 0, 0, None) == -1
     assert lib.gdn2_selftest_mma(null, one, one, None) == -1
 
 
@@ -92,10 +92,10 @@ def test_batch_times_heads_limit_is_a_clear_status(lib):
     """The chunk-local kernels put (batch, head) on gridDim.y: more than 65535 pairs is refused as a bad shape
     before anything is enqueued, not reported as a failed launch."""
     one = ctypes.c_void_p(16)
-    assert lib.gdn2_prefill_workspace_bytes(4095, 64, 16, 128, 128, _cabi.GDN2_BF16, 0) > 0       # 65520 pairs
-    assert lib.gdn2_prefill_workspace_bytes(4096, 64, 16, 128, 128, _cabi.GDN2_BF16, 0) == 0      # 65536 pairs
-    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 1 << 40, 4097, 64, 16, 128, 128, 64, 1.0, 1, 0, None) == -2
-    assert lib.gdn2_prefill_scan(one, 1 << 40, None, one, None, None, 4097, 64, 16, 128, 128, 64, 1, 0, None) == -2
+    assert lib.gdn2_prefill_workspace_bytes(4095, 64, 16, 16, 128, 128, _cabi.GDN2_BF16, 0) > 0       # 65520 pairs
+    assert lib.gdn2_prefill_workspace_bytes(4096, 64, 16, 16, 128, 128, _cabi.GDN2_BF16, 0) == 0      # 65536 pairs
+    assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 1 << 40, 4097, 64, 16, 16, 128, 128, 64, 1.0, 1, 0, None) == -2
+    assert lib.gdn2_prefill_scan(one, 1 << 40, None, one, None, None, 4097, 64, 16, 16, 128, 128, 64, 1, 0, None) == -2
 
 
 def test_scan_segments_rule(lib):
@@ -116,15 +116,15 @@ def test_scan_segments_rule(lib):
     assert f(4, 16000, 2, 64, 64, bf, _cabi.PATH_AUTO) == 1          # SIMT family
     assert f(4, 100, 2, 128, 128, bf, _cabi.PATH_AUTO) == 0          # invalid shape
     w = lib.gdn2_prefill_workspace_bytes
-    cut, serial = w(4, 16000, 2, 128, 128, bf, _cabi.PATH_TCGEN05), w(4, 16000, 2, 128, 128, bf, _cabi.PATH_TCGEN05_SERIAL)
+    cut, serial = w(4, 16000, 2, 2, 128, 128, bf, _cabi.PATH_TCGEN05), w(4, 16000, 2, 2, 128, 128, bf, _cabi.PATH_TCGEN05_SERIAL)
     want = 8 * 9 * (3 * 128 * 128 * 4 + 4)
     assert want <= cut - serial <= want + 1024
     out = (ctypes.c_int64 * 8)()
-    assert lib.gdn2_prefill_workspace_layout(4, 16000, 2, 128, 128, bf, _cabi.PATH_TCGEN05, out) == 0
+    assert lib.gdn2_prefill_workspace_layout(4, 16000, 2, 2, 128, 128, bf, _cabi.PATH_TCGEN05, out) == 0
     offs = list(out)
     assert offs == sorted(offs) and offs[0] == 0 and offs[7] == cut and offs[6] == serial
-    assert lib.gdn2_prefill_workspace_layout(4, 100, 2, 128, 128, bf, 0, out) == -2
-    assert lib.gdn2_prefill_workspace_layout(4, 128, 2, 128, 128, bf, 0, None) == -1
+    assert lib.gdn2_prefill_workspace_layout(4, 100, 2, 2, 128, 128, bf, 0, out) == -2
+    assert lib.gdn2_prefill_workspace_layout(4, 128, 2, 2, 128, 128, bf, 0, None) == -1
 
 
 def test_wait_selftest_rejects_unbounded_limits(lib):

@@ -543,18 +543,18 @@ def test_kernels_stay_inside_their_buffers(K, H, NC):
     code = _cabi.GDN2_BF16
     st = torch.cuda.current_stream().cuda_stream
     for path in (_cabi.PATH_TCGEN05, _cabi.PATH_TCGEN05_SERIAL, _cabi.PATH_SIMT):
-        nbytes = K.lib.gdn2_prefill_workspace_bytes(B, S, H, D, D, code, path)
+        nbytes = K.lib.gdn2_prefill_workspace_bytes(B, S, H, H, D, D, code, path)
         wbuf, ws, gd = _guarded((nbytes,), torch.uint8)
         obuf, o, _ = _guarded((B, S, H, D), torch.bfloat16)
         sbuf, sT, _ = _guarded((B, H, D, D), torch.float32)
         hbuf, hs, _ = _guarded((B, NC, H, D, D), torch.float32)
         ptrs = [t.data_ptr() for t in dev]
-        assert K.lib.gdn2_chunk_prep(*ptrs, ws.data_ptr(), nbytes, B, S, H, D, D, S, D**-0.5, code, path, st) == 0
+        assert K.lib.gdn2_chunk_prep(*ptrs, ws.data_ptr(), nbytes, B, S, H, H, D, D, S, D**-0.5, code, path, st) == 0
         assert K.lib.gdn2_prefill_scan(ws.data_ptr(), nbytes, None, o.data_ptr(), sT.data_ptr(), None,
-                                       B, S, H, D, D, S, code, path, st) == 0
+                                       B, S, H, H, D, D, S, code, path, st) == 0
         assert K.lib.gdn2_prefill_scan(ws.data_ptr(), nbytes, None, o.data_ptr(), sT.data_ptr(), hs.data_ptr(),
-                                       B, S, H, D, D, S, code, path, st) == 0
-        assert K.lib.gdn2_chunk_output(ws.data_ptr(), nbytes, hs.data_ptr(), o.data_ptr(), B, S, H, D, D, S,
+                                       B, S, H, H, D, D, S, code, path, st) == 0
+        assert K.lib.gdn2_chunk_output(ws.data_ptr(), nbytes, hs.data_ptr(), o.data_ptr(), B, S, H, H, D, D, S,
                                        code, path, st) == 0
         torch.cuda.synchronize()
         for name, buf in (("workspace", wbuf), ("o", obuf), ("state", sbuf), ("chunk states", hbuf)):
@@ -564,7 +564,7 @@ def test_kernels_stay_inside_their_buffers(K, H, NC):
         state.zero_()
         obuf, o, _ = _guarded((B, n, H, D), torch.bfloat16)
         ptrs = [t[:, :n].contiguous() for t in dev]
-        assert K.lib.gdn2_decode(*(t.data_ptr() for t in ptrs), state.data_ptr(), o.data_ptr(), B, n, H, D, D, n, n,
+        assert K.lib.gdn2_decode(*(t.data_ptr() for t in ptrs), state.data_ptr(), o.data_ptr(), B, n, H, H, D, D, n, n,
                                  D**-0.5, code, st) == 0
         torch.cuda.synchronize()
         assert _guards_intact(sbuf, gd) and _guards_intact(obuf, gd), n
@@ -591,3 +591,72 @@ def test_packed_variable_length_batch_on_device(K):
         o_one, s_one = gdn2.gdn2_attention(*(t[:, lo:hi].contiguous() for t in dev), initial_state=s0[i:i + 1].to(DEV),
                                            output_final_state=True)
         assert torch.equal(o[:, lo:hi], o_one) and torch.equal(s[i:i + 1], s_one)
+
+
+# ---- grouped-query heads: key heads indexed by the kernels, nothing repeated in memory ------------------------
+
+
+def _gqa_inputs(B, S, H, HK, D, seed, dtype=torch.bfloat16):
+    """q, k, b, g with HK heads, v, w with H heads; returns (device tensors, the same with key heads repeated,
+    host fp32 copies of the repeated form for the oracle)."""
+    q, k, _, g, b, _ = orc.make_inputs(B, S, HK, D, D, seed=seed)
+    _, _, v, _, _, w = orc.make_inputs(B, S, H, D, D, seed=seed + 1)
+    lo = [t.to(dtype) for t in (q, k, v, b, w)]
+    dev = (lo[0].to(DEV), lo[1].to(DEV), lo[2].to(DEV), g.to(DEV), lo[3].to(DEV), lo[4].to(DEV))
+    rep = H // HK
+    ex = lambda t: t.repeat_interleave(rep, dim=2)     # noqa: E731
+    dev_rep = (ex(dev[0]), ex(dev[1]), dev[2], ex(dev[3]), ex(dev[4]), dev[5])
+    host = (ex(lo[0]).float(), ex(lo[1]).float(), lo[2].float(), ex(g), ex(lo[3]).float(), lo[4].float())
+    return dev, dev_rep, host
+
+
+@pytest.mark.parametrize("H,HK,D,path", [(4, 2, 128, "tcgen05"), (6, 2, 128, "tcgen05"), (4, 1, 128, "tcgen05"),
+                                         (4, 2, 128, "simt"), (6, 3, 64, "simt")])
+def test_grouped_query_heads_chunkwise(K, H, HK, D, path):
+    """Fewer key heads than value heads through the chunkwise kernels: bit-equal to the same call on repeated key
+    heads (the arithmetic per value head is the same, only done once per key head), right against the oracle,
+    chunk states and the chunk-parallel output included."""
+    B, S = 2, 64 * 24
+    dev, dev_rep, host = _gqa_inputs(B, S, H, HK, D, seed=67)
+    s0 = golden_state(B, H, D, D, 67, 0.1)
+    o, s, h = K.chunk_forward(*dev, D**-0.5, s0.to(DEV), want_chunk_states=True, path=path)
+    o_r, s_r, h_r = K.chunk_forward(*dev_rep, D**-0.5, s0.to(DEV), want_chunk_states=True, path=path)
+    K.check_device_status()
+    assert torch.equal(o, o_r) and torch.equal(s, s_r) and torch.equal(h, h_r)
+    o_ref, s_ref, h_ref = orc.chunkwise(*host, None, s0, return_chunk_states=True)
+    assert orc.max_abs_err(o.float().cpu(), o_ref) < O_ABS_BF16
+    assert orc.rel_fro_err(s.cpu(), s_ref) < STATE_FRO and orc.rel_fro_err(h.cpu(), h_ref) < STATE_FRO
+    o2 = K.chunk_output(*dev, D**-0.5, h, path=path)
+    assert orc.max_abs_err(o2.float().cpu(), o_ref) < O_ABS_BF16
+    if path == "tcgen05":                                   # the scan cut into segments reads the shared records too
+        o3, s3, _ = K.chunk_forward(*dev, D**-0.5, s0.to(DEV), path=path)
+        assert orc.max_abs_err(o3.float().cpu(), o_ref) < O_ABS_BF16 and orc.rel_fro_err(s3.cpu(), s_ref) < STATE_FRO
+
+
+@pytest.mark.parametrize("n", [1, 3, 8, 21])
+@pytest.mark.parametrize("H,HK,D", [(4, 2, 128), (6, 3, 64), (8, 1, 128)])
+def test_grouped_query_heads_decode_and_prefill(K, n, H, HK, D):
+    B = 3
+    dev, dev_rep, host = _gqa_inputs(B, n, H, HK, D, seed=69 + n)
+    s0 = golden_state(B, H, D, D, 69, 0.3)
+    st, st_r = s0.to(DEV), s0.to(DEV)
+    o = gdn2.gdn2_decode(*dev, st)
+    o_r = gdn2.gdn2_decode(*dev_rep, st_r)
+    assert torch.equal(o, o_r) and torch.equal(st, st_r)
+    s_ref = s0.clone()
+    o_ref = orc.decode(*host, s_ref)
+    assert orc.max_abs_err(o.float().cpu(), o_ref) < O_ABS_BF16 and orc.rel_fro_err(st.cpu(), s_ref) < 1e-5
+    # ragged prefill through the public op: whole chunks + tail
+    S = 64 * 3 + n
+    dev, dev_rep, host = _gqa_inputs(B, S, H, HK, D, seed=71 + n)
+    o, s = gdn2.gdn2_prefill(*dev, s0.to(DEV))
+    o_ref, s_ref = orc.prefill(*host, s0.clone())
+    assert o.shape == (B, S, H, D)
+    assert orc.max_abs_err(o.float().cpu(), o_ref) < O_ABS_BF16 and orc.rel_fro_err(s.cpu(), s_ref) < STATE_FRO
+
+
+def test_grouped_query_heads_reject_uneven_groups(K):
+    dev, _, _ = _gqa_inputs(1, 4, 4, 2, 128, seed=3)
+    q3 = dev[0][:, :, :1].repeat(1, 1, 3, 1)
+    with pytest.raises(ValueError, match="multiple"):
+        gdn2.gdn2_decode(q3, q3, dev[2], q3.float(), q3, dev[5], torch.zeros(1, 4, 128, 128, device=DEV))

@@ -84,5 +84,5 @@ def test_prefill_does_not_allocate_chunk_states():
     peak_prefill = torch.cuda.max_memory_allocated() - base
     h_bytes = B * (S // 64) * H * DK * DV * 4                 # fp32 per-chunk states
     assert peak_prefill < peak_train - h_bytes * 0.5
-    ws = _cabi.kernels().lib.gdn2_prefill_workspace_bytes(B, S, H, DK, DV, _cabi.GDN2_BF16, _cabi.PATH_AUTO)
+    ws = _cabi.kernels().lib.gdn2_prefill_workspace_bytes(B, S, H, H, DK, DV, _cabi.GDN2_BF16, _cabi.PATH_AUTO)
     assert peak_prefill < ws + B * S * H * DV * 2 + 4 * B * H * DK * DV * 4 + (8 << 20)

@@ -22,15 +22,15 @@ pytestmark = pytest.mark.gpu
 
 def _two_call_form(lib, dev_in, s0, B, S, H, D, code, stream):
     q, k, v, g, b, w = dev_in
-    nbytes = lib.gdn2_prefill_workspace_bytes(B, S, H, D, D, code, _cabi.PATH_AUTO)
+    nbytes = lib.gdn2_prefill_workspace_bytes(B, S, H, H, D, D, code, _cabi.PATH_AUTO)
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     o = torch.empty(B, S, H, D, dtype=v.dtype, device=q.device)
     fin = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device)
     rc = lib.gdn2_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(), w.data_ptr(),
-                             ws.data_ptr(), nbytes, B, S, H, D, D, S, D**-0.5, code, _cabi.PATH_AUTO, stream)
+                             ws.data_ptr(), nbytes, B, S, H, H, D, D, S, D**-0.5, code, _cabi.PATH_AUTO, stream)
     assert rc == 0
     rc = lib.gdn2_prefill_scan(ws.data_ptr(), nbytes, s0.data_ptr(), o.data_ptr(), fin.data_ptr(), None,
-                               B, S, H, D, D, S, code, _cabi.PATH_AUTO, stream)
+                               B, S, H, H, D, D, S, code, _cabi.PATH_AUTO, stream)
     assert rc == 0
     return o, fin
 
@@ -92,8 +92,8 @@ def test_static_scratch_limit_is_exact():
     dev = torch.device("cuda", 0)
     code, D = _cabi.GDN2_BF16, 128
     limit = 32 * 1024 * 1024
-    nc = max(n for n in range(1, 600) if lib.gdn2_prefill_workspace_bytes(1, 64 * n, 1, D, D, code, _cabi.PATH_AUTO) <= limit)
-    assert lib.gdn2_prefill_workspace_bytes(1, 64 * (nc + 1), 1, D, D, code, _cabi.PATH_AUTO) > limit
+    nc = max(n for n in range(1, 600) if lib.gdn2_prefill_workspace_bytes(1, 64 * n, 1, 1, D, D, code, _cabi.PATH_AUTO) <= limit)
+    assert lib.gdn2_prefill_workspace_bytes(1, 64 * (nc + 1), 1, 1, D, D, code, _cabi.PATH_AUTO) > limit
     with torch.cuda.device(dev):
         stream = torch.cuda.current_stream(dev).cuda_stream
         q, k, v, g, b, w = orc.make_inputs(1, 64 * (nc + 1), 1, D, D, seed=33)
