@@ -331,9 +331,9 @@ class NativeKernels:
         _require_cuda(proj)
         B, S, NP = proj.shape
         dt, dev = proj.dtype, proj.device
-        q = torch.empty(B, S, H, DK, dtype=dt, device=dev)
+        q = torch.empty(B, S, HK, DK, dtype=dt, device=dev)        # one copy per key head: the kernels index them
         k, b = torch.empty_like(q), torch.empty_like(q)
-        g = torch.empty(B, S, H, DK, dtype=torch.float32, device=dev)
+        g = torch.empty(B, S, HK, DK, dtype=torch.float32, device=dev)
         v = torch.empty(B, S, H, DV, dtype=dt, device=dev)
         w = torch.empty_like(v)
         new_conv = None
