@@ -201,7 +201,8 @@ layer_front_d128_kernel(gdn2_layer_front_args a) {
   const T* cb = static_cast<const T*>(a.conv_bias);
   const size_t prow = ((size_t)b * S + t) * NP;
   const int c = 4 * lane;
-  const size_t tokh = ((size_t)b * S + t) * H;
+  const size_t tokh = ((size_t)b * S + t) * H;          // first value head of this token
+  const size_t tokk = ((size_t)b * S + t) * HK + hk;    // this key head: q, k, b, g are written once per key head
 
   for (int which = 0; which < 2; ++which) {
     float y[4];
@@ -211,7 +212,7 @@ layer_front_d128_kernel(gdn2_layer_front_args a) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) y[i] *= inv;
     T* dst = static_cast<T*>(which == 0 ? a.q : a.k);
-    for (int r = 0; r < rep; ++r) store4(dst + (tokh + hk * rep + r) * DK + c, y);
+    store4(dst + tokk * DK + c, y);
   }
   {
     float pb[4], pf[4], db[4], bo[4], go[4];
@@ -224,11 +225,8 @@ layer_front_d128_kernel(gdn2_layer_front_args a) {
       bo[i] = to_f32(from_f32<T>(sigmoidf_(pb[i]))) * a.erase_scale;
       go[i] = nega * softplusf_(pf[i] + db[i]);
     }
-    for (int r = 0; r < rep; ++r) {
-      const size_t o = (tokh + hk * rep + r) * DK + c;
-      store4(static_cast<T*>(a.b) + o, bo);
-      *reinterpret_cast<float4*>(a.g + o) = make_float4(go[0], go[1], go[2], go[3]);
-    }
+    store4(static_cast<T*>(a.b) + tokk * DK + c, bo);
+    *reinterpret_cast<float4*>(a.g + tokk * DK + c) = make_float4(go[0], go[1], go[2], go[3]);
   }
   for (int r = 0; r < rep; ++r) {
     const int h = hk * rep + r;
