@@ -41,6 +41,7 @@ SIGNATURES = {
     "gdn2_chunk_prep": (_int, [_vp] * 7 + [_sz] + [_i64] * 7 + [_f32, _int, _int, _vp]),
     "gdn2_prefill_scan": (_int, [_vp, _sz, _vp, _vp, _vp, _vp] + [_i64] * 7 + [_int, _int, _vp]),
     "gdn2_chunk_output": (_int, [_vp, _sz, _vp, _vp] + [_i64] * 7 + [_int, _int, _vp]),
+    "gdn2_prefill_scan_gated_norm": (_int, [_vp, _sz, _vp, _vp, _vp] + [_i64] * 7 + [_int, _int, _vp, _vp]),
     "gdn2_check_device_status": (_int, [_vp, ctypes.POINTER(ctypes.c_uint32)]),
     "gdn2_selftest_mma": (_int, [_vp, _vp, _vp, _vp]),
     "gdn2_selftest_wait": (_int, [_i64, _vp, _vp]),
@@ -60,6 +61,12 @@ class LayerFrontArgs(ctypes.Structure):
                 + [(n, _i64) for n in ("B", "S", "H", "HK", "DK", "DV", "K", "NP",
                                        "off_q", "off_k", "off_v", "off_b", "off_w", "off_f")]
                 + [("erase_scale", _f32)])
+
+class GatedNormArgs(ctypes.Structure):
+    """``gdn2_gated_norm`` of include/gdn2_b200.h."""
+
+    _fields_ = [("gate", _vp), ("weight", _vp), ("gate_row_stride", _i64), ("gate_batch_stride", _i64), ("eps", _f32)]
+
 
 class OProjReduceArgs(ctypes.Structure):
     """``gdn2_oproj_reduce_args`` of include/gdn2_b200.h."""
@@ -211,12 +218,20 @@ class NativeKernels:
         return o
 
     # -- chunkwise forward -----------------------------------------------------------------
+    def fuses_gated_norm(self, DK: int, DV: int, dtype: torch.dtype) -> bool:
+        """Whether ``chunk_forward`` can apply the layer's gated RMSNorm as the scan's epilogue for this shape."""
+        return self.resolved_path(DK, DV, dtype) in (PATH_TCGEN05, PATH_TCGEN05_SERIAL)
+
     def chunk_forward(self, q, k, v, g, b, w, scale: float, initial_state=None, want_chunk_states=False,
-                      path=None, out=None, out_batch_stride=None):
+                      path=None, out=None, out_batch_stride=None, gated_norm=None):
         """Whole chunks only (``S % 64 == 0``). Returns ``(o, final_state, chunk_states | None)``.
 
         ``out`` may be a preallocated ``[B, S_total >= S, H, DV]`` tensor whose first ``S`` tokens
         per batch entry receive the result (``out_batch_stride`` = its token stride).
+        ``gated_norm = (gate, gate_column, weight, eps)`` (tensor-core family only): the rows written are
+        ``rmsnorm(o) * weight * silu(gate)`` with the gate of ``o[b, t, h, c]`` read from
+        ``gate[b, t, gate_column + h*DV + c]`` (``gate``: a contiguous ``[B, >= S, NP]`` buffer, e.g. the
+        layer's projection buffer); the plain ``o`` is then never written.
         """
         _require_cuda(q, k, v, g, b, w, initial_state)
         B, S, HK, DK = q.shape
@@ -276,9 +291,21 @@ class NativeKernels:
                     ev.record(main)
                     side.wait_event(ev)
                     scan_stream = side
-                rc = self.lib.gdn2_prefill_scan(ws_i.data_ptr(), nb_i, state_ptr, out.data_ptr() + t0 * H * DV * esz,
-                                                states[i].data_ptr(), None if hs is None else hs.data_ptr(),
-                                                B, S_i, H, HK, DK, DV, out_batch_stride, code, p, scan_stream.cuda_stream)
+                if gated_norm is None:
+                    rc = self.lib.gdn2_prefill_scan(ws_i.data_ptr(), nb_i, state_ptr, out.data_ptr() + t0 * H * DV * esz,
+                                                    states[i].data_ptr(), None if hs is None else hs.data_ptr(),
+                                                    B, S_i, H, HK, DK, DV, out_batch_stride, code, p, scan_stream.cuda_stream)
+                else:
+                    gate, gcol, gweight, geps = gated_norm
+                    if hs is not None or gate.dim() != 3 or not gate.is_contiguous() or gate.dtype != v.dtype:
+                        raise ValueError("gated_norm needs a contiguous [B, S, NP] gate buffer in the input dtype "
+                                         "and cannot be combined with chunk states")
+                    NP = gate.shape[-1]
+                    na = GatedNormArgs(gate.data_ptr() + (t0 * NP + gcol) * gate.element_size(), gweight.data_ptr(),
+                                       NP, gate.shape[1], float(geps))
+                    rc = self.lib.gdn2_prefill_scan_gated_norm(
+                        ws_i.data_ptr(), nb_i, state_ptr, out.data_ptr() + t0 * H * DV * esz, states[i].data_ptr(),
+                        B, S_i, H, HK, DK, DV, out_batch_stride, code, p, ctypes.byref(na), scan_stream.cuda_stream)
                 _check(self.lib, rc, "gdn2_prefill_scan")
                 state_ptr = states[i].data_ptr()
                 cut = 1 if want_chunk_states else self.scan_segments(B, S_i, H, DK, DV, q.dtype, p)

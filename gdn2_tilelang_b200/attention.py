@@ -225,11 +225,28 @@ class GatedDeltaNet2(nn.Module):
             H, HK, DK, DV, K, float(self.erase_scale), want_conv_state=True)
         return q, k, v, g, b, w, new_conv, proj
 
-    def _back(self, x, o, proj):
+    def _back(self, x, o, proj, normed_rows: int = 0):
+        """Gated RMSNorm and output projection. The first ``normed_rows`` tokens of ``o`` have already been
+        normalised by the scan's epilogue; the rest (a ragged tail, or everything) goes through ``gdn2_layer_back``."""
+        B, S, H, DV = o.shape
         off_gate = self._fused_tables()[1][6]
-        normed = _cabi.kernels().layer_back(o.contiguous(), proj, self.o_norm.weight.detach().to(o.dtype),
-                                            off_gate, float(self.o_norm.eps))
+        K = _cabi.kernels()
+        weight = self.o_norm.weight.detach().to(o.dtype)
+        if normed_rows == 0:
+            normed = K.layer_back(o.contiguous(), proj, weight, off_gate, float(self.o_norm.eps))
+        else:
+            normed = o.view(B, S, H * DV)
+            if normed_rows < S:
+                tail = K.layer_back(o[:, normed_rows:].contiguous(), proj[:, normed_rows:].contiguous(), weight, off_gate,
+                                    float(self.o_norm.eps))
+                normed[:, normed_rows:] = tail
         return self._project_out(normed)
+
+    def _gated_norm_args(self, x, proj):
+        """Arguments that make the scan apply the gated RMSNorm itself, or ``None`` where it cannot."""
+        if not _cabi.kernels().fuses_gated_norm(self.head_dim_k, self.head_dim_v, x.dtype):
+            return None
+        return (proj, self._fused_tables()[1][6], self.o_norm.weight.detach().to(x.dtype), float(self.o_norm.eps))
 
     def _project_out(self, normed):
         """``o_proj``; the head-parallel variant overrides it to add the sum over ranks."""
@@ -263,9 +280,12 @@ class GatedDeltaNet2(nn.Module):
         q, k, v, g, b, w, conv, proj = self._front(hidden_states, cache.conv_state, cached=self.q_conv is not None)
         if conv is not None:
             cache.conv_state = conv
-        o, state = gdn2_prefill(q, k, v, g, b, w, cache.recurrent_state, scale=self.scale, config=self.cfg.kernel)
+        norm = self._gated_norm_args(hidden_states, proj)
+        o, state = gdn2_prefill(q, k, v, g, b, w, cache.recurrent_state, scale=self.scale, config=self.cfg.kernel,
+                                gated_norm=norm)
         cache.recurrent_state = state
-        return self._back(hidden_states, o, proj), cache
+        S = hidden_states.shape[1]
+        return self._back(hidden_states, o, proj, normed_rows=0 if norm is None else S // 64 * 64), cache
 
     @torch.no_grad()
     def decode(self, hidden_states, cache: GDN2Cache):

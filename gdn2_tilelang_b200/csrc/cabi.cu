@@ -189,9 +189,34 @@ int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (p == GDN2_PATH_TCGEN05)
     return launch_scan_tc(L, P, initial_state, o, final_state, chunk_states, (int)B, (int)S, (int)H,
-                          o_batch_stride, st);
+                          o_batch_stride, nullptr, st);
   return launch_scan_simt(L, P, initial_state, o, final_state, chunk_states, (int)B, (int)S, (int)H,
                           o_batch_stride, dtype, st);
+}
+
+int gdn2_prefill_scan_gated_norm(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
+                                 float* final_state, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
+                                 int64_t DV, int64_t o_batch_stride, int dtype, int path, const gdn2_gated_norm* norm,
+                                 void* stream) {
+  if (!norm)
+    return gdn2_prefill_scan(workspace, workspace_bytes, initial_state, o, final_state, nullptr, B, S, H, HK, DK, DV,
+                             o_batch_stride, dtype, path, stream);
+  if (!workspace || !o || !norm->gate || !norm->weight) return GDN2_ERR_NULL_POINTER;
+  int rc = check_prefill_shape(B, S, H, HK, DK, DV, dtype);
+  if (rc != GDN2_OK) return rc;
+  if (o_batch_stride < S || norm->gate_batch_stride < S || norm->gate_row_stride < H * DV || norm->gate_row_stride % 8 != 0)
+    return GDN2_ERR_BAD_SHAPE;
+  int p;
+  bool seg;
+  rc = resolve_path(DK, DV, dtype, path, &p, &seg);
+  if (rc != GDN2_OK) return rc;
+  if (p != GDN2_PATH_TCGEN05) return GDN2_ERR_UNSUPPORTED;
+  if (!aligned16(workspace) || !aligned16(norm->gate) || !aligned16(norm->weight)) return GDN2_ERR_MISALIGNED;
+  const WsLayout L = layout_for(B, S, H, HK, DK, DV, p, seg);
+  if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
+  const WsPtrs P = ws_pointers(const_cast<void*>(workspace), L);
+  return launch_scan_tc(L, P, initial_state, o, final_state, nullptr, (int)B, (int)S, (int)H, o_batch_stride, norm,
+                        static_cast<cudaStream_t>(stream));
 }
 
 int gdn2_chunk_output(const void* workspace, size_t workspace_bytes, const float* chunk_states, void* o,

@@ -103,6 +103,16 @@ struct ScanPlan {
   int pass, nseg, guarded;
 };
 
+// Optional epilogue of the output rows: the layer's gated RMSNorm (gdn2/attention.py:218-229 of the reference
+// project), o <- o * rsqrt(mean(o^2) + eps) * weight * silu(gate) per (token, head), applied to the bf16-rounded
+// rows on their way from the staging tile to global memory. gate == nullptr: plain outputs.
+struct ScanNorm {
+  const __nv_bfloat16* gate;     // gate of o[b, t, h, c] at gate[(b * batch_stride + t) * row_stride + h * 128 + c]
+  const __nv_bfloat16* weight;   // [128]
+  int64_t row_stride, batch_stride;
+  float eps;
+};
+
 enum : uint32_t {
   kWaitWq = 0x10, kWaitUt = 0x20, kWaitAqk = 0x40, kWaitKgt = 0x80, kWaitM1 = 0x100, kWaitM2 = 0x200,
   kWaitM3 = 0x400, kWaitSb = 0x800, kWaitUn = 0x4000
@@ -151,9 +161,51 @@ __device__ __forceinline__ void unpack8_f16(const uint4& p, float* x) {
   f = __half22float2(*reinterpret_cast<const __half2*>(&p.w)); x[6] = f.x; x[7] = f.y;
 }
 
+// The output rows of one chunk from the staging tile to global memory through the gated RMSNorm. 128 output
+// threads; the 16 threads that share a row (half a warp) hold its 128 values, 8 each. Kept out of line so that its
+// registers do not add to those of the chunk loop.
+__device__ __noinline__ void store_rows_normed(const __nv_bfloat16* ostage, __nv_bfloat16* obase, const __nv_bfloat16* gbase,
+                                               int64_t gate_row_stride, const __nv_bfloat16* weight, float eps, int otid,
+                                               int H) {
+  float nw[8];                                         // norm weights of this thread's 8 columns
+  {
+    const uint4 wv = __ldg(reinterpret_cast<const uint4*>(weight + (otid & 15) * 8));
+    const uint32_t u[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { nw[2 * i] = __uint_as_float(u[i] << 16); nw[2 * i + 1] = __uint_as_float(u[i] & 0xffff0000u); }
+  }
+  uint4 gv[8];
+#pragma unroll
+  for (int x = 0; x < 8; ++x)                          // all eight gate loads in flight before the first use
+    gv[x] = __ldg(reinterpret_cast<const uint4*>(gbase + (size_t)((otid >> 4) + 8 * x) * gate_row_stride));
+#pragma unroll
+  for (int x = 0; x < 8; ++x) {
+    const int piece = otid + x * kOutputThreads;
+    const int row = piece >> 4, col = (piece & 15) * 8;
+    const uint4 ovv = *reinterpret_cast<const uint4*>(&ostage[row * D + col]);
+    const uint32_t ou[4] = {ovv.x, ovv.y, ovv.z, ovv.w}, gu[4] = {gv[x].x, gv[x].y, gv[x].z, gv[x].w};
+    float xv[8], gt[8], ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      xv[2 * i] = __uint_as_float(ou[i] << 16); xv[2 * i + 1] = __uint_as_float(ou[i] & 0xffff0000u);
+      gt[2 * i] = __uint_as_float(gu[i] << 16); gt[2 * i + 1] = __uint_as_float(gu[i] & 0xffff0000u);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss = fmaf(xv[i], xv[i], ss);
+#pragma unroll
+    for (int off = 8; off; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float r = rsqrtf(ss * (1.f / D) + eps);
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = xv[i] * r * nw[i] * (gt[i] / (1.f + __expf(-gt[i])));
+    *reinterpret_cast<uint4*>(obase + (size_t)row * H * D + col) = tc::pack8_bf16(y);
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
-scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0, __nv_bfloat16* __restrict__ o,
-               float* __restrict__ sT, float* __restrict__ hs, int S, int H, int64_t o_bs, uint32_t* status) {
+scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, ScanNorm norm, const float* __restrict__ s0,
+               __nv_bfloat16* __restrict__ o, float* __restrict__ sT, float* __restrict__ hs, int S, int H, int64_t o_bs,
+               uint32_t* status) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   ScanTcSmem& s = *reinterpret_cast<ScanTcSmem*>(smem_raw);
   const int NC_all = S / BS;
@@ -349,12 +401,18 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, const float* __restrict__ s0
       if (write_o && !s.abort_flag) {
         // 64 rows x 256 bytes = 1024 16-byte pieces, 8 per thread, 128-bit coalesced stores
         __nv_bfloat16* obase = o + (((size_t)ib * o_bs + (size_t)(c_first + n) * BS) * H + ih) * D;
+        if (norm.gate == nullptr) {
 #pragma unroll
-        for (int x = 0; x < 8; ++x) {
-          const int piece = otid + x * kOutputThreads;
-          const int row = piece >> 4, col = (piece & 15) * 8;
-          *reinterpret_cast<uint4*>(obase + (size_t)row * H * D + col) =
-              *reinterpret_cast<const uint4*>(&s.ostage[row * D + col]);
+          for (int x = 0; x < 8; ++x) {
+            const int piece = otid + x * kOutputThreads;
+            const int row = piece >> 4, col = (piece & 15) * 8;
+            *reinterpret_cast<uint4*>(obase + (size_t)row * H * D + col) =
+                *reinterpret_cast<const uint4*>(&s.ostage[row * D + col]);
+          }
+        } else {
+          const __nv_bfloat16* gbase = norm.gate + ((size_t)ib * norm.batch_stride + (size_t)(c_first + n) * BS) * norm.row_stride +
+                                       (size_t)ih * D + (otid & 15) * 8;
+          store_rows_normed(s.ostage, obase, gbase, norm.row_stride, norm.weight, norm.eps, otid, H);
         }
       }
     }
@@ -610,17 +668,20 @@ scan_combine_kernel(WsPtrs P, int nseg, int NC_all, int guarded, float* __restri
 }  // namespace
 
 int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o, float* sT, float* hs,
-                   int B, int S, int H, int64_t o_bs, cudaStream_t st) {
+                   int B, int S, int H, int64_t o_bs, const gdn2_gated_norm* gn, cudaStream_t st) {
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
   const size_t smem = sizeof(ScanTcSmem) + 128;
   GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   __nv_bfloat16* ob = static_cast<__nv_bfloat16*>(o);
   uint32_t* status = device_status_word();
   const int BH = B * H, NC = S / BS;
+  ScanNorm norm{nullptr, nullptr, 0, 0, 0.f};
+  if (gn) norm = ScanNorm{static_cast<const __nv_bfloat16*>(gn->gate), static_cast<const __nv_bfloat16*>(gn->weight),
+                          gn->gate_row_stride, gn->gate_batch_stride, gn->eps};
   // chunk states are a by-product of the one-block-per-head walk only
   const int nseg = hs ? 1 : L.nseg;
   if (nseg <= 1) {
-    scan_tc_kernel<<<BH, kThreads, smem, st>>>(L, P, ScanPlan{kWhole, 1, 0}, s0, ob, sT, hs, S, H, o_bs, status);
+    scan_tc_kernel<<<BH, kThreads, smem, st>>>(L, P, ScanPlan{kWhole, 1, 0}, norm, s0, ob, sT, hs, S, H, o_bs, status);
     GDN2_CUDA_TRY(cudaGetLastError());
     return GDN2_OK;
   }
@@ -631,14 +692,14 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
     scan_mode_kernel<<<(BK * (nseg - 1) + 7) / 8, 256, 0, st>>>(P, BK, nseg, NC);
     GDN2_CUDA_TRY(cudaGetLastError());
   }
-  scan_tc_kernel<<<BH * (2 * nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kFirst, nseg, guarded}, s0, ob, sT, nullptr,
+  scan_tc_kernel<<<BH * (2 * nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kFirst, nseg, guarded}, norm, s0, ob, sT, nullptr,
                                                              S, H, o_bs, status);
   GDN2_CUDA_TRY(cudaGetLastError());
   const size_t csmem = (size_t)(D * kTPad + D * kCombineCols) * sizeof(float);
   GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
   scan_combine_kernel<<<dim3(BH, D / kCombineCols), 256, csmem, st>>>(P, nseg, NC, guarded, sT);
   GDN2_CUDA_TRY(cudaGetLastError());
-  scan_tc_kernel<<<BH * (nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kRedo, nseg, guarded}, nullptr, ob, nullptr, nullptr,
+  scan_tc_kernel<<<BH * (nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kRedo, nseg, guarded}, norm, nullptr, ob, nullptr, nullptr,
                                                          S, H, o_bs, status);
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;
@@ -656,7 +717,8 @@ int launch_output_tc(const WsLayout& L, const WsPtrs& P, const float* hs, void* 
   int runs = (4 * device_sm_count() + BH - 1) / BH;
   if (runs > NC / 4) runs = NC / 4;
   if (runs < 1) runs = 1;
-  scan_tc_kernel<<<BH * runs, kThreads, smem, st>>>(L, P, ScanPlan{kOutput, runs, 0}, nullptr, static_cast<__nv_bfloat16*>(o),
+  scan_tc_kernel<<<BH * runs, kThreads, smem, st>>>(L, P, ScanPlan{kOutput, runs, 0}, ScanNorm{nullptr, nullptr, 0, 0, 0.f}, nullptr,
+                                                   static_cast<__nv_bfloat16*>(o),
                                                    nullptr, const_cast<float*>(hs), S, H, o_bs, device_status_word());
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;

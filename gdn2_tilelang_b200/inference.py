@@ -66,10 +66,15 @@ def gdn2_decode_step(q, k, v, g, b, w, state, scale=None):
 
 
 @torch.no_grad()
-def gdn2_prefill(q, k, v, g, b, w, state=None, scale=None, config: GDN2Config = DEFAULT_KERNEL_CONFIG):
+def gdn2_prefill(q, k, v, g, b, w, state=None, scale=None, config: GDN2Config = DEFAULT_KERNEL_CONFIG,
+                 gated_norm=None):
     """Prefill a prompt. Returns ``(o [B, S, H, DV] in v.dtype, state [B, H, DK, DV] float32)``.
 
     Pass the returned state back in to prefill a long prompt in segments.
+
+    ``gated_norm = (gate, gate_column, weight, eps)`` (no counterpart in the reference's signature; used by the
+    layer): the rows of the WHOLE chunks come out as ``rmsnorm(o) * weight * silu(gate)`` (see
+    ``NativeKernels.chunk_forward``); the rows of a ragged tail are left plain for the caller to finish.
     """
     config.validate()
     B, S, H, DK, DV = _check_inputs(q, k, v, g, b, w)
@@ -88,7 +93,7 @@ def gdn2_prefill(q, k, v, g, b, w, state=None, scale=None, config: GDN2Config = 
     o = torch.empty(B, S, H, DV, dtype=v.dtype, device=q.device)
     if n_full:
         _, state, _ = K.chunk_forward(*(t[:, :n_full] for t in (q, k, v, g, b, w)), scale, state,
-                                      out=o, out_batch_stride=S)
+                                      out=o, out_batch_stride=S, gated_norm=gated_norm)
     if S > n_full:
         K.decode(*(t[:, n_full:] for t in (q, k, v, g, b, w)), state, scale, out=o[:, n_full:])
     K.maybe_check_device_status(q.device)

@@ -143,6 +143,28 @@ int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float
                       int64_t DV, int64_t o_batch_stride, int dtype, int path, void* stream);
 
 /*
+ * gdn2_prefill_scan with the layer's gated RMSNorm as the epilogue of the output rows:
+ *   o[b,t,h,:] <- o * rsqrt(mean(o^2) + eps) * weight * silu(gate[b,t,h,:]),
+ * evaluated on the rows as they leave the chip (rounded to `dtype` first, as the separate kernel would read
+ * them), so the normalised rows are written once and the plain ones never. The gate of o[b,t,h,c] is read at
+ * gate[(b * gate_batch_stride + t) * gate_row_stride + h*DV + c]: pass the o_gate columns of the layer's
+ * projection buffer without copying them. Tensor-core family only (DK = DV = 128, bf16; otherwise
+ * GDN2_ERR_UNSUPPORTED: use gdn2_prefill_scan + gdn2_layer_back). norm == NULL is gdn2_prefill_scan.
+ * Replaces _GatedRMSNorm after the attention call (gdn2/attention.py:218-229, 354-355).
+ */
+typedef struct gdn2_gated_norm {
+  const void* gate;            /* `dtype`, 16-byte aligned, gate_row_stride a multiple of 8 */
+  const void* weight;          /* [DV] `dtype` */
+  int64_t gate_row_stride;     /* elements between tokens */
+  int64_t gate_batch_stride;   /* tokens between batch entries */
+  float eps;
+} gdn2_gated_norm;
+int gdn2_prefill_scan_gated_norm(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
+                                 float* final_state, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
+                                 int64_t DV, int64_t o_batch_stride, int dtype, int path, const gdn2_gated_norm* norm,
+                                 void* stream);
+
+/*
  * Chunk-parallel output from stored chunk states: o = Qg h_n + tril(Aqk) Un_n with
  * Un_n = U - W h_n, one thread block per (chunk, batch, head). Needs the workspace of
  * gdn2_chunk_prep and the chunk_states of gdn2_prefill_scan.

@@ -32,10 +32,13 @@ class OracleKernels:
             return out
         return o
 
+    def fuses_gated_norm(self, DK, DV, dtype):
+        return False                     # the double keeps the norm a separate stage (layer_back)
+
     def chunk_forward(self, q, k, v, g, b, w, scale, initial_state=None, want_chunk_states=False,
-                      path=None, out=None, out_batch_stride=None):
+                      path=None, out=None, out_batch_stride=None, gated_norm=None):
         self.calls.append(("chunk_forward", q.shape[1]))
-        assert q.shape[1] % 64 == 0
+        assert q.shape[1] % 64 == 0 and gated_norm is None
         q, k, v, g, b, w = _expanded(q, k, v, g, b, w)
         res = orc.chunkwise(q, k, v, g, b, w, scale, initial_state, return_chunk_states=want_chunk_states)
         o, s = res[0].to(v.dtype), res[1]

@@ -159,3 +159,28 @@ def test_fused_output_projection_two_ranks_emulated_on_one_gpu():
         want = (x[0].double() @ w[0].double().T + x[1].double() @ w[1].double().T).float()
         assert orc.rel_max_err(out0.float().cpu(), want.cpu()) < 1e-2, step
         assert int(epochs[0][0]) == step + 1 and int(epochs[1][3]) == step + 1
+
+
+@pytest.mark.parametrize("B,S,H,HK", [(2, 64 * 5, 4, 2), (4, 64 * 30, 2, 2), (1, 64 * 40, 16, 8)])
+def test_gated_norm_as_scan_epilogue_equals_separate_kernel(B, S, H, HK):
+    """gdn2_prefill_scan_gated_norm (the norm applied to the rows as they leave the scan; one block per head and
+    the scan cut into segments) against gdn2_prefill_scan followed by gdn2_layer_back on the same bf16 rows: the
+    same arithmetic on the same rounded values, the sum of squares added in another order."""
+    K = gdn2._cabi.kernels()
+    D = 128
+    gen = torch.Generator().manual_seed(81)
+    q, k, _, g, b, _ = orc.make_inputs(B, S, HK, D, D, seed=81)
+    _, _, v, _, _, w = orc.make_inputs(B, S, H, D, D, seed=82)
+    dev = tuple(t.bfloat16().to(DEV) for t in (q, k, v)) + (g.to(DEV), b.bfloat16().to(DEV), w.bfloat16().to(DEV))
+    NP, off = H * D + 3 * 64, 2 * 64                       # gate columns inside a wider projection buffer
+    proj = torch.randn(B, S, NP, generator=gen).bfloat16().to(DEV)
+    weight = (1.0 + 0.1 * torch.randn(D, generator=gen)).bfloat16().to(DEV)
+    eps = 1e-5
+    o_plain, s_plain, _ = K.chunk_forward(*dev, D**-0.5)
+    want = K.layer_back(o_plain, proj, weight, off, eps).view(B, S, H, D)
+    got, s_got, _ = K.chunk_forward(*dev, D**-0.5, gated_norm=(proj, off, weight, eps))
+    K.check_device_status()
+    assert torch.equal(s_got, s_plain)
+    diff = (got.float() - want.float()).abs()
+    assert float(diff.max()) <= 2.0**-7 * float(want.float().abs().max())      # a last-place step of bf16 at most
+    assert float((diff > 0).float().mean()) < 0.02
