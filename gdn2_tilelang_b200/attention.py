@@ -243,7 +243,13 @@ class GatedDeltaNet2(nn.Module):
         return self._project_out(normed)
 
     def _gated_norm_args(self, x, proj):
-        """Arguments that make the scan apply the gated RMSNorm itself, or ``None`` where it cannot."""
+        """Arguments that make the scan apply the gated RMSNorm itself (``cfg.kernel`` unchanged; switched on with
+        ``layer.fuse_output_norm = True``), or ``None``. Off by default: the scan is bound by its chunk-to-chunk
+        chain and its four output warps have little slack, so the epilogue (64 SiLUs and a norm per thread and
+        chunk) stretches a chunk from 1.5 to 2.8 us, which costs more than the separate kernel's 0.06 ms at the
+        benchmark's layer size."""
+        if not getattr(self, "fuse_output_norm", False):
+            return None
         if not _cabi.kernels().fuses_gated_norm(self.head_dim_k, self.head_dim_v, x.dtype):
             return None
         return (proj, self._fused_tables()[1][6], self.o_norm.weight.detach().to(x.dtype), float(self.o_norm.eps))

@@ -74,22 +74,27 @@ struct WsLayout {
 __host__ __device__ inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 // Segments the tensor-core scan cuts a sequence of NC chunks into when a GPU holds BH (batch, head) pairs.
-// The first pass runs nseg "local" blocks and nseg - 1 "transition" blocks per pair, one per SM. While all of
-// them fit on 144 SMs at once the cut can only shorten the chain. With more pairs (transition blocks and local
-// blocks together exceed the SMs, but the local blocks alone fit) the cut still pays when the transition
-// blocks end after a few chunks, which they do when the decay makes the carried state vanish quickly; that cut
-// is "guarded": a decay check on the device takes it back for slowly decaying inputs. A segment is at least 8
-// chunks; 1 = no cut.
+// The first pass runs nseg "local" blocks and nseg - 1 "transition" blocks per pair, one per SM; the correction
+// pass may have to redo whole segments (slow decay), so the cut costs up to two chains of NC / nseg chunks.
+//   * While all 2 nseg - 1 blocks per pair fit on 144 SMs at once and nseg >= 3, the cut can only shorten the
+//     chain: it is made unconditionally.
+//   * Otherwise (two segments, or local blocks that fit while the transition blocks on top of them do not) the
+//     cut pays only when the transition blocks end after a few chunks, which they do when the decay makes the
+//     carried state vanish quickly. That cut is "guarded": a decay check on the device takes it back for slowly
+//     decaying inputs. Its segments are at least 24 chunks, twice what the check looks at.
+// A segment is at least 8 chunks; 1 = no cut.
 __host__ __device__ inline int scan_segments(int64_t BH, int64_t NC, int* guarded) {
   int64_t fit = (144 / BH + 1) / 2, over = 144 / BH, cap = NC / 8 < 16 ? NC / 8 : 16;
   if (fit > cap) fit = cap;
   if (over > cap) over = cap;
   *guarded = 0;
-  if (fit <= 2 && over > fit && over >= 2 && NC / over >= 24) {   // guarded segments keep room for the decay check
-    *guarded = 1;
-    return (int)over;
-  }
-  return fit < 2 ? 1 : (int)fit;
+  if (fit >= 3) return (int)fit;
+  for (int64_t n = over > fit ? over : fit; n >= 2; --n)
+    if (NC / n >= 24) {
+      *guarded = 1;
+      return (int)n;
+    }
+  return 1;
 }
 
 __host__ inline WsLayout make_ws_layout(int64_t B, int64_t S, int64_t H, int64_t HK, int DK, int DV, int esz,

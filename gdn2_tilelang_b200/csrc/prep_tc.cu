@@ -84,18 +84,17 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// Raw values of one channel pair for 4 consecutive tokens, converted only when consumed: g as two floats,
-// k, q, b as the two bf16 bit patterns in one 32-bit word (low half = even channel).
+// Raw values of one channel pair for 4 consecutive tokens, converted only when consumed: k, q, b as the two bf16
+// bit patterns in one 32-bit word (low half = even channel). The decay values are read once for the whole
+// sub-block in step 1a and stay in registers.
 struct Raw4 {
-  float2 g[4];
   uint32_t k[4], q[4], b[4];
 };
-__device__ __forceinline__ void load_raw4(Raw4& r, const float2* gp, const uint32_t* kp, const uint32_t* qp,
-                                          const uint32_t* bp, size_t pstride) {
+__device__ __forceinline__ void load_raw4(Raw4& r, const uint32_t* kp, const uint32_t* qp, const uint32_t* bp, size_t pstride) {
 #pragma unroll
   for (int u = 0; u < 4; ++u) {
     const size_t off = u * pstride;
-    r.g[u] = __ldg(gp + off); r.k[u] = __ldg(kp + off); r.q[u] = __ldg(qp + off); r.b[u] = __ldg(bp + off);
+    r.k[u] = __ldg(kp + off); r.q[u] = __ldg(qp + off); r.b[u] = __ldg(bp + off);
   }
 }
 // the two bf16 values of a packed word as fp32 (a bf16 is the top half of an fp32)
@@ -182,10 +181,15 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   //          Each thread sums its own sub-block (two channels); the four meet through shared memory.
   float2 ref0, ref1, ref2, ref3, g_last, run0;
   bool bad = false;
+  float2 gv[16];                                         // this thread's 16 decay values: read once, used again in step 1b
+  const uint32_t* qp = reinterpret_cast<const uint32_t*>(q + row0 * D + soff) + cp;
+  const uint32_t* kp = reinterpret_cast<const uint32_t*>(k + row0 * D + soff) + cp;
+  const uint32_t* bp = reinterpret_cast<const uint32_t*>(b + row0 * D + soff) + cp;
+  Raw4 ra;                                               // first group of step 1b: its loads fly across the barrier below
   {
-    float2 gv[16];
 #pragma unroll
     for (int t = 0; t < 16; ++t) gv[t] = __ldg(gp + t * pstride);                 // 16 independent loads in flight
+    load_raw4(ra, kp, qp, bp, pstride);
     float2 run = make_float2(0.f, 0.f);
     float2 mid = make_float2(0.f, 0.f);                  // G at row 8 of the sub-block: its reference row
 #pragma unroll
@@ -233,13 +237,11 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
   tc::tc_fence_after_sync();
   const uint32_t tm = s.tmem_base;
 
-  // ---- 1b. gated operands of the channel pair for this thread's 16 tokens, in four groups of 4; the next
-  //          group's 16 loads are issued (raw, unconverted) before the current one is processed. Two
+  // ---- 1b. gated operands of the channel pair for this thread's 16 tokens, in four groups of 4 (written out,
+  //          so that the decay values of step 1a are addressed statically and stay in registers); the next
+  //          group's 12 loads are issued (raw, unconverted) before the current one is processed. Two
   //          channels per thread: every 16-bit operand leaves as a packed pair (one convert, one store).
   {
-    const uint32_t* qp = reinterpret_cast<const uint32_t*>(q + row0 * D + soff) + cp;
-    const uint32_t* kp = reinterpret_cast<const uint32_t*>(k + row0 * D + soff) + cp;
-    const uint32_t* bp = reinterpret_cast<const uint32_t*>(b + row0 * D + soff) + cp;
     uint32_t* a_own32 = reinterpret_cast<uint32_t*>(s.x.ops.a_own) + (cp >> 2) * A_PAD * 4 + (cp & 3);
     uint32_t* bfam32 = reinterpret_cast<uint32_t*>(s.x.ops.bfam) + (cp >> 2) * B_PAD * 4 + (cp & 3);
     char* kgt_g = P.kgt + (size_t)ch * (D * BS * 2) + c0 * 16;   // fp16 image [tok/8][128 dk][8]
@@ -258,13 +260,13 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
     uint32_t kgx[4], kgy[4];                                    // fp16 pairs of KG for 8 tokens of each channel
 
     // one group: tokens t0 .. t0 + 3 of the chunk (t0 a multiple of 4); hi = second group of an 8-token pair
-    auto gate4 = [&](const Raw4& r, int t0, int hi) {
+    auto gate4 = [&](const Raw4& r, const float2* gq, int t0, int hi) {
       float e4x[4], e4y[4], kx[4], ky[4];
       uint32_t qgp[4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         const int t = t0 + u;
-        run.x = fmaf(r.g[u].x, kLog2e, run.x); run.y = fmaf(r.g[u].y, kLog2e, run.y);
+        run.x = fmaf(gq[u].x, kLog2e, run.x); run.y = fmaf(gq[u].y, kLog2e, run.y);
         const float2 kf = bf16x2_bits_to_f32(r.k[u]), qf = bf16x2_bits_to_f32(r.q[u]);
         const float2 a = ex2(run - ref);                      // both bounded by the half-span check
         const float2 co = ex2(ref - run);
@@ -299,19 +301,16 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       }
     };
 
-    Raw4 ra, rb;
-    load_raw4(ra, gp, kp, qp, bp, pstride);
-#pragma unroll 1
-    for (int s2 = 0; s2 < 2; ++s2) {                            // two 8-token halves of the sub-block
-      const int t0 = 16 * sbk + 8 * s2;
-      const size_t o4 = (size_t)(8 * s2 + 4) * pstride;
-      load_raw4(rb, gp + o4, kp + o4, qp + o4, bp + o4, pstride);
-      gate4(ra, t0, 0);
-      if (s2 == 0) {
-        const size_t o8 = (size_t)8 * pstride;
-        load_raw4(ra, gp + o8, kp + o8, qp + o8, bp + o8, pstride);
-      }
-      gate4(rb, t0 + 4, 1);
+    Raw4 rb;
+    {
+      const int t0 = 16 * sbk;
+      load_raw4(rb, kp + 4 * pstride, qp + 4 * pstride, bp + 4 * pstride, pstride);
+      gate4(ra, gv, t0, 0);
+      load_raw4(ra, kp + 8 * pstride, qp + 8 * pstride, bp + 8 * pstride, pstride);
+      gate4(rb, gv + 4, t0 + 4, 1);
+      load_raw4(rb, kp + 12 * pstride, qp + 12 * pstride, bp + 12 * pstride, pstride);
+      gate4(ra, gv + 8, t0 + 8, 0);
+      gate4(rb, gv + 12, t0 + 12, 1);
     }
     tc::tmem_st_wait();
     if (sbk == 3) *reinterpret_cast<float2*>(&P.gl[(size_t)ch * D + c0]) = ex2(g_last);
@@ -495,24 +494,38 @@ prep_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restr
       }
     }
     __syncthreads();
-    // X_ij, distance d = i - j = 1, 2, 3; warp w < 4 - d takes block (w + d, w)
+    // X_ij, distance d = i - j = 1, 2, 3. Block column j belongs to warps 2j and 2j + 1, eight columns each: a
+    // warp reads only N (finished above), the diagonal inverse and what it wrote itself in earlier rounds, so the
+    // rounds need a warp barrier only; every product is half as wide as a 16 x 16 block product.
+    {
+      const int bj = wid >> 1, nh = wid & 1;
+      auto half_mma = [&](float (&acc)[4], auto a_at, auto b_at) {
+#pragma unroll
+        for (int kt = 0; kt < 2; ++kt) {
+          const uint32_t a[4] = {__float_as_uint(tf32_rn(a_at(g8, 8 * kt + t4))), __float_as_uint(tf32_rn(a_at(g8 + 8, 8 * kt + t4))),
+                                 __float_as_uint(tf32_rn(a_at(g8, 8 * kt + t4 + 4))),
+                                 __float_as_uint(tf32_rn(a_at(g8 + 8, 8 * kt + t4 + 4)))};
+          const uint32_t b0 = __float_as_uint(tf32_rn(b_at(8 * kt + t4, 8 * nh + g8)));
+          const uint32_t b1 = __float_as_uint(tf32_rn(b_at(8 * kt + t4 + 4, 8 * nh + g8)));
+          asm volatile(
+              "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+              : "+f"(acc[0]), "+f"(acc[1]), "+f"(acc[2]), "+f"(acc[3])
+              : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+        }
+      };
 #pragma unroll 1
-    for (int d = 1; d < 4; ++d) {
-      if (wid + d < 4) {
-        const int bj = wid, bi = wid + d;
-        float acc[2][4] = {};
+      for (int bi = bj + 1; bi < 4; ++bi) {
+        float acc[4] = {};
 #pragma unroll 1
         for (int bk = bj; bk < bi; ++bk)
-          block_mma(acc, [&](int r, int cidx) { return T_at(bi, bk, r, cidx); }, [&](int r, int cidx) { return X_at(bk, bj, r, cidx); });
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-          aim[AI(16 * bi + g8, 16 * bj + 8 * nt + 2 * t4)] = tf32_rn(-acc[nt][0]);
-          aim[AI(16 * bi + g8, 16 * bj + 8 * nt + 2 * t4 + 1)] = tf32_rn(-acc[nt][1]);
-          aim[AI(16 * bi + g8 + 8, 16 * bj + 8 * nt + 2 * t4)] = tf32_rn(-acc[nt][2]);
-          aim[AI(16 * bi + g8 + 8, 16 * bj + 8 * nt + 2 * t4 + 1)] = tf32_rn(-acc[nt][3]);
-        }
+          half_mma(acc, [&](int r, int cidx) { return T_at(bi, bk, r, cidx); }, [&](int r, int cidx) { return X_at(bk, bj, r, cidx); });
+        const int col = 16 * bj + 8 * nh + 2 * t4;
+        aim[AI(16 * bi + g8, col)] = tf32_rn(-acc[0]);
+        aim[AI(16 * bi + g8, col + 1)] = tf32_rn(-acc[1]);
+        aim[AI(16 * bi + g8 + 8, col)] = tf32_rn(-acc[2]);
+        aim[AI(16 * bi + g8 + 8, col + 1)] = tf32_rn(-acc[3]);
+        __syncwarp();
       }
-      __syncthreads();
     }
   }
   tc::fence_async_smem();

@@ -197,7 +197,13 @@ __device__ __noinline__ void store_rows_normed(const __nv_bfloat16* ostage, __nv
     const float r = rsqrtf(ss * (1.f / D) + eps);
     float y[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) y[i] = xv[i] * r * nw[i] * (gt[i] / (1.f + __expf(-gt[i])));
+    for (int i = 0; i < 8; ++i) {
+      // silu(g) = g * sigmoid(g) = g * (0.5 + 0.5 tanh(g / 2)): one special-function instruction per element (the
+      // output warps have one special-function pipe each and 64 elements per thread and chunk to get through)
+      float th;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * gt[i]));
+      y[i] = xv[i] * r * nw[i] * gt[i] * fmaf(0.5f, th, 0.5f);
+    }
     *reinterpret_cast<uint4*>(obase + (size_t)row * H * D + col) = tc::pack8_bf16(y);
   }
 }
@@ -387,6 +393,12 @@ scan_tc_kernel(WsLayout L, WsPtrs P, ScanPlan plan, ScanNorm norm, const float* 
     if (!transition) warp_arrive(&s.bar_sb, lane);         // nothing to read out before chunk 0
     for (int n = 0; n < (transition ? 0 : NC); ++n) {
       float ov[64];
+      if (norm.gate) {                                     // this chunk's gate rows towards L2 while its products run
+        const __nv_bfloat16* gp_ = norm.gate + ((size_t)ib * norm.batch_stride + (size_t)(c_first + n) * BS + (otid >> 4)) * norm.row_stride +
+                                   (size_t)ih * D + (otid & 15) * 8;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) asm volatile("prefetch.global.L2 [%0];" ::"l"(gp_ + (size_t)(8 * x) * norm.row_stride));
+      }
       tc::mbar_wait(&s.bar_m2, n & 1, &s.abort_flag, status, kWaitM2);
       tc::tc_fence_after_sync();
       tc::tmem_ld32(t_o, *reinterpret_cast<float(*)[32]>(&ov[0]));

@@ -182,5 +182,21 @@ def test_gated_norm_as_scan_epilogue_equals_separate_kernel(B, S, H, HK):
     K.check_device_status()
     assert torch.equal(s_got, s_plain)
     diff = (got.float() - want.float()).abs()
-    assert float(diff.max()) <= 2.0**-7 * float(want.float().abs().max())      # a last-place step of bf16 at most
-    assert float((diff > 0).float().mean()) < 0.02
+    # the epilogue evaluates SiLU through tanh.approx (relative error 2^-11): a last-place step of bf16 at most,
+    # on a minority of the entries
+    assert float(diff.max()) <= 2.0**-7 * float(want.float().abs().max())
+    assert float((diff > 0).float().mean()) < 0.25
+
+
+def test_layer_prefill_with_the_norm_fused_into_the_scan():
+    """`layer.fuse_output_norm = True` routes the gated RMSNorm through the scan's epilogue (whole chunks) and the
+    separate kernel (ragged tail): same outputs as the default up to a last-place step of bf16 before o_proj."""
+    cfg = gdn2.GatedDeltaNet2Config(hidden_size=256, num_heads=4, num_kv_heads=2)
+    layer = gdn2.GatedDeltaNet2(cfg).to(torch.bfloat16).eval().to(DEV)
+    x = (torch.randn(2, 64 * 5 + 19, 256, generator=torch.Generator().manual_seed(9)) * 0.5).bfloat16().to(DEV)
+    want, cache_a = layer.prefill(x)
+    layer.fuse_output_norm = True
+    got, cache_b = layer.prefill(x)
+    assert torch.equal(cache_a.recurrent_state, cache_b.recurrent_state)
+    assert orc.rel_max_err(got.float().cpu(), want.float().cpu()) < 2e-2
+    assert float((got.float() - want.float()).abs().mean()) < 2e-3 * float(want.float().abs().max())
