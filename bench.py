@@ -304,7 +304,6 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG", "WARN")      # keeps NCCL's version banner off stdout: one JSON line only
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # exchange buffers use plain peer stores only
         import datetime
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
@@ -521,6 +520,7 @@ def layer_bench(gdn2, dist, dev, rank, world, barrier, max_over_ranks):
     for both message sizes, and every rank's output is compared with the unsharded layer run on the same GPU."""
     cfg = gdn2.GatedDeltaNet2Config(hidden_size=2048, num_heads=16, num_kv_heads=8)
     gen = torch.Generator(device=dev).manual_seed(0)
+    torch.manual_seed(0)                                   # the constructor's own draws (conv, gates): the same layer on every rank
     full = gdn2.GatedDeltaNet2(cfg).to(torch.bfloat16).eval().to(dev)
     with torch.no_grad():
         for name, prm in full.named_parameters():      # projections ~ N(0, 0.02); gate parameters keep their init
