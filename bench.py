@@ -283,7 +283,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="omit the end-to-end leg (launch-list captures)")
     ap.add_argument("--heads", type=int, default=None,
                     help="single GPU only: run the problem of ONE rank of a head-sharded job (this many of the 16 heads)")
-    ap.add_argument("--profile-case", choices=["prefill", "prefill-sharded", "decode", "output"],
+    ap.add_argument("--profile-case", choices=["prefill", "prefill-sharded", "decode", "output", "layer"],
                     help="run a small case a profiler can capture (3 iterations, no JSON line) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -312,7 +312,8 @@ def main():
     if args.profile_case:
         # small enough for a multi-pass capture, larger than L2: prefill B=1 S=4096+37 (workspace 107 MB),
         # the same with 2 heads and the full length (the scan cut into segments), decode B=128 (state 134 MB),
-        # chunk-parallel output B=1 S=4096 H=16 (chunk states 67 MB + workspace 76 MB)
+        # chunk-parallel output B=1 S=4096 H=16 (chunk states 67 MB + workspace 76 MB), the layer's prefill at the
+        # benchmark's layer size
         if args.profile_case == "prefill":
             ins = device_inputs(1, 4096 + 37, H, DK, DV, dev, seed=0)
             for _ in range(3):
@@ -321,6 +322,13 @@ def main():
             ins = device_inputs(4, 16037, 2, DK, DV, dev, seed=0)
             for _ in range(3):
                 gdn2.gdn2_prefill(*ins)
+        elif args.profile_case == "layer":
+            cfg = gdn2.GatedDeltaNet2Config(hidden_size=2048, num_heads=16, num_kv_heads=8)
+            torch.manual_seed(0)
+            layer = gdn2.GatedDeltaNet2(cfg).to(torch.bfloat16).eval().to(dev)
+            x = torch.randn(2, 4096, 2048, device=dev).bfloat16()      # projection buffer 201 MB, larger than L2
+            for _ in range(3):
+                layer.prefill(x)
         elif args.profile_case == "output":
             ins = device_inputs(1, 4096, H, DK, DV, dev, seed=0)
             _, _, hs = gdn2.chunk_gdn2_fwd(*ins, DK**-0.5, None, False, return_chunk_states=True)

@@ -240,6 +240,117 @@ layer_front_d128_kernel(gdn2_layer_front_args a) {
   }
 }
 
+// The same for prompts: one warp per (key head, FOUR consecutive tokens). The four outputs of a convolved channel
+// need the projection rows of 7 tokens, read once (the one-token form reads 16 for the same four outputs), and
+// the warp has all its loads in flight before the first use. Arithmetic and summation order are those of the
+// one-token form, so the two agree bit for bit.
+template <typename T>
+__global__ void __launch_bounds__(32 * kWarps)
+layer_front_d128x4_kernel(gdn2_layer_front_args a) {
+  constexpr int DK = 128, DV = 128, K = 4, TT = 4;
+  const int lane = threadIdx.x & 31;
+  const int S = (int)a.S, NP = (int)a.NP, H = (int)a.H, HK = (int)a.HK;
+  const int groups = (S + TT - 1) / TT;
+  const int64_t item = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
+  if (item >= a.B * groups * HK) return;
+  const int hk = (int)(item % HK);
+  const int64_t bg = item / HK;
+  const int t0 = (int)(bg % groups) * TT;
+  const int64_t b = bg / groups;
+  const int rep = H / HK;
+  const int Cqk = HK * DK, CC = 2 * Cqk + H * DV;
+  const T* P = static_cast<const T*>(a.proj);
+  const T* cs = static_cast<const T*>(a.conv_state);
+  const T* cw = static_cast<const T*>(a.conv_weight);
+  const T* cb = static_cast<const T*>(a.conv_bias);
+  const int c = 4 * lane;
+  const int nt = S - t0 < TT ? S - t0 : TT;               // tokens of this group that exist
+
+  // convolution + SiLU of 4 adjacent channels for the group's tokens: y[u] = token t0 + u
+  auto conv = [&](int col, int cch, float (&y)[TT][4]) {
+    float wt[4][4], bias[4], x[TT + K - 1][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) load4(cw + (size_t)(cch + i) * K, wt[i]);
+    if (cb) load4(cb + cch, bias);
+    else { bias[0] = bias[1] = bias[2] = bias[3] = 0.f; }
+#pragma unroll
+    for (int r = 0; r < TT + K - 1; ++r) {
+      const int tt = t0 - (K - 1) + r;
+      if (tt >= 0 && tt < S) {
+        load4(P + ((size_t)b * S + tt) * NP + col, x[r]);
+      } else if (tt < 0 && cs) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[r][i] = to_f32(cs[((size_t)b * CC + cch + i) * (K - 1) + (K - 1 + tt)]);
+      } else {
+        x[r][0] = x[r][1] = x[r][2] = x[r][3] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < TT; ++u)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float acc = bias[i];
+#pragma unroll
+        for (int j = 0; j < K; ++j) acc = fmaf(wt[i][j], x[u + j][i], acc);
+        y[u][i] = silu(acc);
+      }
+  };
+
+  for (int which = 0; which < 2; ++which) {
+    float y[TT][4];
+    conv((which == 0 ? (int)a.off_q : (int)a.off_k) + hk * DK + c, which * Cqk + hk * DK + c, y);
+    T* dst = static_cast<T*>(which == 0 ? a.q : a.k);
+#pragma unroll
+    for (int u = 0; u < TT; ++u) {
+      const float ss = warp_sum(y[u][0] * y[u][0] + y[u][1] * y[u][1] + y[u][2] * y[u][2] + y[u][3] * y[u][3]);
+      const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[u][i] *= inv;
+      if (u < nt) store4(dst + (((size_t)b * S + t0 + u) * HK + hk) * DK + c, y[u]);
+    }
+  }
+  {
+    float db[4];
+    load4(static_cast<const T*>(a.dt_bias) + hk * DK + c, db);
+    const float nega = -__expf(to_f32(static_cast<const T*>(a.A_log)[hk]));
+#pragma unroll
+    for (int u = 0; u < TT; ++u) {
+      if (u < nt) {
+        const size_t prow = ((size_t)b * S + t0 + u) * NP;
+        float pb[4], pf[4], bo[4], go[4];
+        load4(P + prow + a.off_b + hk * DK + c, pb);
+        load4(P + prow + a.off_f + hk * DK + c, pf);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          bo[i] = to_f32(from_f32<T>(sigmoidf_(pb[i]))) * a.erase_scale;
+          go[i] = nega * softplusf_(pf[i] + db[i]);
+        }
+        const size_t o = (((size_t)b * S + t0 + u) * HK + hk) * DK + c;
+        store4(static_cast<T*>(a.b) + o, bo);
+        *reinterpret_cast<float4*>(a.g + o) = make_float4(go[0], go[1], go[2], go[3]);
+      }
+    }
+  }
+  for (int r = 0; r < rep; ++r) {
+    const int h = hk * rep + r;
+    float y[TT][4];
+    conv((int)a.off_v + h * DV + c, 2 * Cqk + h * DV + c, y);
+#pragma unroll
+    for (int u = 0; u < TT; ++u) {
+      if (u < nt) {
+        const size_t prow = ((size_t)b * S + t0 + u) * NP;
+        float pw[4];
+        load4(P + prow + a.off_w + h * DV + c, pw);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) pw[i] = sigmoidf_(pw[i]);
+        const size_t o = (((size_t)b * S + t0 + u) * H + h) * DV + c;
+        store4(static_cast<T*>(a.v) + o, y[u]);
+        store4(static_cast<T*>(a.w) + o, pw);
+      }
+    }
+  }
+}
+
 // new_conv[b, cch, s] = pre-convolution value at time S - (K-1) + s (from P, the old cache, or zero)
 template <typename T>
 __global__ void layer_conv_tail_kernel(gdn2_layer_front_args a) {
@@ -289,7 +400,10 @@ int launch_front_typed(const gdn2_layer_front_args& a, cudaStream_t st) {
   const int64_t items = a.B * a.S * a.HK;
   const bool aligned = a.NP % 4 == 0 && a.off_q % 4 == 0 && a.off_k % 4 == 0 && a.off_v % 4 == 0 && a.off_b % 4 == 0 &&
                        a.off_w % 4 == 0 && a.off_f % 4 == 0;
-  if (sizeof(T) == 2 && a.DK == 128 && a.DV == 128 && a.K == 4 && aligned)
+  if (sizeof(T) == 2 && a.DK == 128 && a.DV == 128 && a.K == 4 && aligned && a.S >= 8) {
+    const int64_t items4 = a.B * ((a.S + 3) / 4) * a.HK;     // prompts: four tokens per warp
+    layer_front_d128x4_kernel<T><<<(unsigned)((items4 + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
+  } else if (sizeof(T) == 2 && a.DK == 128 && a.DV == 128 && a.K == 4 && aligned)
     layer_front_d128_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
   else
     layer_front_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);

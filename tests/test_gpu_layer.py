@@ -200,3 +200,31 @@ def test_layer_prefill_with_the_norm_fused_into_the_scan():
     assert torch.equal(cache_a.recurrent_state, cache_b.recurrent_state)
     assert orc.rel_max_err(got.float().cpu(), want.float().cpu()) < 2e-2
     assert float((got.float() - want.float()).abs().mean()) < 2e-3 * float(want.float().abs().max())
+
+
+@pytest.mark.parametrize("cached", [False, True])
+@pytest.mark.parametrize("S", [1, 3, 7, 8, 9, 13, 64])
+def test_fused_front_d128_bf16_matches_the_operator_chain(cached, S):
+    """The D = 128 16-bit forms of gdn2_layer_front (one token per warp for S < 8, four tokens per warp for
+    prompts, ragged last group included) against the operator chain evaluated in float32 on the same bf16
+    projection buffer: every output within bf16 rounding, the convolution cache exactly."""
+    from tests.fake_kernels import layer_front_chain
+
+    cfg = gdn2.GatedDeltaNet2Config(hidden_size=128, num_heads=4, num_kv_heads=2)
+    layer = gdn2.GatedDeltaNet2(cfg).to(torch.bfloat16).eval().to(DEV)
+    gen = torch.Generator().manual_seed(12)
+    with torch.no_grad():
+        for prm in layer.parameters():
+            prm.copy_((torch.randn(prm.shape, generator=gen) * 0.3).to(DEV))
+    x = torch.randn(3, S, 128, generator=gen).bfloat16().to(DEV)
+    state = torch.randn(3, 2 * 2 * 128 + 4 * 128, 3, generator=gen).bfloat16().to(DEV) if cached else None
+    fused = layer._front(x, state, cached=cached)
+    proj = fused[7].float().cpu()
+    _, offs, cw, cb = layer._fused_tables()
+    chain = layer_front_chain(proj, offs[:6], None if state is None else state.float().cpu(), cw.float().cpu(),
+                              cb.float().cpu(), layer.A_log.detach().float().cpu(), layer.dt_bias.detach().float().cpu(),
+                              4, 2, 128, 128, cfg.conv_size, float(layer.erase_scale))
+    for name, a, b in zip("q k v g b w".split(), fused[:6], chain[:6]):
+        assert a.shape == b.shape, name
+        assert orc.rel_max_err(a.float().cpu(), b.float()) < 1e-2, name
+    assert torch.equal(fused[6].float().cpu(), chain[6])          # the cache holds copies of bf16 values
