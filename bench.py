@@ -306,7 +306,19 @@ def main():
     if world > 1:
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # exchange buffers use plain peer stores only
         import datetime
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+        # NCCL writes its version banner to the C-level stdout when the first communicator comes up; this process's
+        # stdout is for the one JSON line, so file descriptor 1 points at stderr until the communicator exists
+        sys.stdout.flush()
+        saved_fd = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved_fd, 1)
+            os.close(saved_fd)
     B, S, H, DK, DV = (CFG[x] for x in ("B", "S", "H", "DK", "DV"))
     K = _cabi.kernels()
     if args.profile_case:
