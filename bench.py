@@ -283,7 +283,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="omit the end-to-end leg (launch-list captures)")
     ap.add_argument("--heads", type=int, default=None,
                     help="single GPU only: run the problem of ONE rank of a head-sharded job (this many of the 16 heads)")
-    ap.add_argument("--profile-case", choices=["prefill", "prefill-sharded", "decode", "output", "layer"],
+    ap.add_argument("--profile-case", choices=["prefill", "prefill-sharded", "decode", "output", "layer", "simt"],
                     help="run a small case a profiler can capture (3 iterations, no JSON line) and exit")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
@@ -341,6 +341,11 @@ def main():
             x = torch.randn(2, 4096, 2048, device=dev).bfloat16()      # projection buffer 201 MB, larger than L2
             for _ in range(3):
                 layer.prefill(x)
+        elif args.profile_case == "simt":
+            # the exact CUDA-core family (what fp32 / fp16 inputs and head sizes other than 128 take): fp32, D = 128
+            ins = tuple(t.float() for t in device_inputs(1, 2048, H, DK, DV, dev, seed=0))
+            for _ in range(3):
+                gdn2.gdn2_prefill(*ins)
         elif args.profile_case == "output":
             ins = device_inputs(1, 4096, H, DK, DV, dev, seed=0)
             _, _, hs = gdn2.chunk_gdn2_fwd(*ins, DK**-0.5, None, False, return_chunk_states=True)
@@ -420,6 +425,7 @@ def main():
         parity = {"o_max_abs": float((o_gpu.float().cpu() - o_cpu).abs().max()),
                   "state_rel_fro": float((s_gpu.cpu() - s_cpu).norm() / s_cpu.norm()),
                   "against": cpu["kind"], "bounds": {"o_max_abs": 2e-2, "state_rel_fro": 1e-3}}
+        parity["ok"] = bool(parity["o_max_abs"] <= 2e-2 and parity["state_rel_fro"] <= 1e-3)
         del o_gpu, s_gpu, cpu_ref
 
     # ---- end to end: pinned host inputs, H2D + kernels + D2H of o per step
@@ -571,6 +577,7 @@ def layer_bench(gdn2, dist, dev, rank, world, barrier, max_over_ranks):
         s_err = float((got_cache.recurrent_state - s_ref).norm() / s_ref.norm())
         leg["tp_parity"] = {"out_rel_max": max_over_ranks(max(errs)), "state_rel_fro": max_over_ranks(s_err),
                             "bounds": {"out_rel_max": 2e-2, "state_rel_fro": 1e-3}}
+        leg["tp_parity"]["ok"] = bool(leg["tp_parity"]["out_rel_max"] <= 2e-2 and leg["tp_parity"]["state_rel_fro"] <= 1e-3)
         del ref_out, got_out, ref_cache, got_cache
     ms_pre = max_over_ranks(time_events(lambda: layer.prefill(x), 5, 3, sync))
     _, cache = layer.prefill(x)
