@@ -37,6 +37,7 @@ SIGNATURES = {
     "gdn2_decode": (_int, [_vp] * 8 + [_i64] * 8 + [_f32, _int, _vp]),
     "gdn2_prefill_workspace_bytes": (_sz, [_i64] * 6 + [_int, _int]),
     "gdn2_prefill_scan_segments": (_int, [_i64] * 5 + [_int, _int]),
+    "gdn2_prefill_scan_launches": (_int, [_i64] * 5 + [_int, _int]),
     "gdn2_prefill_workspace_layout": (_int, [_i64] * 6 + [_int, _int, ctypes.POINTER(ctypes.c_int64)]),
     "gdn2_chunk_prep": (_int, [_vp] * 7 + [_sz] + [_i64] * 7 + [_f32, _int, _int, _vp]),
     "gdn2_prefill_scan": (_int, [_vp, _sz, _vp, _vp, _vp, _vp] + [_i64] * 7 + [_int, _int, _vp]),
@@ -308,8 +309,8 @@ class NativeKernels:
                         B, S_i, H, HK, DK, DV, out_batch_stride, code, p, ctypes.byref(na), scan_stream.cuda_stream)
                 _check(self.lib, rc, "gdn2_prefill_scan")
                 state_ptr = states[i].data_ptr()
-                cut = 1 if want_chunk_states else self.scan_segments(B, S_i, H, DK, DV, q.dtype, p)
-                launched += (2 if p != PATH_SIMT else 1) + (3 if cut > 1 else 1)
+                launched += (2 if p != PATH_SIMT else 1) + (
+                    1 if want_chunk_states else self.lib.gdn2_prefill_scan_launches(B, S_i, H, DK, DV, code, p))
             if side is not None:
                 main.wait_stream(side)             # from here on the caller's stream is ordered after every scan
             del scratch                            # ... so only now may the allocator hand these blocks out again

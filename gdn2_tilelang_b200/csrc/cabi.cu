@@ -144,6 +144,16 @@ int gdn2_prefill_scan_segments(int64_t B, int64_t S, int64_t H, int64_t DK, int6
   return layout_for(B, S, H, HK, DK, DV, p, seg).nseg;
 }
 
+int gdn2_prefill_scan_launches(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path) {
+  const int64_t HK = H;
+  if (check_prefill_shape(B, S, H, HK, DK, DV, dtype) != GDN2_OK) return 0;
+  int p;
+  bool seg;
+  if (resolve_path(DK, DV, dtype, path, &p, &seg) != GDN2_OK) return 0;
+  const WsLayout L = layout_for(B, S, H, HK, DK, DV, p, seg);
+  return L.nseg <= 1 ? 1 : L.nseg_guarded ? 4 : 3;
+}
+
 int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
                     void* workspace, size_t workspace_bytes, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
                     int64_t DV, int64_t in_batch_stride, float scale, int dtype, int path, void* stream) {

@@ -20,9 +20,23 @@ namespace {
 
 constexpr int kWarps = 4;
 
-__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
-__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(__expf(x)); }
+// Hardware exponential, reciprocal, logarithm and reciprocal square root, one instruction each (flush-to-zero
+// forms: no denormal fix-up code). A few ulp each, far inside the 16-bit storage rounding and the 2e-5 the
+// float32 form is tested to; the precise division and log1pf were most of these kernels' instructions.
+__device__ __forceinline__ float ex2_(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float rcp_(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float lg2_(float x) { float y; asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float rsq_(float x) { float y; asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+constexpr float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+__device__ __forceinline__ float silu(float x) { return x * rcp_(1.f + ex2_(-kLog2e * x)); }
+__device__ __forceinline__ float sigmoidf_(float x) { return rcp_(1.f + ex2_(-kLog2e * x)); }
+__device__ __forceinline__ float softplusf_(float x) {
+  const float e = ex2_(-kLog2e * fabsf(x));                // softplus(x) = max(x, 0) + log1p(exp(-|x|))
+  const float l = e < 0x1p-12f ? e * (1.f - 0.5f * e) : kLn2 * lg2_(1.f + e);
+  return fmaxf(x, 0.f) + l;
+}
+// 1 / max(sqrt(ss), 1e-12): the scale of F.normalize
+__device__ __forceinline__ float inv_norm(float ss) { return rsq_(fmaxf(ss, 1e-24f)); }
 __device__ __forceinline__ float warp_sum(float x) {
 #pragma unroll
   for (int o = 16; o; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
@@ -82,7 +96,7 @@ layer_front_kernel(gdn2_layer_front_args a) {
       vals[i] = y;
     }
     ss = warp_sum(ss);
-    const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+    const float inv = inv_norm(ss);
     T* dst = static_cast<T*>(which == 0 ? a.q : a.k);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -208,7 +222,7 @@ layer_front_d128_kernel(gdn2_layer_front_args a) {
     float y[4];
     conv4(P, cs, cw, cb, b, t, S, NP, (which == 0 ? (int)a.off_q : (int)a.off_k) + hk * DK + c, which * Cqk + hk * DK + c, CC, y);
     const float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
-    const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
+    const float inv = inv_norm(ss);
 #pragma unroll
     for (int i = 0; i < 4; ++i) y[i] *= inv;
     T* dst = static_cast<T*>(which == 0 ? a.q : a.k);
@@ -240,39 +254,42 @@ layer_front_d128_kernel(gdn2_layer_front_args a) {
   }
 }
 
-// The same for prompts: one warp per (key head, FOUR consecutive tokens). The four outputs of a convolved channel
-// need the projection rows of 7 tokens, read once (the one-token form reads 16 for the same four outputs), and
-// the warp has all its loads in flight before the first use. Arithmetic and summation order are those of the
-// one-token form, so the two agree bit for bit.
+// The same for prompts, cut finer: one warp per (head-wide slot, FOUR consecutive tokens). A token's slots are its
+// HK q heads, HK k heads, H v heads (convolution kinds), HK erase-gate heads, HK decay heads and H write-gate heads
+// (element-wise kinds); the slot index runs fastest, so the warps in flight sweep whole projection rows. A
+// convolution slot reads the 7 projection rows its four outputs need once (the one-token form reads 16), every
+// warp has all of its loads in flight before the first use and holds few enough registers for 32 warps per SM.
+// Arithmetic and summation order are those of the one-token form, so the two agree bit for bit.
 template <typename T>
-__global__ void __launch_bounds__(32 * kWarps)
+__global__ void __launch_bounds__(32 * kWarps, 6)
 layer_front_d128x4_kernel(gdn2_layer_front_args a) {
-  constexpr int DK = 128, DV = 128, K = 4, TT = 4;
+  constexpr int D = 128, K = 4, TT = 4;
   const int lane = threadIdx.x & 31;
   const int S = (int)a.S, NP = (int)a.NP, H = (int)a.H, HK = (int)a.HK;
   const int groups = (S + TT - 1) / TT;
-  const int64_t item = (int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5);
-  if (item >= a.B * groups * HK) return;
-  const int hk = (int)(item % HK);
-  const int64_t bg = item / HK;
-  const int t0 = (int)(bg % groups) * TT;
-  const int64_t b = bg / groups;
-  const int rep = H / HK;
-  const int Cqk = HK * DK, CC = 2 * Cqk + H * DV;
+  const int nslots = 4 * HK + 2 * H;
+  const unsigned item = blockIdx.x * kWarps + (threadIdx.x >> 5);      // the launcher keeps the count below 2^31
+  if (item >= (unsigned)a.B * groups * nslots) return;
+  const int slot = (int)(item % (unsigned)nslots);
+  const unsigned bg = item / (unsigned)nslots;
+  const int t0 = (int)(bg % (unsigned)groups) * TT;
+  const int64_t b = bg / (unsigned)groups;
+  const int Cqk = HK * D, CC = 2 * Cqk + H * D;
   const T* P = static_cast<const T*>(a.proj);
-  const T* cs = static_cast<const T*>(a.conv_state);
-  const T* cw = static_cast<const T*>(a.conv_weight);
-  const T* cb = static_cast<const T*>(a.conv_bias);
   const int c = 4 * lane;
   const int nt = S - t0 < TT ? S - t0 : TT;               // tokens of this group that exist
+  const size_t tok0 = (size_t)b * S + t0;
 
-  // convolution + SiLU of 4 adjacent channels for the group's tokens: y[u] = token t0 + u
-  auto conv = [&](int col, int cch, float (&y)[TT][4]) {
+  if (slot < 2 * HK + H) {
+    // ---- convolution + SiLU of 4 adjacent channels for the group's tokens; q and k then L2-normalised
+    const bool is_v = slot >= 2 * HK;
+    const int head = is_v ? slot - 2 * HK : slot < HK ? slot : slot - HK;
+    const int col = (int)(is_v ? a.off_v : slot < HK ? a.off_q : a.off_k) + head * D + c;
+    const int cch = (is_v ? 2 * Cqk : slot < HK ? 0 : Cqk) + head * D + c;
+    const T* cs = static_cast<const T*>(a.conv_state);
+    const T* cw = static_cast<const T*>(a.conv_weight);
+    const T* cb = static_cast<const T*>(a.conv_bias);
     float wt[4][4], bias[4], x[TT + K - 1][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) load4(cw + (size_t)(cch + i) * K, wt[i]);
-    if (cb) load4(cb + cch, bias);
-    else { bias[0] = bias[1] = bias[2] = bias[3] = 0.f; }
 #pragma unroll
     for (int r = 0; r < TT + K - 1; ++r) {
       const int tt = t0 - (K - 1) + r;
@@ -286,68 +303,64 @@ layer_front_d128x4_kernel(gdn2_layer_front_args a) {
       }
     }
 #pragma unroll
-    for (int u = 0; u < TT; ++u)
+    for (int i = 0; i < 4; ++i) load4(cw + (size_t)(cch + i) * K, wt[i]);
+    if (cb) load4(cb + cch, bias);
+    else { bias[0] = bias[1] = bias[2] = bias[3] = 0.f; }
+    T* dst = static_cast<T*>(is_v ? a.v : slot < HK ? a.q : a.k);
+    const int heads = is_v ? H : HK;
+#pragma unroll
+    for (int u = 0; u < TT; ++u) {
+      float y[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         float acc = bias[i];
 #pragma unroll
         for (int j = 0; j < K; ++j) acc = fmaf(wt[i][j], x[u + j][i], acc);
-        y[u][i] = silu(acc);
+        y[i] = silu(acc);
       }
-  };
-
-  for (int which = 0; which < 2; ++which) {
-    float y[TT][4];
-    conv((which == 0 ? (int)a.off_q : (int)a.off_k) + hk * DK + c, which * Cqk + hk * DK + c, y);
-    T* dst = static_cast<T*>(which == 0 ? a.q : a.k);
+      if (!is_v) {
+        const float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
+        const float inv = inv_norm(ss);
 #pragma unroll
-    for (int u = 0; u < TT; ++u) {
-      const float ss = warp_sum(y[u][0] * y[u][0] + y[u][1] * y[u][1] + y[u][2] * y[u][2] + y[u][3] * y[u][3]);
-      const float inv = 1.f / fmaxf(sqrtf(ss), 1e-12f);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) y[u][i] *= inv;
-      if (u < nt) store4(dst + (((size_t)b * S + t0 + u) * HK + hk) * DK + c, y[u]);
+        for (int i = 0; i < 4; ++i) y[i] *= inv;
+      }
+      if (u < nt) store4(dst + ((tok0 + u) * heads + head) * D + c, y);
     }
+    return;
   }
-  {
-    float db[4];
-    load4(static_cast<const T*>(a.dt_bias) + hk * DK + c, db);
-    const float nega = -__expf(to_f32(static_cast<const T*>(a.A_log)[hk]));
+  // ---- element-wise slots: erase gate b, decay g (key heads), write gate w (value heads)
+  const int e = slot - (2 * HK + H);
+  const int kind = e < HK ? 0 : e < 2 * HK ? 1 : 2;
+  const int head = kind == 0 ? e : kind == 1 ? e - HK : e - 2 * HK;
+  const int col = (int)(kind == 0 ? a.off_b : kind == 1 ? a.off_f : a.off_w) + head * D + c;
+  float p[TT][4];
 #pragma unroll
-    for (int u = 0; u < TT; ++u) {
+  for (int u = 0; u < TT; ++u)
+    if (u < nt) load4(P + (tok0 + u) * NP + col, p[u]);
+  if (kind == 1) {
+    float db[4];
+    load4(static_cast<const T*>(a.dt_bias) + head * D + c, db);
+    const float nega = -__expf(to_f32(static_cast<const T*>(a.A_log)[head]));
+#pragma unroll
+    for (int u = 0; u < TT; ++u)
+      if (u < nt)
+        *reinterpret_cast<float4*>(a.g + ((tok0 + u) * HK + head) * D + c) =
+            make_float4(nega * softplusf_(p[u][0] + db[0]), nega * softplusf_(p[u][1] + db[1]),
+                        nega * softplusf_(p[u][2] + db[2]), nega * softplusf_(p[u][3] + db[3]));
+  } else {
+    T* dst = static_cast<T*>(kind == 0 ? a.b : a.w);
+    const int heads = kind == 0 ? HK : H;
+#pragma unroll
+    for (int u = 0; u < TT; ++u)
       if (u < nt) {
-        const size_t prow = ((size_t)b * S + t0 + u) * NP;
-        float pb[4], pf[4], bo[4], go[4];
-        load4(P + prow + a.off_b + hk * DK + c, pb);
-        load4(P + prow + a.off_f + hk * DK + c, pf);
+        float y[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          bo[i] = to_f32(from_f32<T>(sigmoidf_(pb[i]))) * a.erase_scale;
-          go[i] = nega * softplusf_(pf[i] + db[i]);
+          y[i] = sigmoidf_(p[u][i]);
+          if (kind == 0) y[i] = to_f32(from_f32<T>(y[i])) * a.erase_scale;
         }
-        const size_t o = (((size_t)b * S + t0 + u) * HK + hk) * DK + c;
-        store4(static_cast<T*>(a.b) + o, bo);
-        *reinterpret_cast<float4*>(a.g + o) = make_float4(go[0], go[1], go[2], go[3]);
+        store4(dst + ((tok0 + u) * heads + head) * D + c, y);
       }
-    }
-  }
-  for (int r = 0; r < rep; ++r) {
-    const int h = hk * rep + r;
-    float y[TT][4];
-    conv((int)a.off_v + h * DV + c, 2 * Cqk + h * DV + c, y);
-#pragma unroll
-    for (int u = 0; u < TT; ++u) {
-      if (u < nt) {
-        const size_t prow = ((size_t)b * S + t0 + u) * NP;
-        float pw[4];
-        load4(P + prow + a.off_w + h * DV + c, pw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) pw[i] = sigmoidf_(pw[i]);
-        const size_t o = (((size_t)b * S + t0 + u) * H + h) * DV + c;
-        store4(static_cast<T*>(a.v) + o, y[u]);
-        store4(static_cast<T*>(a.w) + o, pw);
-      }
-    }
   }
 }
 
@@ -399,9 +412,15 @@ template <typename T>
 int launch_front_typed(const gdn2_layer_front_args& a, cudaStream_t st) {
   const int64_t items = a.B * a.S * a.HK;
   const bool aligned = a.NP % 4 == 0 && a.off_q % 4 == 0 && a.off_k % 4 == 0 && a.off_v % 4 == 0 && a.off_b % 4 == 0 &&
-                       a.off_w % 4 == 0 && a.off_f % 4 == 0;
-  if (sizeof(T) == 2 && a.DK == 128 && a.DV == 128 && a.K == 4 && aligned && a.S >= 8) {
-    const int64_t items4 = a.B * ((a.S + 3) / 4) * a.HK;     // prompts: four tokens per warp
+                       a.off_w % 4 == 0 && a.off_f % 4 == 0 &&
+                       ((reinterpret_cast<uintptr_t>(a.proj) | reinterpret_cast<uintptr_t>(a.conv_weight) |
+                         reinterpret_cast<uintptr_t>(a.conv_bias) | reinterpret_cast<uintptr_t>(a.dt_bias) |
+                         reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v) |
+                         reinterpret_cast<uintptr_t>(a.b) | reinterpret_cast<uintptr_t>(a.w)) & 7) == 0 &&
+                       (reinterpret_cast<uintptr_t>(a.g) & 15) == 0;
+  if (sizeof(T) == 2 && a.DK == 128 && a.DV == 128 && a.K == 4 && aligned && a.S >= 8 &&
+      a.B * ((a.S + 3) / 4) * (4 * a.HK + 2 * a.H) < (int64_t)1 << 31) {
+    const int64_t items4 = a.B * ((a.S + 3) / 4) * (4 * a.HK + 2 * a.H);   // prompts: a slot of four tokens per warp
     layer_front_d128x4_kernel<T><<<(unsigned)((items4 + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
   } else if (sizeof(T) == 2 && a.DK == 128 && a.DV == 128 && a.K == 4 && aligned)
     layer_front_d128_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
@@ -416,10 +435,57 @@ int launch_front_typed(const gdn2_layer_front_args& a, cudaStream_t st) {
   return GDN2_OK;
 }
 
+// DV = 128, 16-bit storage: lane owns channels 4 lane .. 4 lane + 3, a warp takes FOUR consecutive (token, head)
+// rows with all eight row loads in flight before the first use.
+template <typename T>
+__global__ void __launch_bounds__(32 * kWarps)
+layer_back_d128_kernel(const T* __restrict__ o, const T* __restrict__ proj, const T* __restrict__ weight, T* __restrict__ out,
+                       int64_t items, int H, int NP, int off_gate, float eps) {
+  constexpr int DV = 128, R = 4;
+  const int lane = threadIdx.x & 31;
+  const int c = 4 * lane;
+  const int64_t item0 = ((int64_t)blockIdx.x * kWarps + (threadIdx.x >> 5)) * R;
+  if (item0 >= items) return;
+  float x[R][4], g[R][4], wv[4];
+#pragma unroll
+  for (int u = 0; u < R; ++u) {
+    const int64_t item = item0 + u;
+    if (item < items) {
+      load4(o + (size_t)item * DV + c, x[u]);
+      const uint32_t tok = (uint32_t)item / (uint32_t)H;  // the launcher keeps the row count below 2^32
+      load4(proj + (size_t)tok * NP + off_gate + (int)((uint32_t)item - tok * (uint32_t)H) * DV + c, g[u]);
+    }
+  }
+  load4(weight + c, wv);
+#pragma unroll
+  for (int u = 0; u < R; ++u) {
+    const int64_t item = item0 + u;
+    if (item < items) {                                  // uniform over the warp
+      const float ss = warp_sum(x[u][0] * x[u][0] + x[u][1] * x[u][1] + x[u][2] * x[u][2] + x[u][3] * x[u][3]);
+      const float r = rsqrtf(ss / (float)DV + eps);
+      float y[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) y[i] = x[u][i] * r * wv[i] * silu(g[u][i]);
+      store4(out + (size_t)item * DV + c, y);
+    }
+  }
+}
+
 template <typename T>
 int launch_back_typed(const void* o, const void* proj, const void* weight, void* out, int64_t BS, int H, int DV, int NP,
                       int off_gate, float eps, cudaStream_t st) {
   const int64_t items = BS * H;
+  const bool aligned = NP % 4 == 0 && off_gate % 4 == 0 &&
+                       ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(weight) |
+                         reinterpret_cast<uintptr_t>(out)) & 7) == 0;
+  if (sizeof(T) == 2 && DV == 128 && aligned && items < (int64_t)1 << 32) {
+    const int64_t warps = (items + 3) / 4;
+    layer_back_d128_kernel<T><<<(unsigned)((warps + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(
+        static_cast<const T*>(o), static_cast<const T*>(proj), static_cast<const T*>(weight), static_cast<T*>(out), items, H,
+        NP, off_gate, eps);
+    GDN2_CUDA_TRY(cudaGetLastError());
+    return GDN2_OK;
+  }
   layer_back_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(
       static_cast<const T*>(o), static_cast<const T*>(proj), static_cast<const T*>(weight), static_cast<T*>(out), BS, H,
       DV, NP, off_gate, eps);

@@ -112,6 +112,13 @@ int gdn2_prefill_workspace_layout(int64_t B, int64_t S, int64_t H, int64_t HK, i
 int gdn2_prefill_scan_segments(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path);
 
 /*
+ * Kernels gdn2_prefill_scan launches for this problem without chunk_states: 1 (one walk), 3 (first pass, chaining
+ * of the segment records, redo pass) or 4 (the same behind the decay check of a guarded cut); 0 for an
+ * unsupported combination. For callers that account for their launches. No counterpart in the reference.
+ */
+int gdn2_prefill_scan_launches(int64_t B, int64_t S, int64_t H, int64_t DK, int64_t DV, int dtype, int path);
+
+/*
  * Chunk-local stage of the chunkwise forward (chunk = 64 tokens): cumulative log2 decay, the
  * intra-chunk matrices Aqk / Akk, the (I + Akk)^-1 solve and the WY factors W, U, KG, plus the
  * decayed queries, written into `workspace` in the operand layout the scan consumes.
@@ -131,8 +138,9 @@ int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g,
  * Replaces prefill_scan_kernel (gdn2/inference.py:356-479) and, with chunk_states, the
  * state_kernel + output_kernel pair of the training-style forward (gdn2/forward.py:538-727).
  *
- * Few (batch, head) pairs (B*H <= 36, sequences of 16 chunks or more, tcgen05 family, no chunk_states):
- * the sequence is cut into segments. Every segment is scanned from a zero state while a second block
+ * Few (batch, head) pairs (tcgen05 family, no chunk_states; B*H <= 28 and 24 chunks or more: always; B*H <= 72 and
+ * 48 chunks or more: "guarded", only when a check of the decay on the device finds that a segment forgets the
+ * state entering it): the sequence is cut into segments. Every segment is scanned from a zero state while a second block
  * accumulates the segment's state-transition matrix; a small kernel chains the segments' affine maps
  * and a last launch redoes, from the true entering state, the leading chunks of each segment that the
  * entering state still reaches. The result equals the one-block walk up to the rounding of the state

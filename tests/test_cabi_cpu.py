@@ -115,6 +115,14 @@ def test_scan_segments_rule(lib):
     assert f(4, 16000, 2, 128, 128, bf, _cabi.PATH_TCGEN05_SERIAL) == 1
     assert f(4, 16000, 2, 64, 64, bf, _cabi.PATH_AUTO) == 1          # SIMT family
     assert f(4, 100, 2, 128, 128, bf, _cabi.PATH_AUTO) == 0          # invalid shape
+    n = lib.gdn2_prefill_scan_launches                                # what the scan launches for those cuts
+    assert n(4, 16000, 16, 128, 128, bf, _cabi.PATH_AUTO) == 4       # guarded: decay check, first pass, chaining, redo
+    assert n(4, 16000, 8, 128, 128, bf, _cabi.PATH_AUTO) == 4
+    assert n(4, 16000, 2, 128, 128, bf, _cabi.PATH_AUTO) == 3        # every block resident: no guard
+    assert n(4, 16000, 4, 128, 128, bf, _cabi.PATH_AUTO) == 3        # unguarded
+    assert n(5, 16000, 16, 128, 128, bf, _cabi.PATH_AUTO) == 1
+    assert n(4, 16000, 2, 64, 64, bf, _cabi.PATH_AUTO) == 1
+    assert n(4, 100, 2, 128, 128, bf, _cabi.PATH_AUTO) == 0
     w = lib.gdn2_prefill_workspace_bytes
     cut, serial = w(4, 16000, 2, 2, 128, 128, bf, _cabi.PATH_TCGEN05), w(4, 16000, 2, 2, 128, 128, bf, _cabi.PATH_TCGEN05_SERIAL)
     want = 8 * 9 * (3 * 128 * 128 * 4 + 4)

@@ -228,3 +228,13 @@ def test_fused_front_d128_bf16_matches_the_operator_chain(cached, S):
         assert a.shape == b.shape, name
         assert orc.rel_max_err(a.float().cpu(), b.float()) < 1e-2, name
     assert torch.equal(fused[6].float().cpu(), chain[6])          # the cache holds copies of bf16 values
+    # the D = 128 form of gdn2_layer_back (four rows per warp), a row count that is not a multiple of four included
+    from tests.fake_kernels import layer_back_chain
+
+    for rows, heads in ((3, 4), (1, 3)):
+        o = torch.randn(rows, S, heads, 128, generator=gen).bfloat16()
+        want = layer_back_chain(o.float(), proj[:rows], layer.o_norm.weight.detach().float().cpu(), offs[6], layer.o_norm.eps)
+        got = gdn2._cabi.kernels().layer_back(o.to(DEV), fused[7][:rows].contiguous(), layer.o_norm.weight.detach(), offs[6],
+                                               float(layer.o_norm.eps))
+        assert got.dtype == torch.bfloat16
+        assert orc.rel_max_err(got.float().cpu(), want) < 1e-2
