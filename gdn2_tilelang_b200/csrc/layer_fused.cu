@@ -279,6 +279,20 @@ layer_front_d128x4_kernel(gdn2_layer_front_args a) {
   const int c = 4 * lane;
   const int nt = S - t0 < TT ? S - t0 : TT;               // tokens of this group that exist
   const size_t tok0 = (size_t)b * S + t0;
+  {
+    // Pull the rows of the same slot some 4096 warps ahead (about what the GPU holds at once, a whole number of
+    // token groups of this batch row) towards L2: 4 rows x 256 B = 8 lines, one per lane 0..7.
+    const int ahead = ((4096 + nslots - 1) / nslots) * TT;
+    const int scol = slot < HK ? (int)a.off_q + slot * D
+                   : slot < 2 * HK ? (int)a.off_k + (slot - HK) * D
+                   : slot < 2 * HK + H ? (int)a.off_v + (slot - 2 * HK) * D
+                   : slot < 3 * HK + H ? (int)a.off_b + (slot - 2 * HK - H) * D
+                   : slot < 4 * HK + H ? (int)a.off_f + (slot - 3 * HK - H) * D
+                   : (int)a.off_w + (slot - 4 * HK - H) * D;
+    const int tp = t0 + ahead + (lane >> 1);
+    if (lane < 2 * TT && tp < S)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(P + ((size_t)b * S + tp) * NP + scol) + (lane & 1) * 128));
+  }
 
   if (slot < 2 * HK + H) {
     // ---- convolution + SiLU of 4 adjacent channels for the group's tokens; q and k then L2-normalised
