@@ -14,7 +14,7 @@ One JSON line on rank 0:
   value       prefill tokens/s with inputs resident in HBM (CUDA events, max over ranks)
   e2e         the same metric through the public API with pinned-host inputs: per step the H2D copy
               of all six inputs and the D2H read of o are inside the timed region
-  parity      (N = 1) the outputs of the timed GPU step against the CPU baseline's outputs on the same
+  parity      the outputs of the timed GPU step (N > 1: of rank 0's head shard) against the CPU path's outputs on the same
               bf16-rounded inputs: output max-abs error and final-state relative Frobenius error
   roofline    the dominant kernel's algorithmic HBM bytes per launch / its event-timed duration,
               against the measured copy bandwidth in MEASURED_PEAKS.json
@@ -427,6 +427,23 @@ def main():
                   "against": cpu["kind"], "bounds": {"o_max_abs": 2e-2, "state_rel_fro": 1e-3}}
         parity["ok"] = bool(parity["o_max_abs"] <= 2e-2 and parity["state_rel_fro"] <= 1e-3)
         del o_gpu, s_gpu, cpu_ref
+    elif world > 1 and rank == 0 and not args.skip_cpu:
+        # N GPUs: rank 0 checks its own head shard (heads are independent) against the CPU path on the same values
+        torch.set_num_threads(os.cpu_count() or 1)
+        prefill_cpu, kind = cpu_prefill_fn()
+        o_gpu, s_gpu = step()
+        torch.cuda.synchronize()
+        o_err, num, den = 0.0, 0.0, 0.0
+        for i in range(B):
+            o_c, s_c = prefill_cpu(*(t[i:i + 1].float().cpu() for t in ins))
+            o_err = max(o_err, float((o_gpu[i:i + 1].float().cpu() - o_c).abs().max()))
+            num += float((s_gpu[i:i + 1].cpu() - s_c).pow(2).sum())
+            den += float(s_c.pow(2).sum())
+        parity = {"o_max_abs": o_err, "state_rel_fro": (num / den) ** 0.5, "against": kind,
+                  "scope": f"rank 0's shard: heads 0..{Hl - 1} of {H}, all {B} sequences",
+                  "bounds": {"o_max_abs": 2e-2, "state_rel_fro": 1e-3}}
+        parity["ok"] = bool(parity["o_max_abs"] <= 2e-2 and parity["state_rel_fro"] <= 1e-3)
+        del o_gpu, s_gpu
 
     # ---- end to end: pinned host inputs, H2D + kernels + D2H of o per step
     host = [x.cpu().pin_memory() for x in ins]
