@@ -106,7 +106,9 @@ int gdn2_decode(const void* q, const void* k, const void* v, const float* g, con
   if (HK <= 0 || H % HK != 0) return GDN2_ERR_BAD_SHAPE;
   if (B * H > 2147483647LL / 4 || n > (1 << 24)) return GDN2_ERR_BAD_SHAPE;
   if (in_batch_stride < n || o_batch_stride < n) return GDN2_ERR_BAD_SHAPE;
-  if (DK == 128 && DV == 128 && !aligned16(state)) return GDN2_ERR_MISALIGNED;
+  if (DK == 128 && DV == 128 && (!aligned16(state) || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(g) ||
+                                 !aligned16(b) || !aligned16(w) || !aligned16(o)))
+    return GDN2_ERR_MISALIGNED;                            // bulk copies and 16-byte loads on this path
   return launch_decode(q, k, v, g, b, w, state, o, (int)B, (int)n, (int)H, (int)HK, (int)DK, (int)DV, in_batch_stride,
                        o_batch_stride, scale, dtype, static_cast<cudaStream_t>(stream));
 }

@@ -72,14 +72,18 @@ struct alignas(128) BlockedSmem {
   float tile[2][kTileFloats];         // the state of two (batch, head) tiles
   Tables tab[2];                      // coefficient tables of two consecutive steps
   float part[4][64];                  // per 32-channel group: partial sums of the 64 pair entries
+  // one step's token vectors as they lie in memory: q, k, b, v, w rows of D elements (up to 4 bytes each), then g
+  alignas(16) unsigned char stage[6 * NB * D * 4];
   uint64_t tile_full[2], tile_done[2];   // copy thread -> sweep warps (bytes landed); sweep warps -> copy thread
   uint64_t tab_full[2], tab_empty[2];    // table warps -> sweep warps; sweep warps -> table warps
+  uint64_t o_full[2], o_free[2];         // sweep warps -> output thread (rows staged); output thread -> sweep warps
   int abort_flag;
+  alignas(16) unsigned char ostage[2][NB * D * 4];   // a step's output rows [token][value channel] on their way out
 };
 
 constexpr int kSweepThreads = 256;    // warps 0..7
 constexpr int kTableThreads = 128;    // warps 8..11
-constexpr int kAllThreads = kSweepThreads + kTableThreads + 32;   // + warp 12: one thread drives the bulk copies
+constexpr int kAllThreads = kSweepThreads + kTableThreads + 64;   // + warp 12: one thread drives the state copies; warp 13: one thread sends the outputs
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc::smem_u32(bar)) : "memory");
@@ -106,7 +110,7 @@ __device__ __forceinline__ bool table_sync_or(bool pred) {
   return r != 0;
 }
 
-enum : uint32_t { kWaitTile = 0x10000u, kWaitTab = 0x20000u, kWaitEmpty = 0x40000u, kWaitDone = 0x80000u };
+enum : uint32_t { kWaitTile = 0x10000u, kWaitTab = 0x20000u, kWaitEmpty = 0x40000u, kWaitDone = 0x80000u, kWaitOut = 0x100000u };
 
 template <typename T>
 __global__ void __launch_bounds__(kAllThreads, 1)
@@ -124,13 +128,36 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
       tc::mbar_init(&s.tile_done[i], kSweepThreads / 32);     // one arrival per warp
       tc::mbar_init(&s.tab_full[i], kTableThreads / 32);
       tc::mbar_init(&s.tab_empty[i], kSweepThreads / 32);
+      tc::mbar_init(&s.o_full[i], kSweepThreads / 32);
+      tc::mbar_init(&s.o_free[i], 1);
     }
     s.abort_flag = 0;
     tc::mbar_init_fence();
   }
   __syncthreads();
 
-  if (wid == 12) {
+  if (wid == 13) {
+    // =============================== output thread: a step's rows leave as bulk copies ==========
+    // (256-byte rows for 16-bit outputs: eight scattered 2-byte stores per lane of the sweep warps otherwise)
+    if (lane == 0) {
+      const int spt = (n + NB - 1) / NB;
+      const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+      const int total_steps = my_tiles * spt;
+      for (int step = 0; step < total_steps; ++step) {
+        const int tile = blockIdx.x + (step / spt) * gridDim.x, t0 = (step % spt) * NB;
+        const int ib = tile / H, ih = tile % H;
+        const int nb = min(NB, n - t0);
+        if (!tc::mbar_wait(&s.o_full[step & 1], (step >> 1) & 1, &s.abort_flag, status, kWaitOut)) break;
+        const T* src = reinterpret_cast<const T*>(s.ostage[step & 1]);
+        for (int t = 0; t < nb; ++t)
+          tc::bulk_s2g(o + (((size_t)ib * o_bs + (t0 + t)) * H + ih) * D, src + t * D, D * sizeof(T));
+        tc::bulk_commit();
+        tc::bulk_wait_read_all();                        // the staging rows may be overwritten
+        mbar_arrive(&s.o_free[step & 1]);
+      }
+      tc::bulk_wait_all();
+    }
+  } else if (wid == 12) {
     // =============================== copy thread: tiles in, tiles out ==========================
     if (lane == 0) {
       auto load_tile = [&](int tile, int buf) {          // 8 bulk copies of 16 rows each
@@ -163,22 +190,63 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     // =============================== table warps: thread = key / value channel =================
     const int c = tid - kSweepThreads;
     const int pw_ = wid - 8;                             // 32-channel group
-    int step = 0;
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-      const int ib = tile / H, ih = tile % H;
-      const int ihk = ih / (H / HK);                     // the key head this value head reads q, k, b, g from
-      for (int t0 = 0; t0 < n; t0 += NB, ++step) {
+    const int spt = (n + NB - 1) / NB;                   // steps per tile
+    const int my_tiles = blockIdx.x < ntiles ? (ntiles - blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+    const int total_steps = my_tiles * spt;
+    // A step's token vectors are 8 rows of D elements per tensor, contiguous per row: the 128 threads fetch them
+    // as 16-byte pieces (CH pieces per thread and tensor, two for g), ONE STEP AHEAD, into registers; at the
+    // top of a step the pieces go to the staging buffer and every thread reads its own channel from there.
+    constexpr int CH = sizeof(T) / 2;                    // 16-byte pieces per thread: 8 rows x D x sizeof(T) / 16 / 128
+    constexpr int kRowPieces = D * (int)sizeof(T) / 16;  // pieces per row
+    uint4 ldT[5][CH], ldG[2];
+    auto issue_loads = [&](int pstep) {
+      const int ptile = blockIdx.x + (pstep / spt) * gridDim.x, pt0 = (pstep % spt) * NB;
+      const int pib = ptile / H, pih = ptile % H, pihk = pih / (H / HK);
+      const int pnb = min(NB, n - pt0);
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int e = c + kTableThreads * j, tokr = e / kRowPieces, within = e % kRowPieces;
+        const int tt = pt0 + (tokr < pnb ? tokr : pnb - 1);                 // padding tokens re-read the last real one
+        const size_t rowk = (((size_t)pib * in_bs + tt) * HK + pihk) * D, rowv = (((size_t)pib * in_bs + tt) * H + pih) * D;
+        ldT[0][j] = __ldg(reinterpret_cast<const uint4*>(q + rowk) + within);
+        ldT[1][j] = __ldg(reinterpret_cast<const uint4*>(k + rowk) + within);
+        ldT[2][j] = __ldg(reinterpret_cast<const uint4*>(b + rowk) + within);
+        ldT[3][j] = __ldg(reinterpret_cast<const uint4*>(v + rowv) + within);
+        ldT[4][j] = __ldg(reinterpret_cast<const uint4*>(w + rowv) + within);
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int e = c + kTableThreads * j, tokr = e / (D / 4), within = e % (D / 4);
+        const int tt = pt0 + (tokr < pnb ? tokr : pnb - 1);
+        ldG[j] = __ldg(reinterpret_cast<const uint4*>(g + (((size_t)pib * in_bs + tt) * HK + pihk) * D) + within);
+      }
+    };
+    T* stT = reinterpret_cast<T*>(s.stage);                                // [5][NB][D]
+    float* stG = reinterpret_cast<float*>(s.stage + 5 * NB * D * sizeof(T));   // [NB][D]
+    if (total_steps > 0) issue_loads(0);
+    for (int step = 0; step < total_steps; ++step) {
+      {
+        const int t0 = (step % spt) * NB;
         const int nb = min(NB, n - t0);
         Tables& tb = s.tab[step & 1];
-        // all 48 loads of the step are issued before any is used (padding tokens re-read the last real one)
+        // every thread has read the previous step's staging buffer (two table barriers lie in between)
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+#pragma unroll
+          for (int x = 0; x < 5; ++x)
+            reinterpret_cast<uint4*>(stT + (size_t)x * NB * D)[c + kTableThreads * j] = ldT[x][j];
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) reinterpret_cast<uint4*>(stG)[c + kTableThreads * j] = ldG[j];
+        if (step + 1 < total_steps) issue_loads(step + 1);
+        table_sync();
         float graw[NB];
         T kraw[NB], braw[NB], qraw[NB], wraw[NB], vraw[NB];
 #pragma unroll
         for (int t = 0; t < NB; ++t) {
-          const int tt = t < nb ? t : nb - 1;
-          const size_t tok = (((size_t)ib * in_bs + (t0 + tt)) * H + ih) * D + c;
-          const size_t tokk = (((size_t)ib * in_bs + (t0 + tt)) * HK + ihk) * D + c;
-          graw[t] = g[tokk]; kraw[t] = k[tokk]; braw[t] = b[tokk]; qraw[t] = q[tokk]; wraw[t] = w[tok]; vraw[t] = v[tok];
+          graw[t] = stG[t * D + c];
+          qraw[t] = stT[(0 * NB + t) * D + c]; kraw[t] = stT[(1 * NB + t) * D + c]; braw[t] = stT[(2 * NB + t) * D + c];
+          vraw[t] = stT[(3 * NB + t) * D + c]; wraw[t] = stT[(4 * NB + t) * D + c];
         }
         float G[NB], kk[NB], bk[NB], qs[NB], wvv[NB];
         float run = 0.f;
@@ -266,7 +334,6 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
     int it = 0, step = 0;
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ++it) {
       const int buf = it & 1;
-      const int ib = tile / H, ih = tile % H;
       float* S = s.tile[buf];
       bool ok = true;
       for (int t0 = 0; t0 < n; t0 += NB, ++step) {
@@ -274,6 +341,7 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         const Tables& tb = s.tab[step & 1];
         ok = tc::mbar_wait(&s.tab_full[step & 1], (step >> 1) & 1, &s.abort_flag, status, kWaitTab);
         if (ok && t0 == 0) ok = tc::mbar_wait(&s.tile_full[buf], (it >> 1) & 1, &s.abort_flag, status, kWaitTile);
+        if (ok) ok = tc::mbar_wait(&s.o_free[step & 1], ((step >> 1) & 1) ^ 1, &s.abort_flag, status, kWaitOut);
         ok = __all_sync(0xffffffffu, ok);                // the warp leaves together: what follows uses full-warp shuffles
         if (!ok) break;
 
@@ -289,7 +357,7 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         }
         const float* Srow = S + rgl * kGroupFloats + col0;
         const int cr0 = 17 * rgl;
-#pragma unroll 2
+#pragma unroll                             // all 16 rows: the loads of later rows are scheduled under the FMAs of earlier ones
         for (int i = 0; i < 16; ++i) {
           const float4 sv = *reinterpret_cast<const float4*>(Srow + i * D);
           const float2 sd[4] = {make_float2(sv.x, sv.x), make_float2(sv.y, sv.y), make_float2(sv.z, sv.z),
@@ -368,9 +436,11 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
             float ov = pv[t];
 #pragma unroll
             for (int sx = 0; sx <= t; ++sx) ov = fmaf(arow[sx], u[sx], ov);
-            if (t < nb) o[(((size_t)ib * o_bs + (t0 + t)) * H + ih) * D + mycol] = from_f32<T>(ov);
+            reinterpret_cast<T*>(s.ostage[step & 1])[t * D + mycol] = from_f32<T>(ov);
           }
         }
+        tc::fence_async_smem();                          // the staged rows are read by the bulk store
+        warp_arrive(&s.o_full[step & 1], lane);
         // gather u of the thread's four columns from the lanes that share cq (rgl bits 0 and 1 = lane bits 2, 3)
         //      and pair them over tokens: up[tp][c] = (u_{2tp}, u_{2tp+1}) of column col0 + c
         float2 up[4][4];

@@ -72,7 +72,8 @@ int gdn2_last_cuda_error(void);
 /*
  * n-token recurrent decode; `state` is read once, updated in place and written once.
  *   q,k,b [B,n,HK,DK]  v,w [B,n,H,DV]  g [B,n,HK,DK] fp32  state [B,H,DK,DV] fp32  o [B,n,H,DV]
- * n = 1 is the single-token step. Supported: DK <= 256, any DV >= 1, n >= 1.
+ * n = 1 is the single-token step. Supported: DK <= 256, any DV >= 1, n >= 1. With DK = DV = 128 (the fast
+ * kernels: 16-byte loads and bulk copies) every pointer must be 16-byte aligned, else GDN2_ERR_MISALIGNED.
  * Replaces decode_step_kernel / decode_multi_kernel and the device branch of gdn2_decode and
  * gdn2_decode_step (gdn2/inference.py:61-153, 199-303, 306-353, 156-196).
  */
