@@ -10,12 +10,15 @@
 // o = scale S^T q with the sums regrouped: two sweeps over the state tile with 64 and 36 independent
 // accumulation chains per thread instead of 2 n sweeps that each wait for a cross-thread reduction.
 //
-// Persistent blocks, one per SM, walk over the (batch, head) tiles with three kinds of warps:
+// Persistent blocks, one per SM, walk over the (batch, head) tiles with four kinds of warps:
 //   * one copy thread brings a tile's 64 KiB of fp32 state into shared memory by bulk copies (TMA) two
 //     tiles ahead and sends the updated tile back the same way: HBM traffic is the state once in, once
 //     out, and no compute thread ever waits on a global load of it;
-//   * four table warps (thread = channel) read the token vectors of the next step and build its
-//     coefficient tables and the 8 x 8 pair matrices while the current step is swept;
+//   * one output thread sends each step's output rows, staged in shared memory by the sweep warps, as one
+//     bulk copy per token row;
+//   * four table warps (thread = channel) fetch the token vectors a step ahead as 16-byte pieces, pass them
+//     through a staging buffer to read their own channel, and build the step's coefficient tables and the
+//     8 x 8 pair matrices while the current step is swept;
 //   * eight sweep warps do the two sweeps in place: warp w owns value columns 16w .. 16w+15, lane
 //     (rgl = lane >> 2, cq = lane & 3) columns 16w + 4cq .. +3 of key rows 16 rgl .. 16 rgl + 15.
 // Hand-offs are mbarriers with bounded waits.
