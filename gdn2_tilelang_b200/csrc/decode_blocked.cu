@@ -79,7 +79,7 @@ struct alignas(128) BlockedSmem {
   alignas(16) unsigned char stage[6 * NB * D * 4];
   uint64_t tile_full[2], tile_done[2];   // copy thread -> sweep warps (bytes landed); sweep warps -> copy thread
   uint64_t tab_full[2], tab_empty[2];    // table warps -> sweep warps; sweep warps -> table warps
-  uint64_t o_full[2], o_free[2];         // sweep warps -> output thread (rows staged); output thread -> sweep warps
+  uint64_t o_full[2];                    // sweep warps -> output thread (a step's rows are staged)
   int abort_flag;
   alignas(16) unsigned char ostage[2][NB * D * 4];   // a step's output rows [token][value channel] on their way out
 };
@@ -113,6 +113,24 @@ __device__ __forceinline__ bool table_sync_or(bool pred) {
   return r != 0;
 }
 
+// Bounded wait for hand-offs that have thousands of cycles of slack: the polling thread sleeps between probes
+// instead of competing with the sweep warps for issue slots.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint32_t* status_word, uint32_t code) {
+  if (tc::mbar_try_wait(bar, parity)) return true;
+  const long long t_begin = clock64();
+  while (true) {
+    __nanosleep(128);
+    if (tc::mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t_begin > tc::kWaitCycles) {
+      *abort_flag = 1;
+      atomicOr(status_word, code);
+      return false;
+    }
+  }
+}
+
 enum : uint32_t { kWaitTile = 0x10000u, kWaitTab = 0x20000u, kWaitEmpty = 0x40000u, kWaitDone = 0x80000u, kWaitOut = 0x100000u };
 
 template <typename T>
@@ -130,9 +148,11 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
       tc::mbar_init(&s.tile_full[i], 1);
       tc::mbar_init(&s.tile_done[i], kSweepThreads / 32);     // one arrival per warp
       tc::mbar_init(&s.tab_full[i], kTableThreads / 32);
-      tc::mbar_init(&s.tab_empty[i], kSweepThreads / 32);
+      // a table buffer is free when the eight sweep warps have finished its step AND the output thread has sent
+      // the step's rows: the tables of step k + 2 are then built after the staging rows of step k were read, and
+      // the sweep warps (which wait for those tables) may overwrite the rows without a hand-off of their own
+      tc::mbar_init(&s.tab_empty[i], kSweepThreads / 32 + 1);
       tc::mbar_init(&s.o_full[i], kSweepThreads / 32);
-      tc::mbar_init(&s.o_free[i], 1);
     }
     s.abort_flag = 0;
     tc::mbar_init_fence();
@@ -150,13 +170,13 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         const int tile = blockIdx.x + (step / spt) * gridDim.x, t0 = (step % spt) * NB;
         const int ib = tile / H, ih = tile % H;
         const int nb = min(NB, n - t0);
-        if (!tc::mbar_wait(&s.o_full[step & 1], (step >> 1) & 1, &s.abort_flag, status, kWaitOut)) break;
+        if (!mbar_wait_relaxed(&s.o_full[step & 1], (step >> 1) & 1, &s.abort_flag, status, kWaitOut)) break;
         const T* src = reinterpret_cast<const T*>(s.ostage[step & 1]);
         for (int t = 0; t < nb; ++t)
           tc::bulk_s2g(o + (((size_t)ib * o_bs + (t0 + t)) * H + ih) * D, src + t * D, D * sizeof(T));
         tc::bulk_commit();
         tc::bulk_wait_read_all();                        // the staging rows may be overwritten
-        mbar_arrive(&s.o_free[step & 1]);
+        mbar_arrive(&s.tab_empty[step & 1]);
       }
       tc::bulk_wait_all();
     }
@@ -176,7 +196,7 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
       int it = 0;
       for (int tile = first; tile < ntiles; tile += stride, ++it) {
         const int buf = it & 1;
-        if (!tc::mbar_wait(&s.tile_done[buf], (it >> 1) & 1, &s.abort_flag, status, kWaitDone)) break;
+        if (!mbar_wait_relaxed(&s.tile_done[buf], (it >> 1) & 1, &s.abort_flag, status, kWaitDone)) break;
         float* dst = state + (size_t)tile * D * D;
 #pragma unroll
         for (int gidx = 0; gidx < 8; ++gidx)
@@ -264,7 +284,9 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
           G[t] = run;                                    // log2 of A_t
         }
         // the sweep warps have finished with this table buffer (two steps ago)
-        const bool okw = tc::mbar_wait(&s.tab_empty[step & 1], ((step >> 1) & 1) ^ 1, &s.abort_flag, status, kWaitEmpty);
+        // (one warp polls, with pauses; the other three sleep at the barrier below)
+        bool okw = true;
+        if (wid == 8) okw = mbar_wait_relaxed(&s.tab_empty[step & 1], ((step >> 1) & 1) ^ 1, &s.abort_flag, status, kWaitEmpty);
         // uniform over the table warps; it also orders this step after the reads of the previous step's partial sums
         if (table_sync_or(!okw)) break;
         {
@@ -344,7 +366,6 @@ decode_blocked_kernel(const T* __restrict__ q, const T* __restrict__ k, const T*
         const Tables& tb = s.tab[step & 1];
         ok = tc::mbar_wait(&s.tab_full[step & 1], (step >> 1) & 1, &s.abort_flag, status, kWaitTab);
         if (ok && t0 == 0) ok = tc::mbar_wait(&s.tile_full[buf], (it >> 1) & 1, &s.abort_flag, status, kWaitTile);
-        if (ok) ok = tc::mbar_wait(&s.o_free[step & 1], ((step >> 1) & 1) ^ 1, &s.abort_flag, status, kWaitOut);
         ok = __all_sync(0xffffffffu, ok);                // the warp leaves together: what follows uses full-warp shuffles
         if (!ok) break;
 
