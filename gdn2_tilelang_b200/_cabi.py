@@ -352,10 +352,20 @@ class NativeKernels:
             raise GDN2KernelError(f"device status word = {detail.value:#x}: "
                                   f"{self.lib.gdn2_status_string(rc).decode()}")
 
+    @staticmethod
+    def layer_front_updates_cache_itself(proj, offsets, DK, DV, K) -> bool:
+        """True when ``gdn2_layer_front`` writes the new convolution cache from the kernel that reads the old one
+        (its one-token form: 16-bit storage, DK = DV = 128, four taps, fewer than 8 tokens), so that for ONE token
+        the new cache may be the old cache's own memory."""
+        return (proj.dtype in (torch.bfloat16, torch.float16) and DK == 128 and DV == 128 and K == 4
+                and proj.shape[1] < 8 and proj.shape[2] % 4 == 0 and all(o % 4 == 0 for o in offsets))
+
     def layer_front(self, proj, offsets, conv_state, conv_weight, conv_bias, A_log, dt_bias, H, HK, DK, DV, K,
-                    erase_scale, want_conv_state):
+                    erase_scale, want_conv_state, conv_out=None):
         """Fused pre-processing of the layer: ``proj [B, S, NP]`` -> ``(q, k, v, g, b, w, new_conv_state)``.
-        ``offsets`` = columns of the q, k, v, b, w, f projections inside ``proj``."""
+        ``offsets`` = columns of the q, k, v, b, w, f projections inside ``proj``. ``conv_out``: where the new
+        convolution cache goes instead of a fresh tensor; it may be ``conv_state`` itself only for a single token
+        and only when ``layer_front_updates_cache_itself`` holds."""
         _require_cuda(proj)
         B, S, NP = proj.shape
         dt, dev = proj.dtype, proj.device
@@ -365,8 +375,16 @@ class NativeKernels:
         v = torch.empty(B, S, H, DV, dtype=dt, device=dev)
         w = torch.empty_like(v)
         new_conv = None
+        fused_tail = self.layer_front_updates_cache_itself(proj, offsets, DK, DV, K)
         if K > 1 and want_conv_state:
-            new_conv = torch.empty(B, 2 * HK * DK + H * DV, K - 1, dtype=dt, device=dev)
+            if conv_out is not None:
+                if conv_out.shape != (B, 2 * HK * DK + H * DV, K - 1) or conv_out.dtype != dt or not conv_out.is_contiguous():
+                    raise ValueError("conv_out must be a contiguous [B, 2*HK*DK + H*DV, K-1] tensor of the input dtype")
+                if conv_state is not None and conv_out.data_ptr() == conv_state.data_ptr() and not (fused_tail and S == 1):
+                    raise ValueError("the convolution cache can be updated in place only for one token on the fused path")
+                new_conv = conv_out
+            else:
+                new_conv = torch.empty(B, 2 * HK * DK + H * DV, K - 1, dtype=dt, device=dev)
         ptr = lambda t: None if t is None else t.data_ptr()
         a = LayerFrontArgs(ptr(proj), ptr(conv_state), ptr(conv_weight), ptr(conv_bias), ptr(A_log), ptr(dt_bias),
                            ptr(q), ptr(k), ptr(v), ptr(g), ptr(b), ptr(w), ptr(new_conv),
@@ -374,7 +392,7 @@ class NativeKernels:
         with torch.cuda.device(dev):
             rc = self.lib.gdn2_layer_front(ctypes.byref(a), dtype_code(dt), self._stream(proj))
         _check(self.lib, rc, "gdn2_layer_front")
-        self.launches += 2 if new_conv is not None else 1
+        self.launches += 2 if (new_conv is not None and not fused_tail) else 1
         return q, k, v, g, b, w, new_conv
 
     def layer_back(self, o, proj, norm_weight, off_gate, eps):

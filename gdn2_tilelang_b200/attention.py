@@ -207,10 +207,12 @@ class GatedDeltaNet2(nn.Module):
                                             self.f_proj, self.o_gate_proj)):
             raise ValueError("projection biases are not supported (the reference layer has none)")
 
-    def _front(self, x, conv_state, cached: bool):
+    def _front(self, x, conv_state, cached: bool, update_cache_in_place: bool = False):
         """Everything before the attention kernels: ONE GEMM for the seven input projections, then one kernel
         for everything element-wise. Returns ``(q, k, v, g, b, w, new_conv_state, proj)``; the o_gate columns
-        of the projection buffer ``proj`` feed ``_back``."""
+        of the projection buffer ``proj`` feed ``_back``. ``update_cache_in_place``: for a single token, let the
+        kernel write the new convolution cache into ``conv_state`` itself where it can (the returned
+        ``new_conv_state`` is then ``conv_state``)."""
         self._check_supported(x)
         H, HK, DK, DV = self.num_heads, self.num_kv_heads, self.head_dim_k, self.head_dim_v
         w_cat, offs, cw, cb = self._fused_tables()
@@ -220,9 +222,14 @@ class GatedDeltaNet2(nn.Module):
         if cached and conv_state is not None:
             state = conv_state if conv_state.dtype == x.dtype else conv_state.to(x.dtype)
             state = state.contiguous()
-        q, k, v, g, b, w, new_conv = _cabi.kernels().layer_front(
+        K_ = _cabi.kernels()
+        conv_out = None
+        if (update_cache_in_place and state is not None and state is conv_state and x.shape[1] == 1
+                and K_.layer_front_updates_cache_itself(proj, offs[:6], DK, DV, K)):
+            conv_out = state
+        q, k, v, g, b, w, new_conv = K_.layer_front(
             proj, offs[:6], state, cw, cb, self.A_log.detach().to(x.dtype), self.dt_bias.detach().to(x.dtype).contiguous(),
-            H, HK, DK, DV, K, float(self.erase_scale), want_conv_state=True)
+            H, HK, DK, DV, K, float(self.erase_scale), want_conv_state=True, conv_out=conv_out)
         return q, k, v, g, b, w, new_conv, proj
 
     def _back(self, x, o, proj, normed_rows: int = 0):
@@ -363,8 +370,9 @@ class GraphedStep:
     def _step_in_place(self):
         layer, cache = self.layer, self.cache
         x = self.x.unsqueeze(1)
-        q, k, v, g, b, w, conv, proj = layer._front(x, cache.conv_state, cached=layer.q_conv is not None)
-        if conv is not None:
+        q, k, v, g, b, w, conv, proj = layer._front(x, cache.conv_state, cached=layer.q_conv is not None,
+                                                     update_cache_in_place=True)
+        if conv is not None and conv is not cache.conv_state:
             cache.conv_state.copy_(conv)
         o = gdn2_decode(q, k, v, g, b, w, cache.recurrent_state, scale=layer.scale)
         return layer._back(x, o, proj)[:, 0]

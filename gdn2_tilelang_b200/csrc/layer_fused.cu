@@ -167,9 +167,11 @@ __device__ __forceinline__ void store4(T* p, const float (&o)[4]) {
 }
 
 // convolution + SiLU of 4 adjacent channels: projection columns col.., convolved-channel index cch..
+// `tail` (or null): where the new convolution cache of these channels goes, [4 channels][K - 1]; the last three taps
+// of the LAST token are exactly its contents.
 template <typename T>
 __device__ __forceinline__ void conv4(const T* P, const T* cs, const T* cw, const T* cb, int64_t b, int t, int S, int NP,
-                                      int col, int cch, int CC, float (&y)[4]) {
+                                      int col, int cch, int CC, float (&y)[4], T* tail) {
   constexpr int K = 4;
   float wt[4][4];                                        // [channel][tap]
 #pragma unroll
@@ -190,6 +192,10 @@ __device__ __forceinline__ void conv4(const T* P, const T* cs, const T* cw, cons
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) y[i] = fmaf(wt[i][j], x[i], y[i]);
+    if (tail && j >= 1) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) tail[i * (K - 1) + (j - 1)] = from_f32<T>(x[i]);   // x came from a T: exact
+    }
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) y[i] = silu(y[i]);
@@ -218,9 +224,13 @@ layer_front_d128_kernel(gdn2_layer_front_args a) {
   const size_t tokh = ((size_t)b * S + t) * H;          // first value head of this token
   const size_t tokk = ((size_t)b * S + t) * HK + hk;    // this key head: q, k, b, g are written once per key head
 
+  // the warp of the last token also writes the new convolution cache of its channels (no separate launch)
+  T* tails = (t == S - 1 && a.new_conv_state) ? static_cast<T*>(a.new_conv_state) + (size_t)b * CC * 3 : nullptr;
   for (int which = 0; which < 2; ++which) {
     float y[4];
-    conv4(P, cs, cw, cb, b, t, S, NP, (which == 0 ? (int)a.off_q : (int)a.off_k) + hk * DK + c, which * Cqk + hk * DK + c, CC, y);
+    const int cchq = which * Cqk + hk * DK + c;
+    conv4(P, cs, cw, cb, b, t, S, NP, (which == 0 ? (int)a.off_q : (int)a.off_k) + hk * DK + c, cchq, CC, y,
+          tails ? tails + (size_t)cchq * 3 : nullptr);
     const float ss = warp_sum(y[0] * y[0] + y[1] * y[1] + y[2] * y[2] + y[3] * y[3]);
     const float inv = inv_norm(ss);
 #pragma unroll
@@ -245,7 +255,8 @@ layer_front_d128_kernel(gdn2_layer_front_args a) {
   for (int r = 0; r < rep; ++r) {
     const int h = hk * rep + r;
     float y[4], pw[4];
-    conv4(P, cs, cw, cb, b, t, S, NP, (int)a.off_v + h * DV + c, 2 * Cqk + h * DV + c, CC, y);
+    conv4(P, cs, cw, cb, b, t, S, NP, (int)a.off_v + h * DV + c, 2 * Cqk + h * DV + c, CC, y,
+          tails ? tails + (size_t)(2 * Cqk + h * DV + c) * 3 : nullptr);
     load4(P + prow + a.off_w + h * DV + c, pw);
 #pragma unroll
     for (int i = 0; i < 4; ++i) pw[i] = sigmoidf_(pw[i]);
@@ -436,9 +447,11 @@ int launch_front_typed(const gdn2_layer_front_args& a, cudaStream_t st) {
       a.B * ((a.S + 3) / 4) * (4 * a.HK + 2 * a.H) < (int64_t)1 << 31) {
     const int64_t items4 = a.B * ((a.S + 3) / 4) * (4 * a.HK + 2 * a.H);   // prompts: a slot of four tokens per warp
     layer_front_d128x4_kernel<T><<<(unsigned)((items4 + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
-  } else if (sizeof(T) == 2 && a.DK == 128 && a.DV == 128 && a.K == 4 && aligned)
+  } else if (sizeof(T) == 2 && a.DK == 128 && a.DV == 128 && a.K == 4 && aligned) {
     layer_front_d128_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
-  else
+    GDN2_CUDA_TRY(cudaGetLastError());
+    return GDN2_OK;                                          // this form writes the new convolution cache itself
+  } else
     layer_front_kernel<T><<<(unsigned)((items + kWarps - 1) / kWarps), 32 * kWarps, 0, st>>>(a);
   GDN2_CUDA_TRY(cudaGetLastError());
   if (a.K > 1 && a.new_conv_state) {

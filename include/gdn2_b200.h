@@ -257,7 +257,10 @@ int gdn2_prefill_static(const void* q, const void* k, const void* v, const float
  *   b = erase_scale * sigmoid(proj_b)  w = sigmoid(proj_w)  g = -exp(A_log[hk]) * softplus(proj_f + dt_bias[hk]),
  *   conv_state [B, 2*HK*DK + H*DV, K-1] (or NULL = zeros)
  *   supplies the columns before the first token; new_conv_state (or NULL) receives the last K-1
- *   pre-convolution columns. A_log [HK] and dt_bias [HK, DK] are in `dtype`.
+ *   pre-convolution columns. new_conv_state may be conv_state itself (the cache updated in place) only for
+ *   S = 1 with 16-bit `dtype`, DK = DV = 128, K = 4 and NP and the column offsets multiples of 4: there one
+ *   kernel reads a channel's old columns and writes its new ones from the same thread. In every other case the
+ *   two must not overlap. A_log [HK] and dt_bias [HK, DK] are in `dtype`.
  * gdn2_layer_back writes out [B*S, H*DV] = rmsnorm_per_head(o) * norm_weight[DV] * silu(proj_o_gate).
  * Replaces the operator chains of _ShortConv, F.normalize, the gate expressions, repeat_interleave and
  * _GatedRMSNorm (gdn2/attention.py:186-229, 290-297, 323-340, 352-354).

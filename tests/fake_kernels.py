@@ -58,8 +58,12 @@ class OracleKernels:
 
     # -- the layer's element-wise stages, restated with torch operators (gdn2/attention.py:186-229, 290-297 of
     #    the reference project): what gdn2_layer_front / gdn2_layer_back compute on the device
+    @staticmethod
+    def layer_front_updates_cache_itself(proj, offsets, DK, DV, K):
+        return False
+
     def layer_front(self, proj, offsets, conv_state, conv_weight, conv_bias, A_log, dt_bias, H, HK, DK, DV, K,
-                    erase_scale, want_conv_state):
+                    erase_scale, want_conv_state, conv_out=None):
         return layer_front_chain(proj, offsets, conv_state, conv_weight, conv_bias, A_log, dt_bias, H, HK, DK, DV, K,
                                  erase_scale)
 
