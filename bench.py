@@ -52,8 +52,8 @@ FALLBACK_HBM_GBS = 6650.0
 
 # dram__bytes_read.sum + dram__bytes_write.sum per chunk-head (64 tokens of one head), from the ncu captures
 # in the committed ncu summaries (1024 chunk-heads per launch): traffic grows in proportion to the chunk-heads
-NCU_DRAM_BYTES_PER_CHUNK_HEAD = {"chunk_prep": (117.602560e6 + 39.747328e6) / 1024,
-                                 "prefill_scan": (77.114112e6 + 5.137408e6) / 1024}
+NCU_DRAM_BYTES_PER_CHUNK_HEAD = {"chunk_prep": (117.523456e6 + 38.075648e6) / 1024,
+                                 "prefill_scan": (77.139968e6 + 4.598784e6 + 37.224704e6 + 0.046848e6) / 1024}   # first + redo pass
 
 
 def measured_peaks():
