@@ -611,6 +611,7 @@ def _gqa_inputs(B, S, H, HK, D, seed, dtype=torch.bfloat16):
 
 
 @pytest.mark.parametrize("H,HK,D,path", [(4, 2, 128, "tcgen05"), (6, 2, 128, "tcgen05"), (4, 1, 128, "tcgen05"),
+                                         (2, 1, 128, "tcgen05"), (16, 8, 128, "tcgen05"),
                                          (4, 2, 128, "simt"), (6, 3, 64, "simt")])
 def test_grouped_query_heads_chunkwise(K, H, HK, D, path):
     """Fewer key heads than value heads through the chunkwise kernels: bit-equal to the same call on repeated key
