@@ -413,6 +413,8 @@ class NativeKernels:
         kernel that gave up on a bounded wait raises at the call that launched it (debugging aid; off by default
         because it serialises the host with the device)."""
         if os.environ.get("GDN2_B200_CHECK_STATUS", "0") not in ("", "0"):
+            if torch.cuda.is_current_stream_capturing():
+                return                   # a captured stream cannot be synchronised; the replaying caller checks
             self.check_device_status(device)
 
     def workspace_layout(self, B, S, H, DK, DV, dtype, path=None, HK=None) -> dict:
