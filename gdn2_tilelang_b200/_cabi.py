@@ -38,6 +38,7 @@ SIGNATURES = {
     "gdn2_prefill_workspace_bytes": (_sz, [_i64] * 6 + [_int, _int]),
     "gdn2_prefill_scan_segments": (_int, [_i64] * 5 + [_int, _int]),
     "gdn2_prefill_scan_launches": (_int, [_i64] * 5 + [_int, _int]),
+    "gdn2_prefill_scan_part": (_int, [_vp, _sz, _vp, _vp, _vp] + [_i64] * 7 + [_int, _int, _int, _vp]),
     "gdn2_prefill_workspace_layout": (_int, [_i64] * 6 + [_int, _int, ctypes.POINTER(ctypes.c_int64)]),
     "gdn2_chunk_prep": (_int, [_vp] * 7 + [_sz] + [_i64] * 7 + [_f32, _int, _int, _vp]),
     "gdn2_prefill_scan": (_int, [_vp, _sz, _vp, _vp, _vp, _vp] + [_i64] * 7 + [_int, _int, _vp]),
@@ -224,8 +225,14 @@ class NativeKernels:
         return self.resolved_path(DK, DV, dtype) in (PATH_TCGEN05, PATH_TCGEN05_SERIAL)
 
     def chunk_forward(self, q, k, v, g, b, w, scale: float, initial_state=None, want_chunk_states=False,
-                      path=None, out=None, out_batch_stride=None, gated_norm=None):
+                      path=None, out=None, out_batch_stride=None, gated_norm=None, then_with_state=None):
         """Whole chunks only (``S % 64 == 0``). Returns ``(o, final_state, chunk_states | None)``.
+
+        ``then_with_state``: a callable ``f(final_state)`` for work that needs only the final state (the decode
+        of a ragged tail, which updates it in place and writes other rows of ``out``). It is always called, after
+        the scan; when the scan runs as a cut scan it is called on a side stream between the scan's two parts
+        (``gdn2_prefill_scan_part``), so that it runs beside the correction pass, and the caller's stream waits
+        for it before this method returns.
 
         ``out`` may be a preallocated ``[B, S_total >= S, H, DV]`` tensor whose first ``S`` tokens
         per batch entry receive the result (``out_batch_stride`` = its token stride).
@@ -292,7 +299,24 @@ class NativeKernels:
                     ev.record(main)
                     side.wait_event(ev)
                     scan_stream = side
-                if gated_norm is None:
+                two_parts = (then_with_state is not None and gated_norm is None and hs is None and nseg == 1
+                             and self.lib.gdn2_prefill_scan_launches(B, S_i, H, DK, DV, code, p) > 1)
+                if two_parts:
+                    part = lambda which: self.lib.gdn2_prefill_scan_part(       # noqa: E731
+                        ws_i.data_ptr(), nb_i, state_ptr, out.data_ptr(), final_state.data_ptr(), B, S_i, H, HK, DK, DV,
+                        out_batch_stride, code, p, which, main.cuda_stream)
+                    rc = part(1)
+                    _check(self.lib, rc, "gdn2_prefill_scan_part")
+                    tail_stream = self._side_stream(dev)
+                    ready = torch.cuda.Event()
+                    ready.record(main)
+                    tail_stream.wait_event(ready)
+                    with torch.cuda.stream(tail_stream):
+                        then_with_state(final_state)
+                    then_with_state = None
+                    rc = part(2)
+                    main.wait_stream(tail_stream)
+                elif gated_norm is None:
                     rc = self.lib.gdn2_prefill_scan(ws_i.data_ptr(), nb_i, state_ptr, out.data_ptr() + t0 * H * DV * esz,
                                                     states[i].data_ptr(), None if hs is None else hs.data_ptr(),
                                                     B, S_i, H, HK, DK, DV, out_batch_stride, code, p, scan_stream.cuda_stream)
@@ -315,6 +339,8 @@ class NativeKernels:
                 main.wait_stream(side)             # from here on the caller's stream is ordered after every scan
             del scratch                            # ... so only now may the allocator hand these blocks out again
         self.launches += launched
+        if then_with_state is not None:
+            then_with_state(final_state)
         return out, final_state, hs
 
     def chunk_output(self, q, k, v, g, b, w, scale: float, chunk_states, path=None):

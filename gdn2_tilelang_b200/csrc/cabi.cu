@@ -183,9 +183,31 @@ int gdn2_chunk_prep(const void* q, const void* k, const void* v, const float* g,
   return launch_prep_simt(q, k, v, g, b, w, L, P, (int)B, (int)S, (int)H, (int)HK, in_batch_stride, scale, dtype, false, st);
 }
 
+namespace {
+int prefill_scan_impl(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
+                      float* final_state, float* chunk_states, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
+                      int64_t DV, int64_t o_batch_stride, int dtype, int path, int part, void* stream);
+}
+
 int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
                       float* final_state, float* chunk_states, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
                       int64_t DV, int64_t o_batch_stride, int dtype, int path, void* stream) {
+  return prefill_scan_impl(workspace, workspace_bytes, initial_state, o, final_state, chunk_states, B, S, H, HK, DK, DV,
+                           o_batch_stride, dtype, path, 0, stream);
+}
+
+int gdn2_prefill_scan_part(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
+                           float* final_state, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV,
+                           int64_t o_batch_stride, int dtype, int path, int part, void* stream) {
+  if (part != 1 && part != 2) return GDN2_ERR_BAD_SHAPE;
+  return prefill_scan_impl(workspace, workspace_bytes, initial_state, o, final_state, nullptr, B, S, H, HK, DK, DV,
+                           o_batch_stride, dtype, path, part, stream);
+}
+
+namespace {
+int prefill_scan_impl(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
+                      float* final_state, float* chunk_states, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
+                      int64_t DV, int64_t o_batch_stride, int dtype, int path, int part, void* stream) {
   if (!workspace || !o) return GDN2_ERR_NULL_POINTER;
   int rc = check_prefill_shape(B, S, H, HK, DK, DV, dtype);
   if (rc != GDN2_OK) return rc;
@@ -201,10 +223,12 @@ int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (p == GDN2_PATH_TCGEN05)
     return launch_scan_tc(L, P, initial_state, o, final_state, chunk_states, (int)B, (int)S, (int)H,
-                          o_batch_stride, nullptr, st);
+                          o_batch_stride, nullptr, part, st);
+  if (part == 2) return GDN2_OK;                           // the exact family's scan is one launch
   return launch_scan_simt(L, P, initial_state, o, final_state, chunk_states, (int)B, (int)S, (int)H,
                           o_batch_stride, dtype, st);
 }
+}  // namespace
 
 int gdn2_prefill_scan_gated_norm(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
                                  float* final_state, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
@@ -227,7 +251,7 @@ int gdn2_prefill_scan_gated_norm(const void* workspace, size_t workspace_bytes, 
   const WsLayout L = layout_for(B, S, H, HK, DK, DV, p, seg);
   if (workspace_bytes < L.total) return GDN2_ERR_WORKSPACE;
   const WsPtrs P = ws_pointers(const_cast<void*>(workspace), L);
-  return launch_scan_tc(L, P, initial_state, o, final_state, nullptr, (int)B, (int)S, (int)H, o_batch_stride, norm,
+  return launch_scan_tc(L, P, initial_state, o, final_state, nullptr, (int)B, (int)S, (int)H, o_batch_stride, norm, 0,
                         static_cast<cudaStream_t>(stream));
 }
 

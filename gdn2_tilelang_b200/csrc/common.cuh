@@ -204,7 +204,7 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
                    const WsLayout& L, const WsPtrs& P, int B, int S, int H, int HK, int64_t in_bs, float scale,
                    cudaStream_t st);
 int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o, float* sT, float* hs,
-                   int B, int S, int H, int64_t o_bs, const gdn2_gated_norm* norm, cudaStream_t st);
+                   int B, int S, int H, int64_t o_bs, const gdn2_gated_norm* norm, int part, cudaStream_t st);
 int launch_output_tc(const WsLayout& L, const WsPtrs& P, const float* hs, void* o, int B, int S, int H, int64_t o_bs,
                      cudaStream_t st);
 int launch_oproj_reduce(const gdn2_oproj_reduce_args& a, int dtype, cudaStream_t st);

@@ -679,8 +679,10 @@ scan_combine_kernel(WsPtrs P, int nseg, int NC_all, int guarded, float* __restri
 
 }  // namespace
 
+// part: 0 = the whole scan; 1 = everything up to the final state (for a cut scan: decay check, first pass, chaining
+// of the segments; otherwise the whole scan); 2 = what is left (the correction pass of a cut scan, else nothing).
 int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o, float* sT, float* hs,
-                   int B, int S, int H, int64_t o_bs, const gdn2_gated_norm* gn, cudaStream_t st) {
+                   int B, int S, int H, int64_t o_bs, const gdn2_gated_norm* gn, int part, cudaStream_t st) {
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
   const size_t smem = sizeof(ScanTcSmem) + 128;
   GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -693,11 +695,18 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
   // chunk states are a by-product of the one-block-per-head walk only
   const int nseg = hs ? 1 : L.nseg;
   if (nseg <= 1) {
+    if (part == 2) return GDN2_OK;
     scan_tc_kernel<<<BH, kThreads, smem, st>>>(L, P, ScanPlan{kWhole, 1, 0}, norm, s0, ob, sT, hs, S, H, o_bs, status);
     GDN2_CUDA_TRY(cudaGetLastError());
     return GDN2_OK;
   }
   const int guarded = L.nseg_guarded ? 1 : 0;
+  if (part == 2) {
+    scan_tc_kernel<<<BH * (nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kRedo, nseg, guarded}, norm, nullptr, ob, nullptr, nullptr,
+                                                           S, H, o_bs, status);
+    GDN2_CUDA_TRY(cudaGetLastError());
+    return GDN2_OK;
+  }
   if (guarded) {
     GDN2_CUDA_TRY(cudaMemsetAsync(P.seg_mode, 0, sizeof(int), st));
     const int BK = BH / L.rep;
@@ -711,6 +720,7 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
   GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
   scan_combine_kernel<<<dim3(BH, D / kCombineCols), 256, csmem, st>>>(P, nseg, NC, guarded, sT);
   GDN2_CUDA_TRY(cudaGetLastError());
+  if (part == 1) return GDN2_OK;
   scan_tc_kernel<<<BH * (nseg - 1), kThreads, smem, st>>>(L, P, ScanPlan{kRedo, nseg, guarded}, norm, nullptr, ob, nullptr, nullptr,
                                                          S, H, o_bs, status);
   GDN2_CUDA_TRY(cudaGetLastError());

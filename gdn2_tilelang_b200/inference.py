@@ -91,11 +91,17 @@ def gdn2_prefill(q, k, v, g, b, w, state=None, scale=None, config: GDN2Config = 
         state = state.to(config.state_dtype).contiguous()
 
     o = torch.empty(B, S, H, DV, dtype=v.dtype, device=q.device)
+
+    def tail(st):                                          # the ragged tail through the decode kernel, state in place
+        K.decode(*(t[:, n_full:] for t in (q, k, v, g, b, w)), st, scale, out=o[:, n_full:])
+
     if n_full:
+        # the tail needs the final state only: a cut scan lets it run beside its correction pass
         _, state, _ = K.chunk_forward(*(t[:, :n_full] for t in (q, k, v, g, b, w)), scale, state,
-                                      out=o, out_batch_stride=S, gated_norm=gated_norm)
-    if S > n_full:
-        K.decode(*(t[:, n_full:] for t in (q, k, v, g, b, w)), state, scale, out=o[:, n_full:])
+                                      out=o, out_batch_stride=S, gated_norm=gated_norm,
+                                      then_with_state=tail if S > n_full else None)
+    elif S > n_full:
+        tail(state)
     K.maybe_check_device_status(q.device)
     return o, state
 

@@ -152,6 +152,20 @@ int gdn2_prefill_scan(const void* workspace, size_t workspace_bytes, const float
                       int64_t DV, int64_t o_batch_stride, int dtype, int path, void* stream);
 
 /*
+ * gdn2_prefill_scan (without chunk_states) in two calls, for a caller that has work which needs only the final state
+ * -- the decode of a ragged tail -- and wants it to run beside the rest of the scan on another stream:
+ *   part 1  everything up to the final state: for a cut scan the decay check, the first pass and the chaining of
+ *           the segments (final_state is complete when it ends, the outputs of the leading chunks of every
+ *           segment are not yet); for a scan that is not cut, the whole scan;
+ *   part 2  what is left: the correction pass of a cut scan (initial_state and final_state are ignored), else
+ *           nothing.
+ * Both parts take the same arguments. No counterpart in the reference.
+ */
+int gdn2_prefill_scan_part(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
+                           float* final_state, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV,
+                           int64_t o_batch_stride, int dtype, int path, int part, void* stream);
+
+/*
  * gdn2_prefill_scan with the layer's gated RMSNorm as the epilogue of the output rows:
  *   o[b,t,h,:] <- o * rsqrt(mean(o^2) + eps) * weight * silu(gate[b,t,h,:]),
  * evaluated on the rows as they leave the chip (rounded to `dtype` first, as the separate kernel would read

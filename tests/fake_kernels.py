@@ -36,7 +36,7 @@ class OracleKernels:
         return False                     # the double keeps the norm a separate stage (layer_back)
 
     def chunk_forward(self, q, k, v, g, b, w, scale, initial_state=None, want_chunk_states=False,
-                      path=None, out=None, out_batch_stride=None, gated_norm=None):
+                      path=None, out=None, out_batch_stride=None, gated_norm=None, then_with_state=None):
         self.calls.append(("chunk_forward", q.shape[1]))
         assert q.shape[1] % 64 == 0 and gated_norm is None
         q, k, v, g, b, w = _expanded(q, k, v, g, b, w)
@@ -45,6 +45,8 @@ class OracleKernels:
         if out is not None:
             out[:, : q.shape[1]].copy_(o)
             o = out
+        if then_with_state is not None:
+            then_with_state(s)
         return o, s, (res[2] if want_chunk_states else None)
 
     def chunk_output(self, q, k, v, g, b, w, scale, chunk_states, path=None):
