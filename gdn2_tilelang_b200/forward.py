@@ -45,15 +45,20 @@ def chunk_gdn2_fwd(q, k, v, g, b, w, scale, initial_state=None, output_final_sta
     state, hs = initial_state, None
     if state is not None and state.shape != (B, H, DK, DV):
         raise ValueError(f"initial_state must have shape {(B, H, DK, DV)}, got {tuple(state.shape)}")
+    def tail(st):                                     # the ragged tail through the decode kernel, state in place
+        K.decode(*(t[:, n_full:] for t in (q, k, v, g, b, w)), st, scale, out=o[:, n_full:])
+
     if n_full:
+        # the tail needs the final state only: a cut scan lets it run beside its correction pass
         _, state, hs = K.chunk_forward(*(t[:, :n_full] for t in (q, k, v, g, b, w)), scale, state,
-                                       want_chunk_states=return_chunk_states, out=o, out_batch_stride=o_bs)
-    if S > n_full:
+                                       want_chunk_states=return_chunk_states, out=o, out_batch_stride=o_bs,
+                                       then_with_state=tail if S > n_full else None)
+    elif S > n_full:
         if state is None:
             state = torch.zeros(B, H, DK, DV, dtype=torch.float32, device=q.device)
-        elif n_full == 0:
+        else:
             state = state.to(torch.float32).clone()   # never write into the caller's initial state
-        K.decode(*(t[:, n_full:] for t in (q, k, v, g, b, w)), state, scale, out=o[:, n_full:])
+        tail(state)
     K.maybe_check_device_status(q.device)
     final = state if output_final_state else None
     return (o, final, hs) if return_chunk_states else (o, final)
