@@ -132,6 +132,29 @@ def _require_cuda(*tensors):
             )
 
 
+class _on_device:
+    """``with _on_device(dev):`` makes ``dev`` the current CUDA device for the C calls inside, like
+    ``torch.cuda.device`` but without touching the driver when it already is (the usual case, and these calls sit
+    on paths where a microsecond of host time counts)."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, dev):
+        dev = torch.device(dev) if not isinstance(dev, torch.device) else dev
+        self.idx, self.prev = dev.index, -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if self.idx is not None and cur != self.idx:
+            torch.cuda.set_device(self.idx)
+            self.prev = cur
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
 def _seq_view(t: torch.Tensor):
     """(tensor, batch stride in tokens) for a ``[B,S,H,D]`` tensor whose ``[S,H,D]`` block is dense.
 
@@ -211,7 +234,7 @@ class NativeKernels:
             o, o_bs = _seq_view(out)
             if o is not out or out.dtype != v.dtype or tuple(out.shape) != (B, n, H, DV):
                 raise ValueError("`out` must be a [B,n,H,DV] view with dense [n,H,DV] blocks in v's dtype")
-        with torch.cuda.device(q.device):
+        with _on_device(q.device):
             rc = self.lib.gdn2_decode(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
                                       w.data_ptr(), state.data_ptr(), o.data_ptr(), B, n, H, HK, DK, DV, in_bs, o_bs,
                                       float(scale), code, self._stream(q))
@@ -269,7 +292,7 @@ class NativeKernels:
         NC = S // CHUNK
         nseg = 1 if want_chunk_states else self._segments(B, S, H, DK, DV, q.dtype, p)
         esz = out.element_size()
-        with torch.cuda.device(dev):
+        with _on_device(dev):
             main = torch.cuda.current_stream(dev)
             # The scan runs on only B*H thread blocks and is bound by its chunk-to-chunk chain, while the
             # chunk-local stage is chunk-parallel. With several segments, the chunk-local stage of segment i+1
@@ -355,7 +378,7 @@ class NativeKernels:
         ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
         out = torch.empty(B, S, H, DV, dtype=v.dtype, device=q.device)
         st = self._stream(q)
-        with torch.cuda.device(q.device):
+        with _on_device(q.device):
             rc = self.lib.gdn2_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
                                           w.data_ptr(), ws.data_ptr(), nbytes, B, S, H, HK, DK, DV, S, float(scale),
                                           code, p, st)
@@ -371,7 +394,7 @@ class NativeKernels:
         """Raise if any kernel on ``device`` gave up on a bounded wait since the last check."""
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         detail = ctypes.c_uint32(0)
-        with torch.cuda.device(device):
+        with _on_device(device):
             rc = self.lib.gdn2_check_device_status(torch.cuda.current_stream(device).cuda_stream,
                                                    ctypes.byref(detail))
         if rc != 0:
@@ -415,7 +438,7 @@ class NativeKernels:
         a = LayerFrontArgs(ptr(proj), ptr(conv_state), ptr(conv_weight), ptr(conv_bias), ptr(A_log), ptr(dt_bias),
                            ptr(q), ptr(k), ptr(v), ptr(g), ptr(b), ptr(w), ptr(new_conv),
                            B, S, H, HK, DK, DV, K, NP, *offsets, erase_scale)
-        with torch.cuda.device(dev):
+        with _on_device(dev):
             rc = self.lib.gdn2_layer_front(ctypes.byref(a), dtype_code(dt), self._stream(proj))
         _check(self.lib, rc, "gdn2_layer_front")
         self.launches += 2 if (new_conv is not None and not fused_tail) else 1
@@ -426,7 +449,7 @@ class NativeKernels:
         _require_cuda(o, proj)
         B, S, H, DV = o.shape
         out = torch.empty(B, S, H * DV, dtype=o.dtype, device=o.device)
-        with torch.cuda.device(o.device):
+        with _on_device(o.device):
             rc = self.lib.gdn2_layer_back(o.data_ptr(), proj.data_ptr(), norm_weight.data_ptr(), out.data_ptr(),
                                           B * S, H, DV, proj.shape[-1], off_gate, eps, dtype_code(o.dtype),
                                           self._stream(o))
@@ -461,7 +484,7 @@ class NativeKernels:
         q, k, v, g, b, w = (t.contiguous() for t in (q, k, v, g, b, w))
         nbytes = self.lib.gdn2_prefill_workspace_bytes(B, S, H, HK, DK, DV, code, p)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
-        with torch.cuda.device(q.device):
+        with _on_device(q.device):
             rc = self.lib.gdn2_chunk_prep(q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(),
                                           w.data_ptr(), ws.data_ptr(), nbytes, B, S, H, HK, DK, DV, S, float(scale),
                                           code, p, self._stream(q))
@@ -478,7 +501,7 @@ class NativeKernels:
                             None if peer_slots is None else peer_slots.data_ptr(),
                             None if peer_flags is None else peer_flags.data_ptr(), epochs.data_ptr(),
                             rows, K, weight.shape[0], rank, world, wait_cycles)
-        with torch.cuda.device(x.device):
+        with _on_device(x.device):
             rc = self.lib.gdn2_oproj_reduce(ctypes.byref(a), dtype_code(x.dtype), self._stream(x))
         _check(self.lib, rc, "gdn2_oproj_reduce")
         self.launches += 1
@@ -488,7 +511,7 @@ class NativeKernels:
         """Launch the block whose bounded wait nothing satisfies; returns how many threads gave up."""
         device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         counter = torch.zeros(1, dtype=torch.int32, device=device)
-        with torch.cuda.device(device):
+        with _on_device(device):
             rc = self.lib.gdn2_selftest_wait(limit_cycles, counter.data_ptr(),
                                              torch.cuda.current_stream(device).cuda_stream)
         _check(self.lib, rc, "gdn2_selftest_wait")
@@ -497,7 +520,7 @@ class NativeKernels:
     def selftest_mma(self, a: torch.Tensor, bt: torch.Tensor) -> torch.Tensor:
         _require_cuda(a, bt)
         out = torch.zeros(4, 128, 128, dtype=torch.float32, device=a.device)
-        with torch.cuda.device(a.device):
+        with _on_device(a.device):
             rc = self.lib.gdn2_selftest_mma(a.data_ptr(), bt.data_ptr(), out.data_ptr(), self._stream(a))
         _check(self.lib, rc, "gdn2_selftest_mma")
         return out

@@ -2,6 +2,9 @@
 // dispatch and error reporting. Nothing here allocates device memory.
 #include <cstdio>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace gdn2 {
@@ -17,9 +20,35 @@ int record_cuda_error(cudaError_t e) {
 }
 
 uint32_t* device_status_word() {
+  static void* cached[64] = {};                   // per device ordinal: the address is looked up once
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  if (dev >= 0 && dev < 64 && cached[dev]) return static_cast<uint32_t*>(cached[dev]);
   void* p = nullptr;
   if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) return nullptr;
+  if (dev >= 0 && dev < 64) cached[dev] = p;
   return static_cast<uint32_t*>(p);
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) sticks to a (kernel, device) pair: made once, not on every launch
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes) {
+  static std::mutex mu;
+  static std::unordered_map<unsigned long long, size_t> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const unsigned long long key = reinterpret_cast<unsigned long long>(kernel) ^ (static_cast<unsigned long long>(dev) << 56);
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    auto it = done.find(key);
+    if (it != done.end() && it->second >= bytes) return cudaSuccess;
+  }
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e == cudaSuccess) {
+    std::lock_guard<std::mutex> lk(mu);
+    done[key] = bytes;
+  }
+  return e;
 }
 
 int device_sm_count() {

@@ -186,6 +186,8 @@ int record_cuda_error(cudaError_t e);   // stores e for gdn2_last_cuda_error(), 
 // Device status word: kernels OR a code into it when a bounded wait runs out.
 uint32_t* device_status_word();   // device pointer for the current device (lazily initialised)
 int device_sm_count();            // streaming multiprocessors of the current device
+// raises the dynamic shared-memory limit of `kernel` to `bytes` on the current device, once per (kernel, device)
+cudaError_t ensure_dynamic_smem(const void* kernel, size_t bytes);
 
 // ---------------------------------------------------------------- launchers (one per .cu file)
 

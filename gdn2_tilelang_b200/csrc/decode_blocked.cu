@@ -518,7 +518,7 @@ template <typename T>
 int launch_decode_blocked(const T* q, const T* k, const T* v, const float* g, const T* b, const T* w, float* state,
                           T* o, int B, int n, int H, int HK, int64_t in_bs, int64_t o_bs, float scale, cudaStream_t st) {
   const size_t smem = sizeof(BlockedSmem) + 128;
-  GDN2_CUDA_TRY(cudaFuncSetAttribute(decode_blocked_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(decode_blocked_kernel<T>), smem));
   const int ntiles = B * H;
   const int sms = device_sm_count();
   const int grid = ntiles < sms ? ntiles : sms;

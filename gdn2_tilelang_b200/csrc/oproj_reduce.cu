@@ -180,7 +180,7 @@ int launch_oproj_reduce(const gdn2_oproj_reduce_args& a, int dtype, cudaStream_t
   const size_t smem = (size_t)a.rows * a.K * esz;
   const int grid = (int)(a.hidden / kCols);
   auto launch = [&](auto kern) -> int {
-    GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
     kern<<<grid, kThreads, smem, st>>>(a, device_status_word());
     GDN2_CUDA_TRY(cudaGetLastError());
     return GDN2_OK;

@@ -187,13 +187,13 @@ int launch_typed(const void* q, const void* k, const void* v, const float* g, co
   const TIn* tw = static_cast<const TIn*>(w);
   if (only_flagged) {
     auto kern = prep_simt_flagged_kernel<TIn, TW>;
-    GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
     // the tensor-core kernel has appended the flagged chunks to the list behind the flags
     const int nch = (int)L.nch;
     kern<<<nch < 296 ? nch : 296, 256, smem, st>>>(tq, tk, tv, g, tb, tw, L, P, S, H, HK, in_bs, scale);
   } else {
     auto kern = prep_simt_kernel<TIn, TW>;
-    GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
     dim3 grid(S / kChunk, B * HK);
     kern<<<grid, 256, smem, st>>>(tq, tk, tv, g, tb, tw, L, P, S, H, HK, in_bs, scale);
   }

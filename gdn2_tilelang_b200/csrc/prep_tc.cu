@@ -663,7 +663,7 @@ int launch_prep_tc(const void* q, const void* k, const void* v, const float* g, 
   using bf16 = __nv_bfloat16;
   GDN2_CUDA_TRY(cudaMemsetAsync(P.flags + 2 * (size_t)L.nch, 0, sizeof(int), st));   // length of the flagged list
   auto launch = [&](auto kern) -> int {
-    GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
     kern<<<grid, kThreads, smem, st>>>(static_cast<const bf16*>(q), static_cast<const bf16*>(k),
                                        static_cast<const bf16*>(v), g, static_cast<const bf16*>(b),
                                        static_cast<const bf16*>(w), P, S, H, HK, in_bs, scale, device_sm_count(),

@@ -171,7 +171,7 @@ int launch_scan_typed(const WsLayout& L, const WsPtrs& P, const float* s0, void*
                       int B, int S, int H, int64_t o_bs, cudaStream_t st) {
   const size_t smem = ScanSmem::bytes(L.DK);
   auto kern = scan_simt_kernel<TOut, TW>;
-  GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
   dim3 grid((L.DV + NV - 1) / NV, B * H);
   kern<<<grid, 256, smem, st>>>(L, P, s0, static_cast<TOut*>(o), sT, hs, S, H, o_bs);
   GDN2_CUDA_TRY(cudaGetLastError());
@@ -183,7 +183,7 @@ int launch_output_typed(const WsLayout& L, const WsPtrs& P, const float* hs, voi
                         int64_t o_bs, cudaStream_t st) {
   const size_t smem = ScanSmem::bytes(L.DK);
   auto kern = output_simt_kernel<TOut, TW>;
-  GDN2_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem));
   dim3 grid((L.DV + NV - 1) / NV, S / kChunk, B * H);
   kern<<<grid, 256, smem, st>>>(L, P, hs, static_cast<TOut*>(o), S, H, o_bs);
   GDN2_CUDA_TRY(cudaGetLastError());

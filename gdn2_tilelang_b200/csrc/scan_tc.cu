@@ -685,7 +685,7 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
                    int B, int S, int H, int64_t o_bs, const gdn2_gated_norm* gn, int part, cudaStream_t st) {
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
   const size_t smem = sizeof(ScanTcSmem) + 128;
-  GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(scan_tc_kernel), smem));
   __nv_bfloat16* ob = static_cast<__nv_bfloat16*>(o);
   uint32_t* status = device_status_word();
   const int BH = B * H, NC = S / BS;
@@ -717,7 +717,7 @@ int launch_scan_tc(const WsLayout& L, const WsPtrs& P, const float* s0, void* o,
                                                              S, H, o_bs, status);
   GDN2_CUDA_TRY(cudaGetLastError());
   const size_t csmem = (size_t)(D * kTPad + D * kCombineCols) * sizeof(float);
-  GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
+  GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(scan_combine_kernel), csmem));
   scan_combine_kernel<<<dim3(BH, D / kCombineCols), 256, csmem, st>>>(P, nseg, NC, guarded, sT);
   GDN2_CUDA_TRY(cudaGetLastError());
   if (part == 1) return GDN2_OK;
@@ -733,7 +733,7 @@ int launch_output_tc(const WsLayout& L, const WsPtrs& P, const float* hs, void* 
                      cudaStream_t st) {
   if (L.DK != D || L.DV != D || L.esz != 2) return GDN2_ERR_UNSUPPORTED;
   const size_t smem = sizeof(ScanTcSmem) + 128;
-  GDN2_CUDA_TRY(cudaFuncSetAttribute(scan_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(scan_tc_kernel), smem));
   const int BH = B * H, NC = S / BS;
   // enough runs to give every SM a few blocks, none shorter than 4 chunks
   int runs = (4 * device_sm_count() + BH - 1) / BH;

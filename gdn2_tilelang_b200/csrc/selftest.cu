@@ -151,7 +151,7 @@ int launch_selftest_wait(long long limit_cycles, int* gave_up, cudaStream_t st) 
 
 int launch_selftest_mma(const float* a, const float* bt, float* out, cudaStream_t st) {
   const size_t smem = sizeof(SelfSmem) + 1024;
-  GDN2_CUDA_TRY(cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  GDN2_CUDA_TRY(ensure_dynamic_smem(reinterpret_cast<const void*>(selftest_kernel), smem));
   selftest_kernel<<<1, 128, smem, st>>>(a, bt, out, device_status_word());
   GDN2_CUDA_TRY(cudaGetLastError());
   return GDN2_OK;

@@ -84,7 +84,8 @@ def gdn2_prefill(q, k, v, g, b, w, state=None, scale=None, config: GDN2Config = 
     K = _cabi.kernels()
     g = g.float()
     if state is None:
-        state = torch.zeros(B, H, DK, DV, dtype=config.state_dtype, device=q.device)
+        if n_full == 0:                                    # the chunkwise kernels take "no state" as zeros themselves
+            state = torch.zeros(B, H, DK, DV, dtype=config.state_dtype, device=q.device)
     else:
         if state.shape != (B, H, DK, DV):
             raise ValueError(f"state must have shape {(B, H, DK, DV)}, got {tuple(state.shape)}")
