@@ -39,6 +39,7 @@ SIGNATURES = {
     "gdn2_prefill_scan_segments": (_int, [_i64] * 5 + [_int, _int]),
     "gdn2_prefill_scan_launches": (_int, [_i64] * 5 + [_int, _int]),
     "gdn2_prefill_scan_part": (_int, [_vp, _sz, _vp, _vp, _vp] + [_i64] * 7 + [_int, _int, _int, _vp]),
+    "gdn2_prefill_ragged": (_int, [_vp] * 10 + [_sz] + [_i64] * 8 + [_f32, _int, _int, _vp, _vp]),
     "gdn2_prefill_workspace_layout": (_int, [_i64] * 6 + [_int, _int, ctypes.POINTER(ctypes.c_int64)]),
     "gdn2_chunk_prep": (_int, [_vp] * 7 + [_sz] + [_i64] * 7 + [_f32, _int, _int, _vp]),
     "gdn2_prefill_scan": (_int, [_vp, _sz, _vp, _vp, _vp, _vp] + [_i64] * 7 + [_int, _int, _vp]),
@@ -241,6 +242,50 @@ class NativeKernels:
         _check(self.lib, rc, "gdn2_decode")
         self.launches += 1
         return o
+
+    # -- prefill in one call ---------------------------------------------------------------
+    def prefill_ragged(self, q, k, v, g, b, w, scale: float, initial_state=None):
+        """``gdn2_prefill`` as ONE library call (``gdn2_prefill_ragged``): chunk-local stage and scan on the whole
+        chunks, decode on the ragged tail, the tail beside the scan's correction pass when the scan is cut.
+        Returns ``(o, final_state)`` or ``None`` when this form does not apply (fewer than 64 tokens; a problem
+        whose two stages the host overlaps segment by segment) and the caller composes the stages itself."""
+        _require_cuda(q, k, v, g, b, w, initial_state)
+        B, S, HK, DK = q.shape
+        H, DV = v.shape[2], v.shape[-1]
+        n_full = S // CHUNK * CHUNK
+        if n_full == 0:
+            return None
+        code = dtype_code(q.dtype)
+        p = self.resolved_path(DK, DV, q.dtype, None)
+        if self._segments(B, n_full, H, DK, DV, q.dtype, p) > 1:
+            return None
+        views = [_seq_view(t) for t in (q, k, v, g, b, w)]
+        if len({s_ for _, s_ in views}) != 1:
+            views = [(t.contiguous(), S) for t, _ in views]
+        in_bs = views[0][1]
+        q, k, v, g, b, w = (t for t, _ in views)
+        dev = q.device
+        nbytes = self.lib.gdn2_prefill_workspace_bytes(B, n_full, H, HK, DK, DV, code, p)
+        if nbytes == 0:
+            raise GDN2KernelError(
+                f"no kernel for DK={DK}, DV={DV}, dtype={q.dtype} (SIMT family: DK<=128, DK%8==0, DV%4==0)")
+        if initial_state is not None and (initial_state.dtype != torch.float32 or not initial_state.is_contiguous()):
+            initial_state = initial_state.to(torch.float32).contiguous()
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        o = torch.empty(B, S, H, DV, dtype=v.dtype, device=dev)
+        final_state = torch.empty(B, H, DK, DV, dtype=torch.float32, device=dev)
+        with _on_device(dev):
+            main = torch.cuda.current_stream(dev)
+            side = self._side_stream(dev) if S > n_full else None
+            rc = self.lib.gdn2_prefill_ragged(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), g.data_ptr(), b.data_ptr(), w.data_ptr(),
+                None if initial_state is None else initial_state.data_ptr(), o.data_ptr(), final_state.data_ptr(),
+                ws.data_ptr(), nbytes, B, S, H, HK, DK, DV, in_bs, S, float(scale), code, p,
+                None if side is None else side.cuda_stream, main.cuda_stream)
+        _check(self.lib, rc, "gdn2_prefill_ragged")
+        self.launches += (2 if p != PATH_SIMT else 1) + self.lib.gdn2_prefill_scan_launches(B, n_full, H, DK, DV, code, p) \
+            + (1 if S > n_full else 0)
+        return o, final_state
 
     # -- chunkwise forward -----------------------------------------------------------------
     def fuses_gated_norm(self, DK: int, DV: int, dtype: torch.dtype) -> bool:

@@ -259,6 +259,70 @@ int prefill_scan_impl(const void* workspace, size_t workspace_bytes, const float
 }
 }  // namespace
 
+int gdn2_prefill_ragged(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                        const float* initial_state, void* o, float* final_state, void* workspace, size_t workspace_bytes,
+                        int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV, int64_t in_batch_stride,
+                        int64_t o_batch_stride, float scale, int dtype, int path, void* side_stream, void* stream) {
+  if (!q || !k || !v || !g || !b || !w || !o || !final_state) return GDN2_ERR_NULL_POINTER;
+  if (!valid_dtype(dtype)) return GDN2_ERR_BAD_DTYPE;
+  if (B <= 0 || S <= 0 || H <= 0 || HK <= 0 || H % HK != 0 || DK <= 0 || DV <= 0) return GDN2_ERR_BAD_SHAPE;
+  if (in_batch_stride < S || o_batch_stride < S) return GDN2_ERR_BAD_SHAPE;
+  const int64_t n_full = S / kChunk * kChunk, n_tail = S - n_full;
+  const size_t esz = dtype == GDN2_F32 ? 4 : 2;
+  cudaStream_t st = static_cast<cudaStream_t>(stream), side = static_cast<cudaStream_t>(side_stream);
+  int rc = GDN2_OK;
+  if (n_full) {
+    if (!workspace) return GDN2_ERR_NULL_POINTER;
+    rc = gdn2_chunk_prep(q, k, v, g, b, w, workspace, workspace_bytes, B, n_full, H, HK, DK, DV, in_batch_stride, scale,
+                         dtype, path, stream);
+    if (rc != GDN2_OK) return rc;
+    rc = gdn2_prefill_scan_part(workspace, workspace_bytes, initial_state, o, final_state, B, n_full, H, HK, DK, DV,
+                                o_batch_stride, dtype, path, 1, stream);
+    if (rc != GDN2_OK) return rc;
+  } else {
+    const size_t sbytes = (size_t)B * H * DK * DV * sizeof(float);
+    if (!initial_state) GDN2_CUDA_TRY(cudaMemsetAsync(final_state, 0, sbytes, st));
+    else if (initial_state != final_state)
+      GDN2_CUDA_TRY(cudaMemcpyAsync(final_state, initial_state, sbytes, cudaMemcpyDeviceToDevice, st));
+  }
+  auto scan_rest = [&]() -> int {
+    return n_full ? gdn2_prefill_scan_part(workspace, workspace_bytes, initial_state, o, final_state, B, n_full, H, HK, DK,
+                                           DV, o_batch_stride, dtype, path, 2, stream)
+                  : GDN2_OK;
+  };
+  if (!n_tail) return scan_rest();
+  // the ragged tail: the same tensors from token n_full on, the state in place
+  auto at = [&](const void* p, int64_t heads, int64_t d, size_t es) {
+    return static_cast<const void*>(static_cast<const char*>(p) + (size_t)n_full * heads * d * es);
+  };
+  auto decode_tail = [&](void* on) -> int {
+    return gdn2_decode(at(q, HK, DK, esz), at(k, HK, DK, esz), at(v, H, DV, esz),
+                       static_cast<const float*>(at(g, HK, DK, sizeof(float))), at(b, HK, DK, esz), at(w, H, DV, esz),
+                       final_state, const_cast<void*>(at(o, H, DV, esz)), B, n_tail, H, HK, DK, DV, in_batch_stride,
+                       o_batch_stride, scale, dtype, on);
+  };
+  const bool beside = n_full && side && side != st &&
+                      gdn2_prefill_scan_launches(B, n_full, H, DK, DV, dtype, path) > 1;
+  if (!beside) {
+    rc = scan_rest();
+    return rc != GDN2_OK ? rc : decode_tail(stream);
+  }
+  // the tail needs the final state only: it runs on the side stream beside the cut scan's correction pass
+  cudaEvent_t ready = nullptr, done = nullptr;
+  GDN2_CUDA_TRY(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
+  cudaError_t ce = cudaEventCreateWithFlags(&done, cudaEventDisableTiming);
+  if (ce != cudaSuccess) { cudaEventDestroy(ready); return record_cuda_error(ce); }
+  auto finish = [&](int code) { cudaEventDestroy(ready); cudaEventDestroy(done); return code; };
+  if ((ce = cudaEventRecord(ready, st)) != cudaSuccess || (ce = cudaStreamWaitEvent(side, ready, 0)) != cudaSuccess)
+    return finish(record_cuda_error(ce));
+  rc = decode_tail(side_stream);
+  // whatever happened on the side stream, the caller's stream is ordered after it
+  if ((ce = cudaEventRecord(done, side)) != cudaSuccess) return finish(record_cuda_error(ce));
+  const int rc2 = scan_rest();
+  if ((ce = cudaStreamWaitEvent(st, done, 0)) != cudaSuccess) return finish(record_cuda_error(ce));
+  return finish(rc != GDN2_OK ? rc : rc2);
+}
+
 int gdn2_prefill_scan_gated_norm(const void* workspace, size_t workspace_bytes, const float* initial_state, void* o,
                                  float* final_state, int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK,
                                  int64_t DV, int64_t o_batch_stride, int dtype, int path, const gdn2_gated_norm* norm,

@@ -91,6 +91,12 @@ def gdn2_prefill(q, k, v, g, b, w, state=None, scale=None, config: GDN2Config = 
             raise ValueError(f"state must have shape {(B, H, DK, DV)}, got {tuple(state.shape)}")
         state = state.to(config.state_dtype).contiguous()
 
+    if gated_norm is None and n_full:
+        res = K.prefill_ragged(q, k, v, g, b, w, scale, state)      # the whole call in the library, where it applies
+        if res is not None:
+            K.maybe_check_device_status(q.device)
+            return res
+
     o = torch.empty(B, S, H, DV, dtype=v.dtype, device=q.device)
 
     def tail(st):                                          # the ragged tail through the decode kernel, state in place

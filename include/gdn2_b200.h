@@ -166,6 +166,23 @@ int gdn2_prefill_scan_part(const void* workspace, size_t workspace_bytes, const 
                            int64_t o_batch_stride, int dtype, int path, int part, void* stream);
 
 /*
+ * The whole of gdn2_prefill (gdn2/inference.py:482-555) in one call, for callers that count host microseconds:
+ * gdn2_chunk_prep + gdn2_prefill_scan on the floor(S/64)*64 leading tokens and gdn2_decode on the ragged tail
+ * (S need not be a multiple of 64), the state chained through final_state (written even without a tail; must not be
+ * initial_state unless S < 64).
+ *   workspace     gdn2_prefill_workspace_bytes(B, floor(S/64)*64, ...) bytes; NULL is accepted when S < 64
+ *   side_stream   NULL, or a second stream of the same device: when the scan is cut into segments the tail's decode,
+ *                 which needs only the final state, runs there beside the scan's correction pass; `stream` is ordered
+ *                 after it when the call returns
+ * Results are those of the three calls made one after the other. No counterpart in the reference as ONE function:
+ * its gdn2_prefill is the same sequence in Python.
+ */
+int gdn2_prefill_ragged(const void* q, const void* k, const void* v, const float* g, const void* b, const void* w,
+                        const float* initial_state, void* o, float* final_state, void* workspace, size_t workspace_bytes,
+                        int64_t B, int64_t S, int64_t H, int64_t HK, int64_t DK, int64_t DV, int64_t in_batch_stride,
+                        int64_t o_batch_stride, float scale, int dtype, int path, void* side_stream, void* stream);
+
+/*
  * gdn2_prefill_scan with the layer's gated RMSNorm as the epilogue of the output rows:
  *   o[b,t,h,:] <- o * rsqrt(mean(o^2) + eps) * weight * silu(gate[b,t,h,:]),
  * evaluated on the rows as they leave the chip (rounded to `dtype` first, as the separate kernel would read

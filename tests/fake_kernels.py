@@ -32,6 +32,9 @@ class OracleKernels:
             return out
         return o
 
+    def prefill_ragged(self, q, k, v, g, b, w, scale, initial_state=None):
+        return None                      # the double composes the stages, which is what the host-logic tests watch
+
     def fuses_gated_norm(self, DK, DV, dtype):
         return False                     # the double keeps the norm a separate stage (layer_back)
 

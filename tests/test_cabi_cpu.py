@@ -96,6 +96,15 @@ def test_batch_times_heads_limit_is_a_clear_status(lib):
     assert lib.gdn2_prefill_workspace_bytes(4096, 64, 16, 16, 128, 128, _cabi.GDN2_BF16, 0) == 0      # 65536 pairs
     assert lib.gdn2_chunk_prep(one, one, one, one, one, one, one, 1 << 40, 4097, 64, 16, 16, 128, 128, 64, 1.0, 1, 0, None) == -2
     assert lib.gdn2_prefill_scan(one, 1 << 40, None, one, None, None, 4097, 64, 16, 16, 128, 128, 64, 1, 0, None) == -2
+    # the one-call prefill: null pointers, head counts and strides are checked before anything is launched
+    assert lib.gdn2_prefill_ragged(one, one, one, one, one, one, None, None, one, one, 1 << 40, 1, 100, 2, 2, 128, 128,
+                                   100, 100, 1.0, 1, 0, None, None) == -1
+    assert lib.gdn2_prefill_ragged(one, one, one, one, one, one, None, one, one, one, 1 << 40, 1, 100, 3, 2, 128, 128,
+                                   100, 100, 1.0, 1, 0, None, None) == -2
+    assert lib.gdn2_prefill_ragged(one, one, one, one, one, one, None, one, one, one, 1 << 40, 1, 100, 2, 2, 128, 128,
+                                   99, 100, 1.0, 1, 0, None, None) == -2
+    assert lib.gdn2_prefill_ragged(one, one, one, one, one, one, None, one, one, None, 0, 1, 100, 2, 2, 128, 128,
+                                   100, 100, 1.0, 1, 0, None, None) == -1          # 64 whole tokens need a workspace
     # the scan in two parts takes part 1 or 2 only, and the same shape checks
     assert lib.gdn2_prefill_scan_part(one, 1 << 40, None, one, None, 1, 64, 16, 16, 128, 128, 64, 1, 0, 0, None) == -2
     assert lib.gdn2_prefill_scan_part(one, 1 << 40, None, one, None, 1, 64, 16, 16, 128, 128, 64, 1, 0, 3, None) == -2
